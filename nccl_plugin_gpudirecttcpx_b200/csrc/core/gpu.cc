@@ -1,0 +1,193 @@
+#include "tcpxb/gpu.h"
+
+#include <ctype.h>
+#include <mutex>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifndef TCPXB_NO_CUDA
+#include <cuda_runtime_api.h>
+#endif
+
+namespace tcpxb {
+namespace gpu {
+
+namespace {
+thread_local char g_err[256] = "";
+}
+const char* lastError() { return g_err; }
+
+#ifdef TCPXB_NO_CUDA
+
+bool compiledWithCuda() { return false; }
+bool available() { return false; }
+int deviceCount() { return 0; }
+static Result none() {
+  snprintf(g_err, sizeof g_err, "built without CUDA");
+  return kUnhandledCudaError;
+}
+Result currentDevice(int*) { return none(); }
+Result setDevice(int) { return none(); }
+Result pointerInfo(const void*, int* device, bool* is_device) {
+  *device = -1;
+  *is_device = false;
+  return kSuccess;
+}
+std::string pciBusId(int) { return ""; }
+int numaNode(int) { return 0; }
+Result hostAllocMapped(size_t bytes, void** host_ptr, void** dev_ptr) {
+  void* p = nullptr;
+  if (posix_memalign(&p, 4096, bytes ? bytes : 4096) != 0) return kSystemError;
+  *host_ptr = p;
+  *dev_ptr = p;
+  return kSuccess;
+}
+void hostFreeMapped(void* p) { free(p); }
+Result deviceAlloc(size_t, void**) { return none(); }
+void deviceFree(void*) {}
+Result streamCreate(Stream*) { return none(); }
+void streamDestroy(Stream) {}
+Result eventCreate(Event*) { return none(); }
+void eventDestroy(Event) {}
+Result eventRecord(Event, Stream) { return none(); }
+Result eventQuery(Event) { return none(); }
+Result streamSynchronize(Stream) { return none(); }
+Result copyToHostAsync(void*, const void*, size_t, Stream) { return none(); }
+Result copyToDeviceAsync(void*, const void*, size_t, Stream) { return none(); }
+Result memsetAsync(void*, int, size_t, Stream) { return none(); }
+
+#else  // CUDA build
+
+namespace {
+Result check(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return kSuccess;
+  snprintf(g_err, sizeof g_err, "%s: %s", what, cudaGetErrorString(e));
+  WARN("CUDA call failed: %s", g_err);
+  return kUnhandledCudaError;
+}
+#define CU(expr) check((expr), #expr)
+
+int probeCount() {
+  static int count = [] {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();  // clear the sticky "no device / no driver" state
+      return 0;
+    }
+    return n;
+  }();
+  return count;
+}
+}  // namespace
+
+bool compiledWithCuda() { return true; }
+int deviceCount() { return probeCount(); }
+bool available() { return probeCount() > 0; }
+
+Result currentDevice(int* dev) { return CU(cudaGetDevice(dev)); }
+Result setDevice(int dev) { return CU(cudaSetDevice(dev)); }
+
+Result pointerInfo(const void* p, int* device, bool* is_device) {
+  *device = -1;
+  *is_device = false;
+  if (!available()) return kSuccess;
+  cudaPointerAttributes a;
+  cudaError_t e = cudaPointerGetAttributes(&a, p);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return kSuccess;  // plain host memory on older runtimes
+  }
+  if (a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged) {
+    *is_device = true;
+    *device = a.device;
+  }
+  return kSuccess;
+}
+
+std::string pciBusId(int dev) {
+  char buf[32] = "";
+  if (!available() || cudaDeviceGetPCIBusId(buf, sizeof buf, dev) != cudaSuccess) return "";
+  for (char* c = buf; *c; ++c) *c = (char)tolower(*c);
+  return buf;
+}
+
+int numaNode(int dev) {
+  std::string id = pciBusId(dev);
+  if (!id.empty()) {
+    std::string path = "/sys/bus/pci/devices/" + id + "/numa_node";
+    if (FILE* f = fopen(path.c_str(), "r")) {
+      int node = -1;
+      int got = fscanf(f, "%d", &node);
+      fclose(f);
+      if (got == 1 && node >= 0) return node;
+    }
+  }
+  const int n = deviceCount();
+  return (n > 1 && dev >= n / 2) ? 1 : 0;
+}
+
+Result hostAllocMapped(size_t bytes, void** host_ptr, void** dev_ptr) {
+  if (!available()) {
+    void* p = nullptr;
+    if (posix_memalign(&p, 4096, bytes ? bytes : 4096) != 0) return kSystemError;
+    *host_ptr = *dev_ptr = p;
+    return kSuccess;
+  }
+  Result r = CU(cudaHostAlloc(host_ptr, bytes, cudaHostAllocMapped | cudaHostAllocPortable));
+  if (r != kSuccess) return r;
+  return CU(cudaHostGetDevicePointer(dev_ptr, *host_ptr, 0));
+}
+
+void hostFreeMapped(void* p) {
+  if (p == nullptr) return;
+  if (!available()) { free(p); return; }
+  if (cudaFreeHost(p) != cudaSuccess) (void)cudaGetLastError();
+}
+
+Result deviceAlloc(size_t bytes, void** ptr) { return CU(cudaMalloc(ptr, bytes)); }
+void deviceFree(void* p) {
+  if (p != nullptr && cudaFree(p) != cudaSuccess) (void)cudaGetLastError();
+}
+
+Result streamCreate(Stream* s) {
+  cudaStream_t st;
+  Result r = CU(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+  *s = st;
+  return r;
+}
+void streamDestroy(Stream s) {
+  if (s != nullptr && cudaStreamDestroy((cudaStream_t)s) != cudaSuccess) (void)cudaGetLastError();
+}
+Result eventCreate(Event* e) {
+  cudaEvent_t ev;
+  Result r = CU(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+  *e = ev;
+  return r;
+}
+void eventDestroy(Event e) {
+  if (e != nullptr && cudaEventDestroy((cudaEvent_t)e) != cudaSuccess) (void)cudaGetLastError();
+}
+Result eventRecord(Event e, Stream s) { return CU(cudaEventRecord((cudaEvent_t)e, (cudaStream_t)s)); }
+Result eventQuery(Event e) {
+  cudaError_t r = cudaEventQuery((cudaEvent_t)e);
+  if (r == cudaSuccess) return kSuccess;
+  if (r == cudaErrorNotReady) return kInProgress;
+  return check(r, "cudaEventQuery");
+}
+Result streamSynchronize(Stream s) { return CU(cudaStreamSynchronize((cudaStream_t)s)); }
+Result copyToHostAsync(void* h, const void* d, size_t n, Stream s) {
+  return CU(cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, (cudaStream_t)s));
+}
+Result copyToDeviceAsync(void* d, const void* h, size_t n, Stream s) {
+  return CU(cudaMemcpyAsync(d, h, n, cudaMemcpyHostToDevice, (cudaStream_t)s));
+}
+Result memsetAsync(void* d, int v, size_t n, Stream s) {
+  return CU(cudaMemsetAsync(d, v, n, (cudaStream_t)s));
+}
+
+#endif
+
+}  // namespace gpu
+}  // namespace tcpxb

@@ -1,0 +1,173 @@
+#include "tcpxb/rx_buf_mgr.h"
+
+#include <algorithm>
+#include <map>
+#include <memory>
+#include <unistd.h>
+
+#include "tcpxb/flags.h"
+#include "tcpxb/gpu.h"
+
+namespace tcpxb {
+
+PageAllocator::PageAllocator(uint32_t n_pages, bool scatter, uint64_t seed)
+    : total_(n_pages), in_use_(n_pages, 0) {
+  stack_.resize(n_pages);
+  // ascending hand-out order = descending stack
+  for (uint32_t i = 0; i < n_pages; ++i) stack_[i] = n_pages - 1 - i;
+  if (scatter && n_pages > 1) {
+    // Fisher-Yates with a fixed xorshift stream: reproducible scatter
+    uint64_t x = seed ? seed : 1;
+    for (uint32_t i = n_pages - 1; i > 0; --i) {
+      x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+      uint32_t j = (uint32_t)(x % (i + 1));
+      std::swap(stack_[i], stack_[j]);
+    }
+  }
+}
+
+bool PageAllocator::alloc(uint32_t n, std::vector<PageRun>* out) {
+  if (n > stack_.size()) return false;
+  for (uint32_t i = 0; i < n; ++i) {
+    const uint32_t page = stack_.back();
+    stack_.pop_back();
+    in_use_[page] = 1;
+    if (!out->empty() && i > 0 && out->back().first + out->back().count == page) ++out->back().count;
+    else out->push_back({page, 1});
+  }
+  return true;
+}
+
+void PageAllocator::release(uint32_t first, uint32_t count) {
+  // pushed in descending order so the run comes out ascending (contiguous) again
+  for (uint32_t i = count; i > 0; --i) {
+    const uint32_t page = first + i - 1;
+    if (page >= total_ || !in_use_[page]) {
+      WARN("rx page %u released twice or out of range", page);
+      continue;
+    }
+    in_use_[page] = 0;
+    stack_.push_back(page);
+  }
+}
+
+namespace {
+
+class EmulatedRxBufMgr final : public RxBufMgr {
+ public:
+  EmulatedRxBufMgr(int dev, uint64_t bytes, bool scatter, bool device_resident)
+      : dev_(dev), bytes_(bytes / kRxPageBytes * kRxPageBytes), device_resident_(device_resident),
+        alloc_((uint32_t)(bytes / kRxPageBytes), scatter) {}
+
+  ~EmulatedRxBufMgr() override {
+    if (device_resident_) gpu::deviceFree(dev_base_);
+    gpu::hostFreeMapped(host_base_);
+  }
+
+  Result init() {
+    void* h = nullptr;
+    void* d = nullptr;
+    TCPXB_CHECK(gpu::hostAllocMapped(bytes_, &h, &d));
+    host_base_ = static_cast<uint8_t*>(h);
+    dev_base_ = static_cast<uint8_t*>(d);
+    if (device_resident_) {
+      void* p = nullptr;
+      TCPXB_CHECK(gpu::deviceAlloc(bytes_, &p));
+      dev_base_ = static_cast<uint8_t*>(p);
+    }
+    INFO(kSubInit | kSubNet, "rx pool for GPU %d: %lu MiB, %s, host %p device %p", dev_,
+         (unsigned long)(bytes_ >> 20), device_resident_ ? "device memory + pinned mirror" : "pinned, device-mapped",
+         (void*)host_base_, (void*)dev_base_);
+    return kSuccess;
+  }
+
+  uint8_t* hostBase() override { return host_base_; }
+  uint8_t* devBase() override { return dev_base_; }
+  uint64_t bytes() const override { return bytes_; }
+  bool deviceResident() const override { return device_resident_; }
+
+  bool allocPages(uint32_t n, std::vector<PageRun>* out) override {
+    std::lock_guard<std::mutex> l(mu_);
+    return alloc_.alloc(n, out);
+  }
+  void releasePages(const PageRun* runs, size_t n) override {
+    std::lock_guard<std::mutex> l(mu_);
+    for (size_t i = 0; i < n; ++i) alloc_.release(runs[i].first, runs[i].count);
+  }
+  uint32_t freePages() override {
+    std::lock_guard<std::mutex> l(mu_);
+    return alloc_.freePages();
+  }
+
+  Result installFlowRule(int fd, const std::string& gpu_pci) override {
+    FlowRule r;
+    memset(&r.local, 0, sizeof r.local);
+    memset(&r.peer, 0, sizeof r.peer);
+    socklen_t ll = sizeof r.local, pl = sizeof r.peer;
+    if (getsockname(fd, &r.local.sa, &ll) != 0 || getpeername(fd, &r.peer.sa, &pl) != 0) return kSystemError;
+    r.gpu_pci = gpu_pci;
+    r.fd = fd;
+    std::lock_guard<std::mutex> l(mu_);
+    rules_.push_back(r);
+    TRACE(kSubNet, "flow rule %s -> %s steers to GPU %s", addressToString(r.peer).c_str(),
+          addressToString(r.local).c_str(), gpu_pci.c_str());
+    return kSuccess;
+  }
+  Result removeFlowRule(int fd) override {
+    std::lock_guard<std::mutex> l(mu_);
+    rules_.erase(std::remove_if(rules_.begin(), rules_.end(), [fd](const FlowRule& r) { return r.fd == fd; }),
+                 rules_.end());
+    return kSuccess;
+  }
+  Result registerApplication(int pid) override {
+    std::lock_guard<std::mutex> l(mu_);
+    apps_.push_back(pid);
+    return kSuccess;
+  }
+  Result deregisterApplication(int pid) override {
+    std::lock_guard<std::mutex> l(mu_);
+    apps_.erase(std::remove(apps_.begin(), apps_.end(), pid), apps_.end());
+    return kSuccess;
+  }
+  std::vector<FlowRule> flowRules() override {
+    std::lock_guard<std::mutex> l(mu_);
+    return rules_;
+  }
+
+ private:
+  int dev_;
+  uint64_t bytes_;
+  bool device_resident_;
+  std::mutex mu_;
+  PageAllocator alloc_;
+  uint8_t* host_base_ = nullptr;
+  uint8_t* dev_base_ = nullptr;
+  std::vector<FlowRule> rules_;
+  std::vector<int> apps_;
+};
+
+std::mutex g_mu;
+std::map<int, std::unique_ptr<EmulatedRxBufMgr>> g_mgrs;
+
+}  // namespace
+
+RxBufMgr* rxBufMgrFor(int dev) {
+  std::lock_guard<std::mutex> l(g_mu);
+  auto it = g_mgrs.find(dev);
+  if (it != g_mgrs.end()) return it->second.get();
+  const Flags& f = flags();
+  const bool device_resident = dev >= 0 && f.rx_pool_mode == kRxPoolDevice && gpu::available();
+  auto m = std::make_unique<EmulatedRxBufMgr>(dev, (uint64_t)f.rx_pool_bytes, f.rx_pool_scatter != 0, device_resident);
+  if (m->init() != kSuccess) return nullptr;
+  RxBufMgr* raw = m.get();
+  g_mgrs[dev] = std::move(m);
+  return raw;
+}
+
+RxBufMgr* newHostRxBufMgr(uint64_t bytes, bool scatter) {
+  auto* m = new EmulatedRxBufMgr(-1, bytes, scatter, false);
+  if (m->init() != kSuccess) { delete m; return nullptr; }
+  return m;
+}
+
+}  // namespace tcpxb

@@ -1,0 +1,1102 @@
+// Core transport: init, memory registration, the progress engine, helper threads,
+// completion and teardown.  See transport.h for the overall contract.
+#include "tcpxb/transport.h"
+
+#include <linux/errqueue.h>
+#include <poll.h>
+#include <pthread.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <sys/prctl.h>
+#include <unistd.h>
+
+#include <algorithm>
+
+#ifndef TCPXB_NO_CUDA
+#include "tcpxb/kernels.h"
+#endif
+
+#ifndef SO_EE_ORIGIN_ZEROCOPY
+#define SO_EE_ORIGIN_ZEROCOPY 5
+#endif
+#ifndef MSG_ZEROCOPY
+#define MSG_ZEROCOPY 0x4000000
+#endif
+
+namespace tcpxb {
+
+namespace {
+
+struct CoreGlobal {
+  std::mutex mu;
+  bool inited = false;
+  CpuBindings tx_bind, rx_bind, tx_irq_bind, rx_irq_bind;
+  std::unique_ptr<LogGarbageCollector> gc;
+  bool registered_app = false;
+};
+CoreGlobal cg;
+
+const char* kTaskStageName[] = {"FREE", "ACTIVE", "COMPLETING", "INACTIVE"};
+const char* kReqStageName[] = {"FREE", "POSTED", "ACTIVE", "TRANSMITTING", "INACTIVE"};
+
+inline void traceTask(Comm* c, const Task* t, int stage) {
+  if (traceConfig().task_level) traceTransition(c->events.get(), 'T', t, c->passive, kTaskStageName[stage]);
+}
+inline void traceReq(Comm* c, const Request* r, int stage) {
+  if (traceConfig().request_level) traceTransition(c->events.get(), 'R', r, c->passive, kReqStageName[stage]);
+}
+
+void setError(Comm* c, Result r) {
+  int expected = kSuccess;
+  c->error.compare_exchange_strong(expected, (int)r);
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ CPU bindings
+bool parseCoreRanges(const char* text, const std::vector<std::string>& if_names, CpuBindings* out) {
+  *out = CpuBindings();
+  if (text == nullptr || *text == 0) return true;
+  bool ok = true;
+  std::string s(text);
+  size_t pos = 0;
+  while (pos <= s.size()) {
+    size_t end = s.find(';', pos);
+    if (end == std::string::npos) end = s.size();
+    std::string item = s.substr(pos, end - pos);
+    pos = end + 1;
+    if (item.empty()) continue;
+    size_t colon = item.find(':');
+    if (colon == std::string::npos) { ok = false; continue; }
+    const std::string nic = item.substr(0, colon);
+    int idx = -1;
+    for (size_t i = 0; i < if_names.size() && i < (size_t)kMaxIfs; ++i) {
+      std::string base = if_names[i].substr(0, if_names[i].find('#'));
+      if (if_names[i] == nic || base == nic) { idx = (int)i;
+        // a physical name binds every virtual device carved out of it
+        std::string ranges = item.substr(colon + 1);
+        size_t rp = 0;
+        out->n_ranges[idx] = 0;
+        while (rp <= ranges.size() && out->n_ranges[idx] < kMaxRanges) {
+          size_t re = ranges.find(',', rp);
+          if (re == std::string::npos) re = ranges.size();
+          std::string r = ranges.substr(rp, re - rp);
+          rp = re + 1;
+          if (r.empty()) continue;
+          int lo = 0, hi = 0;
+          int got = sscanf(r.c_str(), "%d-%d", &lo, &hi);
+          if (got == 1) hi = lo;
+          if (got < 1 || lo < 0 || hi < lo) { ok = false; continue; }
+          out->lo[idx][out->n_ranges[idx]] = lo;
+          out->hi[idx][out->n_ranges[idx]] = hi;
+          ++out->n_ranges[idx];
+        }
+      }
+    }
+    if (idx < 0) ok = false;
+  }
+  return ok;
+}
+
+namespace {
+
+void applyAffinity(Comm* comm, int tid) {
+  const CpuBindings& b = comm->passive ? cg.rx_bind : cg.tx_bind;
+  const int dev = comm->dev;
+  if (dev < 0 || dev >= kMaxIfs || b.n_ranges[dev] == 0) return;
+  const long ncpu = sysconf(_SC_NPROCESSORS_ONLN);
+  std::vector<int> cores;
+  for (int r = 0; r < b.n_ranges[dev]; ++r)
+    for (int c = b.lo[dev][r]; c <= b.hi[dev][r] && c < ncpu; ++c) cores.push_back(c);
+  if (cores.empty()) return;
+  cpu_set_t set;
+  CPU_ZERO(&set);
+  const Flags& f = flags();
+  if (f.worker_pin_threads) {
+    // one core per helper: comms are strided so that neighbours do not collide
+    size_t pick = ((size_t)f.worker_spray_stride * comm->num_threads * comm->stride + (size_t)tid) % cores.size();
+    for (int j = 0; j < (int)f.worker_spray_count; ++j)
+      CPU_SET(cores[(pick + (size_t)j * (size_t)comm->num_threads) % cores.size()], &set);
+  } else {
+    for (int c : cores) CPU_SET(c, &set);
+  }
+  pthread_setaffinity_np(pthread_self(), sizeof set, &set);
+}
+
+// ------------------------------------------------------------- zero-copy notices
+// Reads completion notifications from the socket's error queue; returns how many
+// sendmsg calls completed, or -1 on a socket error.
+int readZerocopyCompletions(SocketCtx* s) {
+  int completed = 0;
+  for (;;) {
+    char control[128];
+    struct msghdr msg;
+    memset(&msg, 0, sizeof msg);
+    msg.msg_control = control;
+    msg.msg_controllen = sizeof control;
+    ssize_t rc = recvmsg(s->fd, &msg, MSG_ERRQUEUE | MSG_DONTWAIT);
+    if (rc < 0) {
+      if (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR) return completed;
+      return -1;
+    }
+    for (struct cmsghdr* cm = CMSG_FIRSTHDR(&msg); cm != nullptr; cm = CMSG_NXTHDR(&msg, cm)) {
+      if (!((cm->cmsg_level == SOL_IP && cm->cmsg_type == IP_RECVERR) ||
+            (cm->cmsg_level == SOL_IPV6 && cm->cmsg_type == IPV6_RECVERR)))
+        continue;
+      struct sock_extended_err* ee = (struct sock_extended_err*)CMSG_DATA(cm);
+      if (ee->ee_errno != 0 || ee->ee_origin != SO_EE_ORIGIN_ZEROCOPY) continue;
+      // ids [ee_info, ee_data] completed; sequence numbers wrap at 2^32
+      completed += (int)(ee->ee_data - ee->ee_info + 1);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ helper thread
+// Moves bytes for the oldest active task of socket `s`.  Returns 1 when the task
+// finished its I/O, 0 when the socket would block, -1 on error.
+int progressTask(Comm* comm, SocketCtx* s, Task* t) {
+  const bool slow_on = flags().slow_switch[kSlowSendRecv];
+  while (t->offset < t->size) {
+    ssize_t n;
+    if (t->op == kSockSend) {
+      int fl = MSG_DONTWAIT | MSG_NOSIGNAL;
+      if (t->zerocopy) fl |= MSG_ZEROCOPY;
+      n = send(s->fd, t->host_ptr + t->offset, (size_t)(t->size - t->offset), fl);
+      if (n > 0) {
+        s->stats.tx_cnt.fetch_add(1, std::memory_order_relaxed);
+        if (t->zerocopy) { if (t->zc_count++ == 0) t->zc_first = s->zc_next; ++s->zc_next; }
+      }
+    } else if (t->host_ptr != nullptr) {
+      n = recv(s->fd, t->host_ptr + t->offset, (size_t)(t->size - t->offset), MSG_DONTWAIT);
+      if (n > 0) s->stats.rx_cnt.fetch_add(1, std::memory_order_relaxed);
+    } else {
+      // scattered landing: one recvmsg fills as many pool pages as have data
+      struct msghdr msg;
+      memset(&msg, 0, sizeof msg);
+      msg.msg_iov = t->iov.data() + t->iov_pos;
+      msg.msg_iovlen = std::min<size_t>(t->iov.size() - t->iov_pos, 512);
+      n = recvmsg(s->fd, &msg, MSG_DONTWAIT);
+      if (n > 0) {
+        s->stats.rx_cnt.fetch_add(1, std::memory_order_relaxed);
+        size_t left = (size_t)n;
+        while (left > 0) {
+          struct iovec& v = t->iov[t->iov_pos];
+          if (left >= v.iov_len) { left -= v.iov_len; ++t->iov_pos; }
+          else { v.iov_base = (char*)v.iov_base + left; v.iov_len -= left; left = 0; }
+        }
+      }
+    }
+    if (n > 0) {
+      t->offset += (int)n;
+      s->stats.bytes_posted.fetch_add((uint64_t)n, std::memory_order_relaxed);
+      if (slow_on) s->stall.reset();
+      continue;
+    }
+    if (n == 0 && t->op == kSockRecv) {
+      WARN("%s: peer closed the connection in mid-message", s->flow.c_str());
+      setError(comm, kRemoteError);
+      return -1;
+    }
+    if (n < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) {
+      if (slow_on) {
+        uint64_t ns = 0;
+        if (s->stall.shouldWarn(&ns)) {
+          (t->op == kSockSend ? s->stats.tx_slow_cnt : s->stats.rx_slow_cnt).fetch_add(1);
+          if (flags().slow_report[kSlowSendRecv])
+            WARN("%s: %s stalled for %lu ms at %d/%d bytes", s->flow.c_str(), t->op == kSockSend ? "send" : "recv",
+                 (unsigned long)(ns / 1000000), t->offset, t->size);
+        }
+      }
+      return 0;
+    }
+    if (n < 0 && t->zerocopy && errno == ENOBUFS) { t->zerocopy = false; continue; }  // optmem exhausted: copy instead
+    WARN("%s: %s failed: %s", s->flow.c_str(), t->op == kSockSend ? "send" : "recv", strerror(errno));
+    setError(comm, (errno == ECONNRESET || errno == EPIPE) ? kRemoteError : kSystemError);
+    return -1;
+  }
+  return 1;
+}
+
+void helperMain(Comm* comm, int tid) {
+  char name[16];
+  snprintf(name, sizeof name, "tcpxb-%s%d", comm->passive ? "rx" : "tx", tid);
+  prctl(PR_SET_NAME, name, 0, 0, 0);
+  applyAffinity(comm, tid);
+  HelperThread& me = comm->helpers[tid];
+  const Flags& f = flags();
+  const bool spin = f.thread_spin != 0;
+  const bool slow_txc = f.slow_switch[kSlowTxComp];
+  int idle_rounds = 0;
+  while (!comm->stop.load(std::memory_order_acquire)) {
+    bool moved = false, blocked = false;
+    struct pollfd pfds[kMaxSockets];
+    int npfd = 0;
+    for (int idx = tid; idx < comm->num_socks; idx += comm->num_threads) {
+      SocketCtx* s = &comm->sock[idx];
+      while (s->tasks.has(kTaskActive)) {
+        Task* t = &s->tasks.front(kTaskActive);
+        int rc = progressTask(comm, s, t);
+        if (rc < 0) return;
+        if (rc == 0) {
+          blocked = true;
+          pfds[npfd].fd = s->fd;
+          pfds[npfd].events = (short)(t->op == kSockSend ? POLLOUT : POLLIN);
+          pfds[npfd].revents = 0;
+          ++npfd;
+          break;
+        }
+        moved = true;
+        traceTask(comm, t, kTaskCompleting);
+        s->tasks.advance(kTaskActive);
+      }
+      // completion stage: zero-copy sends wait for the kernel's notification
+      if (s->zc_done != s->zc_next) {
+        int c = readZerocopyCompletions(s);
+        if (c < 0) { setError(comm, kSystemError); return; }
+        if (c > 0) { s->zc_done += (uint32_t)c; s->stats.tx_completion_cnt.fetch_add((uint64_t)c); s->stall.reset(); moved = true; }
+        else if (slow_txc) {
+          uint64_t ns = 0;
+          if (s->stall.shouldWarn(&ns)) {
+            s->stats.tx_completion_slow_cnt.fetch_add(1);
+            if (f.slow_report[kSlowTxComp])
+              WARN("%s: no tx completion for %lu ms (%u outstanding)", s->flow.c_str(), (unsigned long)(ns / 1000000),
+                   s->zc_next - s->zc_done);
+          }
+          if (f.tx_completion_nanosleep > 0) {
+            struct timespec ts = {0, (long)f.tx_completion_nanosleep};
+            nanosleep(&ts, nullptr);
+          }
+        }
+      }
+      while (s->tasks.has(kTaskCompleting)) {
+        Task* t = &s->tasks.front(kTaskCompleting);
+        if (t->zerocopy && t->zc_count > 0) {
+          // done once every notification id of this task is below zc_done (wrap-safe)
+          const uint32_t last = t->zc_first + t->zc_count;
+          if ((int32_t)(s->zc_done - last) < 0) break;
+        } else if (t->op == kSockSend) {
+          s->stats.tx_completion_cnt.fetch_add(1, std::memory_order_relaxed);
+        }
+        s->stats.bytes_done.fetch_add((uint64_t)t->size, std::memory_order_relaxed);
+        traceTask(comm, t, kTaskInactive);
+        s->tasks.advance(kTaskCompleting);
+        moved = true;
+      }
+    }
+    if (moved) { idle_rounds = 0; continue; }
+    if (spin) continue;
+    if (blocked) {
+      // every owned socket with work would block: sleep in the kernel until one is ready
+      if (++idle_rounds > 8 && f.poll_block_us > 0) {
+        poll(pfds, (nfds_t)npfd, (int)std::max<int64_t>(1, f.poll_block_us / 1000));
+      }
+      continue;
+    }
+    if (++idle_rounds < 64) continue;  // short spin: the next chunk usually follows at once
+    std::unique_lock<std::mutex> l(me.mu);
+    me.cv.wait_for(l, std::chrono::milliseconds(50), [&] {
+      return me.kicks.load(std::memory_order_acquire) != me.seen || comm->stop.load(std::memory_order_acquire);
+    });
+    me.seen = me.kicks.load(std::memory_order_acquire);
+    idle_rounds = 0;
+  }
+}
+
+void kick(Comm* comm, int sock_idx) {
+  HelperThread& h = comm->helpers[sock_idx % comm->num_threads];
+  h.kicks.fetch_add(1, std::memory_order_release);
+  if (!flags().thread_spin) {
+    // Taking the lock after the increment closes the window in which a helper has
+    // evaluated its wait predicate but is not yet blocked.
+    { std::lock_guard<std::mutex> l(h.mu); }
+    h.cv.notify_one();
+  }
+}
+
+// --------------------------------------------------------------- CUDA resources
+Result ensureCudaComm(Comm* comm, int gpu_dev) {
+  if (comm->stream != nullptr) return kSuccess;
+  if (!gpu::available()) { WARN("CUDA buffer given but no CUDA device is usable"); return kInvalidUsage; }
+  comm->gpu_dev = gpu_dev;
+  int cur = -1;
+  TCPXB_CHECK(gpu::currentDevice(&cur));
+  if (cur != gpu_dev) TCPXB_CHECK(gpu::setDevice(gpu_dev));
+  TCPXB_CHECK(gpu::streamCreate(&comm->stream));
+  return kSuccess;
+}
+
+Result ensureCudaRecv(Comm* comm, int gpu_dev, bool want_device_handle = false) {
+  TCPXB_CHECK(ensureCudaComm(comm, gpu_dev));
+  if (comm->rxmgr == nullptr) {
+    comm->rxmgr = rxBufMgrFor(gpu_dev);
+    if (comm->rxmgr == nullptr) return kUnhandledCudaError;
+    const std::string pci = gpu::pciBusId(gpu_dev);
+    for (int i = 0; i < comm->num_socks; ++i) comm->rxmgr->installFlowRule(comm->sock[i].fd, pci);
+  }
+  if (comm->devq == nullptr || (want_device_handle && comm->devq->deviceHandle() == nullptr)) {
+    if (comm->devq != nullptr && comm->devq->inUse() != 0) return kInvalidUsage;
+    comm->devq = std::make_unique<DevQueue>();
+    TCPXB_CHECK(comm->devq->init(comm->rxmgr->devBase(), want_device_handle));
+  }
+  if (comm->unpack_status_host == nullptr) {
+    void* h = nullptr;
+    void* d = nullptr;
+    TCPXB_CHECK(gpu::hostAllocMapped(64, &h, &d));
+    memset(h, 0, 64);
+    comm->unpack_status_host = static_cast<uint32_t*>(h);
+    comm->unpack_status_dev = static_cast<uint32_t*>(d);
+  }
+  return kSuccess;
+}
+
+// Reserves `bytes` of the pinned tx staging ring (FIFO); false when it is full.
+bool stageAlloc(Comm* comm, uint64_t bytes, uint8_t** out, uint64_t* charged) {
+  const uint64_t cap = comm->tx_stage_bytes;
+  if (bytes > cap) return false;
+  uint64_t head = comm->tx_head;
+  uint64_t pos = head % cap;
+  uint64_t skip = (pos + bytes > cap) ? cap - pos : 0;  // do not wrap inside a request
+  if (head + skip + bytes - comm->tx_tail > cap) return false;
+  *out = comm->tx_stage + (head + skip) % cap;
+  *charged = skip + bytes;
+  comm->tx_head = head + skip + bytes;
+  return true;
+}
+
+Result startCudaSend(Comm* comm, Request* r, MemHandle* mh) {
+  TCPXB_CHECK(ensureCudaComm(comm, mh != nullptr && mh->gpu_dev >= 0 ? mh->gpu_dev : comm->gpu_dev));
+  if (comm->tx_stage == nullptr) {
+    void* h = nullptr;
+    void* d = nullptr;
+    comm->tx_stage_bytes = (uint64_t)flags().tx_staging_bytes;
+    TCPXB_CHECK(gpu::hostAllocMapped(comm->tx_stage_bytes, &h, &d));
+    comm->tx_stage = static_cast<uint8_t*>(h);
+  }
+  if (r->size == 0) return kSuccess;
+  if (!stageAlloc(comm, (uint64_t)r->size, &r->stage, &r->stage_bytes)) return kInProgress;
+  const int chunk = (int)flags().dynamic_chunk_size;
+  int seg = (r->size + kMaxTxSegments - 1) / kMaxTxSegments;
+  seg = (seg + chunk - 1) / chunk * chunk;
+  r->seg_bytes = seg;
+  r->n_segs = (r->size + seg - 1) / seg;
+  r->segs_done = 0;
+  for (int i = 0; i < r->n_segs; ++i) {
+    const int off = i * seg;
+    const int len = std::min(seg, r->size - off);
+    TCPXB_CHECK(gpu::copyToHostAsync(r->stage + off, r->data + off, (size_t)len, comm->stream));
+    if (r->seg_event[i] == nullptr) TCPXB_CHECK(gpu::eventCreate(&r->seg_event[i]));
+    TCPXB_CHECK(gpu::eventRecord(r->seg_event[i], comm->stream));
+  }
+  return kSuccess;
+}
+
+// True when the staged bytes [0, upto) of a CUDA send have reached host memory.
+bool stagedUpTo(Request* r, int upto) {
+  const int need = (upto + r->seg_bytes - 1) / r->seg_bytes;
+  while (r->segs_done < need) {
+    if (gpu::eventQuery(r->seg_event[r->segs_done]) != kSuccess) return false;
+    ++r->segs_done;
+  }
+  return true;
+}
+
+void releasePages(Comm* comm, Request* r) {
+  if (!r->pages.empty() && comm->rxmgr != nullptr) comm->rxmgr->releasePages(r->pages.data(), r->pages.size());
+  r->pages.clear();
+}
+
+// ------------------------------------------------------------------ task set-up
+void fillSendTask(Comm* comm, Request* r, int sock_idx, int chunk) {
+  SocketCtx& s = comm->sock[sock_idx];
+  Task& t = s.tasks.nextFree();
+  t.r = r;
+  t.op = kSockSend;
+  t.host_ptr = (r->mem_type == kPtrCuda ? r->stage : r->data) + r->offset;
+  t.size = chunk;
+  t.offset = 0;
+  t.msg_offset = r->offset;
+  t.pages.clear();
+  t.iov.clear();
+  t.iov_pos = 0;
+  t.zc_first = t.zc_count = 0;
+  t.zerocopy = s.zerocopy_enabled && r->mem_type == kPtrHost && flags().min_zcopy_size > 0 &&
+               chunk >= flags().min_zcopy_size;
+  traceTask(comm, &t, kTaskActive);
+  s.tasks.admit();
+  r->offset += chunk;
+  kick(comm, sock_idx);
+}
+
+// Receive task into pool pages; false when the pool has no room right now.
+bool fillRecvTask(Comm* comm, Request* r, int sock_idx, int chunk, int msg_offset) {
+  SocketCtx& s = comm->sock[sock_idx];
+  Task& t = s.tasks.nextFree();
+  t.pages.clear();
+  t.iov.clear();
+  t.iov_pos = 0;
+  if (r->mem_type == kPtrCuda) {
+    const uint32_t n_pages = ((uint32_t)chunk + kRxPageBytes - 1) / kRxPageBytes;
+    if (!comm->rxmgr->allocPages(n_pages, &t.pages)) return false;
+    uint8_t* base = comm->rxmgr->hostBase();
+    int left = chunk;
+    for (const PageRun& run : t.pages) {
+      const int run_bytes = std::min<int64_t>((int64_t)run.count * kRxPageBytes, left);
+      t.iov.push_back({base + (uint64_t)run.first * kRxPageBytes, (size_t)run_bytes});
+      left -= run_bytes;
+    }
+    t.host_ptr = nullptr;
+  } else {
+    t.host_ptr = r->data + msg_offset;
+  }
+  t.r = r;
+  t.op = kSockRecv;
+  t.size = chunk;
+  t.offset = 0;
+  t.msg_offset = msg_offset;
+  t.zerocopy = false;
+  t.zc_first = t.zc_count = 0;
+  traceTask(comm, &t, kTaskActive);
+  s.tasks.admit();
+  kick(comm, sock_idx);
+  return true;
+}
+
+// A finished receive task of a CUDA request: describe its pages in the request's
+// slot (one record per page fragment) and keep the pages until the consumer is done.
+Result describePages(Comm* comm, Request* r, Task* t) {
+  int left = t->size;
+  uint64_t dst = (uint64_t)t->msg_offset;
+  for (const PageRun& run : t->pages) {
+    r->pages.push_back(run);
+    if (comm->rxmgr->deviceResident() && left > 0) {
+      // device pool: the copy engine places the run (it landed in the pinned mirror)
+      const uint64_t off = (uint64_t)run.first * kRxPageBytes;
+      const size_t len = (size_t)std::min<int64_t>((int64_t)run.count * kRxPageBytes, left);
+      TCPXB_CHECK(gpu::copyToDeviceAsync(comm->rxmgr->devBase() + off, comm->rxmgr->hostBase() + off, len, comm->stream));
+    }
+    for (uint32_t p = 0; p < run.count && left > 0; ++p) {
+      if (r->slot.filled >= (uint64_t)kUnpackMaxSlicePages) {
+        WARN("receive of %d bytes needs more than %d page fragments", r->size, kUnpackMaxSlicePages);
+        return kInternalError;
+      }
+      const uint32_t len = (uint32_t)std::min<int>(left, (int)kRxPageBytes);
+      LoadMeta& m = r->slot.mem[r->slot.filled++];
+      m.src_off = (run.first + p) * kRxPageBytes;
+      m.len = len;
+      m.dst_off = dst;
+      dst += len;
+      left -= (int)len;
+    }
+  }
+  t->pages.clear();
+  return kSuccess;
+}
+
+Result launchUnpack(Comm* comm, Request* r) {
+#ifdef TCPXB_NO_CUDA
+  (void)comm; (void)r;
+  return kInvalidUsage;
+#else
+  if (r->slot.filled > 0) {
+    int rc = tcpxb_unpack_copy(comm->rxmgr->devBase(), comm->rxmgr->bytes(), r->data, (uint64_t)r->size,
+                               reinterpret_cast<const tcpxbLoadMeta*>(r->slot.mem_dev), (uint32_t)r->slot.filled,
+                               comm->unpack_status_dev, nullptr, comm->stream);
+    if (rc != 0) { WARN("unpack launch failed: %s", tcpxb_kernel_last_error()); return kUnhandledCudaError; }
+  }
+  if (r->unpack_event == nullptr) TCPXB_CHECK(gpu::eventCreate(&r->unpack_event));
+  TCPXB_CHECK(gpu::eventRecord(r->unpack_event, comm->stream));
+  r->unpack_launched = true;
+  return kSuccess;
+#endif
+}
+
+// ------------------------------------------------------------- progress engine
+Result progressSendRequest(Comm* comm, Request* r) {
+  const Flags& f = flags();
+  if (r->size <= f.inline_threshold || r->size == 0) {
+    // small message: record + payload ride the control socket
+    if (!r->inline_queued) {
+      if (r->mem_type == kPtrCuda && r->size > 0 && !stagedUpTo(r, r->size)) return kSuccess;
+      CtrlMsg m = {kCtrlInline, 0, (uint32_t)r->size, 0, (uint32_t)r->size};
+      Result pr = comm->ctrl_send.push(m);
+      if (pr == kInProgress) return kSuccess;
+      TCPXB_CHECK(pr);
+      r->inline_queued = true;  // payload follows
+    }
+    Result fr = comm->ctrl_send.flush();
+    if (fr == kInProgress) return kSuccess;
+    TCPXB_CHECK(fr);
+    if (r->size > 0) {
+      uint8_t* src = r->mem_type == kPtrCuda ? r->stage : r->data;
+      TCPXB_CHECK(socketProgress(kSockSend, comm->ctrl_fd, src, r->size, &r->offset));
+      if (r->offset < r->size) return kSuccess;
+    }
+    r->offset = r->size;
+    r->size_pending = 0;
+    comm->ctrl_stats.tx_cnt.fetch_add(1);
+    comm->ctrl_stats.bytes_done.fetch_add((uint64_t)r->size);
+    traceReq(comm, r, kReqTransmitting);
+    comm->rq.advance(kReqActive);
+    return kSuccess;
+  }
+  const int chunk_size = (int)f.dynamic_chunk_size;
+  while (r->offset < r->size && comm->mapper->hasFlow()) {
+    const int chunk = std::min(chunk_size, r->size - r->offset);
+    if (r->mem_type == kPtrCuda && !stagedUpTo(r, r->offset + chunk)) break;
+    if (comm->ctrl_send.full()) {
+      Result fr = comm->ctrl_send.flush();
+      if (fr == kInProgress) break;
+      TCPXB_CHECK(fr);
+    }
+    const int s = comm->mapper->pick();
+    if (s < 0) break;
+    CtrlMsg m = {kCtrlNormal, (uint16_t)s, (uint32_t)chunk, (uint32_t)r->offset, (uint32_t)r->size};
+    TCPXB_CHECK(comm->ctrl_send.push(m));
+    fillSendTask(comm, r, s, chunk);
+  }
+  Result fr = comm->ctrl_send.flush();
+  if (fr != kInProgress) TCPXB_CHECK(fr);
+  if (r->offset == r->size) {
+    traceReq(comm, r, kReqTransmitting);
+    comm->rq.advance(kReqActive);
+  }
+  return kSuccess;
+}
+
+Result progressRecvRequest(Comm* comm, Request* r) {
+  const Flags& f = flags();
+  for (;;) {
+    if (!comm->have_ctrl) {
+      Result pr = comm->ctrl_recv.pop(&comm->ctrl);
+      if (pr == kInProgress) {
+        if (f.slow_switch[kSlowRxCtrl]) {
+          uint64_t ns = 0;
+          if (comm->ctrl_stall.shouldWarn(&ns) && f.slow_report[kSlowRxCtrl])
+            WARN("%s: no control record for %lu ms (request %p)", comm->ctrl_flow.c_str(), (unsigned long)(ns / 1000000), (void*)r);
+        }
+        return kSuccess;
+      }
+      if (pr != kSuccess) {
+        WARN("%s: control socket failed (%s)", comm->ctrl_flow.c_str(), resultString(pr));
+        return pr;
+      }
+      if (f.slow_switch[kSlowRxCtrl]) comm->ctrl_stall.reset();
+      comm->have_ctrl = true;
+      comm->ctrl_stats.rx_cnt.fetch_add(1);
+      const CtrlMsg& c = comm->ctrl;
+      if (c.type >= kCtrlMaxType || (c.type == kCtrlNormal && c.index >= comm->num_socks) ||
+          (uint64_t)c.offset + c.size > c.total) {
+        WARN("%s: malformed control record type %u index %u size %u offset %u total %u", comm->ctrl_flow.c_str(), c.type,
+             c.index, c.size, c.offset, c.total);
+        return kRemoteError;
+      }
+      if (!r->size_known) {
+        if ((int64_t)c.total > (int64_t)r->capacity) {
+          WARN("message of %u bytes does not fit the posted receive of %d bytes", c.total, r->capacity);
+          return kInvalidUsage;
+        }
+        r->size = (int)c.total;
+        r->size_pending = r->size;
+        r->size_known = true;
+      }
+      if (c.offset != (uint32_t)r->offset) {
+        WARN("control record for offset %u arrived at offset %d", c.offset, r->offset);
+        return kRemoteError;
+      }
+    }
+    const CtrlMsg& c = comm->ctrl;
+    if (c.type == kCtrlInline) {
+      if (r->size > 0) {
+        uint8_t* dst = r->data;
+        if (r->mem_type == kPtrCuda) {
+          // land in one pool page; the unpack path then treats it like any fragment
+          if (r->pages.empty() && !comm->rxmgr->allocPages(1, &r->pages)) return kSuccess;
+          dst = comm->rxmgr->hostBase() + (uint64_t)r->pages[0].first * kRxPageBytes;
+        }
+        if (r->inline_off < r->size) r->inline_off += comm->ctrl_recv.drain(dst + r->inline_off, r->size - r->inline_off);
+        if (r->inline_off < r->size) {
+          Result sr = socketProgress(kSockRecv, comm->ctrl_fd, dst, r->size, &r->inline_off);
+          if (sr != kSuccess) return sr;
+          if (r->inline_off < r->size) return kSuccess;
+        }
+        if (r->mem_type == kPtrCuda) {
+          if (comm->rxmgr->deviceResident()) {
+            const uint64_t off = (uint64_t)r->pages[0].first * kRxPageBytes;
+            TCPXB_CHECK(gpu::copyToDeviceAsync(comm->rxmgr->devBase() + off, comm->rxmgr->hostBase() + off, (size_t)r->size, comm->stream));
+          }
+          LoadMeta& m = r->slot.mem[r->slot.filled++];
+          m.src_off = r->pages[0].first * kRxPageBytes;
+          m.len = (uint32_t)r->size;
+          m.dst_off = 0;
+        }
+        comm->ctrl_stats.bytes_done.fetch_add((uint64_t)r->size);
+      }
+      r->offset = r->size;
+      r->size_pending = 0;
+      comm->have_ctrl = false;
+      traceReq(comm, r, kReqTransmitting);
+      comm->rq.advance(kReqActive);
+      return kSuccess;
+    }
+    TaskRing& tasks = comm->sock[c.index].tasks;
+    if (!tasks.hasFree()) return kSuccess;  // keep the record; retry when a slot frees
+    if (!fillRecvTask(comm, r, c.index, (int)c.size, (int)c.offset)) return kSuccess;  // pool full for now
+    r->offset += (int)c.size;
+    comm->have_ctrl = false;
+    if (r->offset == r->size) {
+      traceReq(comm, r, kReqTransmitting);
+      comm->rq.advance(kReqActive);
+      return kSuccess;
+    }
+  }
+}
+
+Result progress(Comm* comm) {
+  const int err = comm->error.load(std::memory_order_acquire);
+  if (err != kSuccess) return (Result)err;
+  if (comm->rq.empty()) return kSuccess;
+  const Flags& f = flags();
+  comm->mapper->reset();
+  // 1. reap finished tasks, offer sockets with room
+  for (int i = 0; i < comm->num_socks; ++i) {
+    const int idx = (comm->rotate + i) % comm->num_socks;
+    SocketCtx& s = comm->sock[idx];
+    while (s.tasks.has(kTaskInactive)) {
+      Task* t = &s.tasks.front(kTaskInactive);
+      Request* r = t->r;
+      r->size_pending -= t->size;
+      if (t->op == kSockRecv && r->mem_type == kPtrCuda) TCPXB_CHECK(describePages(comm, r, t));
+      traceTask(comm, t, 0);
+      s.tasks.advance(kTaskInactive);
+      if (f.force_ack && t->op == kSockRecv && s.tasks.empty()) setQuickAck(s.fd);
+    }
+    if (s.tasks.hasFree()) comm->mapper->offer(idx, (int)(kMaxTasks - s.tasks.numFree()));
+  }
+  comm->rotate = (comm->rotate + 1) % comm->num_socks;
+  // 2. posted -> active (optionally synchronised: the receiver names the request it posted)
+  while (comm->rq.has(kReqPosted)) {
+    Request* r = &comm->rq.front(kReqPosted);
+    if (f.recv_sync) {
+      uint32_t idx = comm->rq.frontIndex(kReqPosted);
+      if (r->op == kSockRecv) {
+        Result sr = socketSend(comm->ctrl_fd, &idx, sizeof idx, 1000);
+        if (sr != kSuccess) return sr == kInProgress ? kSystemError : sr;
+      } else {
+        // non-blocking: read what is there, finish next round
+        Result sr = socketProgress(kSockRecv, comm->ctrl_fd, &r->sync_word, (int)sizeof r->sync_word, &r->sync_got);
+        if (sr != kSuccess) return sr;
+        if (r->sync_got < (int)sizeof r->sync_word) break;
+        const uint32_t peer = r->sync_word;
+        if (peer != idx) WARN("receive-sync mismatch: local request %u, peer %u", idx, peer);
+      }
+    }
+    traceReq(comm, r, kReqActive);
+    comm->rq.advance(kReqPosted);
+  }
+  // 3. schedule the active requests, oldest first
+  if (!comm->passive && comm->ctrl_send.pending()) {
+    Result fr = comm->ctrl_send.flush();
+    if (fr != kInProgress) TCPXB_CHECK(fr);
+  }
+  while (comm->rq.has(kReqActive)) {
+    Request* r = &comm->rq.front(kReqActive);
+    const uint32_t before = comm->rq.frontIndex(kReqActive);
+    if (r->op == kSockSend) {
+      if (!comm->mapper->hasFlow() && r->size > f.inline_threshold && r->size != 0) break;
+      TCPXB_CHECK(progressSendRequest(comm, r));
+    } else {
+      TCPXB_CHECK(progressRecvRequest(comm, r));
+    }
+    if (comm->rq.frontIndex(kReqActive) == before) break;  // no further progress possible now
+  }
+  // 4. transmitting -> finished, in order
+  while (comm->rq.has(kReqTransmitting)) {
+    Request* r = &comm->rq.front(kReqTransmitting);
+    if (!r->size_known || r->size_pending != 0) break;
+    if (r->op == kSockRecv && r->mem_type == kPtrCuda) {
+      if (comm->recv_mode == kRecvModeUnpack) {
+        // publish the scatter list: records first, then the count
+        std::atomic_thread_fence(std::memory_order_release);
+        *r->slot.cnt = r->slot.filled;
+        std::atomic_thread_fence(std::memory_order_seq_cst);
+        if (comm->rxmgr->deviceResident()) {
+          if (!r->unpack_launched) {
+            if (r->unpack_event == nullptr) TCPXB_CHECK(gpu::eventCreate(&r->unpack_event));
+            TCPXB_CHECK(gpu::eventRecord(r->unpack_event, comm->stream));
+            r->unpack_launched = true;
+          }
+          Result q = gpu::eventQuery(r->unpack_event);
+          if (q == kInProgress) break;
+          TCPXB_CHECK(q);
+        }
+      } else {
+        if (!r->unpack_launched) TCPXB_CHECK(launchUnpack(comm, r));
+        Result q = gpu::eventQuery(r->unpack_event);
+        if (q == kInProgress) break;
+        TCPXB_CHECK(q);
+        if (comm->unpack_status_host[0] != 0) {
+          WARN("unpack kernel reported status %u at record %u", comm->unpack_status_host[0], comm->unpack_status_host[1]);
+          return kInternalError;
+        }
+        releasePages(comm, r);
+        comm->devq->release(r->slot.index);
+        r->slot.active = false;
+      }
+    }
+    if (r->op == kSockSend && r->mem_type == kPtrCuda) comm->tx_tail += r->stage_bytes;
+    traceReq(comm, r, kReqFinished);
+    comm->rq.advance(kReqTransmitting);
+  }
+  return kSuccess;
+}
+
+// Frees finished requests from the head of the ring once the user has seen them
+// (and, in unpack mode, has consumed the pages).
+void retireRequests(Comm* comm) {
+  while (comm->rq.has(kReqFinished)) {
+    Request* r = &comm->rq.front(kReqFinished);
+    if (!r->reported) break;
+    const bool needs_consume = r->op == kSockRecv && r->mem_type == kPtrCuda && comm->recv_mode == kRecvModeUnpack;
+    if (needs_consume && !r->consumed) break;
+    traceReq(comm, r, 0);
+    comm->rq.advance(kReqFinished);
+  }
+}
+
+Result waitConnected(Comm* comm) {
+  for (;;) {
+    const int st = comm->conn_state.load(std::memory_order_acquire);
+    if (st == kConnOk) return kSuccess;
+    if (st == kConnFailed) return kRemoteError;
+    if (!flags().spinwait_connect) return kInProgress;
+    sched_yield();
+  }
+}
+
+Request* claimRequest(Comm* comm) {
+  retireRequests(comm);
+  if (!comm->rq.hasFree()) return nullptr;
+  Request* r = &comm->rq.nextFree();
+  gpu::Event seg[kMaxTxSegments];
+  memcpy(seg, r->seg_event, sizeof seg);
+  gpu::Event ue = r->unpack_event;
+  std::vector<PageRun> pages = std::move(r->pages);
+  pages.clear();
+  *r = Request();
+  memcpy(r->seg_event, seg, sizeof seg);  // events are created once per slot and reused
+  r->unpack_event = ue;
+  r->pages = std::move(pages);
+  r->comm = comm;
+  return r;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------- public API
+Result netInit(LoggerFn logger_fn) {
+  if (logger_fn != nullptr) setLogger(logger_fn);
+  std::lock_guard<std::mutex> l(cg.mu);
+  reloadFlags();
+  const Flags& f = flags();
+  if (!f.enable) {
+    INFO(kSubInit | kSubNet, "NET/GPUDirectTCPX-B200 disabled by NCCL_GPUDIRECTTCPX_SOCKET_ENABLE=0");
+    return kInternalError;
+  }
+  if (cg.inited) return kSuccess;
+  prctl(PR_SET_TIMERSLACK, 1, 0, 0, 0);
+  TCPXB_CHECK(connectionInit());
+  int ndev = 0;
+  netDevices(&ndev);
+  std::vector<std::string> names;
+  for (int i = 0; i < ndev; ++i) names.push_back(netDevice(i)->nif.name);
+  parseCoreRanges(f.tx_bindings.c_str(), names, &cg.tx_bind);
+  parseCoreRanges(f.rx_bindings.c_str(), names, &cg.rx_bind);
+  parseCoreRanges(f.tx_irq_bindings.c_str(), names, &cg.tx_irq_bind);
+  parseCoreRanges(f.rx_irq_bindings.c_str(), names, &cg.rx_irq_bind);
+  TraceConfig tc;
+  tc.task_level = f.task_level_stats != 0;
+  tc.request_level = f.request_level_stats != 0;
+  tc.to_file = f.export_stats_to_file != 0;
+  tc.sampling = (uint64_t)f.sampling_factor;
+  setTraceConfig(tc);
+  if (f.export_stats_to_file && f.file_life_min > 0)
+    cg.gc = std::make_unique<LogGarbageCollector>(f.exporter_path, f.file_life_min, f.file_remove_frequency_s, (int)f.gc_core_index);
+  if (f.report_lifecycle) {
+    RxBufMgr* m = rxBufMgrFor(-1);
+    if (m != nullptr && m->registerApplication((int)getpid()) == kSuccess) cg.registered_app = true;
+  }
+  INFO(kSubInit | kSubNet, "NET/GPUDirectTCPX-B200 ver. 0.1.0: %d device(s), scheduler %s, chunk %ld B, receive mode %s", ndev,
+       f.sched_alg == kSchedKaty ? "KATY" : "RR", (long)f.dynamic_chunk_size, f.recv_mode == kRecvModeUnpack ? "unpack" : "host");
+  cg.inited = true;
+  return kSuccess;
+}
+
+Result netGetProperties(int dev, NetProperties* p) {
+  const NetDevice* d = netDevice(dev);
+  if (d == nullptr || p == nullptr) return kInvalidArgument;
+  p->name = d->nif.name;
+  p->pci_path = d->pci_path.empty() ? nullptr : d->pci_path.c_str();
+  p->guid = (uint64_t)dev;
+  p->ptr_support = kPtrHost | (gpu::compiledWithCuda() ? kPtrCuda : 0);
+  p->speed_mbps = d->speed_mbps;
+  p->port = 0;
+  p->latency = 0;
+  p->max_comms = 65536;
+  p->max_recvs = 1;
+  const bool unpack = flags().recv_mode == kRecvModeUnpack && gpu::compiledWithCuda();
+  p->device_type = unpack ? 1 : 0;
+  p->device_version = unpack ? kUnpackVersion : 0;
+  return kSuccess;
+}
+
+Result startHelpers(Comm* comm) {
+  if (comm->threads_started) return kSuccess;
+  const Flags& f = flags();
+  if (traceConfig().to_file && (traceConfig().task_level || traceConfig().request_level)) {
+    comm->events = std::make_unique<EventLog>(10000, (size_t)f.log_line_limit);
+    char tag[32];
+    snprintf(tag, sizeof tag, "%lx", (unsigned long)comm->id);
+    comm->exporter = std::make_unique<Exporter>(comm->events.get(), f.exporter_path, tag, (int)f.exporter_core_index);
+  }
+  for (int t = 0; t < comm->num_threads; ++t) {
+    comm->helpers[t].id = t;
+    comm->helpers[t].thread = std::thread(helperMain, comm, t);
+  }
+  comm->threads_started = true;
+  return kSuccess;
+}
+
+Result netRegMr(Comm* /*comm*/, void* data, size_t size, int type, MemHandle** out) {
+  if (out == nullptr) return kInvalidArgument;
+  if (type != kPtrHost && type != kPtrCuda) { WARN("memory type %d is not supported", type); return kInvalidArgument; }
+  auto* mh = new MemHandle{data, size, type, -1};
+  if (type == kPtrCuda) {
+    bool is_dev = false;
+    gpu::pointerInfo(data, &mh->gpu_dev, &is_dev);
+    if (!is_dev) {
+      WARN("regMr: %p is not device memory", data);
+      delete mh;
+      return kInvalidArgument;
+    }
+  }
+  *out = mh;
+  return kSuccess;
+}
+
+Result netDeregMr(Comm* /*comm*/, MemHandle* mh) {
+  delete mh;
+  return kSuccess;
+}
+
+Result netIsend(Comm* comm, void* data, int size, int tag, MemHandle* mh, Request** out) {
+  if (comm == nullptr || out == nullptr || size < 0) return kInvalidArgument;
+  *out = nullptr;
+  Result cr = waitConnected(comm);
+  if (cr == kInProgress) return kSuccess;
+  TCPXB_CHECK(cr);
+  const int err = comm->error.load();
+  if (err != kSuccess) return (Result)err;
+  Request* r = claimRequest(comm);
+  if (r == nullptr) return kSuccess;  // ring full: the caller retries
+  r->op = kSockSend;
+  r->data = static_cast<uint8_t*>(data);
+  r->size = size;
+  r->capacity = size;
+  r->tag = tag;
+  r->mem_type = mh != nullptr ? mh->type : kPtrHost;
+  r->gpu_dev = mh != nullptr ? mh->gpu_dev : -1;
+  r->size_pending = size;
+  r->size_known = true;
+  if (r->mem_type == kPtrCuda) {
+    Result sr = startCudaSend(comm, r, mh);
+    if (sr == kInProgress) return kSuccess;  // staging ring full: retry later
+    TCPXB_CHECK(sr);
+  }
+  traceReq(comm, r, kReqPosted);
+  comm->rq.admit();
+  *out = r;
+  return progress(comm);
+}
+
+Result netIrecv(Comm* comm, int n, void** data, int* sizes, int* tags, MemHandle** mhs, Request** out) {
+  if (comm == nullptr || out == nullptr || n != 1) return kInvalidArgument;
+  *out = nullptr;
+  Result cr = waitConnected(comm);
+  if (cr == kInProgress) return kSuccess;
+  TCPXB_CHECK(cr);
+  const int err = comm->error.load();
+  if (err != kSuccess) return (Result)err;
+  MemHandle* mh = mhs != nullptr ? mhs[0] : nullptr;
+  const int mem_type = mh != nullptr ? mh->type : kPtrHost;
+  if (mem_type == kPtrCuda) {
+    TCPXB_CHECK(ensureCudaRecv(comm, mh->gpu_dev >= 0 ? mh->gpu_dev : comm->gpu_dev));
+    if (comm->devq->inUse() >= (uint64_t)kUnpackQueueDepth) return kSuccess;  // consumer is behind
+  }
+  Request* r = claimRequest(comm);
+  if (r == nullptr) return kSuccess;
+  r->op = kSockRecv;
+  r->data = static_cast<uint8_t*>(data[0]);
+  r->capacity = sizes[0];
+  r->size = sizes[0];
+  r->tag = tags != nullptr ? tags[0] : 0;
+  r->mem_type = mem_type;
+  r->gpu_dev = mh != nullptr ? mh->gpu_dev : -1;
+  r->size_pending = -1;
+  r->size_known = false;
+  if (mem_type == kPtrCuda) {
+    comm->devq->nextFree(&r->slot);
+    *r->slot.cnt = 0;
+  }
+  traceReq(comm, r, kReqPosted);
+  comm->rq.admit();
+  *out = r;
+  return progress(comm);
+}
+
+Result netIflush(Comm* /*comm*/, int /*n*/, void** /*data*/, int* /*sizes*/, MemHandle** /*mhs*/, Request** req) {
+  // Data is made visible by stream order (copy engine or unpack kernel) before
+  // test() reports completion; nothing is left to flush.
+  if (req != nullptr) *req = nullptr;
+  return kSuccess;
+}
+
+Result netTest(Request* r, int* done, int* size) {
+  if (r == nullptr || done == nullptr) return kInvalidArgument;
+  *done = 0;
+  Comm* comm = r->comm;
+  TCPXB_CHECK(progress(comm));
+  // finished = the request has left the transmitting stage
+  bool finished = false;
+  const uint32_t nfin = comm->rq.count(kReqFinished);
+  for (uint32_t k = 0; k < nfin; ++k)
+    if (&comm->rq.at(kReqFinished, k) == r) { finished = true; break; }
+  if (!finished) return kSuccess;
+  *done = 1;
+  if (size != nullptr) *size = r->size;
+  r->reported = true;
+  retireRequests(comm);
+  return kSuccess;
+}
+
+Result netGetDeviceHandle(Comm* comm, void** dev_handle, size_t* size) {
+  if (comm == nullptr || dev_handle == nullptr) return kInvalidArgument;
+  int cur = comm->gpu_dev;
+  if (cur < 0 && gpu::currentDevice(&cur) != kSuccess) return kUnhandledCudaError;
+  TCPXB_CHECK(ensureCudaRecv(comm, cur, /*want_device_handle=*/true));
+  *dev_handle = comm->devq->deviceHandle();
+  if (size != nullptr) *size = sizeof(UnpackDeviceHandle);
+  return kSuccess;
+}
+
+Result netGetDeviceMr(Comm* /*comm*/, MemHandle* mh, void** dptr) {
+  if (mh == nullptr || dptr == nullptr) return kInvalidArgument;
+  *dptr = mh->ptr;  // the unpack consumer indexes the user buffer directly
+  return kSuccess;
+}
+
+Result netIrecvConsumed(Comm* comm, int n, Request* r) {
+  if (comm == nullptr || r == nullptr || n != 1) return kInvalidArgument;
+  if (r->mem_type != kPtrCuda || comm->recv_mode != kRecvModeUnpack) { r->consumed = true; retireRequests(comm); return kSuccess; }
+  if (!comm->devq->release(r->slot.index)) {
+    WARN("irecvConsumed out of order: slot %lu is not the oldest", (unsigned long)r->slot.index);
+    return kInvalidUsage;
+  }
+  releasePages(comm, r);
+  r->slot.active = false;
+  r->consumed = true;
+  retireRequests(comm);
+  return kSuccess;
+}
+
+Result netRequestScatterList(Request* r, ScatterList* out) {
+  if (r == nullptr || out == nullptr || r->op != kSockRecv || r->mem_type != kPtrCuda) return kInvalidArgument;
+  out->host = r->slot.mem;
+  out->dev = r->slot.mem_dev;
+  out->count = r->slot.filled;
+  out->pool_dev = r->comm->rxmgr->devBase();
+  out->pool_bytes = r->comm->rxmgr->bytes();
+  return kSuccess;
+}
+
+int netCommFlowCounters(Comm* comm, FlowCounters* out, int max) {
+  int n = 0;
+  for (int i = 0; i < comm->num_socks && n < max; ++i, ++n) {
+    const FlowStats& s = comm->sock[i].stats;
+    out[n] = {s.flow_id, s.bytes_posted.load(), s.bytes_done.load(), s.tx_cnt.load(), s.tx_completion_cnt.load(), s.rx_cnt.load()};
+  }
+  return n;
+}
+
+std::vector<std::string> netCommStatsLines(Comm* comm) {
+  std::vector<std::string> lines;
+  for (int i = 0; i < comm->num_socks; ++i) lines.push_back(flowStatsLine(comm->sock[i].stats, comm->sock[i].flow, comm->passive));
+  return lines;
+}
+
+void freeComm(Comm* comm) {
+  if (comm == nullptr) return;
+  comm->stop.store(true, std::memory_order_release);
+  if (comm->threads_started) {
+    for (int t = 0; t < comm->num_threads; ++t) {
+      { std::lock_guard<std::mutex> l(comm->helpers[t].mu); }
+      comm->helpers[t].cv.notify_all();
+      if (comm->helpers[t].thread.joinable()) comm->helpers[t].thread.join();
+    }
+  }
+  if (comm->ctrl_fd >= 0) close(comm->ctrl_fd);
+  for (int i = 0; i < kMaxSockets; ++i) {
+    if (comm->sock[i].fd < 0) continue;
+    if (comm->passive && comm->rxmgr != nullptr) comm->rxmgr->removeFlowRule(comm->sock[i].fd);
+    close(comm->sock[i].fd);
+  }
+  if (comm->exporter) comm->exporter->stop();
+  // anything still holding pool pages gives them back
+  for (uint32_t i = 0; i < kMaxRequests; ++i) {
+    Request& r = comm->rq.slot(i);
+    if (comm->rxmgr != nullptr && !r.pages.empty()) comm->rxmgr->releasePages(r.pages.data(), r.pages.size());
+    r.pages.clear();
+    for (auto& e : r.seg_event) { gpu::eventDestroy(e); e = nullptr; }
+    gpu::eventDestroy(r.unpack_event);
+    r.unpack_event = nullptr;
+  }
+  for (int i = 0; i < kMaxSockets; ++i) {
+    for (uint32_t k = 0; k < kMaxTasks; ++k) {
+      Task& t = comm->sock[i].tasks.slot(k);
+      if (comm->rxmgr != nullptr && !t.pages.empty()) comm->rxmgr->releasePages(t.pages.data(), t.pages.size());
+      t.pages.clear();
+    }
+  }
+  comm->devq.reset();
+  gpu::hostFreeMapped(comm->tx_stage);
+  gpu::hostFreeMapped(comm->unpack_status_host);
+  gpu::streamDestroy(comm->stream);
+  delete comm;
+}
+
+Result netClose(Comm* comm) {
+  if (comm == nullptr) return kSuccess;
+  const Flags& f = flags();
+  if (comm->devq && comm->devq->inUse() != 0)
+    WARN("closing a receive comm with %lu scatter lists not consumed", (unsigned long)comm->devq->inUse());
+  uint64_t posted = 0, done = 0;
+  for (int i = 0; i < comm->num_socks; ++i) {
+    posted += comm->sock[i].stats.bytes_posted.load();
+    done += comm->sock[i].stats.bytes_done.load();
+  }
+  INFO(kSubNet, "closing %s comm %lx: %lu bytes handed to the kernel, %lu completed, %d sockets", comm->passive ? "recv" : "send",
+       (unsigned long)comm->id, (unsigned long)posted, (unsigned long)done, comm->num_socks);
+  std::vector<std::string> lines = netCommStatsLines(comm);
+  if (f.log_stats_to_stdout) {
+    for (const auto& l : lines) printf("%s\n", l.c_str());
+    fflush(stdout);
+  }
+  if (f.export_stats_to_file) {
+    char tag[32];
+    snprintf(tag, sizeof tag, "%lx", (unsigned long)comm->id);
+    Exporter::writeStatsFile(Exporter::statsPath(f.exporter_path, tag), lines);
+  }
+  freeComm(comm);
+  return kSuccess;
+}
+
+}  // namespace tcpxb

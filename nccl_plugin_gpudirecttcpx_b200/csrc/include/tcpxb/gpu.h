@@ -1,0 +1,59 @@
+// Thin, lazily initialised wrapper over the CUDA runtime for the host core.
+//
+// Plays the part of the reference's GPU wrapper (reference: src/gpu/cuda_wrapper.h:22-41,
+// src/gpu/cuda_wrapper.cu:68-143 lazy per-GPU init and current-device lookup,
+// :278-282 NUMA heuristic).  Differences: the runtime is linked statically and only
+// touched when a CUDA pointer or a device handle shows up, so the host-memory path
+// runs on machines with no GPU and no driver; and when the core is compiled with
+// TCPXB_NO_CUDA every call reports "no CUDA" and pinned allocations fall back to
+// page-aligned host memory, which keeps the buffer-manager logic testable on CPUs.
+#ifndef TCPXB_GPU_H_
+#define TCPXB_GPU_H_
+
+#include <stddef.h>
+#include <stdint.h>
+#include <string>
+
+#include "tcpxb/base.h"
+
+namespace tcpxb {
+namespace gpu {
+
+bool compiledWithCuda();
+// True when the CUDA runtime initialises and reports at least one device.
+bool available();
+int deviceCount();
+Result currentDevice(int* dev);
+Result setDevice(int dev);
+// Classifies a pointer: *is_device is true for device (and managed) memory.
+Result pointerInfo(const void* p, int* device, bool* is_device);
+std::string pciBusId(int dev);  // lower case, "" when unknown
+int numaNode(int dev);          // sysfs, else dev < count/2 ? 0 : 1
+
+// Pinned, portable, device-mapped host memory.  *dev_ptr receives the address the
+// GPU uses (equal to the host address under unified addressing).  Without CUDA
+// this is page-aligned host memory and *dev_ptr == *host_ptr.
+Result hostAllocMapped(size_t bytes, void** host_ptr, void** dev_ptr);
+void hostFreeMapped(void* host_ptr);
+Result deviceAlloc(size_t bytes, void** ptr);
+void deviceFree(void* ptr);
+
+using Stream = void*;
+using Event = void*;
+Result streamCreate(Stream* s);      // non-blocking stream
+void streamDestroy(Stream s);
+Result eventCreate(Event* e);        // timing disabled
+void eventDestroy(Event e);
+Result eventRecord(Event e, Stream s);
+// kSuccess when complete, kInProgress when not, error otherwise.
+Result eventQuery(Event e);
+Result streamSynchronize(Stream s);
+Result copyToHostAsync(void* host_dst, const void* dev_src, size_t bytes, Stream s);
+Result copyToDeviceAsync(void* dev_dst, const void* host_src, size_t bytes, Stream s);
+Result memsetAsync(void* dev, int value, size_t bytes, Stream s);
+
+const char* lastError();
+
+}  // namespace gpu
+}  // namespace tcpxb
+#endif  // TCPXB_GPU_H_

@@ -1,0 +1,138 @@
+// The slice of NCCL's external network API this plugin implements, written out
+// from the public ext-net interface (versions 7 and 8) because the headers are not
+// shipped with NCCL binaries.  Only declarations: every struct below is what NCCL
+// reads when it dlopen()s libnccl-net.so and looks up ncclNetPlugin_v8 /
+// ncclNetPlugin_v7.  The reference exports v7 only (reference: src/nccl_plugin.cc:22-42).
+#ifndef TCPXB_NCCL_NET_ABI_H_
+#define TCPXB_NCCL_NET_ABI_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  ncclSuccess = 0,
+  ncclUnhandledCudaError = 1,
+  ncclSystemError = 2,
+  ncclInternalError = 3,
+  ncclInvalidArgument = 4,
+  ncclInvalidUsage = 5,
+  ncclRemoteError = 6,
+  ncclInProgress = 7,
+} ncclResult_t;
+
+typedef enum {
+  NCCL_LOG_NONE = 0, NCCL_LOG_VERSION = 1, NCCL_LOG_WARN = 2, NCCL_LOG_INFO = 3, NCCL_LOG_ABORT = 4, NCCL_LOG_TRACE = 5
+} ncclDebugLogLevel;
+typedef void (*ncclDebugLogger_t)(ncclDebugLogLevel level, unsigned long flags, const char* file, int line,
+                                  const char* fmt, ...);
+
+#define NCCL_NET_HANDLE_MAXSIZE 128
+#define NCCL_PTR_HOST 0x1
+#define NCCL_PTR_CUDA 0x2
+#define NCCL_PTR_DMABUF 0x4
+#define NCCL_NET_MAX_REQUESTS 32
+
+typedef enum { NCCL_NET_DEVICE_HOST = 0, NCCL_NET_DEVICE_UNPACK = 1 } ncclNetDeviceType;
+
+typedef struct {
+  ncclNetDeviceType netDeviceType;
+  int netDeviceVersion;
+  void* handle;
+  size_t size;
+  int needsProxyProgress;
+} ncclNetDeviceHandle_v7_t;
+typedef ncclNetDeviceHandle_v7_t ncclNetDeviceHandle_v8_t;
+
+typedef struct {
+  char* name;
+  char* pciPath;
+  uint64_t guid;
+  int ptrSupport;
+  int speed;
+  int port;
+  float latency;
+  int maxComms;
+  int maxRecvs;
+  ncclNetDeviceType netDeviceType;
+  int netDeviceVersion;
+} ncclNetProperties_v7_t;
+
+typedef struct {
+  char* name;
+  char* pciPath;
+  uint64_t guid;
+  int ptrSupport;
+  int regIsGlobal;
+  int speed;
+  int port;
+  float latency;
+  int maxComms;
+  int maxRecvs;
+  ncclNetDeviceType netDeviceType;
+  int netDeviceVersion;
+} ncclNetProperties_v8_t;
+
+typedef struct {
+  const char* name;
+  ncclResult_t (*init)(ncclDebugLogger_t logFunction);
+  ncclResult_t (*devices)(int* ndev);
+  ncclResult_t (*getProperties)(int dev, ncclNetProperties_v7_t* props);
+  ncclResult_t (*listen)(int dev, void* handle, void** listenComm);
+  ncclResult_t (*connect)(int dev, void* handle, void** sendComm, ncclNetDeviceHandle_v7_t** sendDevComm);
+  ncclResult_t (*accept)(void* listenComm, void** recvComm, ncclNetDeviceHandle_v7_t** recvDevComm);
+  ncclResult_t (*regMr)(void* comm, void* data, int size, int type, void** mhandle);
+  ncclResult_t (*regMrDmaBuf)(void* comm, void* data, size_t size, int type, uint64_t offset, int fd, void** mhandle);
+  ncclResult_t (*deregMr)(void* comm, void* mhandle);
+  ncclResult_t (*isend)(void* sendComm, void* data, int size, int tag, void* mhandle, void** request);
+  ncclResult_t (*irecv)(void* recvComm, int n, void** data, int* sizes, int* tags, void** mhandles, void** request);
+  ncclResult_t (*iflush)(void* recvComm, int n, void** data, int* sizes, void** mhandles, void** request);
+  ncclResult_t (*test)(void* request, int* done, int* sizes);
+  ncclResult_t (*closeSend)(void* sendComm);
+  ncclResult_t (*closeRecv)(void* recvComm);
+  ncclResult_t (*closeListen)(void* listenComm);
+  ncclResult_t (*getDeviceMr)(void* comm, void* mhandle, void** dptr_mhandle);
+  ncclResult_t (*irecvConsumed)(void* recvComm, int n, void* request);
+} ncclNet_v7_t;
+
+typedef struct {
+  const char* name;
+  ncclResult_t (*init)(ncclDebugLogger_t logFunction);
+  ncclResult_t (*devices)(int* ndev);
+  ncclResult_t (*getProperties)(int dev, ncclNetProperties_v8_t* props);
+  ncclResult_t (*listen)(int dev, void* handle, void** listenComm);
+  ncclResult_t (*connect)(int dev, void* handle, void** sendComm, ncclNetDeviceHandle_v8_t** sendDevComm);
+  ncclResult_t (*accept)(void* listenComm, void** recvComm, ncclNetDeviceHandle_v8_t** recvDevComm);
+  ncclResult_t (*regMr)(void* comm, void* data, size_t size, int type, void** mhandle);
+  ncclResult_t (*regMrDmaBuf)(void* comm, void* data, size_t size, int type, uint64_t offset, int fd, void** mhandle);
+  ncclResult_t (*deregMr)(void* comm, void* mhandle);
+  ncclResult_t (*isend)(void* sendComm, void* data, int size, int tag, void* mhandle, void** request);
+  ncclResult_t (*irecv)(void* recvComm, int n, void** data, int* sizes, int* tags, void** mhandles, void** request);
+  ncclResult_t (*iflush)(void* recvComm, int n, void** data, int* sizes, void** mhandles, void** request);
+  ncclResult_t (*test)(void* request, int* done, int* sizes);
+  ncclResult_t (*closeSend)(void* sendComm);
+  ncclResult_t (*closeRecv)(void* recvComm);
+  ncclResult_t (*closeListen)(void* listenComm);
+  ncclResult_t (*getDeviceMr)(void* comm, void* mhandle, void** dptr_mhandle);
+  ncclResult_t (*irecvConsumed)(void* recvComm, int n, void* request);
+} ncclNet_v8_t;
+
+// Extra, non-NCCL exports for tests and tools.
+typedef struct {
+  uint64_t flow_id, bytes_posted, bytes_done, tx_cnt, tx_completion_cnt, rx_cnt;
+} tcpxbFlowCounters;
+// Per-data-socket counters of a send or receive comm; returns how many were written.
+int tcpxb_comm_flow_counters(void* comm, tcpxbFlowCounters* out, int max);
+// Writes the comm's per-flow summary lines, '\n'-separated, into buf; returns the length needed.
+int tcpxb_comm_stats_text(void* comm, char* buf, int len);
+// Number of documented environment variables; fills env/kind/default/doc of entry i.
+int tcpxb_flag_count(void);
+int tcpxb_flag_doc(int i, const char** env, const char** kind, const char** dflt, const char** doc);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  // TCPXB_NCCL_NET_ABI_H_

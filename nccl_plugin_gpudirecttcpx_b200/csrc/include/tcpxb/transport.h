@@ -1,0 +1,274 @@
+// Core transport: communicators striped over several TCP sockets, the progress
+// engine behind isend / irecv / test, helper threads, and the public C++ API the
+// plugin table and the collective engine call.
+//
+// Functional counterpart of the reference's core (reference: src/net_tcpx.cc:454-1543,
+// structures in src/common.h:42-219, connection layer src/connect.cc).  What is
+// kept: the connect handle layout, the control-record wire format, the
+// ctrl-first handshake, one request ring (16) per comm and one task ring (6) per
+// socket, chunk striping by a flow mapper, in-order completion.  What differs:
+// errors propagate to test() instead of exiting or hanging, helper threads block
+// in poll() when every socket would block, test() writes the received size, CUDA
+// buffers are served by staging plus the emulated rx page pool, and nothing
+// sleeps during connection setup unless asked to.
+#ifndef TCPXB_TRANSPORT_H_
+#define TCPXB_TRANSPORT_H_
+
+#include <sys/uio.h>
+
+#include <atomic>
+#include <condition_variable>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "tcpxb/base.h"
+#include "tcpxb/ctrl_sock.h"
+#include "tcpxb/dev_queue.h"
+#include "tcpxb/flags.h"
+#include "tcpxb/flow_mapper.h"
+#include "tcpxb/gpu.h"
+#include "tcpxb/rx_buf_mgr.h"
+#include "tcpxb/socket_utils.h"
+#include "tcpxb/stage_ring.h"
+#include "tcpxb/telemetry.h"
+#include "tcpxb/timeout.h"
+
+namespace tcpxb {
+
+constexpr int kPtrHost = 1, kPtrCuda = 2;
+constexpr int kHandleMaxSize = 128;  // NCCL_NET_HANDLE_MAXSIZE
+constexpr int kMaxInlineThreshold = 2048;
+constexpr int kMaxTxSegments = 8;
+
+// ---- devices ------------------------------------------------------------------
+struct NetDevice {
+  NetIf nif;
+  std::string pci_path;  // realpath of /sys/class/net/<if>/device, "" for virtual ones
+  int speed_mbps = 10000;
+};
+
+// Core ranges per NIC, "eth1:8-21,112-125;eth2:..." (reference: src/common.cc:65-123).
+constexpr int kMaxRanges = 8;
+struct CpuBindings {
+  int n_ranges[kMaxIfs] = {};
+  int lo[kMaxIfs][kMaxRanges] = {};
+  int hi[kMaxIfs][kMaxRanges] = {};
+};
+// `if_names[i]` is the name of device i; entries naming unknown NICs are skipped.
+bool parseCoreRanges(const char* text, const std::vector<std::string>& if_names, CpuBindings* out);
+
+// ---- wire: connect handle (reference: src/common.h:101-110) ----------------------
+struct Handle {
+  SocketAddress connect_addr;
+  int port_start, port_count;
+  int num_socks;
+  int num_threads;
+  bool redirect_ctrl;
+  SocketAddress ctrl_addr;
+  void* connect_args;  // scratch of the connecting side, zero on the wire
+};
+static_assert(sizeof(Handle) <= kHandleMaxSize, "handle must fit NCCL's handle buffer");
+
+enum ConnState : int { kConnOk = 0, kConnPending = 1, kConnFailed = 2 };
+
+struct Comm;
+struct Request;
+
+struct MemHandle {
+  void* ptr;
+  size_t size;
+  int type;     // kPtrHost / kPtrCuda
+  int gpu_dev;  // owning GPU for CUDA memory, else -1
+};
+
+// ---- tasks: one chunk on one data socket ------------------------------------------
+enum TaskStage { kTaskActive = 1, kTaskCompleting = 2, kTaskInactive = 3 };
+struct Task {
+  Request* r = nullptr;
+  int op = 0;                 // SockOp
+  uint8_t* host_ptr = nullptr;  // contiguous source / destination, or null when scattered
+  int size = 0;
+  int offset = 0;             // bytes moved so far
+  int msg_offset = 0;         // chunk offset in the message
+  // receive into pool pages
+  std::vector<PageRun> pages;
+  std::vector<struct iovec> iov;
+  size_t iov_pos = 0;
+  // zero-copy accounting: notification ids [zc_first, zc_first + zc_count)
+  uint32_t zc_first = 0, zc_count = 0;
+  bool zerocopy = false;
+};
+
+enum ReqStage { kReqPosted = 1, kReqActive = 2, kReqTransmitting = 3, kReqFinished = 4 };
+struct Request {
+  Comm* comm = nullptr;
+  int op = 0;
+  uint8_t* data = nullptr;
+  int size = 0;             // send: message bytes; recv: buffer bytes, then message bytes
+  int capacity = 0;         // recv: posted buffer bytes
+  int tag = 0;
+  int mem_type = kPtrHost;
+  int gpu_dev = -1;
+  int offset = 0;           // bytes scheduled into tasks
+  int size_pending = 0;     // bytes not yet moved (-1: size still unknown)
+  bool size_known = false;
+  bool reported = false;    // test() returned done
+  bool consumed = false;    // unpack mode: irecvConsumed arrived
+  // CUDA send: staging
+  uint8_t* stage = nullptr;
+  uint64_t stage_bytes = 0;
+  int seg_bytes = 0, n_segs = 0, segs_done = 0;
+  gpu::Event seg_event[kMaxTxSegments] = {};
+  // CUDA receive
+  UnpackSlot slot;
+  std::vector<PageRun> pages;
+  bool unpack_launched = false;
+  gpu::Event unpack_event = nullptr;
+  // inline transfer progress
+  int inline_off = 0;
+  bool inline_queued = false;  // send: the inline record is in the control buffer
+  // receive-sync word read from the control socket
+  uint32_t sync_word = 0;
+  int sync_got = 0;
+};
+
+using TaskRing = StageRing<Task, kMaxTasks, 3, true>;
+using RequestRing = StageRing<Request, kMaxRequests, 4, false>;
+
+struct SocketCtx {
+  int fd = -1;
+  TaskRing tasks;
+  FlowStats stats;
+  std::string flow;
+  StallDetector stall;
+  // zero-copy notification ids: [zc_done, zc_next) are outstanding
+  uint32_t zc_next = 0, zc_done = 0;
+  bool zerocopy_enabled = false;
+};
+
+struct HelperThread {
+  int id = 0;
+  std::thread thread;
+  std::mutex mu;
+  std::condition_variable cv;
+  std::atomic<uint32_t> kicks{0};
+  uint32_t seen = 0;
+};
+
+struct Comm {
+  bool passive = false;  // receiving side
+  std::atomic<int> conn_state{kConnPending};
+  std::atomic<int> error{kSuccess};  // first fatal Result seen by any thread
+  int dev = 0;
+  int num_socks = 0, num_threads = 0;
+  SocketCtx sock[kMaxSockets];
+  int ctrl_fd = -1;
+  std::string ctrl_flow;
+  CtrlSendBuffer ctrl_send;
+  CtrlRecvBuffer ctrl_recv;
+  StallDetector ctrl_stall;
+  FlowStats ctrl_stats;
+  RequestRing rq;
+  std::unique_ptr<FlowMapper> mapper;
+  HelperThread helpers[kMaxThreads];
+  std::atomic<bool> stop{false};
+  bool threads_started = false;
+  int rotate = 0;  // socket the reaping pass starts from
+  // pending control record on the receive side
+  bool have_ctrl = false;
+  CtrlMsg ctrl;
+  // CUDA resources (lazy)
+  int gpu_dev = -1;
+  int recv_mode = kRecvModeHost;
+  gpu::Stream stream = nullptr;
+  RxBufMgr* rxmgr = nullptr;
+  std::unique_ptr<DevQueue> devq;
+  uint8_t* tx_stage = nullptr;
+  uint64_t tx_stage_bytes = 0, tx_head = 0, tx_tail = 0;  // ring offsets (monotonic)
+  uint32_t* unpack_status_host = nullptr;
+  uint32_t* unpack_status_dev = nullptr;
+  // telemetry
+  std::unique_ptr<EventLog> events;
+  std::unique_ptr<Exporter> exporter;
+  uint64_t id = 0;
+  uint32_t stride = 0;
+  SocketAddress peer_addr;
+};
+
+struct ListenComm {
+  int dev = 0;
+  int data_fd = -1;
+  int ctrl_fd = -1;
+  int num_socks = 0, num_threads = 0;
+  void* accept_state = nullptr;
+};
+
+// ---- public API --------------------------------------------------------------------
+Result netInit(LoggerFn logger);
+Result netDevices(int* ndev);
+const NetDevice* netDevice(int dev);
+struct NetProperties {
+  const char* name;
+  const char* pci_path;  // nullptr for virtual interfaces
+  uint64_t guid;
+  int ptr_support;
+  int speed_mbps;
+  int port;
+  float latency;
+  int max_comms;
+  int max_recvs;
+  int device_type;     // 0 host, 1 unpack
+  int device_version;
+};
+Result netGetProperties(int dev, NetProperties* props);
+Result netListen(int dev, void* handle, ListenComm** lcomm);
+// Non-blocking: *comm stays null until the connection is up.
+Result netConnect(int dev, void* handle, Comm** comm);
+Result netAccept(ListenComm* lcomm, Comm** comm);
+Result netRegMr(Comm* comm, void* data, size_t size, int type, MemHandle** mh);
+Result netDeregMr(Comm* comm, MemHandle* mh);
+Result netIsend(Comm* comm, void* data, int size, int tag, MemHandle* mh, Request** req);
+Result netIrecv(Comm* comm, int n, void** data, int* sizes, int* tags, MemHandle** mhs, Request** req);
+Result netIflush(Comm* comm, int n, void** data, int* sizes, MemHandle** mhs, Request** req);
+Result netTest(Request* req, int* done, int* size);
+Result netClose(Comm* comm);
+Result netCloseListen(ListenComm* lcomm);
+// Unpack mode.  The device handle NCCL's kernels read; the memory handle they get.
+Result netGetDeviceHandle(Comm* comm, void** dev_handle, size_t* size);
+Result netGetDeviceMr(Comm* comm, MemHandle* mh, void** dptr_mhandle);
+Result netIrecvConsumed(Comm* comm, int n, Request* req);
+// Selects the receive mode of comms accepted from now on by this thread's next
+// netAccept (used by the collective engine, which unpacks with its own kernels).
+void netSetAcceptRecvMode(ListenComm* lcomm, int recv_mode);
+
+// Scatter list of a finished unpack-mode receive.
+struct ScatterList {
+  const LoadMeta* host;
+  const LoadMeta* dev;
+  uint64_t count;
+  void* pool_dev;
+  uint64_t pool_bytes;
+};
+Result netRequestScatterList(Request* req, ScatterList* out);
+
+// Test and statistics accessors.
+struct FlowCounters {
+  uint64_t flow_id, bytes_posted, bytes_done, tx_cnt, tx_completion_cnt, rx_cnt;
+};
+int netCommFlowCounters(Comm* comm, FlowCounters* out, int max);
+std::vector<std::string> netCommStatsLines(Comm* comm);
+void netResetForTests();
+
+// Connection layer internals shared by transport.cc and connect.cc.
+Result connectionInit();
+Result startHelpers(Comm* comm);
+Comm* newComm(int dev, bool passive);
+void freeComm(Comm* comm);
+// threads x sockets-per-thread for device `dev` (reference: src/connect.cc:165-220).
+void chooseSocksThreads(int dev, int* nsocks, int* nthreads);
+
+}  // namespace tcpxb
+#endif  // TCPXB_TRANSPORT_H_

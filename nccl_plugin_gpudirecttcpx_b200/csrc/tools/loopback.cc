@@ -1,0 +1,289 @@
+// Stand-alone driver of the ncclNet table: two processes on one machine exchange
+// seeded random payloads through the plugin, with no NCCL and no GPU involved.
+//
+//   tcpxb_loopback --plugin <libnccl-net.so | libtcpxb_host.so> [--v7]
+//                  [--sizes 1024,65536,4194304,67108864] [--inflight 8] [--iters 4]
+//
+// The parent is the receiver, the forked child the sender.  One comm is opened per
+// device the plugin reports (set NCCL_GPUDIRECTTCPX_VIRTUAL_NICS=2 to get two
+// "NICs" on lo); every comm moves `inflight` messages per iteration with tags
+// 0..inflight-1.  Payload bytes are a pure function of (seed, comm, iteration,
+// tag), so the receiver regenerates and compares them byte for byte.  At the end
+// each side prints per-flow byte counters and one JSON line per size.
+// The reference has no such tool: its only tests are two unit tests of the stats
+// code (reference: src/stats/tracepoint_test.cc, src/stats/stats_buffer_test.cc).
+#include <dlfcn.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/wait.h>
+#include <time.h>
+#include <unistd.h>
+
+#include <string>
+#include <vector>
+
+#include "tcpxb/nccl_net_abi.h"
+
+namespace {
+
+struct Api {
+  const char* name;
+  ncclResult_t (*init)(ncclDebugLogger_t);
+  ncclResult_t (*devices)(int*);
+  ncclResult_t (*listen)(int, void*, void**);
+  ncclResult_t (*connect)(int, void*, void**, ncclNetDeviceHandle_v8_t**);
+  ncclResult_t (*accept)(void*, void**, ncclNetDeviceHandle_v8_t**);
+  ncclResult_t (*regMr8)(void*, void*, size_t, int, void**);
+  ncclResult_t (*regMr7)(void*, void*, int, int, void**);
+  ncclResult_t (*deregMr)(void*, void*);
+  ncclResult_t (*isend)(void*, void*, int, int, void*, void**);
+  ncclResult_t (*irecv)(void*, int, void**, int*, int*, void**, void**);
+  ncclResult_t (*test)(void*, int*, int*);
+  ncclResult_t (*closeSend)(void*);
+  ncclResult_t (*closeRecv)(void*);
+  ncclResult_t (*closeListen)(void*);
+};
+
+int (*flow_counters)(void*, tcpxbFlowCounters*, int) = nullptr;
+int (*stats_text)(void*, char*, int) = nullptr;
+
+#define CHECK(call)                                                          \
+  do {                                                                       \
+    ncclResult_t r_ = (call);                                                \
+    if (r_ != ncclSuccess) {                                                 \
+      fprintf(stderr, "%s:%d %s -> %d\n", __FILE__, __LINE__, #call, (int)r_); \
+      return 1;                                                              \
+    }                                                                        \
+  } while (0)
+
+double nowSec() {
+  struct timespec ts;
+  clock_gettime(CLOCK_MONOTONIC, &ts);
+  return ts.tv_sec + ts.tv_nsec * 1e-9;
+}
+
+// xorshift64*: payload = f(seed, comm, iter, tag)
+void fillPayload(uint8_t* p, size_t n, uint64_t key) {
+  uint64_t x = key * 0x9e3779b97f4a7c15ull + 0x1234567;
+  if (x == 0) x = 1;
+  size_t i = 0;
+  for (; i + 8 <= n; i += 8) {
+    x ^= x >> 12; x ^= x << 25; x ^= x >> 27;
+    uint64_t v = x * 0x2545f4914f6cdd1dull;
+    memcpy(p + i, &v, 8);
+  }
+  for (; i < n; ++i) {
+    x ^= x >> 12; x ^= x << 25; x ^= x >> 27;
+    p[i] = (uint8_t)(x * 0x2545f4914f6cdd1dull >> 56);
+  }
+}
+uint64_t keyOf(uint64_t seed, int comm, int size_idx, int iter, int tag) {
+  return ((((seed * 131 + (uint64_t)comm) * 131 + (uint64_t)size_idx) * 131 + (uint64_t)iter) * 131) + (uint64_t)tag;
+}
+
+bool loadApi(const char* path, bool v7, Api* api) {
+  void* h = dlopen(path, RTLD_NOW | RTLD_LOCAL);
+  if (h == nullptr) { fprintf(stderr, "dlopen(%s): %s\n", path, dlerror()); return false; }
+  flow_counters = (int (*)(void*, tcpxbFlowCounters*, int))dlsym(h, "tcpxb_comm_flow_counters");
+  stats_text = (int (*)(void*, char*, int))dlsym(h, "tcpxb_comm_stats_text");
+  memset(api, 0, sizeof *api);
+  if (v7) {
+    auto* t = (ncclNet_v7_t*)dlsym(h, "ncclNetPlugin_v7");
+    if (t == nullptr) return false;
+    *api = {t->name, t->init, t->devices, t->listen, t->connect, t->accept, nullptr, t->regMr, t->deregMr,
+            t->isend, t->irecv, t->test, t->closeSend, t->closeRecv, t->closeListen};
+  } else {
+    auto* t = (ncclNet_v8_t*)dlsym(h, "ncclNetPlugin_v8");
+    if (t == nullptr) return false;
+    *api = {t->name, t->init, t->devices, t->listen, t->connect, t->accept, t->regMr, nullptr, t->deregMr,
+            t->isend, t->irecv, t->test, t->closeSend, t->closeRecv, t->closeListen};
+  }
+  return true;
+}
+
+ncclResult_t regMr(const Api& api, void* comm, void* data, size_t size, void** mh) {
+  if (api.regMr8) return api.regMr8(comm, data, size, NCCL_PTR_HOST, mh);
+  return api.regMr7(comm, data, (int)size, NCCL_PTR_HOST, mh);
+}
+
+void printFlows(const char* side, int ci, void* comm) {
+  if (flow_counters == nullptr) return;
+  tcpxbFlowCounters fc[16];
+  int n = flow_counters(comm, fc, 16);
+  for (int i = 0; i < n; ++i)
+    printf("FLOW %s comm %d sock %d id %lu bytes_posted %lu bytes_done %lu tx %lu txc %lu rx %lu\n", side, ci, i,
+           (unsigned long)fc[i].flow_id, (unsigned long)fc[i].bytes_posted, (unsigned long)fc[i].bytes_done,
+           (unsigned long)fc[i].tx_cnt, (unsigned long)fc[i].tx_completion_cnt, (unsigned long)fc[i].rx_cnt);
+  if (stats_text != nullptr) {
+    char buf[4096];
+    stats_text(comm, buf, sizeof buf);
+    fputs(buf, stdout);
+  }
+}
+
+struct Options {
+  std::string plugin;
+  bool v7 = false;
+  std::vector<size_t> sizes = {1024, 65536, 4194304, 67108864};
+  int inflight = 8;
+  int iters = 4;
+  uint64_t seed = 42;
+};
+
+int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
+  Api api;
+  if (!loadApi(opt.plugin.c_str(), opt.v7, &api)) return 1;
+  CHECK(api.init(nullptr));
+  int ndev = 0;
+  CHECK(api.devices(&ndev));
+  if (ndev < 1) { fprintf(stderr, "no devices\n"); return 1; }
+  const int ncomm = ndev;
+  std::vector<void*> comms(ncomm, nullptr), listens(ncomm, nullptr);
+  if (receiver) {
+    std::vector<char> handles((size_t)ncomm * NCCL_NET_HANDLE_MAXSIZE, 0);
+    for (int c = 0; c < ncomm; ++c) CHECK(api.listen(c, &handles[(size_t)c * NCCL_NET_HANDLE_MAXSIZE], &listens[c]));
+    if (write(wfd, handles.data(), handles.size()) != (ssize_t)handles.size()) return 1;
+    for (int c = 0; c < ncomm; ++c)
+      while (comms[c] == nullptr) { ncclNetDeviceHandle_v8_t* dh = nullptr; CHECK(api.accept(listens[c], &comms[c], &dh)); }
+  } else {
+    std::vector<char> handles((size_t)ncomm * NCCL_NET_HANDLE_MAXSIZE, 0);
+    size_t got = 0;
+    while (got < handles.size()) {
+      ssize_t n = read(rfd, handles.data() + got, handles.size() - got);
+      if (n <= 0) return 1;
+      got += (size_t)n;
+    }
+    for (int c = 0; c < ncomm; ++c)
+      while (comms[c] == nullptr) {
+        ncclNetDeviceHandle_v8_t* dh = nullptr;
+        CHECK(api.connect(c, &handles[(size_t)c * NCCL_NET_HANDLE_MAXSIZE], &comms[c], &dh));
+      }
+  }
+  printf("%s: %s, %d comm(s) up\n", receiver ? "receiver" : "sender", api.name, ncomm);
+
+  int rc = 0;
+  for (size_t si = 0; si < opt.sizes.size() && rc == 0; ++si) {
+    const size_t size = opt.sizes[si];
+    const int nbuf = ncomm * opt.inflight;
+    std::vector<std::vector<uint8_t>> bufs(nbuf, std::vector<uint8_t>(size ? size : 1));
+    std::vector<uint8_t> expect(size ? size : 1);
+    std::vector<void*> mh(nbuf, nullptr);
+    for (int b = 0; b < nbuf; ++b) CHECK(regMr(api, comms[b / opt.inflight], bufs[b].data(), size, &mh[b]));
+    // both sides start a size together: receiver -> sender token, sender waits
+    char tok = 'g';
+    if (receiver) { if (write(wfd, &tok, 1) != 1) return 1; }
+    else if (read(rfd, &tok, 1) != 1) return 1;
+    double dt = 0;
+    for (int it = 0; it < opt.iters && rc == 0; ++it) {
+      std::vector<void*> reqs(nbuf, nullptr);
+      if (!receiver)
+        for (int b = 0; b < nbuf; ++b) fillPayload(bufs[b].data(), size, keyOf(opt.seed, b / opt.inflight, (int)si, it, b % opt.inflight));
+      else
+        for (int b = 0; b < nbuf; ++b) memset(bufs[b].data(), 0xEE, size);
+      int posted = 0, finished = 0;
+      std::vector<char> done(nbuf, 0);
+      std::vector<int> got_size(nbuf, -1);
+      const double t0 = nowSec();  // payload generation and checking stay outside the clock
+      while (finished < nbuf) {
+        // post in tag order per comm; a null request means "try again"
+        if (posted < nbuf) {
+          const int b = posted;
+          void* comm = comms[b / opt.inflight];
+          if (receiver) {
+            void* data = bufs[b].data();
+            int sz = (int)size, tag = b % opt.inflight;
+            CHECK(api.irecv(comm, 1, &data, &sz, &tag, &mh[b], &reqs[b]));
+          } else {
+            CHECK(api.isend(comm, bufs[b].data(), (int)size, b % opt.inflight, mh[b], &reqs[b]));
+          }
+          if (reqs[b] != nullptr) ++posted;
+        }
+        for (int b = 0; b < posted; ++b) {
+          if (done[b]) continue;
+          int d = 0, sz = -1;
+          CHECK(api.test(reqs[b], &d, &sz));
+          if (!d) continue;
+          done[b] = 1;
+          ++finished;
+          got_size[b] = sz;
+        }
+      }
+      dt += nowSec() - t0;
+      for (int b = 0; b < nbuf; ++b) {
+        if (got_size[b] != (int)size) { fprintf(stderr, "size mismatch: test reported %d, expected %zu\n", got_size[b], size); rc = 1; }
+        if (!receiver) continue;
+        fillPayload(expect.data(), size, keyOf(opt.seed, b / opt.inflight, (int)si, it, b % opt.inflight));
+        if (memcmp(expect.data(), bufs[b].data(), size) != 0) {
+          fprintf(stderr, "payload mismatch: size %zu iter %d comm %d tag %d\n", size, it, b / opt.inflight, b % opt.inflight);
+          rc = 1;
+        }
+      }
+    }
+    const double bytes = (double)size * nbuf * opt.iters;
+    if (receiver)
+      printf("{\"tool\": \"loopback\", \"side\": \"recv\", \"size\": %zu, \"messages\": %d, \"inflight\": %d, \"comms\": %d, "
+             "\"seconds\": %.6f, \"GBps\": %.3f, \"byte_exact\": %s}\n",
+             size, nbuf * opt.iters, opt.inflight, ncomm, dt, bytes / dt / 1e9, rc == 0 ? "true" : "false");
+    for (int b = 0; b < nbuf; ++b) CHECK(api.deregMr(comms[b / opt.inflight], mh[b]));
+  }
+  for (int c = 0; c < ncomm; ++c) printFlows(receiver ? "recv" : "send", c, comms[c]);
+  fflush(stdout);
+  // the sender closes after the receiver confirmed it has everything
+  char tok = 'c';
+  if (receiver) { if (write(wfd, &tok, 1) != 1) rc = 1; }
+  else if (read(rfd, &tok, 1) != 1) rc = 1;
+  for (int c = 0; c < ncomm; ++c) {
+    if (receiver) { CHECK(api.closeRecv(comms[c])); CHECK(api.closeListen(listens[c])); }
+    else CHECK(api.closeSend(comms[c]));
+  }
+  return rc;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  Options opt;
+  for (int i = 1; i < argc; ++i) {
+    std::string a = argv[i];
+    auto next = [&]() -> const char* { return i + 1 < argc ? argv[++i] : ""; };
+    if (a == "--plugin") opt.plugin = next();
+    else if (a == "--v7") opt.v7 = true;
+    else if (a == "--inflight") opt.inflight = atoi(next());
+    else if (a == "--iters") opt.iters = atoi(next());
+    else if (a == "--seed") opt.seed = strtoull(next(), nullptr, 0);
+    else if (a == "--sizes") {
+      opt.sizes.clear();
+      std::string s = next();
+      size_t pos = 0;
+      while (pos < s.size()) {
+        size_t end = s.find(',', pos);
+        if (end == std::string::npos) end = s.size();
+        opt.sizes.push_back(strtoull(s.substr(pos, end - pos).c_str(), nullptr, 0));
+        pos = end + 1;
+      }
+    } else { fprintf(stderr, "unknown argument %s\n", a.c_str()); return 2; }
+  }
+  if (opt.plugin.empty()) { fprintf(stderr, "--plugin is required\n"); return 2; }
+  if (opt.inflight < 1 || opt.inflight > 16) { fprintf(stderr, "--inflight must be 1..16\n"); return 2; }
+  int to_child[2], to_parent[2];
+  if (pipe(to_child) != 0 || pipe(to_parent) != 0) return 1;
+  fflush(stdout);
+  pid_t pid = fork();
+  if (pid < 0) return 1;
+  if (pid == 0) {
+    close(to_child[1]);
+    close(to_parent[0]);
+    int rc = runSide(false, opt, to_child[0], to_parent[1]);
+    fflush(stdout);
+    _exit(rc);
+  }
+  close(to_child[0]);
+  close(to_parent[1]);
+  int rc = runSide(true, opt, to_parent[0], to_child[1]);
+  int status = 0;
+  waitpid(pid, &status, 0);
+  if (!WIFEXITED(status) || WEXITSTATUS(status) != 0) rc = 1;
+  printf("loopback %s\n", rc == 0 ? "PASSED" : "FAILED");
+  return rc;
+}
