@@ -99,7 +99,8 @@ def build_host(verbose: bool = False, sanitize: str | None = None) -> Path:
     for t in tool_srcs:
         exe = OUT / f"tcpxb_{t.stem}{suffix}"
         if _stale(exe, [t, lib], hdr):
-            cmd = ["g++"] + flags + [str(t), "-o", str(exe), "-ldl", "-pthread"]
+            cmd = ["g++"] + flags + [str(t), "-o", str(exe), "-L", str(OUT), f"-l:{lib.name}",
+                                     "-Wl,-rpath,$ORIGIN", "-ldl", "-pthread"]
             if sanitize:
                 cmd.append(f"-fsanitize={sanitize}")
             _run(cmd)

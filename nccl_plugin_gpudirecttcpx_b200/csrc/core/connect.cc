@@ -140,6 +140,8 @@ void connectThread(AsyncSetup* st, Handle h, int dev) {
   }
   if (res == kSuccess) {
     comm->peer_addr = h.connect_addr;
+    INFO(kSubNet, "send comm %lx connected to %s: %d sockets, %d threads", (unsigned long)comm->id,
+         addressToString(h.connect_addr).c_str(), comm->num_socks, comm->num_threads);
     comm->conn_state.store(kConnOk, std::memory_order_release);
   } else {
     comm->conn_state.store(kConnFailed, std::memory_order_release);
@@ -199,6 +201,8 @@ void acceptThread(AsyncSetup* st, ListenComm* l) {
   if (res == kSuccess) {
     const int64_t wait_us = flags().flow_steering_wait_us;
     if (wait_us > 0) usleep((useconds_t)wait_us);
+    INFO(kSubNet, "recv comm %lx accepted %s: %d sockets, %d threads, gpu %d", (unsigned long)comm->id, comm->ctrl_flow.c_str(),
+         comm->num_socks, comm->num_threads, comm->gpu_dev);
     comm->conn_state.store(kConnOk, std::memory_order_release);
   } else {
     comm->conn_state.store(kConnFailed, std::memory_order_release);

@@ -53,6 +53,9 @@ void eventDestroy(Event) {}
 Result eventRecord(Event, Stream) { return none(); }
 Result eventQuery(Event) { return none(); }
 Result streamSynchronize(Stream) { return none(); }
+Result streamWaitEvent(Stream, Event) { return none(); }
+Result eventSynchronize(Event) { return none(); }
+Result copyDeviceToDeviceAsync(void*, const void*, size_t, Stream) { return none(); }
 Result copyToHostAsync(void*, const void*, size_t, Stream) { return none(); }
 Result copyToDeviceAsync(void*, const void*, size_t, Stream) { return none(); }
 Result memsetAsync(void*, int, size_t, Stream) { return none(); }
@@ -177,6 +180,11 @@ Result eventQuery(Event e) {
   return check(r, "cudaEventQuery");
 }
 Result streamSynchronize(Stream s) { return CU(cudaStreamSynchronize((cudaStream_t)s)); }
+Result streamWaitEvent(Stream s, Event e) { return CU(cudaStreamWaitEvent((cudaStream_t)s, (cudaEvent_t)e, 0)); }
+Result eventSynchronize(Event e) { return CU(cudaEventSynchronize((cudaEvent_t)e)); }
+Result copyDeviceToDeviceAsync(void* d, const void* s_, size_t n, Stream s) {
+  return CU(cudaMemcpyAsync(d, s_, n, cudaMemcpyDeviceToDevice, (cudaStream_t)s));
+}
 Result copyToHostAsync(void* h, const void* d, size_t n, Stream s) {
   return CU(cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, (cudaStream_t)s));
 }

@@ -377,6 +377,10 @@ Result startCudaSend(Comm* comm, Request* r, MemHandle* mh) {
   const int chunk = (int)flags().dynamic_chunk_size;
   int seg = (r->size + kMaxTxSegments - 1) / kMaxTxSegments;
   seg = (seg + chunk - 1) / chunk * chunk;
+  if (comm->send_dependency != nullptr) {
+    TCPXB_CHECK(gpu::streamWaitEvent(comm->stream, comm->send_dependency));
+    comm->send_dependency = nullptr;
+  }
   r->seg_bytes = seg;
   r->n_segs = (r->size + seg - 1) / seg;
   r->segs_done = 0;
@@ -773,6 +777,29 @@ Result waitConnected(Comm* comm) {
   }
 }
 
+// A request that makes no progress for seconds gets its whole pipeline state
+// logged (WARN), at most once per threshold: which ring stage it sits in, what the
+// sockets' task rings hold, whether a control record is pending.
+void reportStall(Comm* comm, Request* r) {
+  const uint64_t now = monotonicNanos();
+  const uint64_t every = (uint64_t)flags().timeout_threshold_ns;
+  if (now - r->posted_ns < every || now - r->last_stall_report_ns < every) return;
+  r->last_stall_report_ns = now;
+  std::string socks;
+  for (int i = 0; i < comm->num_socks; ++i) {
+    char b[96];
+    TaskRing& t = comm->sock[i].tasks;
+    snprintf(b, sizeof b, " s%d[a%u c%u i%u]", i, t.count(kTaskActive), t.count(kTaskCompleting), t.count(kTaskInactive));
+    socks += b;
+  }
+  WARN("%s request %p (%s, %d bytes, %s memory) stalled %lu ms: offset %d pending %d size_known %d; ring posted %u active %u "
+       "transmitting %u finished %u; ctrl pending %d have_ctrl %d;%s; error %d",
+       comm->passive ? "recv" : "send", (void*)r, comm->ctrl_flow.c_str(), r->size, r->mem_type == kPtrCuda ? "cuda" : "host",
+       (unsigned long)((now - r->posted_ns) / 1000000), r->offset, r->size_pending, (int)r->size_known,
+       comm->rq.count(kReqPosted), comm->rq.count(kReqActive), comm->rq.count(kReqTransmitting), comm->rq.count(kReqFinished),
+       (int)comm->ctrl_send.pending(), (int)comm->have_ctrl, socks.c_str(), comm->error.load());
+}
+
 Request* claimRequest(Comm* comm) {
   retireRequests(comm);
   if (!comm->rq.hasFree()) return nullptr;
@@ -787,6 +814,7 @@ Request* claimRequest(Comm* comm) {
   r->unpack_event = ue;
   r->pages = std::move(pages);
   r->comm = comm;
+  r->posted_ns = monotonicNanos();
   return r;
 }
 
@@ -970,7 +998,10 @@ Result netTest(Request* r, int* done, int* size) {
   const uint32_t nfin = comm->rq.count(kReqFinished);
   for (uint32_t k = 0; k < nfin; ++k)
     if (&comm->rq.at(kReqFinished, k) == r) { finished = true; break; }
-  if (!finished) return kSuccess;
+  if (!finished) {
+    reportStall(comm, r);
+    return kSuccess;
+  }
   *done = 1;
   if (size != nullptr) *size = r->size;
   r->reported = true;
@@ -1007,6 +1038,8 @@ Result netIrecvConsumed(Comm* comm, int n, Request* r) {
   retireRequests(comm);
   return kSuccess;
 }
+
+void netSetSendDependency(Comm* comm, gpu::Event event) { comm->send_dependency = event; }
 
 Result netRequestScatterList(Request* r, ScatterList* out) {
   if (r == nullptr || out == nullptr || r->op != kSockRecv || r->mem_type != kPtrCuda) return kInvalidArgument;

@@ -1,0 +1,623 @@
+// Hierarchical collective engine; see tcpxb/engine.h for the algorithms.
+#include "tcpxb/engine.h"
+
+#include <stdio.h>
+#include <string.h>
+#include <time.h>
+
+#include <algorithm>
+#include <deque>
+#include <vector>
+
+#include "tcpxb/kernels.h"
+#include "tcpxb/transport.h"
+
+using namespace tcpxb;
+
+namespace {
+
+thread_local char g_err[512] = "";
+int fail(const char* fmt, const char* a = "", long b = 0) {
+  snprintf(g_err, sizeof g_err, fmt, a, b);
+  return -1;
+}
+#define ENG_NET(expr)                                                           \
+  do {                                                                          \
+    Result r_ = (expr);                                                         \
+    if (r_ != kSuccess) return fail("%s -> %ld", #expr, (long)r_);              \
+  } while (0)
+#define ENG_K(expr)                                                             \
+  do {                                                                          \
+    ++e->stats.kernel_launches;                                                 \
+    if ((expr) != 0) {                                                          \
+      snprintf(g_err, sizeof g_err, "%s: %s", #expr, tcpxb_kernel_last_error()); \
+      return -1;                                                                \
+    }                                                                           \
+  } while (0)
+#define ENG_TRY(expr)                                                           \
+  do {                                                                          \
+    if ((expr) != 0) return -1;                                                 \
+  } while (0)
+
+double nowSec() {
+  struct timespec ts;
+  clock_gettime(CLOCK_MONOTONIC, &ts);
+  return ts.tv_sec + ts.tv_nsec * 1e-9;
+}
+
+struct Rail {
+  ListenComm* listen = nullptr;
+  Comm* send = nullptr;
+  Comm* recv = nullptr;
+};
+
+// What to do with the bytes that arrive in one exchange.
+struct RecvSpec {
+  uint64_t bytes = 0;
+  uint8_t* dst = nullptr;        // local destination of the region
+  const uint8_t* acc = nullptr;  // addend region; null = plain copy
+  int dtype = TCPXB_U8;
+  bool fanout = false;           // also store into the local peers' output buffers
+  uint64_t out_offset = 0;       // offset of `dst` inside the output buffer (for the peer addresses)
+  bool last = false;             // the final kernel publishes the fan-out flags
+};
+struct SendSpec {
+  uint64_t bytes = 0;
+  const uint8_t* src = nullptr;
+};
+
+struct PendingUnpack {
+  Request* req;
+  gpu::Event event;
+};
+
+struct Engine {
+  tcpxbEngineConfig cfg;
+  int nodes = 1, node = 0, local = 0, G = 1;
+  bool twin = false;  // world == 1: the rank is its own network peer
+  std::vector<Rail> rails;
+  bool connected = false;
+  // intra-node mappings
+  std::vector<uint8_t*> work, out;
+  std::vector<uint32_t*> flags;
+  uint8_t* mc_out = nullptr;
+  uint64_t buffer_bytes = 0;
+  uint32_t epoch = 0;
+  // device scratch
+  uint8_t* scratch = nullptr;
+  uint64_t scratch_bytes = 0;
+  uint32_t* ticket = nullptr;       // fan-out completion counter (device)
+  uint32_t* status_host = nullptr;  // kernel status block (pinned, device-mapped)
+  uint32_t* status_dev = nullptr;
+  std::vector<gpu::Event> event_pool;
+  gpu::Event dep_event = nullptr;
+  tcpxbEngineStats stats;
+  int req_bytes = 4 << 20, inflight = 8, ctas = 16;
+};
+
+int ensureScratch(Engine* e, uint64_t bytes) {
+  if (e->scratch_bytes >= bytes) return 0;
+  gpu::deviceFree(e->scratch);
+  e->scratch = nullptr;
+  void* p = nullptr;
+  ENG_NET(gpu::deviceAlloc(bytes, &p));
+  e->scratch = static_cast<uint8_t*>(p);
+  e->scratch_bytes = bytes;
+  return 0;
+}
+
+gpu::Event takeEvent(Engine* e) {
+  if (!e->event_pool.empty()) {
+    gpu::Event ev = e->event_pool.back();
+    e->event_pool.pop_back();
+    return ev;
+  }
+  gpu::Event ev = nullptr;
+  gpu::eventCreate(&ev);
+  return ev;
+}
+
+// Launches the unpack kernel for one finished receive request.
+int launchUnpack(Engine* e, Request* req, const RecvSpec& rs, uint64_t region_off, uint64_t len, bool publish,
+                 void* stream) {
+  ScatterList sl;
+  ENG_NET(netRequestScatterList(req, &sl));
+  e->stats.fragments += sl.count;
+  ++e->stats.unpack_launches;
+  tcpxbUnpackOpts opts;
+  memset(&opts, 0, sizeof opts);
+  opts.max_ctas = e->ctas;
+  uint8_t* dst = rs.dst + region_off;
+  const uint8_t* acc = rs.acc ? rs.acc + region_off : nullptr;
+  const tcpxbLoadMeta* descs = reinterpret_cast<const tcpxbLoadMeta*>(sl.dev);
+  const uint32_t count = (uint32_t)sl.count;
+  void* peers[TCPXB_MAX_PEERS];
+  int npeers = 0;
+  const bool fan = rs.fanout && e->G > 1;
+  if (fan) {
+    for (int l = 0; l < e->G; ++l) {
+      if (l == e->local) continue;
+      peers[npeers] = e->out[l] + rs.out_offset + region_off;
+      if (publish) opts.peer_flags[npeers] = e->flags[l] + 32 + e->local;  // block B, my slot
+      ++npeers;
+    }
+    if (publish) {
+      opts.flag_value = e->epoch;
+      opts.ticket = e->ticket;
+    }
+  }
+  if (e->cfg.plain_mode) {
+    // Baseline: unpack to a bounce buffer, add in a second pass, copy to the peers.
+    ENG_TRY(ensureScratch(e, e->scratch_bytes));
+    uint8_t* bounce = e->scratch + e->scratch_bytes - (uint64_t)e->req_bytes;
+    ENG_K(tcpxb_unpack_copy(sl.pool_dev, sl.pool_bytes, acc ? bounce : dst, len, descs, count, e->status_dev, &opts, stream));
+    if (acc) {
+      void* srcs[2] = {const_cast<uint8_t*>(acc), bounce};
+      ENG_K(tcpxb_peer_reduce(dst, srcs, 2, 0, len & ~15ull, rs.dtype, stream));
+    }
+    for (int i = 0; i < npeers; ++i) ENG_NET(gpu::copyDeviceToDeviceAsync(peers[i], dst, len, stream));
+    if (fan && publish) {
+      uint32_t* pf[TCPXB_MAX_PEERS];
+      for (int i = 0; i < npeers; ++i) pf[i] = opts.peer_flags[i];
+      ENG_K(tcpxb_signal_flags(pf, npeers, e->epoch, stream));
+    }
+    return 0;
+  }
+  const bool nvls = fan && e->cfg.use_nvls && e->mc_out != nullptr;
+  if (acc == nullptr) {
+    if (!fan) ENG_K(tcpxb_unpack_copy(sl.pool_dev, sl.pool_bytes, dst, len, descs, count, e->status_dev, &opts, stream));
+    else if (nvls)
+      ENG_K(tcpxb_unpack_fanout_nvls(sl.pool_dev, sl.pool_bytes, dst, e->mc_out + rs.out_offset + region_off, len, peers,
+                                     npeers, descs, count, e->status_dev, &opts, stream));
+    else
+      ENG_K(tcpxb_unpack_fanout(sl.pool_dev, sl.pool_bytes, dst, len, peers, npeers, descs, count, e->status_dev, &opts, stream));
+  } else {
+    if (!fan)
+      ENG_K(tcpxb_unpack_reduce(sl.pool_dev, sl.pool_bytes, acc, dst, len, descs, count, rs.dtype,
+                                acc == dst ? e->cfg.reduce_impl : TCPXB_REDUCE_SM, e->status_dev, &opts, stream));
+    else if (nvls)
+      ENG_K(tcpxb_unpack_reduce_fanout_nvls(sl.pool_dev, sl.pool_bytes, acc, dst, e->mc_out + rs.out_offset + region_off, len,
+                                            peers, npeers, descs, count, rs.dtype, e->status_dev, &opts, stream));
+    else
+      ENG_K(tcpxb_unpack_reduce_fanout(sl.pool_dev, sl.pool_bytes, acc, dst, len, peers, npeers, descs, count, rs.dtype,
+                                       TCPXB_REDUCE_SM, e->status_dev, &opts, stream));
+  }
+  return 0;
+}
+
+// One simultaneous send + receive with the ring neighbours, in requests of
+// req_bytes striped over the rails.  Request k of a direction uses rail k % rails
+// on both ends, so the two sides agree without talking about it.
+int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
+  const int R = (int)e->rails.size();
+  const uint64_t rb = (uint64_t)e->req_bytes;
+  const uint64_t n_send = (ss.bytes + rb - 1) / rb, n_recv = (rs.bytes + rb - 1) / rb;
+  uint64_t post_s = 0, post_r = 0, done_s = 0, launched_r = 0;
+  std::vector<std::deque<Request*>> sq(R), rq(R);
+  std::vector<std::deque<uint64_t>> rq_idx(R);
+  std::vector<std::deque<PendingUnpack>> uq(R);
+  if (ss.bytes > 0) {
+    // sends may read only what the stream has produced so far
+    ENG_NET(gpu::eventRecord(e->dep_event, stream));
+    for (int r = 0; r < R; ++r) netSetSendDependency(e->rails[r].send, e->dep_event);
+  }
+  MemHandle send_mh{const_cast<uint8_t*>(ss.src), ss.bytes, kPtrCuda, e->cfg.gpu_dev};
+  MemHandle recv_mh{rs.dst, rs.bytes, kPtrCuda, e->cfg.gpu_dev};
+  const double t0 = nowSec();
+  while (done_s < n_send || launched_r < n_recv) {
+    bool moved = false;
+    // post receives (they claim pool pages as control records arrive)
+    while (post_r < n_recv) {
+      const int r = (int)(post_r % R);
+      if ((int)(rq[r].size() + uq[r].size()) >= e->inflight) break;
+      const uint64_t off = post_r * rb;
+      void* data = rs.dst + off;
+      int sz = (int)std::min<uint64_t>(rb, rs.bytes - off), tag = 0;
+      MemHandle* mh = &recv_mh;
+      Request* req = nullptr;
+      ENG_NET(netIrecv(e->rails[r].recv, 1, &data, &sz, &tag, &mh, &req));
+      if (req == nullptr) break;
+      rq[r].push_back(req);
+      rq_idx[r].push_back(post_r);
+      ++post_r;
+      moved = true;
+    }
+    while (post_s < n_send) {
+      const int r = (int)(post_s % R);
+      if ((int)sq[r].size() >= e->inflight) break;
+      const uint64_t off = post_s * rb;
+      const int sz = (int)std::min<uint64_t>(rb, ss.bytes - off);
+      Request* req = nullptr;
+      ENG_NET(netIsend(e->rails[r].send, const_cast<uint8_t*>(ss.src) + off, sz, 0, &send_mh, &req));
+      if (req == nullptr) break;
+      sq[r].push_back(req);
+      ++post_s;
+      moved = true;
+    }
+    for (int r = 0; r < R; ++r) {
+      while (!rq[r].empty()) {
+        int done = 0, sz = 0;
+        ENG_NET(netTest(rq[r].front(), &done, &sz));
+        if (!done) break;
+        const uint64_t k = rq_idx[r].front();
+        const uint64_t off = k * rb;
+        const uint64_t want = std::min<uint64_t>(rb, rs.bytes - off);
+        if ((uint64_t)sz != want) return fail("received %s bytes short: request size %ld", "", (long)sz);
+        // Whichever request is launched last runs last on the stream, so it is the
+        // one that publishes completion.
+        const bool publish = rs.last && (launched_r + 1 == n_recv);
+        ENG_TRY(launchUnpack(e, rq[r].front(), rs, off, want, publish, stream));
+        gpu::Event ev = takeEvent(e);
+        ENG_NET(gpu::eventRecord(ev, stream));
+        uq[r].push_back({rq[r].front(), ev});
+        rq[r].pop_front();
+        rq_idx[r].pop_front();
+        ++launched_r;
+        ++e->stats.requests;
+        e->stats.bytes_received += want;
+        moved = true;
+      }
+      while (!uq[r].empty()) {
+        Result q = gpu::eventQuery(uq[r].front().event);
+        if (q == kInProgress) break;
+        ENG_NET(q);
+        ENG_NET(netIrecvConsumed(e->rails[r].recv, 1, uq[r].front().req));
+        e->event_pool.push_back(uq[r].front().event);
+        uq[r].pop_front();
+        moved = true;
+      }
+      while (!sq[r].empty()) {
+        int done = 0, sz = 0;
+        ENG_NET(netTest(sq[r].front(), &done, &sz));
+        if (!done) break;
+        e->stats.bytes_sent += (uint64_t)sz;
+        sq[r].pop_front();
+        ++done_s;
+        moved = true;
+      }
+    }
+    if (!moved) sched_yield();
+  }
+  // pool pages go back once the kernels that read them have finished
+  for (int r = 0; r < R; ++r) {
+    while (!uq[r].empty()) {
+      ENG_NET(gpu::eventSynchronize(uq[r].front().event));
+      ENG_NET(netIrecvConsumed(e->rails[r].recv, 1, uq[r].front().req));
+      e->event_pool.push_back(uq[r].front().event);
+      uq[r].pop_front();
+    }
+  }
+  e->stats.seconds_net_wait += nowSec() - t0;
+  return 0;
+}
+
+int checkReady(Engine* e) {
+  if (e == nullptr) return fail("null engine%s", "");
+  if (!e->connected) return fail("engine is not connected%s", "");
+  if (e->G > 1 && e->out.empty()) return fail("set_peers was not called%s", "");
+  ENG_NET(gpu::setDevice(e->cfg.gpu_dev));
+  return 0;
+}
+
+// "Inputs staged" barrier among the local GPUs: block A of the flag pages.
+int barrierInputs(Engine* e, void* stream) {
+  if (e->G <= 1) return 0;
+  uint32_t* pf[TCPXB_MAX_PEERS + 1];
+  int n = 0;
+  for (int l = 0; l < e->G; ++l) pf[n++] = e->flags[l] + e->local;  // my slot in everybody's block A
+  ENG_K(tcpxb_signal_flags(pf, n, e->epoch, stream));
+  ENG_K(tcpxb_wait_flags(e->flags[e->local], e->G, e->epoch, 0, e->status_dev, stream));
+  return 0;
+}
+
+// Waits until every local peer has finished storing into this GPU's output.
+int waitFanout(Engine* e, void* stream) {
+  if (e->G <= 1) return 0;
+  // my own slot of block B is written here, the peers' slots by their last kernel
+  uint32_t* own[1] = {e->flags[e->local] + 32 + e->local};
+  ENG_K(tcpxb_signal_flags(own, 1, e->epoch, stream));
+  ENG_K(tcpxb_wait_flags(e->flags[e->local] + 32, e->G, e->epoch, 0, e->status_dev, stream));
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* tcpxb_engine_last_error(void) { return g_err; }
+
+void* tcpxb_engine_create(const tcpxbEngineConfig* cfg) {
+  if (cfg == nullptr || cfg->world < 1 || cfg->rank < 0 || cfg->rank >= cfg->world || cfg->gpus_per_node < 1 ||
+      cfg->world % cfg->gpus_per_node != 0 || cfg->gpus_per_node > TCPXB_MAX_PEERS) {
+    fail("bad engine configuration%s", "");
+    return nullptr;
+  }
+  if (cfg->world > 1 && cfg->world / cfg->gpus_per_node < 2) {
+    fail("the engine needs at least two emulated nodes%s", "");
+    return nullptr;
+  }
+  if (netInit(nullptr) != kSuccess) { fail("transport init failed%s", ""); return nullptr; }
+  if (!gpu::available() || gpu::setDevice(cfg->gpu_dev) != kSuccess) { fail("CUDA device unavailable%s", ""); return nullptr; }
+  Engine* e = new Engine();
+  e->cfg = *cfg;
+  e->G = cfg->gpus_per_node;
+  e->nodes = cfg->world / e->G;
+  e->node = cfg->rank / e->G;
+  e->local = cfg->rank % e->G;
+  if (cfg->world == 1) { e->twin = true; e->nodes = 2; }
+  if (cfg->request_bytes > 0) e->req_bytes = std::min(cfg->request_bytes, 4 << 20) / 4096 * 4096;
+  if (e->req_bytes < 4096) e->req_bytes = 4096;
+  if (cfg->max_inflight > 0) e->inflight = std::min(cfg->max_inflight, 12);
+  if (cfg->unpack_ctas > 0) e->ctas = cfg->unpack_ctas;
+  memset(&e->stats, 0, sizeof e->stats);
+  int ndev = 0;
+  netDevices(&ndev);
+  e->rails.resize((size_t)std::min(ndev, TCPXB_ENGINE_MAX_RAILS));
+  void* h = nullptr;
+  void* d = nullptr;
+  void* t = nullptr;
+  if (gpu::hostAllocMapped(64, &h, &d) != kSuccess || gpu::deviceAlloc(64, &t) != kSuccess ||
+      gpu::memsetAsync(t, 0, 64, nullptr) != kSuccess || gpu::streamSynchronize(nullptr) != kSuccess ||
+      gpu::eventCreate(&e->dep_event) != kSuccess) {
+    fail("engine device allocations failed: %s", gpu::lastError());
+    delete e;
+    return nullptr;
+  }
+  memset(h, 0, 64);
+  e->status_host = static_cast<uint32_t*>(h);
+  e->status_dev = static_cast<uint32_t*>(d);
+  e->ticket = static_cast<uint32_t*>(t);
+  return e;
+}
+
+void tcpxb_engine_destroy(void* engine) {
+  Engine* e = static_cast<Engine*>(engine);
+  if (e == nullptr) return;
+  for (Rail& r : e->rails) {
+    if (r.send) netClose(r.send);
+    if (r.recv) netClose(r.recv);
+    if (r.listen) netCloseListen(r.listen);
+  }
+  for (gpu::Event ev : e->event_pool) gpu::eventDestroy(ev);
+  gpu::eventDestroy(e->dep_event);
+  gpu::deviceFree(e->scratch);
+  gpu::deviceFree(e->ticket);
+  gpu::hostFreeMapped(e->status_host);
+  delete e;
+}
+
+int tcpxb_engine_rails(void* engine) { return engine ? (int)static_cast<Engine*>(engine)->rails.size() : 0; }
+
+int tcpxb_engine_listen(void* engine, void* handles_out) {
+  Engine* e = static_cast<Engine*>(engine);
+  if (e == nullptr || handles_out == nullptr) return fail("null argument%s", "");
+  ENG_NET(gpu::setDevice(e->cfg.gpu_dev));
+  char* out = static_cast<char*>(handles_out);
+  for (size_t r = 0; r < e->rails.size(); ++r) {
+    memset(out + r * TCPXB_ENGINE_HANDLE_BYTES, 0, TCPXB_ENGINE_HANDLE_BYTES);
+    ENG_NET(netListen((int)r, out + r * TCPXB_ENGINE_HANDLE_BYTES, &e->rails[r].listen));
+    netSetAcceptRecvMode(e->rails[r].listen, kRecvModeUnpack);
+  }
+  return 0;
+}
+
+int tcpxb_engine_connect(void* engine, const void* next_handles) {
+  Engine* e = static_cast<Engine*>(engine);
+  if (e == nullptr || next_handles == nullptr) return fail("null argument%s", "");
+  ENG_NET(gpu::setDevice(e->cfg.gpu_dev));
+  std::vector<char> handles(e->rails.size() * TCPXB_ENGINE_HANDLE_BYTES);
+  memcpy(handles.data(), next_handles, handles.size());
+  const double deadline = nowSec() + 60.0;
+  for (;;) {
+    bool all = true;
+    for (size_t r = 0; r < e->rails.size(); ++r) {
+      Rail& rail = e->rails[r];
+      if (rail.send == nullptr) ENG_NET(netConnect((int)r, handles.data() + r * TCPXB_ENGINE_HANDLE_BYTES, &rail.send));
+      if (rail.recv == nullptr) ENG_NET(netAccept(rail.listen, &rail.recv));
+      all = all && rail.send != nullptr && rail.recv != nullptr;
+    }
+    if (all) break;
+    if (nowSec() > deadline) return fail("connection setup timed out%s", "");
+    sched_yield();
+  }
+  e->connected = true;
+  return 0;
+}
+
+int tcpxb_engine_set_peers(void* engine, void* const* work_ptrs, void* const* out_ptrs, uint32_t* const* flag_ptrs,
+                           void* mc_out, uint64_t buffer_bytes) {
+  Engine* e = static_cast<Engine*>(engine);
+  if (e == nullptr || work_ptrs == nullptr || out_ptrs == nullptr || flag_ptrs == nullptr) return fail("null argument%s", "");
+  e->work.clear(); e->out.clear(); e->flags.clear();
+  for (int l = 0; l < e->G; ++l) {
+    if (work_ptrs[l] == nullptr || out_ptrs[l] == nullptr || flag_ptrs[l] == nullptr) return fail("null peer mapping%s", "");
+    e->work.push_back(static_cast<uint8_t*>(work_ptrs[l]));
+    e->out.push_back(static_cast<uint8_t*>(out_ptrs[l]));
+    e->flags.push_back(flag_ptrs[l]);
+  }
+  e->mc_out = static_cast<uint8_t*>(mc_out);
+  e->buffer_bytes = buffer_bytes;
+  return 0;
+}
+
+int tcpxb_engine_all_reduce(void* engine, const void* in_, void* out_, uint64_t bytes, int dtype, void* stream) {
+  Engine* e = static_cast<Engine*>(engine);
+  ENG_TRY(checkReady(e));
+  if (dtype != TCPXB_BF16 && dtype != TCPXB_F32) return fail("all_reduce needs bf16 or f32%s", "");
+  const uint64_t unit = (uint64_t)e->G * (uint64_t)(e->nodes > 2 ? e->nodes : 1) * 16;
+  if (bytes == 0 || bytes % unit != 0) return fail("all_reduce size must be a multiple of %s%ld bytes", "", (long)unit);
+  const uint8_t* in = static_cast<const uint8_t*>(in_);
+  uint8_t* out = static_cast<uint8_t*>(out_);
+  if (e->G > 1 && (in != e->work[e->local] || out != e->out[e->local] || bytes > e->buffer_bytes))
+    return fail("with several GPUs per node, in/out must be the registered work/output buffers%s", "");
+  ++e->epoch;
+  const uint64_t shard = bytes / (uint64_t)e->G;
+  const uint64_t shard_off = shard * (uint64_t)e->local;
+  // 1. intra-node reduce-scatter into `red`
+  const uint8_t* red = in;
+  if (e->G > 1) {
+    ENG_TRY(ensureScratch(e, shard + (uint64_t)e->req_bytes));
+    ENG_TRY(barrierInputs(e, stream));
+    std::vector<void*> srcs;
+    for (int l = 0; l < e->G; ++l) srcs.push_back(e->work[l]);
+    ENG_K(tcpxb_peer_reduce(e->scratch, srcs.data(), e->G, shard_off, shard, dtype, stream));
+    red = e->scratch;
+  } else if (e->cfg.plain_mode) {
+    ENG_TRY(ensureScratch(e, (uint64_t)e->req_bytes));
+  }
+  uint8_t* out_shard = out + shard_off;
+  if (e->nodes == 2) {
+    // 2a. two nodes: swap whole shards, add on arrival, fan out
+    SendSpec ss{shard, red};
+    RecvSpec rs;
+    rs.bytes = shard; rs.dst = out_shard; rs.acc = red; rs.dtype = dtype; rs.fanout = true; rs.out_offset = shard_off; rs.last = true;
+    ENG_TRY(exchange(e, ss, rs, stream));
+  } else {
+    // 2b. ring over the nodes on this rail.  Pieces of the shard; piece p ends up
+    // fully reduced on node (p - 1) mod nodes after the reduce-scatter half.
+    const int N = e->nodes;
+    const uint64_t piece = shard / (uint64_t)N;
+    // the running sums live in scratch (G > 1) or in a copy of the input (G == 1)
+    uint8_t* acc;
+    if (e->G > 1) {
+      acc = e->scratch;
+    } else {
+      ENG_TRY(ensureScratch(e, shard + (uint64_t)e->req_bytes));
+      ENG_NET(gpu::copyDeviceToDeviceAsync(e->scratch, in, shard, stream));
+      acc = e->scratch;
+    }
+    auto mod = [N](int x) { return ((x % N) + N) % N; };
+    for (int s = 0; s < N - 1; ++s) {
+      const int sp = mod(e->node - s), rp = mod(e->node - s - 1);
+      SendSpec ss{piece, acc + (uint64_t)sp * piece};
+      RecvSpec rs;
+      rs.bytes = piece; rs.dtype = dtype; rs.acc = acc + (uint64_t)rp * piece;
+      if (s == N - 2) {  // final sum of piece rp: write it to the output and fan it out
+        rs.dst = out_shard + (uint64_t)rp * piece; rs.fanout = true; rs.out_offset = shard_off + (uint64_t)rp * piece;
+      } else {
+        rs.dst = acc + (uint64_t)rp * piece;
+      }
+      ENG_TRY(exchange(e, ss, rs, stream));
+    }
+    for (int s = 0; s < N - 1; ++s) {
+      const int sp = mod(e->node + 1 - s), rp = mod(e->node - s);
+      SendSpec ss{piece, out_shard + (uint64_t)sp * piece};
+      RecvSpec rs;
+      rs.bytes = piece; rs.dst = out_shard + (uint64_t)rp * piece; rs.fanout = true;
+      rs.out_offset = shard_off + (uint64_t)rp * piece; rs.last = (s == N - 2);
+      ENG_TRY(exchange(e, ss, rs, stream));
+    }
+  }
+  ENG_TRY(waitFanout(e, stream));
+  return 0;
+}
+
+int tcpxb_engine_all_gather(void* engine, const void* in_, void* out_, uint64_t B, void* stream) {
+  Engine* e = static_cast<Engine*>(engine);
+  ENG_TRY(checkReady(e));
+  if (B == 0 || B % 16 != 0) return fail("all_gather block must be a multiple of 16 bytes%s", "");
+  uint8_t* out = static_cast<uint8_t*>(out_);
+  const int world_blocks = e->nodes * e->G;
+  if (e->G > 1 && (out != e->out[e->local] || B * (uint64_t)world_blocks > e->buffer_bytes))
+    return fail("with several GPUs per node, out must be the registered output buffer%s", "");
+  ++e->epoch;
+  const int me = e->twin ? 0 : e->cfg.rank;
+  // own block into every local GPU's output
+  ENG_TRY(barrierInputs(e, stream));  // the peers' outputs may be overwritten from here on
+  for (int l = 0; l < e->G; ++l) {
+    uint8_t* dst = (l == e->local ? out : e->out[l]) + (uint64_t)me * B;
+    ENG_NET(gpu::copyDeviceToDeviceAsync(dst, in_, B, stream));
+  }
+  const int N = e->nodes;
+  auto mod = [N](int x) { return ((x % N) + N) % N; };
+  for (int s = 0; s < N - 1; ++s) {
+    const int sn = mod(e->node - s), rn = mod(e->node - s - 1);
+    const uint64_t soff = (uint64_t)((e->twin ? rn : sn) * e->G + e->local) * B;  // the twin sends what its peer would
+    const uint64_t roff = (uint64_t)(rn * e->G + e->local) * B;
+    SendSpec ss{B, e->twin ? static_cast<const uint8_t*>(in_) : out + soff};
+    RecvSpec rs;
+    rs.bytes = B; rs.dst = out + roff; rs.fanout = true; rs.out_offset = roff; rs.last = (s == N - 2);
+    ENG_TRY(exchange(e, ss, rs, stream));
+  }
+  ENG_TRY(waitFanout(e, stream));
+  return 0;
+}
+
+int tcpxb_engine_reduce_scatter(void* engine, const void* in_, void* out_, uint64_t B, int dtype, void* stream) {
+  Engine* e = static_cast<Engine*>(engine);
+  ENG_TRY(checkReady(e));
+  if (dtype != TCPXB_BF16 && dtype != TCPXB_F32) return fail("reduce_scatter needs bf16 or f32%s", "");
+  if (B == 0 || B % 16 != 0) return fail("reduce_scatter block must be a multiple of 16 bytes%s", "");
+  const uint8_t* in = static_cast<const uint8_t*>(in_);
+  uint8_t* out = static_cast<uint8_t*>(out_);
+  const int N = e->nodes;
+  if (e->G > 1 && (in != e->work[e->local] || B * (uint64_t)(N * e->G) > e->buffer_bytes))
+    return fail("with several GPUs per node, in must be the registered work buffer%s", "");
+  ++e->epoch;
+  // 1. per node-block j: sum over the local GPUs of block (j, local) -> tmp[j]
+  ENG_TRY(ensureScratch(e, (uint64_t)N * B + (uint64_t)e->req_bytes));
+  uint8_t* tmp = e->scratch;
+  if (e->G > 1) {
+    ENG_TRY(barrierInputs(e, stream));
+    std::vector<void*> srcs;
+    for (int l = 0; l < e->G; ++l) srcs.push_back(e->work[l]);
+    for (int j = 0; j < N; ++j)
+      ENG_K(tcpxb_peer_reduce(tmp + (uint64_t)j * B, srcs.data(), e->G, (uint64_t)(j * e->G + e->local) * B, B, dtype, stream));
+  } else {
+    for (int j = 0; j < N; ++j) {
+      const int blk = e->twin ? 0 : j;  // the twin's input has one block per real rank
+      ENG_NET(gpu::copyDeviceToDeviceAsync(tmp + (uint64_t)j * B, in + (uint64_t)blk * B, B, stream));
+    }
+  }
+  // 2. ring reduce-scatter over the nodes; the last step writes the result
+  auto mod = [N](int x) { return ((x % N) + N) % N; };
+  for (int s = 0; s < N - 1; ++s) {
+    const int sp = mod(e->node - s - 1), rp = mod(e->node - s - 2);
+    SendSpec ss{B, tmp + (uint64_t)(e->twin ? rp : sp) * B};
+    RecvSpec rs;
+    rs.bytes = B; rs.dtype = dtype; rs.acc = tmp + (uint64_t)rp * B;
+    rs.dst = (s == N - 2) ? out : tmp + (uint64_t)rp * B;
+    ENG_TRY(exchange(e, ss, rs, stream));
+  }
+  if (e->G > 1) {
+    // peers may not restage inputs before everyone has read them
+    uint32_t* pf[TCPXB_MAX_PEERS + 1];
+    int n = 0;
+    for (int l = 0; l < e->G; ++l) pf[n++] = e->flags[l] + 32 + e->local;
+    ENG_K(tcpxb_signal_flags(pf, n, e->epoch, stream));
+    ENG_K(tcpxb_wait_flags(e->flags[e->local] + 32, e->G, e->epoch, 0, e->status_dev, stream));
+  }
+  return 0;
+}
+
+int tcpxb_engine_send_next(void* engine, const void* buf, uint64_t bytes, void* stream) {
+  Engine* e = static_cast<Engine*>(engine);
+  ENG_TRY(checkReady(e));
+  SendSpec ss{bytes, static_cast<const uint8_t*>(buf)};
+  RecvSpec rs;
+  return exchange(e, ss, rs, stream);
+}
+
+int tcpxb_engine_recv_prev(void* engine, void* buf, uint64_t bytes, void* stream) {
+  Engine* e = static_cast<Engine*>(engine);
+  ENG_TRY(checkReady(e));
+  SendSpec ss;
+  RecvSpec rs;
+  rs.bytes = bytes; rs.dst = static_cast<uint8_t*>(buf);
+  return exchange(e, ss, rs, stream);
+}
+
+int tcpxb_engine_stats(void* engine, tcpxbEngineStats* out) {
+  if (engine == nullptr || out == nullptr) return -1;
+  *out = static_cast<Engine*>(engine)->stats;
+  return 0;
+}
+
+int tcpxb_engine_device_status(void* engine, uint32_t* words4) {
+  Engine* e = static_cast<Engine*>(engine);
+  if (e == nullptr || words4 == nullptr) return -1;
+  for (int i = 0; i < 4; ++i) words4[i] = e->status_host[i];
+  return 0;
+}
+
+}  // extern "C"

@@ -48,6 +48,9 @@ Result eventRecord(Event e, Stream s);
 // kSuccess when complete, kInProgress when not, error otherwise.
 Result eventQuery(Event e);
 Result streamSynchronize(Stream s);
+Result streamWaitEvent(Stream s, Event e);
+Result eventSynchronize(Event e);
+Result copyDeviceToDeviceAsync(void* dst, const void* src, size_t bytes, Stream s);
 Result copyToHostAsync(void* host_dst, const void* dev_src, size_t bytes, Stream s);
 Result copyToDeviceAsync(void* dev_dst, const void* host_src, size_t bytes, Stream s);
 Result memsetAsync(void* dev, int value, size_t bytes, Stream s);

@@ -69,8 +69,8 @@ typedef struct tcpxbUnpackOpts {
   const uint32_t* ready_count;
   uint64_t wait_ns;        // 0 = default (2 s)
   // Fan-out completion: when flag_value != 0, after every store of the launch has
-  // completed the kernel writes flag_value (release, system scope) to
-  // peer_flags[i] for each peer.  `ticket` is one zero-initialised uint32 of
+  // completed the kernel writes flag_value (release, system scope) to every
+  // non-null peer_flags[i].  `ticket` is one zero-initialised uint32 of
   // scratch on the launching GPU; the kernel leaves it zero again.
   uint32_t* peer_flags[TCPXB_MAX_PEERS];
   uint32_t flag_value;
@@ -123,6 +123,10 @@ int tcpxb_unpack_reduce_fanout_nvls(const void* pool, uint64_t pool_bytes, const
 // TCPXB_ST_TIMEOUT to status and returns.  Runs on the GPU that owns `flags`.
 int tcpxb_wait_flags(const uint32_t* flags, int n, uint32_t value, uint64_t wait_ns,
                      uint32_t* status, void* stream);
+
+// Writes `value` (release, system scope) to each peer_flags[i]: "my buffers are
+// ready for epoch `value`".  The counterpart of tcpxb_wait_flags.
+int tcpxb_signal_flags(uint32_t* const* peer_flags, int n, uint32_t value, void* stream);
 
 // Intra-node reduce-scatter stage over peer memory: out[i] = sum over r of
 // srcs[r][shard_off + i], element-wise, for `bytes` bytes.  srcs are peer-mapped

@@ -127,6 +127,7 @@ struct Request {
   std::vector<PageRun> pages;
   bool unpack_launched = false;
   gpu::Event unpack_event = nullptr;
+  uint64_t posted_ns = 0, last_stall_report_ns = 0;
   // inline transfer progress
   int inline_off = 0;
   bool inline_queued = false;  // send: the inline record is in the control buffer
@@ -190,6 +191,7 @@ struct Comm {
   uint64_t tx_stage_bytes = 0, tx_head = 0, tx_tail = 0;  // ring offsets (monotonic)
   uint32_t* unpack_status_host = nullptr;
   uint32_t* unpack_status_dev = nullptr;
+  gpu::Event send_dependency = nullptr;
   // telemetry
   std::unique_ptr<EventLog> events;
   std::unique_ptr<Exporter> exporter;
@@ -243,6 +245,10 @@ Result netIrecvConsumed(Comm* comm, int n, Request* req);
 // Selects the receive mode of comms accepted from now on by this thread's next
 // netAccept (used by the collective engine, which unpacks with its own kernels).
 void netSetAcceptRecvMode(ListenComm* lcomm, int recv_mode);
+
+// The next netIsend of a CUDA buffer on `comm` first makes the comm's copy stream
+// wait for `event` (the kernel that produces the data), then stages the data.
+void netSetSendDependency(Comm* comm, gpu::Event event);
 
 // Scatter list of a finished unpack-mode receive.
 struct ScatterList {

@@ -506,7 +506,7 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
       if (t == gridDim.x - 1) {
         *p.ticket = 0;
         __threadfence_system();
-        for (int r = 0; r < p.npeers; ++r) {
+        for (int r = 0; r < TCPXB_MAX_PEERS; ++r) {
           if (p.peer_flags[r] != nullptr) st_release_sys(p.peer_flags[r], p.flag_value);
         }
       }
@@ -528,6 +528,19 @@ __global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t value, 
       return;
     }
     __nanosleep(100);
+  }
+}
+
+struct SignalParams {
+  uint32_t* flags[TCPXB_MAX_PEERS + 1];
+  int n;
+  uint32_t value;
+};
+__global__ void signal_flags_kernel(const __grid_constant__ SignalParams p) {
+  const int i = threadIdx.x;
+  if (i < p.n && p.flags[i] != nullptr) {
+    __threadfence_system();
+    st_release_sys(p.flags[i], p.value);
   }
 }
 
@@ -731,7 +744,7 @@ int fill(UnpackParams& p, const void* pool, uint64_t pool_bytes, const void* acc
     p.wait_ns = opts->wait_ns;
     p.flag_value = opts->flag_value;
     p.ticket = opts->ticket;
-    for (int i = 0; i < npeers; ++i) p.peer_flags[i] = opts->peer_flags[i];
+    for (int i = 0; i < TCPXB_MAX_PEERS; ++i) p.peer_flags[i] = opts->peer_flags[i];
   }
   return TCPXB_K_OK;
 }
@@ -831,6 +844,20 @@ int tcpxb_wait_flags(const uint32_t* flags, int n, uint32_t value, uint64_t wait
   if (n == 0) return TCPXB_K_OK;
   wait_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
       flags, n, value, wait_ns ? wait_ns : kDefaultWaitNs, status);
+  CUDA_TRY(cudaGetLastError());
+  return TCPXB_K_OK;
+}
+
+int tcpxb_signal_flags(uint32_t* const* peer_flags, int n, uint32_t value, void* stream) {
+  if (n < 0 || n > TCPXB_MAX_PEERS + 1 || (n > 0 && peer_flags == nullptr))
+    return fail(TCPXB_K_INVALID, "bad flag table");
+  if (n == 0) return TCPXB_K_OK;
+  SignalParams p;
+  memset(&p, 0, sizeof p);
+  for (int i = 0; i < n; ++i) p.flags[i] = peer_flags[i];
+  p.n = n;
+  p.value = value;
+  signal_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
   CUDA_TRY(cudaGetLastError());
   return TCPXB_K_OK;
 }

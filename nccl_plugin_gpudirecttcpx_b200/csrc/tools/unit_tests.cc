@@ -1,0 +1,448 @@
+// Unit tests of the host core, no GPU and no network peer needed.
+// Usage: tcpxb_unit_tests [name-substring]; prints "ok <name>" / "FAIL <name>" lines
+// and exits non-zero when any test failed.
+//
+// Covers what the reference tests (reference: src/stats/tracepoint_test.cc:26-134
+// counter arithmetic, src/stats/stats_buffer_test.cc:37-92 concurrent producers and
+// consumer wake-up) and the rest of the scheduling primitives, which it leaves
+// untested: ring cursor algebra, both flow mappers, control-record coalescing,
+// the stall detector on an injected clock, flag parsing and range fallback,
+// interface-list syntax, the page allocator and the scatter-list ring.
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <functional>
+#include <set>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "tcpxb/ctrl_sock.h"
+#include "tcpxb/dev_queue.h"
+#include "tcpxb/flags.h"
+#include "tcpxb/flow_mapper.h"
+#include "tcpxb/rx_buf_mgr.h"
+#include "tcpxb/socket_utils.h"
+#include "tcpxb/stage_ring.h"
+#include "tcpxb/telemetry.h"
+#include "tcpxb/timeout.h"
+#include "tcpxb/transport.h"
+
+using namespace tcpxb;
+
+namespace {
+
+int g_failures = 0;
+bool g_current_ok = true;
+#define EXPECT(cond)                                                         \
+  do {                                                                       \
+    if (!(cond)) {                                                           \
+      fprintf(stderr, "  %s:%d expectation failed: %s\n", __FILE__, __LINE__, #cond); \
+      g_current_ok = false;                                                  \
+    }                                                                        \
+  } while (0)
+
+struct Test { const char* name; std::function<void()> fn; };
+std::vector<Test>& tests() { static std::vector<Test> t; return t; }
+struct Reg { Reg(const char* n, std::function<void()> f) { tests().push_back({n, f}); } };
+#define TEST(name) void test_##name(); Reg reg_##name(#name, test_##name); void test_##name()
+
+uint64_t g_fake_now = 0;
+uint64_t fakeClock() { return g_fake_now; }
+
+// ---------------------------------------------------------------- stage ring
+TEST(ring_cursor_algebra) {
+  StageRing<int, 6, 3, false> r;
+  EXPECT(r.empty() && r.numFree() == 6 && !r.has(1) && !r.has(2) && !r.has(3));
+  for (int i = 0; i < 6; ++i) { r.nextFree() = 100 + i; r.admit(); }
+  EXPECT(!r.hasFree() && r.count(1) == 6 && r.inFlight() == 6);
+  EXPECT(r.front(1) == 100);
+  r.advance(1);
+  r.advance(1);
+  EXPECT(r.count(1) == 4 && r.count(2) == 2 && r.front(2) == 100 && r.front(1) == 102);
+  r.advance(2);
+  EXPECT(r.count(2) == 1 && r.count(3) == 1 && r.front(3) == 100 && r.at(1, 3) == 105);
+  EXPECT(!r.hasFree());
+  r.advance(3);
+  EXPECT(r.numFree() == 1 && r.inFlight() == 5);
+  r.nextFree() = 999;
+  r.admit();
+  EXPECT(r.at(1, 4) == 999);  // wrapped into slot 0
+  // wrap many times: invariants hold with 32-bit cursor overflow semantics
+  for (int i = 0; i < 100000; ++i) {
+    while (r.has(1)) r.advance(1);
+    while (r.has(2)) r.advance(2);
+    while (r.has(3)) r.advance(3);
+    EXPECT(r.empty());
+    r.nextFree() = i; r.admit();
+    if (!g_current_ok) break;
+  }
+}
+
+TEST(ring_spsc_threads) {
+  // producer admits and reaps, consumer moves the two middle boundaries: the
+  // ownership split used between the proxy thread and a helper thread
+  static StageRing<uint64_t, 6, 3, true> r;
+  r.reset();
+  const uint64_t total = 200000;
+  std::atomic<bool> bad{false};
+  std::thread consumer([&] {
+    uint64_t next = 0;
+    while (next < total) {
+      if (r.has(1)) {
+        if (r.front(1) != next) bad = true;
+        r.advance(1);
+        r.advance(2);
+        ++next;
+      }
+    }
+  });
+  uint64_t sent = 0, reaped = 0;
+  while (reaped < total) {
+    if (sent < total && r.hasFree()) { r.nextFree() = sent++; r.admit(); }
+    while (r.has(3)) { if (r.front(3) != reaped) bad = true; r.advance(3); ++reaped; }
+  }
+  consumer.join();
+  EXPECT(!bad.load() && r.empty());
+}
+
+// --------------------------------------------------------------- flow mappers
+void mapperNeverPicksFull(FlowMapper* m) {
+  srand(7);
+  for (int round = 0; round < 2000; ++round) {
+    int busy[kMaxSockets];
+    m->reset();
+    for (int s = 0; s < kMaxSockets; ++s) {
+      busy[s] = rand() % (kMaxTasks + 1);
+      if (busy[s] < kMaxTasks) m->offer(s, busy[s]);
+    }
+    int picks = 0;
+    for (int s; (s = m->pick()) != -1; ++picks) {
+      EXPECT(s >= 0 && s < kMaxSockets);
+      EXPECT(busy[s] < kMaxTasks);  // never a socket whose task ring is full
+      ++busy[s];
+      if (picks > kMaxSockets * kMaxTasks) { EXPECT(false); break; }
+    }
+    EXPECT(!m->hasFlow() || m->pick() == -1);
+  }
+}
+TEST(flow_mapper_rr) {
+  FlowMapperRR m;
+  mapperNeverPicksFull(&m);
+  // with every socket empty the turn passes round all of them before repeating
+  m.reset();
+  for (int s = 0; s < 4; ++s) m.offer(s, 0);
+  std::set<int> seen;
+  for (int i = 0; i < 4; ++i) seen.insert(m.pick());
+  EXPECT(seen.size() == 4);
+  // all slots are usable: 4 sockets x 6 slots
+  int n = 4;
+  while (m.pick() != -1) ++n;
+  EXPECT(n == 4 * kMaxTasks);
+}
+TEST(flow_mapper_katy) {
+  FlowMapperKaty m;
+  mapperNeverPicksFull(&m);
+  m.reset();
+  m.offer(0, 3); m.offer(1, 1); m.offer(2, 1); m.offer(3, 5);
+  EXPECT(m.pick() == 1);  // least loaded, lowest index
+  EXPECT(m.pick() == 2);
+  EXPECT(m.pick() == -1);  // two picks per round
+  m.reset();
+  m.offer(5, 0);
+  EXPECT(m.pick() == 5 && m.pick() == 5 && m.pick() == -1);  // re-offered one level up
+}
+
+// ------------------------------------------------------- buffered control socket
+TEST(ctrl_buffer_coalescing) {
+  int sv[2];
+  EXPECT(socketpair(AF_UNIX, SOCK_STREAM, 0, sv) == 0);
+  setNonBlocking(sv[0], true);
+  setNonBlocking(sv[1], true);
+  CtrlSendBuffer tx;
+  CtrlRecvBuffer rx;
+  tx.attach(sv[0]);
+  rx.attach(sv[1]);
+  CtrlMsg m;
+  EXPECT(rx.pop(&m) == kInProgress);
+  for (uint32_t i = 0; i < 8; ++i) {
+    CtrlMsg c = {kCtrlNormal, (uint16_t)i, 1000 + i, i * 1000, 8000};
+    EXPECT(tx.push(c) == kSuccess);
+  }
+  EXPECT(tx.full() && tx.pending());
+  EXPECT(rx.pop(&m) == kInProgress);  // nothing on the wire before the flush
+  EXPECT(tx.flush() == kSuccess && !tx.pending());
+  for (uint32_t i = 0; i < 8; ++i) {
+    EXPECT(rx.pop(&m) == kSuccess);
+    EXPECT(m.index == i && m.size == 1000 + i && m.offset == i * 1000 && m.total == 8000);
+  }
+  // a 9th push flushes by itself; an inline payload behind a record is drained raw
+  CtrlMsg in = {kCtrlInline, 0, 5, 0, 5};
+  EXPECT(tx.push(in) == kSuccess && tx.flush() == kSuccess);
+  EXPECT(send(sv[0], "hello", 5, 0) == 5);
+  EXPECT(rx.pop(&m) == kSuccess && m.type == kCtrlInline && m.size == 5);
+  char buf[8] = {0};
+  int got = rx.drain(buf, 5);
+  if (got < 5) got += (int)recv(sv[1], buf + got, (size_t)(5 - got), 0);
+  EXPECT(got == 5 && memcmp(buf, "hello", 5) == 0);
+  close(sv[0]);
+  EXPECT(rx.pop(&m) == kRemoteError);  // peer gone is an error, not a hang
+  close(sv[1]);
+}
+
+// --------------------------------------------------------------- stall detector
+TEST(stall_detector_fake_clock) {
+  StallDetector d;
+  g_fake_now = 1000;
+  d.configure(/*threshold*/ 10000, /*frequency*/ 30000, fakeClock);
+  uint64_t ns = 0;
+  EXPECT(!d.shouldWarn(&ns));  // first poll only starts the clock
+  g_fake_now += 9999;
+  EXPECT(!d.shouldWarn(&ns));
+  g_fake_now += 1;
+  EXPECT(d.shouldWarn(&ns) && ns == 10000);  // first warning at the threshold
+  g_fake_now += 29999;
+  EXPECT(!d.shouldWarn(&ns));
+  g_fake_now += 1;
+  EXPECT(d.shouldWarn(&ns) && ns == 40000);  // then every `frequency`
+  d.reset();
+  EXPECT(!d.shouldWarn(&ns) && d.polls() == 1);
+  g_fake_now += 5000;
+  EXPECT(!d.shouldWarn(&ns));
+}
+
+// ------------------------------------------------------------------------ flags
+TEST(flags_defaults_and_ranges) {
+  unsetenv("NCCL_DYNAMIC_CHUNK_SIZE");
+  unsetenv("NCCL_INLINE_THRESHOLD");
+  Flags f;
+  loadFlags(&f);
+  EXPECT(f.dynamic_chunk_size == 128 * 1024);  // unset means the documented default, never 0
+  EXPECT(f.inline_threshold == 0 && f.connection_retry == 3 && f.enable == 1);
+  EXPECT(f.timeout_threshold_ns == 10000000000ll && f.timeout_frequency_ns == 30000000000ll);
+  setenv("NCCL_DYNAMIC_CHUNK_SIZE", "0", 1);      // out of range: ignored
+  setenv("NCCL_INLINE_THRESHOLD", "4096", 1);     // above the 2048 maximum: ignored
+  setenv("NCCL_GPUDIRECTTCPX_CONNECTION_RETRY", "0x10", 1);  // base detection like strtoll(.., 0)
+  setenv("NCCL_GPUDIRECTTCPX_SCHED_ALG", "katy", 1);
+  setenv("NCCL_GPUDIRECTTCPX_SLOWNESS_SWITCH", "TX_COMP,RX_CTRL", 1);
+  setenv("NCCL_GPUDIRECTTCPX_SLOWNESS_REPORT", "ALL", 1);
+  setenv("NCCL_GPUDIRECTTCPX_TELEMETRY_SAMPLING_FACTOR", "banana", 1);
+  loadFlags(&f);
+  EXPECT(f.dynamic_chunk_size == 128 * 1024 && f.inline_threshold == 0);
+  EXPECT(f.connection_retry == 16 && f.sched_alg == kSchedKaty && f.sampling_factor == 1);
+  EXPECT(f.slow_switch[kSlowTxComp] && !f.slow_switch[kSlowSendRecv] && f.slow_switch[kSlowRxCtrl]);
+  EXPECT(f.slow_report[0] && f.slow_report[1] && f.slow_report[2]);
+  setenv("NCCL_INLINE_THRESHOLD", "2048", 1);
+  setenv("NCCL_DYNAMIC_CHUNK_SIZE", "1024", 1);
+  loadFlags(&f);
+  EXPECT(f.inline_threshold == 1024);  // never above the chunk size
+  for (const char* e : {"NCCL_DYNAMIC_CHUNK_SIZE", "NCCL_INLINE_THRESHOLD", "NCCL_GPUDIRECTTCPX_CONNECTION_RETRY",
+                        "NCCL_GPUDIRECTTCPX_SCHED_ALG", "NCCL_GPUDIRECTTCPX_SLOWNESS_SWITCH",
+                        "NCCL_GPUDIRECTTCPX_SLOWNESS_REPORT", "NCCL_GPUDIRECTTCPX_TELEMETRY_SAMPLING_FACTOR"})
+    unsetenv(e);
+  bool sw[kSlowKinds];
+  EXPECT(!parseSlownessList("SENDRECV,bogus", sw) && sw[kSlowSendRecv] && !sw[kSlowTxComp]);
+  EXPECT(flagDocs().size() > 50);
+}
+
+// ---------------------------------------------------------------- interface lists
+TEST(interface_list_syntax) {
+  IfList l = parseIfList("eth,ib0");
+  EXPECT(!l.exclude && !l.exact && l.specs.size() == 2);
+  EXPECT(matchIfList(l, "eth0") && matchIfList(l, "eth12") && matchIfList(l, "ib0") && !matchIfList(l, "lo"));
+  l = parseIfList("^docker,lo");
+  EXPECT(l.exclude && !matchIfList(l, "docker0") && !matchIfList(l, "lo") && matchIfList(l, "eth0"));
+  l = parseIfList("=eth0");
+  EXPECT(l.exact && matchIfList(l, "eth0") && !matchIfList(l, "eth01"));
+  l = parseIfList("mlx5_0:1,mlx5_1:2");
+  EXPECT(l.specs[0].port == 1 && l.specs[1].port == 2);
+  EXPECT(matchIfList(l, "mlx5_0", 1) && !matchIfList(l, "mlx5_0", 2) && matchIfList(l, "mlx5_1", 2));
+  std::vector<NetIf> lo = findInterfaces("lo", AF_INET, nullptr);
+  EXPECT(lo.size() == 1 && lo[0].loopback);
+  if (!lo.empty()) {
+    std::vector<NetIf> v = expandVirtual(lo[0], 3);
+    EXPECT(v.size() == 3 && std::string(v[2].name) == "lo#2");
+    EXPECT(addressToString(v[0].addr, false) == "127.0.0.1" && addressToString(v[2].addr, false) == "127.0.0.3");
+  }
+  EXPECT(envSocketFamily("AF_INET6") == AF_INET6 && envSocketFamily("") == AF_UNSPEC);
+}
+
+TEST(core_range_bindings) {
+  CpuBindings b;
+  std::vector<std::string> ifs = {"eth1", "eth2", "lo#0", "lo#1"};
+  EXPECT(parseCoreRanges("eth1:8-21,112-125;eth2:30-31", ifs, &b));
+  EXPECT(b.n_ranges[0] == 2 && b.lo[0][0] == 8 && b.hi[0][0] == 21 && b.lo[0][1] == 112 && b.hi[0][1] == 125);
+  EXPECT(b.n_ranges[1] == 1 && b.lo[1][0] == 30 && b.hi[1][0] == 31 && b.n_ranges[2] == 0);
+  EXPECT(parseCoreRanges("lo:0-3", ifs, &b) && b.n_ranges[2] == 1 && b.n_ranges[3] == 1);  // physical name covers its virtual devices
+  EXPECT(!parseCoreRanges("eth9:1-2", ifs, &b));
+  EXPECT(!parseCoreRanges("eth1:5-2", ifs, &b));
+  EXPECT(parseCoreRanges("", ifs, &b) && b.n_ranges[0] == 0);
+}
+
+// --------------------------------------------------------------- page allocator
+TEST(page_allocator) {
+  PageAllocator a(64, /*scatter=*/false);
+  std::vector<PageRun> runs;
+  EXPECT(a.alloc(32, &runs) && runs.size() == 1 && runs[0].first == 0 && runs[0].count == 32);
+  std::vector<PageRun> more;
+  EXPECT(!a.alloc(33, &more) && more.empty() && a.freePages() == 32);
+  a.release(runs[0].first, runs[0].count);
+  EXPECT(a.freePages() == 64);
+  more.clear();
+  EXPECT(a.alloc(32, &more) && more.size() == 1 && more[0].first == 0);  // a released run comes back contiguous
+  PageAllocator s(1024, /*scatter=*/true);
+  std::vector<PageRun> sr;
+  EXPECT(s.alloc(256, &sr));
+  std::set<uint32_t> pages;
+  uint32_t total = 0;
+  for (auto& r : sr) for (uint32_t i = 0; i < r.count; ++i) { pages.insert(r.first + i); ++total; }
+  EXPECT(total == 256 && pages.size() == 256);   // exact count, no duplicates
+  EXPECT(sr.size() > 128);                       // and really scattered
+  for (auto& r : sr) s.release(r.first, r.count);
+  EXPECT(s.freePages() == 1024);
+  s.release(sr[0].first, 1);                     // double release is refused
+  EXPECT(s.freePages() == 1024);
+}
+
+TEST(rx_buf_mgr_host_pool) {
+  RxBufMgr* m = newHostRxBufMgr(1 << 20, true);
+  EXPECT(m != nullptr);
+  if (m == nullptr) return;
+  EXPECT(m->bytes() == (1 << 20) && m->hostBase() != nullptr && m->devBase() == m->hostBase() && !m->deviceResident());
+  std::vector<PageRun> runs;
+  EXPECT(m->allocPages(256, &runs) && m->freePages() == 0);
+  std::vector<PageRun> none;
+  EXPECT(!m->allocPages(1, &none));
+  m->releasePages(runs.data(), runs.size());
+  EXPECT(m->freePages() == 256);
+  EXPECT(m->registerApplication(1234) == kSuccess && m->deregisterApplication(1234) == kSuccess);
+  int sv[2];
+  EXPECT(socketpair(AF_UNIX, SOCK_STREAM, 0, sv) == 0);
+  EXPECT(m->installFlowRule(sv[0], "0000:1b:00.0") == kSuccess && m->flowRules().size() == 1);
+  EXPECT(m->removeFlowRule(sv[0]) == kSuccess && m->flowRules().empty());
+  close(sv[0]);
+  close(sv[1]);
+  delete m;
+}
+
+TEST(dev_queue_fifo) {
+  DevQueue q;
+  EXPECT(q.init(nullptr, false) == kSuccess);
+  UnpackSlot slots[kUnpackQueueDepth + 1];
+  for (int i = 0; i < kUnpackQueueDepth; ++i) {
+    q.nextFree(&slots[i]);
+    EXPECT(slots[i].active && slots[i].index == (uint64_t)i && slots[i].mem == q.metaHost()->mem[i]);
+  }
+  q.nextFree(&slots[kUnpackQueueDepth]);
+  EXPECT(!slots[kUnpackQueueDepth].active && q.inUse() == (uint64_t)kUnpackQueueDepth);
+  EXPECT(!q.release(3));  // only the oldest may go
+  EXPECT(q.release(0) && q.inUse() == (uint64_t)kUnpackQueueDepth - 1);
+  q.nextFree(&slots[kUnpackQueueDepth]);
+  EXPECT(slots[kUnpackQueueDepth].active && slots[kUnpackQueueDepth].index == 0);
+  static_assert(sizeof(UnpackMeta) == (size_t)kUnpackQueueDepth * kUnpackMaxSlicePages * 16 + kUnpackQueueDepth * 8, "layout");
+  static_assert(sizeof(UnpackDeviceHandle) == 24, "layout");
+}
+
+// -------------------------------------------------------------------- telemetry
+TEST(event_log_concurrent_producers) {
+  EventLog log(64, 256);
+  std::vector<std::thread> producers;
+  for (int p = 0; p < 3; ++p) producers.emplace_back([&log, p] { log.push("producer %d", p); });
+  for (auto& t : producers) t.join();
+  int n = 0;
+  std::string line;
+  while (log.pop(&line, 10)) { EXPECT(line.rfind("producer ", 0) == 0); ++n; }
+  EXPECT(n == 3);
+  // a waiting consumer is woken by a push
+  std::atomic<bool> got{false};
+  std::thread consumer([&] { std::string l; got = log.pop(&l, 30000); });
+  usleep(20000);
+  log.push("wake");
+  consumer.join();
+  EXPECT(got.load());
+  // a full log drops and counts, it never blocks the producer
+  EventLog tiny(4, 16);
+  for (int i = 0; i < 10; ++i) tiny.push("line-%d-with-a-long-tail-that-is-cut", i);
+  EXPECT(tiny.size() == 4 && tiny.dropped() == 6);
+  EXPECT(tiny.pop(&line, 0) && line.size() == 16);
+}
+
+TEST(flow_counters_and_lines) {
+  FlowStats s;
+  s.flow_id = flowIdOf("a->b tx");
+  EXPECT(s.flow_id == flowIdOf("a->b tx") && s.flow_id != flowIdOf("a->c tx"));
+  s.tx_cnt = 7; s.tx_completion_cnt = 5; s.tx_slow_cnt = 1; s.tx_completion_slow_cnt = 2; s.rx_cnt = 9; s.rx_slow_cnt = 3;
+  std::string tx = flowStatsLine(s, "a->b tx", false), rx = flowStatsLine(s, "a->b rx", true);
+  EXPECT(tx.find("] = tx [5/7] tx_slow 1 tx_comp_slow 2") != std::string::npos);
+  EXPECT(rx.find("] = rx 9 rx_slow 3") != std::string::npos);
+  EXPECT(tx.rfind("per_flow_stats[", 0) == 0);
+}
+
+TEST(tracepoints_and_exporter) {
+  char dir[] = "/tmp/tcpxb_ut_XXXXXX";
+  EXPECT(mkdtemp(dir) != nullptr);
+  EventLog log(1000, 256);
+  TraceConfig tc;
+  tc.task_level = true; tc.request_level = false; tc.to_file = true; tc.sampling = 1;
+  setTraceConfig(tc);
+  int obj = 0;
+  traceTransition(&log, 'T', &obj, true, "ACTIVE");
+  traceTransition(&log, 'R', &obj, true, "POSTED");  // request level is off
+  EXPECT(log.size() == 1);
+  std::string path;
+  {
+    Exporter ex(&log, dir, "ut", -1);
+    path = ex.path();
+    traceTransition(&log, 'T', &obj, false, "INACTIVE");
+    ex.stop();
+  }
+  FILE* f = fopen(path.c_str(), "r");
+  EXPECT(f != nullptr);
+  int lines = 0;
+  if (f != nullptr) {
+    char buf[512];
+    while (fgets(buf, sizeof buf, f)) {
+      char kind; void* p; int passive; char state[32]; unsigned long ns;
+      EXPECT(sscanf(buf, "%c %p %d %31s %lu", &kind, &p, &passive, state, &ns) == 5);
+      EXPECT(kind == 'T' && p == &obj && ns > 1600000000000000000ul);
+      ++lines;
+    }
+    fclose(f);
+  }
+  EXPECT(lines == 2);
+  EXPECT(Exporter::writeStatsFile(Exporter::statsPath(dir, "ut"), {"a", "b"}));
+  // the collector removes only exporter_*.log files that are old enough
+  EXPECT(LogGarbageCollector::sweepOnce(dir, 1) == 0);
+  EXPECT(LogGarbageCollector::sweepOnce(dir, 0) == 0);
+  setTraceConfig(TraceConfig());
+  std::string cmd = std::string("rm -r ") + dir;
+  EXPECT(system(cmd.c_str()) == 0);
+}
+
+TEST(result_strings_and_handle_layout) {
+  EXPECT(std::string(resultString(kSuccess)) == "success" && std::string(resultString(kRemoteError)) == "remote error");
+  EXPECT(sizeof(Handle) <= 128 && sizeof(CtrlMsg) == 16 && sizeof(LoadMeta) == 16);
+  EXPECT(sizeof(SocketAddress) == sizeof(struct sockaddr_in6));
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  const char* filter = argc > 1 ? argv[1] : "";
+  int ran = 0;
+  for (const Test& t : tests()) {
+    if (*filter && strstr(t.name, filter) == nullptr) continue;
+    g_current_ok = true;
+    t.fn();
+    printf("%s %s\n", g_current_ok ? "ok" : "FAIL", t.name);
+    fflush(stdout);
+    if (!g_current_ok) ++g_failures;
+    ++ran;
+  }
+  printf("%d test(s), %d failure(s)\n", ran, g_failures);
+  return g_failures == 0 && ran > 0 ? 0 : 1;
+}

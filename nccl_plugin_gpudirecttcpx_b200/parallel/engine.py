@@ -1,0 +1,236 @@
+"""Python face of the hierarchical collective engine (csrc/engine/engine.cc).
+
+One `HierarchicalEngine` per rank.  Ranks are grouped into emulated nodes of
+`gpus_per_node` consecutive ranks; traffic between nodes goes through the
+transport's sockets and is unpacked, reduced and fanned out to the local GPUs by
+the sm_100a kernels, traffic inside a node uses NVLink peer mappings obtained from
+torch symmetric memory.  With a single rank the engine is its own network peer (a
+twin node holding the same data), so the whole path runs on one GPU.
+
+torch.distributed is used for plumbing only: exchanging the 128-byte connect
+handles and rendezvous of the symmetric buffers.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+from ..utils import native
+
+HANDLE_BYTES = 128
+DTYPE_CODE = {torch.bfloat16: 1, torch.float32: 2}
+
+
+class _Config(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in (
+        "rank", "world", "gpus_per_node", "gpu_dev", "request_bytes", "max_inflight", "unpack_ctas",
+        "reduce_impl", "use_nvls", "plain_mode")]
+
+
+class EngineStats(ctypes.Structure):
+    _fields_ = [("bytes_sent", ctypes.c_uint64), ("bytes_received", ctypes.c_uint64),
+                ("requests", ctypes.c_uint64), ("unpack_launches", ctypes.c_uint64),
+                ("fragments", ctypes.c_uint64), ("kernel_launches", ctypes.c_uint64),
+                ("seconds_net_wait", ctypes.c_double)]
+
+
+_lib = None
+
+
+def _e():
+    global _lib
+    if _lib is None:
+        lib = native.load("libnccl-net.so")
+        vp, u64, ci = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int
+        lib.tcpxb_engine_create.restype = vp
+        lib.tcpxb_engine_create.argtypes = [ctypes.POINTER(_Config)]
+        lib.tcpxb_engine_destroy.argtypes = [vp]
+        lib.tcpxb_engine_rails.argtypes = [vp]
+        lib.tcpxb_engine_listen.argtypes = [vp, vp]
+        lib.tcpxb_engine_connect.argtypes = [vp, vp]
+        lib.tcpxb_engine_set_peers.argtypes = [vp, vp, vp, vp, vp, u64]
+        lib.tcpxb_engine_all_reduce.argtypes = [vp, vp, vp, u64, ci, vp]
+        lib.tcpxb_engine_all_gather.argtypes = [vp, vp, vp, u64, vp]
+        lib.tcpxb_engine_reduce_scatter.argtypes = [vp, vp, vp, u64, ci, vp]
+        lib.tcpxb_engine_send_next.argtypes = [vp, vp, u64, vp]
+        lib.tcpxb_engine_recv_prev.argtypes = [vp, vp, u64, vp]
+        lib.tcpxb_engine_stats.argtypes = [vp, ctypes.POINTER(EngineStats)]
+        lib.tcpxb_engine_device_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint32 * 4)]
+        lib.tcpxb_engine_last_error.restype = ctypes.c_char_p
+        _lib = lib
+    return _lib
+
+
+def default_transport_env(nics: int = 4, nthreads: int = 4, nsocks_per_thread: int = 1,
+                          chunk_bytes: int = 512 * 1024, pool_mb: int = 1024) -> None:
+    """Environment defaults for the transport under the engine (only where unset)."""
+    for k, v in {
+        "NCCL_GPUDIRECTTCPX_SOCKET_IFNAME": "lo",
+        "NCCL_GPUDIRECTTCPX_VIRTUAL_NICS": str(nics),
+        "NCCL_SOCKET_NTHREADS": str(nthreads),
+        "NCCL_NSOCKS_PERTHREAD": str(nsocks_per_thread),
+        "NCCL_DYNAMIC_CHUNK_SIZE": str(chunk_bytes),
+        "NCCL_GPUDIRECTTCPX_RX_POOL_BYTES": str(pool_mb << 20),
+    }.items():
+        os.environ.setdefault(k, v)
+
+
+class HierarchicalEngine:
+    """Collectives whose inter-node stage runs through the transport and whose receive
+    side is the fused unpack kernel.  All calls are host-blocking and stream-ordered."""
+
+    def __init__(self, gpus_per_node: int = 1, buffer_bytes: int = 0, request_bytes: int = 4 << 20,
+                 max_inflight: int = 8, unpack_ctas: int = 16, reduce_impl: int = 0, use_nvls: bool = False,
+                 plain_mode: bool = False, device: Optional[torch.device] = None):
+        import torch.distributed as dist
+        self._dist = dist if dist.is_available() and dist.is_initialized() else None
+        self.rank = self._dist.get_rank() if self._dist else 0
+        self.world = self._dist.get_world_size() if self._dist else 1
+        self.G = gpus_per_node
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.nodes = max(2, self.world // self.G) if self.world > 1 else 2
+        cfg = _Config(self.rank, self.world, self.G, self.device.index or 0, request_bytes, max_inflight, unpack_ctas,
+                      reduce_impl, int(use_nvls), int(plain_mode))
+        self._h = _e().tcpxb_engine_create(ctypes.byref(cfg))
+        if not self._h:
+            raise RuntimeError("engine create failed: " + _e().tcpxb_engine_last_error().decode())
+        self.rails = _e().tcpxb_engine_rails(self._h)
+        self._connect()
+        self.work = self.out = None
+        self._keep = []
+        if self.G > 1:
+            if buffer_bytes <= 0:
+                raise ValueError("buffer_bytes is required when gpus_per_node > 1")
+            self._setup_symmetric(buffer_bytes, use_nvls)
+
+    # ------------------------------------------------------------------ set-up
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise RuntimeError("engine call failed: " + _e().tcpxb_engine_last_error().decode())
+
+    def _connect(self) -> None:
+        mine = ctypes.create_string_buffer(self.rails * HANDLE_BYTES)
+        self._check(_e().tcpxb_engine_listen(self._h, mine))
+        if self.world == 1:
+            nxt = mine.raw
+        else:
+            allh = [None] * self.world
+            self._dist.all_gather_object(allh, mine.raw)
+            node, local = divmod(self.rank, self.G)
+            nxt = allh[((node + 1) % (self.world // self.G)) * self.G + local]
+        buf = ctypes.create_string_buffer(nxt, len(nxt))
+        self._check(_e().tcpxb_engine_connect(self._h, buf))
+
+    def _setup_symmetric(self, buffer_bytes: int, use_nvls: bool) -> None:
+        import torch.distributed._symmetric_memory as symm
+        dist = self._dist
+        node = self.rank // self.G
+        group = None
+        for n in range(self.world // self.G):
+            g = dist.new_group(list(range(n * self.G, (n + 1) * self.G)))
+            if n == node:
+                group = g
+        n_el = (buffer_bytes + 3) // 4
+        self.buffer_bytes = n_el * 4
+        bufs = {}
+        for name, count in (("work", n_el), ("out", n_el), ("flags", 64)):
+            t = symm.empty(count, dtype=torch.int32, device=self.device)
+            t.zero_()
+            hdl = symm.rendezvous(t, group=group)
+            bufs[name] = (t, hdl)
+        torch.cuda.synchronize()
+        dist.barrier(group)
+        self._keep = bufs
+        self.work = bufs["work"][0]
+        self.out = bufs["out"][0]
+        arr = lambda ptrs: (ctypes.c_void_p * self.G)(*[int(p) for p in ptrs])
+        mc = 0
+        if use_nvls:
+            mc = int(getattr(bufs["out"][1], "multicast_ptr", 0) or 0)
+        self.nvls = bool(mc)
+        self._check(_e().tcpxb_engine_set_peers(self._h, arr(bufs["work"][1].buffer_ptrs), arr(bufs["out"][1].buffer_ptrs),
+                                                arr(bufs["flags"][1].buffer_ptrs), mc or None, self.buffer_bytes))
+
+    # -------------------------------------------------------------- collectives
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def all_reduce(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Sum over all ranks.  G == 1: any contiguous CUDA tensors.  G > 1: `x` is staged
+        into the symmetric work buffer and the result is a view of the symmetric output."""
+        nbytes = x.numel() * x.element_size()
+        code = DTYPE_CODE[x.dtype]
+        if self.G == 1:
+            if out is None:
+                out = torch.empty_like(x)
+            self._check(_e().tcpxb_engine_all_reduce(self._h, x.data_ptr(), out.data_ptr(), nbytes, code, self._stream()))
+            return out
+        w = self.work.view(torch.uint8)[:nbytes].view(x.dtype)
+        if x.data_ptr() != w.data_ptr():
+            w.copy_(x.reshape(-1))
+        self._check(_e().tcpxb_engine_all_reduce(self._h, self.work.data_ptr(), self.out.data_ptr(), nbytes, code, self._stream()))
+        res = self.out.view(torch.uint8)[:nbytes].view(x.dtype).view(x.shape)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+
+    def work_view(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """The symmetric work buffer as a tensor, for producers that write in place."""
+        return self.work.view(torch.uint8)[:numel * dtype.itemsize].view(dtype)
+
+    def all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        nbytes = x.numel() * x.element_size()
+        blocks = self.nodes * self.G
+        if self.G == 1:
+            out = torch.empty(blocks * x.numel(), dtype=x.dtype, device=x.device)
+            self._check(_e().tcpxb_engine_all_gather(self._h, x.data_ptr(), out.data_ptr(), nbytes, self._stream()))
+            return out
+        self._check(_e().tcpxb_engine_all_gather(self._h, x.data_ptr(), self.out.data_ptr(), nbytes, self._stream()))
+        return self.out.view(torch.uint8)[:nbytes * blocks].view(x.dtype)
+
+    def reduce_scatter(self, x: torch.Tensor) -> torch.Tensor:
+        blocks = self.nodes * self.G if self.world > 1 else 1
+        per = x.numel() // blocks
+        nbytes = per * x.element_size()
+        out = torch.empty(per, dtype=x.dtype, device=x.device)
+        src = x
+        if self.G > 1:
+            w = self.work.view(torch.uint8)[:x.numel() * x.element_size()].view(x.dtype)
+            if x.data_ptr() != w.data_ptr():
+                w.copy_(x.reshape(-1))
+            src = self.work
+        self._check(_e().tcpxb_engine_reduce_scatter(self._h, src.data_ptr(), out.data_ptr(), nbytes, DTYPE_CODE[x.dtype], self._stream()))
+        return out
+
+    def send_next(self, x: torch.Tensor) -> None:
+        self._check(_e().tcpxb_engine_send_next(self._h, x.data_ptr(), x.numel() * x.element_size(), self._stream()))
+
+    def recv_prev(self, x: torch.Tensor) -> None:
+        self._check(_e().tcpxb_engine_recv_prev(self._h, x.data_ptr(), x.numel() * x.element_size(), self._stream()))
+
+    # -------------------------------------------------------------------- misc
+    def stats(self) -> EngineStats:
+        s = EngineStats()
+        _e().tcpxb_engine_stats(self._h, ctypes.byref(s))
+        return s
+
+    def device_status(self):
+        w = (ctypes.c_uint32 * 4)()
+        _e().tcpxb_engine_device_status(self._h, ctypes.byref(w))
+        return list(w)
+
+    def close(self) -> None:
+        if self._h:
+            torch.cuda.synchronize(self.device)
+            _e().tcpxb_engine_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,68 @@
+"""Environment that makes NCCL (and therefore torch.distributed) load the plugin and
+push traffic between GPUs of one box through it.
+
+A single 8-GPU box has no inter-node network, so "nodes" are emulated: NCCL's
+peer-to-peer and shared-memory transports are disabled between the ranks that
+should talk over the network, which leaves the net transport, and the plugin is
+given `nics` virtual devices on the loopback interface.  The same generic socket
+variables (NCCL_SOCKET_NTHREADS, NCCL_NSOCKS_PERTHREAD, NCCL_DYNAMIC_CHUNK_SIZE)
+steer both this plugin and NCCL's own socket transport, so a fair comparison pins
+them identically for both; `plugin_env(..., builtin_socket=True)` returns the
+baseline variant of the same environment.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, Optional
+
+from ..utils import native
+
+
+def plugin_env(nics: int = 4, nsocks_per_thread: int = 1, nthreads: int = 4, chunk_bytes: int = 512 * 1024,
+               recv_mode: str = "host", rx_pool_mode: str = "host", rx_pool_mb: int = 1024,
+               gdr: bool = True, builtin_socket: bool = False, speed_mbps: int = 200000,
+               debug: Optional[str] = None, extra: Optional[Dict[str, str]] = None) -> Dict[str, str]:
+    env = {
+        # every GPU is its own "node": nothing but the net transport is left
+        "NCCL_P2P_DISABLE": "1",
+        "NCCL_SHM_DISABLE": "1",
+        "NCCL_IB_DISABLE": "1",
+        "NCCL_SOCKET_IFNAME": "lo",
+        "NCCL_SOCKET_NTHREADS": str(nthreads),
+        "NCCL_NSOCKS_PERTHREAD": str(nsocks_per_thread),
+        "NCCL_DYNAMIC_CHUNK_SIZE": str(chunk_bytes),
+    }
+    if builtin_socket:
+        env["NCCL_NET"] = "Socket"
+        env["NCCL_NET_PLUGIN"] = "none"
+    else:
+        lib = native.plugin_path()
+        if not lib.exists():
+            native.load("libnccl-net.so")
+        env.update({
+            "NCCL_NET_PLUGIN": str(lib),
+            "LD_LIBRARY_PATH": f"{lib.parent}:{os.environ.get('LD_LIBRARY_PATH', '')}",
+            "NCCL_GPUDIRECTTCPX_SOCKET_IFNAME": "lo",
+            "NCCL_GPUDIRECTTCPX_VIRTUAL_NICS": str(nics),
+            "NCCL_GPUDIRECTTCPX_RECV_MODE": recv_mode,
+            "NCCL_GPUDIRECTTCPX_RX_POOL_MODE": rx_pool_mode,
+            "NCCL_GPUDIRECTTCPX_RX_POOL_BYTES": str(rx_pool_mb << 20),
+            "NCCL_GPUDIRECTTCPX_NIC_SPEED_MBPS": str(speed_mbps),
+        })
+        if gdr:
+            # hand CUDA pointers to the plugin although the "NIC" hangs off the CPU
+            env["NCCL_NET_GDR_LEVEL"] = "SYS"
+            env["NCCL_NET_GDR_READ"] = "1"
+    if debug:
+        env["NCCL_DEBUG"] = debug
+        env["NCCL_DEBUG_SUBSYS"] = "INIT,NET,ENV"
+    if extra:
+        env.update(extra)
+    return env
+
+
+def use_plugin(**kw) -> Dict[str, str]:
+    """Applies plugin_env() to os.environ (before torch.distributed initialises NCCL)."""
+    env = plugin_env(**kw)
+    os.environ.update(env)
+    return env

@@ -1,0 +1,63 @@
+"""Hierarchical engine on one GPU: the rank is its own network peer (twin node), so every
+byte goes isend -> pinned staging -> loopback sockets -> rx page pool -> fused unpack kernel."""
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def engine():
+    from nccl_plugin_gpudirecttcpx_b200.parallel.engine import HierarchicalEngine, default_transport_env
+    default_transport_env(nics=2, nthreads=2, nsocks_per_thread=1, pool_mb=256)
+    e = HierarchicalEngine(gpus_per_node=1, request_bytes=1 << 20)
+    yield e
+    e.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("numel", [8, 4096, (1 << 20) + 8, 6 << 20])
+def test_twin_all_reduce_doubles(engine, dtype, numel):
+    x = torch.randn(numel, device="cuda", generator=torch.Generator("cuda").manual_seed(numel)).to(dtype)
+    out = engine.all_reduce(x)
+    torch.cuda.synchronize()
+    want = (x.float() * 2).to(dtype)
+    assert torch.equal(out, want)
+    assert engine.device_status()[0] == 0
+
+
+def test_twin_all_gather_and_reduce_scatter(engine):
+    x = torch.randn(3 << 18, device="cuda").to(torch.bfloat16)
+    g = engine.all_gather(x)
+    torch.cuda.synchronize()
+    assert g.numel() == 2 * x.numel() and torch.equal(g[:x.numel()], x) and torch.equal(g[x.numel():], x)
+    r = engine.reduce_scatter(x)
+    torch.cuda.synchronize()
+    assert torch.equal(r, (x.float() * 2).to(torch.bfloat16))
+
+
+def test_twin_send_recv_and_stats(engine):
+    import threading
+    x = torch.randint(0, 255, (5 << 20,), dtype=torch.uint8, device="cuda")
+    y = torch.zeros_like(x)
+    before = engine.stats().bytes_received
+    # the single rank is both ends: send and receive in one exchange via all_gather's path
+    g = engine.all_gather(x)
+    torch.cuda.synchronize()
+    assert torch.equal(g[x.numel():], x)
+    s = engine.stats()
+    assert s.bytes_received - before == x.numel() and s.fragments > 0 and s.unpack_launches > 0
+
+
+def test_plain_mode_matches_fused():
+    from nccl_plugin_gpudirecttcpx_b200.parallel.engine import HierarchicalEngine
+    e = HierarchicalEngine(gpus_per_node=1, request_bytes=1 << 20, plain_mode=True)
+    try:
+        x = torch.randn(3 << 20, device="cuda").to(torch.bfloat16)
+        out = e.all_reduce(x)
+        torch.cuda.synchronize()
+        assert torch.equal(out, (x.float() * 2).to(torch.bfloat16))
+    finally:
+        e.close()

@@ -1,0 +1,124 @@
+"""CPU tests of the C++ host core: unit tests, the ncclNet API loopback, sanitizer builds."""
+import json
+import os
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+from nccl_plugin_gpudirecttcpx_b200 import _build
+
+LIB = _build.OUT
+
+
+@pytest.fixture(scope="module")
+def host_lib():
+    return _build.build_host()
+
+
+def _env(**kw):
+    env = dict(os.environ)
+    env.update({
+        "NCCL_GPUDIRECTTCPX_SOCKET_IFNAME": "lo",
+        "NCCL_GPUDIRECTTCPX_VIRTUAL_NICS": "2",
+        "NCCL_SOCKET_NTHREADS": "2",
+        "NCCL_NSOCKS_PERTHREAD": "2",   # 4 sockets per comm
+    })
+    env.update({k: str(v) for k, v in kw.items()})
+    return env
+
+
+def _loopback(host_lib, args=(), exe="tcpxb_loopback", plugin=None, timeout=300, **envkw):
+    cmd = [str(LIB / exe), "--plugin", str(plugin or host_lib)] + list(args)
+    r = subprocess.run(cmd, env=_env(**envkw), capture_output=True, text=True, timeout=timeout)
+    return r
+
+
+def test_unit_tests_binary(host_lib):
+    r = subprocess.run([str(LIB / "tcpxb_unit_tests")], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "0 failure(s)" in r.stdout
+    assert len(re.findall(r"^ok ", r.stdout, flags=re.M)) >= 16
+
+
+def _parse(stdout):
+    rows = [json.loads(l) for l in stdout.splitlines() if l.startswith('{"tool"')]
+    flows = [l.split() for l in stdout.splitlines() if l.startswith("FLOW ")]
+    return rows, flows
+
+
+def test_api_loopback_byte_exact_with_flow_stats(host_lib):
+    """2 processes, host buffers, 4 sockets per comm on 2 loopback NICs, 8 in flight,
+    1 KB / 64 KB / 4 MB / 64 MB, byte-exact, per-flow byte counters add up."""
+    sizes = [1024, 65536, 4 << 20, 64 << 20]
+    iters = 2
+    r = _loopback(host_lib, ["--sizes", ",".join(map(str, sizes)), "--inflight", "8", "--iters", str(iters)])
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "loopback PASSED" in r.stdout
+    rows, flows = _parse(r.stdout)
+    assert [row["size"] for row in rows] == sizes and all(row["byte_exact"] for row in rows)
+    assert all(row["comms"] == 2 and row["inflight"] == 8 for row in rows)
+    total = sum(sizes) * 8 * iters  # per comm
+    for side in ("send", "recv"):
+        for comm in ("0", "1"):
+            mine = [f for f in flows if f[1] == side and f[3] == comm]
+            assert len(mine) == 4, "4 data sockets per comm"
+            posted = sum(int(f[f.index("bytes_posted") + 1]) for f in mine)
+            done = sum(int(f[f.index("bytes_done") + 1]) for f in mine)
+            assert posted == total and done == total
+            assert sum(1 for f in mine if int(f[f.index("bytes_done") + 1]) > 0) >= 2, "traffic is striped"
+    assert len(re.findall(r"^per_flow_stats\[\d+:127\.0\.0\.[12]<\d+>->127\.0\.0\.[12]<\d+> (tx|rx)\] = ", r.stdout, flags=re.M)) == 16
+
+
+@pytest.mark.parametrize("variant", [
+    dict(args=["--v7"]),
+    dict(NCCL_GPUDIRECTTCPX_SCHED_ALG="KATY"),
+    dict(NCCL_INLINE_THRESHOLD=2048),
+    dict(NCCL_GPUDIRECTTCPX_RECV_SYNC=1),
+    dict(NCCL_MIN_ZCOPY_SIZE=16384),
+    dict(NCCL_DYNAMIC_CHUNK_SIZE=4096, NCCL_THREAD_SPIN_ENABLE=1),
+    dict(NCCL_SOCKET_NTHREADS=1, NCCL_NSOCKS_PERTHREAD=1, NCCL_GPUDIRECTTCPX_FORCE_ACK=1),
+    dict(NCCL_SOCKET_NTHREADS=8, NCCL_NSOCKS_PERTHREAD=1, NCCL_GPUDIRECTTCPX_SLOWNESS_SWITCH="ALL"),
+])
+def test_api_loopback_variants(host_lib, variant):
+    variant = dict(variant)
+    args = variant.pop("args", []) + ["--sizes", "0,1,1000,2048,2049,300000,3000001", "--inflight", "8", "--iters", "2"]
+    r = _loopback(host_lib, args, **variant)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "loopback PASSED" in r.stdout
+
+
+def test_plugin_disabled_by_env(host_lib):
+    r = _loopback(host_lib, ["--sizes", "1024", "--iters", "1"], NCCL_GPUDIRECTTCPX_SOCKET_ENABLE=0)
+    assert r.returncode != 0  # init fails so that NCCL would fall back
+
+
+def test_telemetry_files(host_lib, tmp_path):
+    r = _loopback(host_lib, ["--sizes", "65536,1000000", "--iters", "2"],
+                  NCCL_GPUDIRECTTCPX_TELEMETRY_EXPORT_STATS_TO_FILE=1,
+                  NCCL_GPUDIRECTTCPX_TELEMETRY_ENABLE_TASK_LEVEL_STATS=1,
+                  NCCL_GPUDIRECTTCPX_TELEMETRY_ENABLE_REQUEST_LEVEL_STATS=1,
+                  NCCL_GPUDIRECTTCPX_TELEMETRY_EXPORTER_PATH=str(tmp_path),
+                  NCCL_GPUDIRECTTCPX_LOG_STATS_TO_STDOUT=1)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    logs = sorted(tmp_path.glob("exporter_[0-9]*_*.log"))
+    stats = sorted(tmp_path.glob("exporter_stats_*_*.log"))
+    assert len(logs) == 4 and len(stats) == 4  # 2 comms on each side
+    text = logs[0].read_text().splitlines()
+    assert text and all(re.match(r"^[TR] 0x[0-9a-f]+ [01] [A-Z]+ \d{19}$", l) for l in text)
+    states = {l.split()[3] for l in text}
+    assert {"ACTIVE", "COMPLETING", "INACTIVE", "POSTED", "TRANSMITTING"} <= states
+    assert all(l.startswith("per_flow_stats[") for l in stats[0].read_text().splitlines())
+
+
+@pytest.mark.parametrize("san", ["address", "thread"])
+def test_loopback_under_sanitizer(san):
+    lib = _build.build_host(sanitize=san)
+    env = {"ASAN_OPTIONS": "detect_leaks=0", "TSAN_OPTIONS": "halt_on_error=1 second_deadlock_stack=1"}
+    r = _loopback(lib, ["--sizes", "0,1000,65536,2000000", "--inflight", "8", "--iters", "2"],
+                  exe=f"tcpxb_loopback_{san}", timeout=600, **env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
+    assert "loopback PASSED" in r.stdout
+    assert "WARNING: ThreadSanitizer" not in r.stderr and "ERROR: AddressSanitizer" not in r.stderr
