@@ -141,6 +141,36 @@ int tcpxb_peer_reduce(void* out, void* const* srcs, int nsrcs, uint64_t shard_of
 size_t tcpxb_checksum_scratch_bytes(void);
 int tcpxb_checksum(const void* buf, uint64_t bytes, uint64_t* out, void* partials, void* stream);
 
+// Checksum for callers that must not allocate device memory.
+//
+// Same result as tcpxb_checksum, but the scratch for the per-block partial sums
+// lives in a fixed array inside this library instead of a buffer the caller
+// provides, so the call performs no cudaMalloc / cudaFree and uses no allocating
+// library routine.  It is meant for code that runs where an allocation is
+// forbidden or dangerous: the transport's progress loop on NCCL's proxy thread
+// (a cudaMalloc there synchronises the device and can deadlock against a
+// collective kernel that is waiting for that same thread), completion callbacks,
+// and processes that were handed a fixed memory budget and may not grow it.
+// The reference has nothing like it (it owns no kernel at all).
+//
+//  * The array takes TCPXB_CHECKSUM_NOALLOC_SCRATCH_BYTES on every GPU that loads
+//    the library, from load until the process exits.
+//  * Buffers larger than TCPXB_CHECKSUM_NOALLOC_MAX_BYTES are refused with
+//    TCPXB_K_TOO_LARGE and an explanatory message; nothing is launched.
+//  * The first call on each device looks up the array's device address
+//    (cudaGetSymbolAddress with that device current).  Make that first call before
+//    any stream capture begins on the device.
+//  * All calls on one GPU share the array: the counter it starts from is cleared
+//    on the stream at the head of every call, and the partial sums keep the
+//    previous call's values until overwritten.  Two calls that overlap in time on
+//    the same GPU (different streams) race on it and may both return garbage;
+//    issue them on one stream or order them with events.
+// `buf`, `out` and `stream` are as for tcpxb_checksum; `out` is device memory the
+// caller owns.
+#define TCPXB_CHECKSUM_NOALLOC_MAX_BYTES (1ull << 34)
+#define TCPXB_CHECKSUM_NOALLOC_SCRATCH_BYTES 4864
+int tcpxb_checksum_noalloc(const void* buf, uint64_t bytes, uint64_t* out, void* stream);
+
 const char* tcpxb_kernel_last_error(void);
 
 #ifdef __cplusplus

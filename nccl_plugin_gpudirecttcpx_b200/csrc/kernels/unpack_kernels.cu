@@ -31,6 +31,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "tcpxb/kernels.h"
 
 namespace {
@@ -647,6 +649,11 @@ checksum_kernel(const uint8_t* buf, uint64_t bytes, uint64_t* out, CsumScratch* 
   }
 }
 
+// Scratch of the allocation-free checksum entry point: one CsumScratch per GPU,
+// resident from library load to process exit.
+static_assert(sizeof(CsumScratch) <= TCPXB_CHECKSUM_NOALLOC_SCRATCH_BYTES, "stated scratch size");
+static __device__ __align__(256) unsigned char g_csum_static[TCPXB_CHECKSUM_NOALLOC_SCRATCH_BYTES];
+
 // ------------------------------------------------------------------ host side
 thread_local char g_err[256] = "";
 int fail(int code, const char* fmt, const char* a = "") {
@@ -905,6 +912,42 @@ int tcpxb_checksum(const void* buf, uint64_t bytes, uint64_t* out, void* partial
   int blocks = (int)(want < 1 ? 1 : (want > (uint64_t)kCsumBlocks ? kCsumBlocks : want));
   checksum_kernel<<<blocks, kCsumThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(buf), bytes, out, static_cast<CsumScratch*>(partials));
+  CUDA_TRY(cudaGetLastError());
+  return TCPXB_K_OK;
+}
+
+// In host code `g_csum_static` is only a handle for the runtime, not an address a
+// kernel could use, so the device address is resolved once per device.
+int tcpxb_checksum_noalloc(const void* buf, uint64_t bytes, uint64_t* out, void* stream) {
+  static std::mutex mu;
+  static void* scratch_of_device[kMaxDevices] = {};
+  if (out == nullptr || (buf == nullptr && bytes != 0))
+    return fail(TCPXB_K_INVALID, "null buffer or output");
+  if (reinterpret_cast<uintptr_t>(buf) & 3)
+    return fail(TCPXB_K_INVALID, "checksum buffer must be 4-byte aligned");
+  if (bytes > TCPXB_CHECKSUM_NOALLOC_MAX_BYTES)
+    return fail(TCPXB_K_TOO_LARGE,
+                "tcpxb_checksum_noalloc handles at most 16 GiB per call; split the buffer or use tcpxb_checksum%s");
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(TCPXB_K_INVALID, "device ordinal out of range");
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> l(mu);
+    if (scratch_of_device[dev] == nullptr) {
+      void* p = nullptr;
+      CUDA_TRY(cudaGetSymbolAddress(&p, g_csum_static));
+      scratch_of_device[dev] = p;
+    }
+    scratch = scratch_of_device[dev];
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the completion counter must start at zero even if an earlier launch was cut short
+  CUDA_TRY(cudaMemsetAsync(scratch, 0, 8, s));
+  uint64_t want = (bytes / 16 + kCsumThreads - 1) / kCsumThreads;
+  int blocks = (int)(want < 1 ? 1 : (want > (uint64_t)kCsumBlocks ? kCsumBlocks : want));
+  checksum_kernel<<<blocks, kCsumThreads, 0, s>>>(static_cast<const uint8_t*>(buf), bytes, out,
+                                                  static_cast<CsumScratch*>(scratch));
   CUDA_TRY(cudaGetLastError());
   return TCPXB_K_OK;
 }
