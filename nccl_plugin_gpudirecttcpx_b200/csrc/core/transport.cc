@@ -46,6 +46,44 @@ inline void traceReq(Comm* c, const Request* r, int stage) {
   if (traceConfig().request_level) traceTransition(c->events.get(), 'R', r, c->passive, kReqStageName[stage]);
 }
 
+// Debug watchdog (TCPXB_WATCHDOG_SECS=n): a thread that prints, every n seconds,
+// the last checkpoint of every comm whose API thread has been inside a call for
+// more than n seconds.  Finds calls that never return.
+std::mutex g_wd_mu;
+std::vector<Comm*> g_wd_comms;
+bool g_wd_started = false;
+inline void mark(Comm* c, const char* where) {
+  c->where.store(where, std::memory_order_relaxed);
+  c->where_ns.store(monotonicNanos(), std::memory_order_relaxed);
+}
+void watchdogRegister(Comm* c) {
+  const char* v = getenv("TCPXB_WATCHDOG_SECS");
+  if (v == nullptr) return;
+  const int secs = std::max(1, atoi(v));
+  std::lock_guard<std::mutex> l(g_wd_mu);
+  g_wd_comms.push_back(c);
+  if (g_wd_started) return;
+  g_wd_started = true;
+  std::thread([secs] {
+    for (;;) {
+      sleep((unsigned)secs);
+      std::lock_guard<std::mutex> l(g_wd_mu);
+      const uint64_t now = monotonicNanos();
+      for (Comm* c : g_wd_comms) {
+        const char* w = c->where.load();
+        const uint64_t t = c->where_ns.load();
+        if (strcmp(w, "idle") != 0 && now - t > (uint64_t)secs * 1000000000ull)
+          WARN("watchdog: %s comm %lx has been at '%s' for %lu ms", c->passive ? "recv" : "send", (unsigned long)c->id, w,
+               (unsigned long)((now - t) / 1000000));
+      }
+    }
+  }).detach();
+}
+void watchdogForget(Comm* c) {
+  std::lock_guard<std::mutex> l(g_wd_mu);
+  g_wd_comms.erase(std::remove(g_wd_comms.begin(), g_wd_comms.end(), c), g_wd_comms.end());
+}
+
 void setError(Comm* c, Result r) {
   int expected = kSuccess;
   c->error.compare_exchange_strong(expected, (int)r);
@@ -349,6 +387,16 @@ Result ensureCudaRecv(Comm* comm, int gpu_dev, bool want_device_handle = false) 
   return kSuccess;
 }
 
+Result ensureTxStage(Comm* comm) {
+  if (comm->tx_stage != nullptr) return kSuccess;
+  void* h = nullptr;
+  void* d = nullptr;
+  comm->tx_stage_bytes = (uint64_t)flags().tx_staging_bytes;
+  TCPXB_CHECK(gpu::hostAllocMapped(comm->tx_stage_bytes, &h, &d));
+  comm->tx_stage = static_cast<uint8_t*>(h);
+  return kSuccess;
+}
+
 // Reserves `bytes` of the pinned tx staging ring (FIFO); false when it is full.
 bool stageAlloc(Comm* comm, uint64_t bytes, uint8_t** out, uint64_t* charged) {
   const uint64_t cap = comm->tx_stage_bytes;
@@ -364,14 +412,12 @@ bool stageAlloc(Comm* comm, uint64_t bytes, uint8_t** out, uint64_t* charged) {
 }
 
 Result startCudaSend(Comm* comm, Request* r, MemHandle* mh) {
+  const bool dbg = getenv("TCPXB_DEBUG_CUDA_SEND") != nullptr && comm->api_calls < 4;
+  if (dbg) INFO(kSubNet, "send comm %lx: cuda send enter (prepared %d stream %p stage %p)", (unsigned long)comm->id,
+                (int)comm->cuda_prepared, comm->stream, (void*)comm->tx_stage);
   TCPXB_CHECK(ensureCudaComm(comm, mh != nullptr && mh->gpu_dev >= 0 ? mh->gpu_dev : comm->gpu_dev));
-  if (comm->tx_stage == nullptr) {
-    void* h = nullptr;
-    void* d = nullptr;
-    comm->tx_stage_bytes = (uint64_t)flags().tx_staging_bytes;
-    TCPXB_CHECK(gpu::hostAllocMapped(comm->tx_stage_bytes, &h, &d));
-    comm->tx_stage = static_cast<uint8_t*>(h);
-  }
+  TCPXB_CHECK(ensureTxStage(comm));
+  if (dbg) INFO(kSubNet, "send comm %lx: resources ready", (unsigned long)comm->id);
   if (r->size == 0) return kSuccess;
   if (!stageAlloc(comm, (uint64_t)r->size, &r->stage, &r->stage_bytes)) return kInProgress;
   const int chunk = (int)flags().dynamic_chunk_size;
@@ -387,9 +433,12 @@ Result startCudaSend(Comm* comm, Request* r, MemHandle* mh) {
   for (int i = 0; i < r->n_segs; ++i) {
     const int off = i * seg;
     const int len = std::min(seg, r->size - off);
+    if (dbg) INFO(kSubNet, "send comm %lx: memcpy %d bytes from %p", (unsigned long)comm->id, len, (void*)(r->data + off));
     TCPXB_CHECK(gpu::copyToHostAsync(r->stage + off, r->data + off, (size_t)len, comm->stream));
+    if (dbg) INFO(kSubNet, "send comm %lx: memcpy queued", (unsigned long)comm->id);
     if (r->seg_event[i] == nullptr) TCPXB_CHECK(gpu::eventCreate(&r->seg_event[i]));
     TCPXB_CHECK(gpu::eventRecord(r->seg_event[i], comm->stream));
+    if (dbg) INFO(kSubNet, "send comm %lx: event recorded", (unsigned long)comm->id);
   }
   return kSuccess;
 }
@@ -398,6 +447,7 @@ Result startCudaSend(Comm* comm, Request* r, MemHandle* mh) {
 bool stagedUpTo(Request* r, int upto) {
   const int need = (upto + r->seg_bytes - 1) / r->seg_bytes;
   while (r->segs_done < need) {
+    mark(r->comm, "stagedUpTo:eventQuery");
     if (gpu::eventQuery(r->seg_event[r->segs_done]) != kSuccess) return false;
     ++r->segs_done;
   }
@@ -501,12 +551,14 @@ Result launchUnpack(Comm* comm, Request* r) {
   (void)comm; (void)r;
   return kInvalidUsage;
 #else
+  mark(comm, "launchUnpack:kernel");
   if (r->slot.filled > 0) {
     int rc = tcpxb_unpack_copy(comm->rxmgr->devBase(), comm->rxmgr->bytes(), r->data, (uint64_t)r->size,
                                reinterpret_cast<const tcpxbLoadMeta*>(r->slot.mem_dev), (uint32_t)r->slot.filled,
                                comm->unpack_status_dev, nullptr, comm->stream);
     if (rc != 0) { WARN("unpack launch failed: %s", tcpxb_kernel_last_error()); return kUnhandledCudaError; }
   }
+  mark(comm, "launchUnpack:event");
   if (r->unpack_event == nullptr) TCPXB_CHECK(gpu::eventCreate(&r->unpack_event));
   TCPXB_CHECK(gpu::eventRecord(r->unpack_event, comm->stream));
   r->unpack_launched = true;
@@ -656,6 +708,7 @@ Result progressRecvRequest(Comm* comm, Request* r) {
 }
 
 Result progress(Comm* comm) {
+  mark(comm, "progress:enter");
   const int err = comm->error.load(std::memory_order_acquire);
   if (err != kSuccess) return (Result)err;
   if (comm->rq.empty()) return kSuccess;
@@ -677,6 +730,7 @@ Result progress(Comm* comm) {
     if (s.tasks.hasFree()) comm->mapper->offer(idx, (int)(kMaxTasks - s.tasks.numFree()));
   }
   comm->rotate = (comm->rotate + 1) % comm->num_socks;
+  mark(comm, "progress:posted");
   // 2. posted -> active (optionally synchronised: the receiver names the request it posted)
   while (comm->rq.has(kReqPosted)) {
     Request* r = &comm->rq.front(kReqPosted);
@@ -697,6 +751,7 @@ Result progress(Comm* comm) {
     traceReq(comm, r, kReqActive);
     comm->rq.advance(kReqPosted);
   }
+  mark(comm, "progress:schedule");
   // 3. schedule the active requests, oldest first
   if (!comm->passive && comm->ctrl_send.pending()) {
     Result fr = comm->ctrl_send.flush();
@@ -713,6 +768,7 @@ Result progress(Comm* comm) {
     }
     if (comm->rq.frontIndex(kReqActive) == before) break;  // no further progress possible now
   }
+  mark(comm, "progress:finish");
   // 4. transmitting -> finished, in order
   while (comm->rq.has(kReqTransmitting)) {
     Request* r = &comm->rq.front(kReqTransmitting);
@@ -735,6 +791,7 @@ Result progress(Comm* comm) {
         }
       } else {
         if (!r->unpack_launched) TCPXB_CHECK(launchUnpack(comm, r));
+        mark(comm, "finish:unpack eventQuery");
         Result q = gpu::eventQuery(r->unpack_event);
         if (q == kInProgress) break;
         TCPXB_CHECK(q);
@@ -782,8 +839,9 @@ Result waitConnected(Comm* comm) {
 // sockets' task rings hold, whether a control record is pending.
 void reportStall(Comm* comm, Request* r) {
   const uint64_t now = monotonicNanos();
-  const uint64_t every = (uint64_t)flags().timeout_threshold_ns;
-  if (now - r->posted_ns < every || now - r->last_stall_report_ns < every) return;
+  const uint64_t first = (uint64_t)flags().timeout_threshold_ns, again = (uint64_t)flags().timeout_frequency_ns;
+  if (now - r->posted_ns < first) return;
+  if (r->last_stall_report_ns != 0 && now - r->last_stall_report_ns < again) return;
   r->last_stall_report_ns = now;
   std::string socks;
   for (int i = 0; i < comm->num_socks; ++i) {
@@ -865,7 +923,11 @@ Result netGetProperties(int dev, NetProperties* p) {
   p->name = d->nif.name;
   p->pci_path = d->pci_path.empty() ? nullptr : d->pci_path.c_str();
   p->guid = (uint64_t)dev;
-  p->ptr_support = kPtrHost | (gpu::compiledWithCuda() ? kPtrCuda : 0);
+  // CUDA pointers are advertised in unpack mode (the consumer's kernel unpacks, the
+  // plugin makes no CUDA call on the data path) and, on request, in host mode,
+  // where the plugin itself queues copies and kernels from the caller's thread.
+  const bool cuda_ptrs = gpu::compiledWithCuda() && (flags().recv_mode == kRecvModeUnpack || flags().cuda_buffers != 0);
+  p->ptr_support = kPtrHost | (cuda_ptrs ? kPtrCuda : 0);
   p->speed_mbps = d->speed_mbps;
   p->port = 0;
   p->latency = 0;
@@ -879,6 +941,7 @@ Result netGetProperties(int dev, NetProperties* p) {
 
 Result startHelpers(Comm* comm) {
   if (comm->threads_started) return kSuccess;
+  watchdogRegister(comm);
   const Flags& f = flags();
   if (traceConfig().to_file && (traceConfig().task_level || traceConfig().request_level)) {
     comm->events = std::make_unique<EventLog>(10000, (size_t)f.log_line_limit);
@@ -894,7 +957,34 @@ Result startHelpers(Comm* comm) {
   return kSuccess;
 }
 
-Result netRegMr(Comm* /*comm*/, void* data, size_t size, int type, MemHandle** out) {
+// Everything the CUDA data path needs, created while no kernel depends on this
+// thread yet: stream, events of every request slot, staging or rx pool, and the
+// kernels themselves (see tcpxb_kernels_preload).  Later calls are no-ops.
+Result netPrepareCuda(Comm* comm, int gpu_dev) {
+  if (comm == nullptr || comm->cuda_prepared) return kSuccess;
+  if (gpu_dev < 0) gpu_dev = comm->gpu_dev;
+  if (gpu_dev < 0 && gpu::currentDevice(&gpu_dev) != kSuccess) return kUnhandledCudaError;
+  if (comm->passive) TCPXB_CHECK(ensureCudaRecv(comm, gpu_dev, comm->recv_mode == kRecvModeUnpack && comm->want_device_handle));
+  else { TCPXB_CHECK(ensureCudaComm(comm, gpu_dev)); TCPXB_CHECK(ensureTxStage(comm)); }
+  for (uint32_t i = 0; i < kMaxRequests; ++i) {
+    Request& r = comm->rq.slot(i);
+    if (comm->passive) {
+      if (r.unpack_event == nullptr) TCPXB_CHECK(gpu::eventCreate(&r.unpack_event));
+    } else {
+      for (auto& e : r.seg_event) if (e == nullptr) TCPXB_CHECK(gpu::eventCreate(&e));
+    }
+  }
+#ifndef TCPXB_NO_CUDA
+  if (comm->passive && tcpxb_kernels_preload() != 0) {
+    WARN("kernel preload failed: %s", tcpxb_kernel_last_error());
+    return kUnhandledCudaError;
+  }
+#endif
+  comm->cuda_prepared = true;
+  return kSuccess;
+}
+
+Result netRegMr(Comm* comm, void* data, size_t size, int type, MemHandle** out) {
   if (out == nullptr) return kInvalidArgument;
   if (type != kPtrHost && type != kPtrCuda) { WARN("memory type %d is not supported", type); return kInvalidArgument; }
   auto* mh = new MemHandle{data, size, type, -1};
@@ -906,6 +996,9 @@ Result netRegMr(Comm* /*comm*/, void* data, size_t size, int type, MemHandle** o
       delete mh;
       return kInvalidArgument;
     }
+    // registration happens during connection set-up, before any collective kernel
+    // can be waiting on this thread: the right moment for allocations and loading
+    if (comm != nullptr) TCPXB_CHECK(netPrepareCuda(comm, mh->gpu_dev));
   }
   *out = mh;
   return kSuccess;
@@ -924,8 +1017,9 @@ Result netIsend(Comm* comm, void* data, int size, int tag, MemHandle* mh, Reques
   TCPXB_CHECK(cr);
   const int err = comm->error.load();
   if (err != kSuccess) return (Result)err;
+  mark(comm, "isend:claim");
   Request* r = claimRequest(comm);
-  if (r == nullptr) return kSuccess;  // ring full: the caller retries
+  if (r == nullptr) { mark(comm, "idle"); return kSuccess; }  // ring full: the caller retries
   r->op = kSockSend;
   r->data = static_cast<uint8_t*>(data);
   r->size = size;
@@ -936,14 +1030,20 @@ Result netIsend(Comm* comm, void* data, int size, int tag, MemHandle* mh, Reques
   r->size_pending = size;
   r->size_known = true;
   if (r->mem_type == kPtrCuda) {
+    mark(comm, "isend:startCudaSend");
     Result sr = startCudaSend(comm, r, mh);
-    if (sr == kInProgress) return kSuccess;  // staging ring full: retry later
+    if (sr == kInProgress) { mark(comm, "idle"); return kSuccess; }  // staging ring full: retry later
     TCPXB_CHECK(sr);
   }
   traceReq(comm, r, kReqPosted);
   comm->rq.admit();
   *out = r;
-  return progress(comm);
+  if (comm->api_calls++ < 3)
+    INFO(kSubNet, "send comm %lx: isend #%u of %d bytes (%s memory)", (unsigned long)comm->id, comm->api_calls, size,
+         r->mem_type == kPtrCuda ? "cuda" : "host");
+  Result pr = progress(comm);
+  mark(comm, "idle");
+  return pr;
 }
 
 Result netIrecv(Comm* comm, int n, void** data, int* sizes, int* tags, MemHandle** mhs, Request** out) {
@@ -978,7 +1078,12 @@ Result netIrecv(Comm* comm, int n, void** data, int* sizes, int* tags, MemHandle
   traceReq(comm, r, kReqPosted);
   comm->rq.admit();
   *out = r;
-  return progress(comm);
+  if (comm->api_calls++ < 3)
+    INFO(kSubNet, "recv comm %lx: irecv #%u of up to %d bytes (%s memory)", (unsigned long)comm->id, comm->api_calls, sizes[0],
+         mem_type == kPtrCuda ? "cuda" : "host");
+  Result pr = progress(comm);
+  mark(comm, "idle");
+  return pr;
 }
 
 Result netIflush(Comm* /*comm*/, int /*n*/, void** /*data*/, int* /*sizes*/, MemHandle** /*mhs*/, Request** req) {
@@ -998,11 +1103,15 @@ Result netTest(Request* r, int* done, int* size) {
   const uint32_t nfin = comm->rq.count(kReqFinished);
   for (uint32_t k = 0; k < nfin; ++k)
     if (&comm->rq.at(kReqFinished, k) == r) { finished = true; break; }
+  mark(comm, "idle");
   if (!finished) {
     reportStall(comm, r);
     return kSuccess;
   }
   *done = 1;
+  if (comm->done_calls++ < 3)
+    INFO(kSubNet, "%s comm %lx: request #%u done, %d bytes", comm->passive ? "recv" : "send", (unsigned long)comm->id,
+         comm->done_calls, r->size);
   if (size != nullptr) *size = r->size;
   r->reported = true;
   retireRequests(comm);
@@ -1013,6 +1122,7 @@ Result netGetDeviceHandle(Comm* comm, void** dev_handle, size_t* size) {
   if (comm == nullptr || dev_handle == nullptr) return kInvalidArgument;
   int cur = comm->gpu_dev;
   if (cur < 0 && gpu::currentDevice(&cur) != kSuccess) return kUnhandledCudaError;
+  comm->want_device_handle = true;
   TCPXB_CHECK(ensureCudaRecv(comm, cur, /*want_device_handle=*/true));
   *dev_handle = comm->devq->deviceHandle();
   if (size != nullptr) *size = sizeof(UnpackDeviceHandle);
@@ -1068,6 +1178,7 @@ std::vector<std::string> netCommStatsLines(Comm* comm) {
 
 void freeComm(Comm* comm) {
   if (comm == nullptr) return;
+  watchdogForget(comm);
   comm->stop.store(true, std::memory_order_release);
   if (comm->threads_started) {
     for (int t = 0; t < comm->num_threads; ++t) {

@@ -420,6 +420,10 @@ int tcpxb_engine_connect(void* engine, const void* next_handles) {
     if (nowSec() > deadline) return fail("connection setup timed out%s", "");
     sched_yield();
   }
+  for (Rail& rail : e->rails) {
+    ENG_NET(netPrepareCuda(rail.send, e->cfg.gpu_dev));
+    ENG_NET(netPrepareCuda(rail.recv, e->cfg.gpu_dev));
+  }
   e->connected = true;
   return 0;
 }

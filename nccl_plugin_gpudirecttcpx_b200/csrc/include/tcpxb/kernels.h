@@ -119,6 +119,13 @@ int tcpxb_unpack_reduce_fanout_nvls(const void* pool, uint64_t pool_bytes, const
                                     uint32_t count, int dtype, uint32_t* status,
                                     const tcpxbUnpackOpts* opts, void* stream);
 
+// Loads every kernel of this library on the current device and applies their
+// launch attributes.  CUDA loads kernels lazily, and a first launch may have to
+// wait for running kernels to finish; a receive path that launches its first
+// unpack kernel while a collective kernel is spinning on that very data would
+// never return.  Call this at set-up time, before such kernels exist.
+int tcpxb_kernels_preload(void);
+
 // Waits (bounded) until flags[i] >= value for i in [0, n); on time-out writes
 // TCPXB_ST_TIMEOUT to status and returns.  Runs on the GPU that owns `flags`.
 int tcpxb_wait_flags(const uint32_t* flags, int n, uint32_t value, uint64_t wait_ns,

@@ -11,6 +11,16 @@
 // in poll() when every socket would block, test() writes the received size, CUDA
 // buffers are served by staging plus the emulated rx page pool, and nothing
 // sleeps during connection setup unless asked to.
+//
+// CUDA buffers and the caller's thread.  Under NCCL the data path runs on NCCL's
+// proxy thread while a collective kernel waits for it.  A CUDA call made there
+// (copy, launch, event) can block behind a synchronous call of the application,
+// e.g. a pageable device-to-host copy waiting for that very collective: both then
+// wait for each other.  So, as with the reference, the mode meant for NCCL is
+// "unpack": payload lands in the mapped page pool, NCCL's kernel copies it out,
+// and this library makes no CUDA call after set-up.  Host receive mode takes CUDA
+// pointers only when NCCL_GPUDIRECTTCPX_CUDA_BUFFERS=1 (the collective engine
+// uses it: there the caller's own thread drives everything).
 #ifndef TCPXB_TRANSPORT_H_
 #define TCPXB_TRANSPORT_H_
 
@@ -192,6 +202,11 @@ struct Comm {
   uint32_t* unpack_status_host = nullptr;
   uint32_t* unpack_status_dev = nullptr;
   gpu::Event send_dependency = nullptr;
+  bool cuda_prepared = false;
+  uint32_t api_calls = 0, done_calls = 0;  // for the first-calls INFO lines
+  std::atomic<const char*> where{"idle"};  // last checkpoint the API thread passed (watchdog)
+  std::atomic<uint64_t> where_ns{0};
+  bool want_device_handle = false;
   // telemetry
   std::unique_ptr<EventLog> events;
   std::unique_ptr<Exporter> exporter;
@@ -232,6 +247,8 @@ Result netConnect(int dev, void* handle, Comm** comm);
 Result netAccept(ListenComm* lcomm, Comm** comm);
 Result netRegMr(Comm* comm, void* data, size_t size, int type, MemHandle** mh);
 Result netDeregMr(Comm* comm, MemHandle* mh);
+// Creates every CUDA resource of the comm's data path ahead of time (see transport.cc).
+Result netPrepareCuda(Comm* comm, int gpu_dev);
 Result netIsend(Comm* comm, void* data, int size, int tag, MemHandle* mh, Request** req);
 Result netIrecv(Comm* comm, int n, void** data, int* sizes, int* tags, MemHandle** mhs, Request** req);
 Result netIflush(Comm* comm, int n, void** data, int* sizes, MemHandle** mhs, Request** req);

@@ -673,31 +673,58 @@ struct DeviceInfo {
 };
 DeviceInfo g_dev[kMaxDevices];
 
+// Applies the shared-memory attribute of one variant on `dev` (this also makes the
+// runtime load the kernel) and records that it is done.
+template <int RED, bool L2RED, int FAN>
+int prepareVariant(int dev) {
+  using C = Cfg<RED, L2RED, FAN>;
+  DeviceInfo& di = g_dev[dev];
+  if (di.attr_done[RED][L2RED][FAN]) return TCPXB_K_OK;
+  CUDA_TRY(cudaFuncSetAttribute(unpack_kernel<RED, L2RED, FAN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                C::kSmemBytes));
+  di.attr_done[RED][L2RED][FAN] = true;
+  return TCPXB_K_OK;
+}
+
+int deviceInfo(int* dev_out) {
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(TCPXB_K_INVALID, "device ordinal out of range");
+  if (g_dev[dev].sms == 0) {
+    int sms = 0;
+    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    g_dev[dev].sms = sms;
+  }
+  *dev_out = dev;
+  return TCPXB_K_OK;
+}
+
 template <int RED, bool L2RED, int FAN>
 int launch(const UnpackParams& p, int max_ctas, cudaStream_t stream) {
   using C = Cfg<RED, L2RED, FAN>;
   int dev = 0;
-  CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= kMaxDevices) return fail(TCPXB_K_INVALID, "device ordinal out of range");
-  DeviceInfo& di = g_dev[dev];
-  if (di.sms == 0) {
-    int sms = 0;
-    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    di.sms = sms;
-  }
-  if (!di.attr_done[RED][L2RED][FAN]) {
-    CUDA_TRY(cudaFuncSetAttribute(unpack_kernel<RED, L2RED, FAN>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-    di.attr_done[RED][L2RED][FAN] = true;
-  }
+  int rc = deviceInfo(&dev);
+  if (rc) return rc;
+  rc = prepareVariant<RED, L2RED, FAN>(dev);
+  if (rc) return rc;
   if (p.count == 0) return TCPXB_K_OK;
   int ctas = (int)((p.count + kWarps - 1) / kWarps);
-  int cap = di.sms;
+  int cap = g_dev[dev].sms;
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (ctas > cap) ctas = cap;
   unpack_kernel<RED, L2RED, FAN><<<ctas, kThreads, C::kSmemBytes, stream>>>(p);
   CUDA_TRY(cudaGetLastError());
   return TCPXB_K_OK;
+}
+
+template <int FAN>
+int prepareFan(int dev) {
+  int rc = prepareVariant<TCPXB_U8, false, FAN>(dev);
+  if (!rc) rc = prepareVariant<TCPXB_BF16, false, FAN>(dev);
+  if (!rc) rc = prepareVariant<TCPXB_BF16, true, FAN>(dev);
+  if (!rc) rc = prepareVariant<TCPXB_F32, false, FAN>(dev);
+  if (!rc) rc = prepareVariant<TCPXB_F32, true, FAN>(dev);
+  return rc;
 }
 
 template <int FAN>
@@ -761,6 +788,51 @@ int fill(UnpackParams& p, const void* pool, uint64_t pool_bytes, const void* acc
 extern "C" {
 
 const char* tcpxb_kernel_last_error(void) { return g_err; }
+
+int tcpxb_kernels_preload(void) {
+  static std::mutex mu;
+  static bool done[kMaxDevices] = {};
+  std::lock_guard<std::mutex> l(mu);
+  int dev = 0;
+  int rc = deviceInfo(&dev);
+  if (rc) return rc;
+  if (done[dev]) return TCPXB_K_OK;
+  rc = prepareFan<FAN_NONE>(dev);
+  if (!rc) rc = prepareFan<FAN_PEER>(dev);
+  if (!rc) rc = prepareFan<FAN_NVLS>(dev);
+  if (rc) return rc;
+  // Setting an attribute does not make the runtime load a kernel; an empty launch
+  // does.  Every kernel runs once with nothing to do, on a private stream.
+  cudaStream_t s = nullptr;
+  CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  UnpackParams p;
+  memset(&p, 0, sizeof p);
+#define TCPXB_DRY(RED, L2, FAN) \
+  unpack_kernel<RED, L2, FAN><<<1, kThreads, Cfg<RED, L2, FAN>::kSmemBytes, s>>>(p)
+#define TCPXB_DRY_FAN(FAN)                                                      \
+  TCPXB_DRY(TCPXB_U8, false, FAN); TCPXB_DRY(TCPXB_BF16, false, FAN); TCPXB_DRY(TCPXB_BF16, true, FAN); \
+  TCPXB_DRY(TCPXB_F32, false, FAN); TCPXB_DRY(TCPXB_F32, true, FAN)
+  TCPXB_DRY_FAN(FAN_NONE);
+  TCPXB_DRY_FAN(FAN_PEER);
+  TCPXB_DRY_FAN(FAN_NVLS);
+#undef TCPXB_DRY_FAN
+#undef TCPXB_DRY
+  wait_flags_kernel<<<1, 32, 0, s>>>(nullptr, 0, 0, 1, nullptr);
+  SignalParams sp;
+  memset(&sp, 0, sizeof sp);
+  signal_flags_kernel<<<1, 32, 0, s>>>(sp);
+  PeerReduceParams pp;
+  memset(&pp, 0, sizeof pp);
+  peer_reduce_kernel<TCPXB_BF16><<<1, 256, 0, s>>>(pp);
+  peer_reduce_kernel<TCPXB_F32><<<1, 256, 0, s>>>(pp);
+  cudaFuncAttributes a;
+  CUDA_TRY(cudaFuncGetAttributes(&a, checksum_kernel));
+  CUDA_TRY(cudaGetLastError());
+  CUDA_TRY(cudaStreamSynchronize(s));
+  CUDA_TRY(cudaStreamDestroy(s));
+  done[dev] = true;
+  return TCPXB_K_OK;
+}
 
 int tcpxb_unpack_copy(const void* pool, uint64_t pool_bytes, void* dst, uint64_t dst_bytes,
                       const tcpxbLoadMeta* descs, uint32_t count, uint32_t* status,

@@ -74,6 +74,7 @@ def default_transport_env(nics: int = 4, nthreads: int = 4, nsocks_per_thread: i
         "NCCL_NSOCKS_PERTHREAD": str(nsocks_per_thread),
         "NCCL_DYNAMIC_CHUNK_SIZE": str(chunk_bytes),
         "NCCL_GPUDIRECTTCPX_RX_POOL_BYTES": str(pool_mb << 20),
+        "NCCL_GPUDIRECTTCPX_CUDA_BUFFERS": "1",
     }.items():
         os.environ.setdefault(k, v)
 

@@ -20,7 +20,7 @@ from ..utils import native
 
 def plugin_env(nics: int = 4, nsocks_per_thread: int = 1, nthreads: int = 4, chunk_bytes: int = 512 * 1024,
                recv_mode: str = "host", rx_pool_mode: str = "host", rx_pool_mb: int = 1024,
-               gdr: bool = True, builtin_socket: bool = False, speed_mbps: int = 200000,
+               gdr: bool = False, builtin_socket: bool = False, speed_mbps: int = 200000,
                debug: Optional[str] = None, extra: Optional[Dict[str, str]] = None) -> Dict[str, str]:
     env = {
         # every GPU is its own "node": nothing but the net transport is left
@@ -49,8 +49,17 @@ def plugin_env(nics: int = 4, nsocks_per_thread: int = 1, nthreads: int = 4, chu
             "NCCL_GPUDIRECTTCPX_RX_POOL_BYTES": str(rx_pool_mb << 20),
             "NCCL_GPUDIRECTTCPX_NIC_SPEED_MBPS": str(speed_mbps),
         })
-        if gdr:
-            # hand CUDA pointers to the plugin although the "NIC" hangs off the CPU
+        if recv_mode == "unpack":
+            # NCCL's kernels unpack from the rx page pool: receive buffers are CUDA
+            # pointers (GDR level SYS because the "NIC" hangs off the CPU), sends stay
+            # in host memory, and only the Simple protocol knows the unpack path.
+            env["NCCL_NET_GDR_LEVEL"] = "SYS"
+            env["NCCL_NET_GDR_READ"] = "0"
+            env["NCCL_PROTO"] = "Simple"
+        elif gdr:
+            # plugin-side copies and kernels: only safe when no application thread
+            # blocks in a synchronous CUDA call while a collective is in flight
+            env["NCCL_GPUDIRECTTCPX_CUDA_BUFFERS"] = "1"
             env["NCCL_NET_GDR_LEVEL"] = "SYS"
             env["NCCL_NET_GDR_READ"] = "1"
     if debug:

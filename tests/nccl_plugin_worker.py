@@ -17,6 +17,8 @@ import torch.distributed as dist
 
 
 def main():
+    import faulthandler
+    faulthandler.dump_traceback_later(int(os.environ.get("TCPXB_TEST_DUMP_AFTER", "60")), exit=False)
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -24,6 +26,18 @@ def main():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = torch.device("cuda", local)
     sizes = [int(s) for s in os.environ.get("TCPXB_TEST_SIZES", "256,65536,4194304").split(",")]
+    rep = int(os.environ.get("TCPXB_TEST_REPEAT_SMALL", "0"))
+    if rep:
+        n = int(os.environ.get("TCPXB_TEST_REPEAT_ELEMS", "256"))
+        pattern = ""
+        for it in range(rep):
+            ins = [torch.randn(n, generator=torch.Generator().manual_seed(77 * it + r)).to(torch.float32) for r in range(world)]
+            x = ins[rank].to(dev)
+            dist.all_reduce(x)
+            torch.cuda.synchronize()
+            want = torch.stack(ins).sum(0)
+            pattern += "." if (x.cpu() - want).abs().max().item() < 1e-3 else "X"
+        print(f"rank {rank} repeat pattern: {pattern}", flush=True)
     ok = True
     detail = []
     for dtype in (torch.bfloat16, torch.float32):
