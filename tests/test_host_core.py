@@ -122,3 +122,11 @@ def test_loopback_under_sanitizer(san):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
     assert "loopback PASSED" in r.stdout
     assert "WARNING: ThreadSanitizer" not in r.stderr and "ERROR: AddressSanitizer" not in r.stderr
+
+
+def test_fault_paths_surface_as_errors(host_lib):
+    """Closed peer, socket shutdown in mid-message, forged control records, oversize message,
+    full request ring, silent sender: error codes or retries, never a hang."""
+    r = subprocess.run([str(LIB / "tcpxb_fault_tests")], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "8 test(s), 0 failure(s)" in r.stdout
