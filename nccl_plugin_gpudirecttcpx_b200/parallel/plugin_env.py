@@ -56,6 +56,8 @@ def plugin_env(nics: int = 4, nsocks_per_thread: int = 1, nthreads: int = 4, chu
             env["NCCL_NET_GDR_LEVEL"] = "SYS"
             env["NCCL_NET_GDR_READ"] = "0"
             env["NCCL_PROTO"] = "Simple"
+            # the unpack hook exists in the ring primitives; tree/PAT paths never call it
+            env["NCCL_ALGO"] = "Ring"
         elif gdr:
             # plugin-side copies and kernels: only safe when no application thread
             # blocks in a synchronous CUDA call while a collective is in flight
