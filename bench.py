@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--request-kb", type=int, default=4096)
     ap.add_argument("--unpack-ctas", type=int, default=16)
     ap.add_argument("--no-microbench", action="store_true")
+    ap.add_argument("--microbench-only", action="store_true", help="run only the unpack-kernel microbench (1 GPU)")
+    ap.add_argument("--micro-iters", type=int, default=20)
+    ap.add_argument("--micro-warm", type=int, default=4)
     return ap.parse_args()
 
 
@@ -59,7 +62,7 @@ def reference_arm():
     return 0
 
 
-def unpack_microbench(torch, peaks):
+def unpack_microbench(torch, peaks, iters=20, warm=4):
     """Config-2 microbench: 64 MiB assembled from 4096-byte fragments at permuted pool
     offsets; plain copy and fused bf16 sum; fraction of the measured copy bandwidth."""
     from nccl_plugin_gpudirecttcpx_b200.ops import unpack as U
@@ -72,7 +75,7 @@ def unpack_microbench(torch, peaks):
     dsts = [torch.randn((64 << 20) // 2, device=dev).to(torch.bfloat16) for _ in range(3)]
     st = U.status_buffer()
 
-    def timed(fn, iters=20, warm=4):
+    def timed(fn):
         for i in range(warm):
             fn(i)
         torch.cuda.synchronize()
@@ -118,6 +121,13 @@ def main():
         raise SystemExit("launch with torch.distributed.run for --gpus > 1")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    if args.microbench_only:
+        try:
+            peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        except Exception:
+            peaks = {}
+        print(json.dumps({"unpack_microbench": unpack_microbench(torch, peaks, args.micro_iters, args.micro_warm)}))
+        return 0
 
     from nccl_plugin_gpudirecttcpx_b200.parallel.engine import HierarchicalEngine, default_transport_env
     from nccl_plugin_gpudirecttcpx_b200.utils.clocks import ClockSampler
@@ -222,7 +232,7 @@ def main():
 
     micro = None
     if rank == 0 and not args.no_microbench:
-        micro = unpack_microbench(torch, peaks)
+        micro = unpack_microbench(torch, peaks, args.micro_iters, args.micro_warm)
 
     if rank == 0:
         agg = world * nbytes / (ms * 1e-3) / 1e9

@@ -1,6 +1,8 @@
 #include "tcpxb/flags.h"
 
 #include <limits.h>
+
+#include <atomic>
 #include <mutex>
 #include <stdlib.h>
 #include <strings.h>
@@ -169,23 +171,31 @@ void loadFlags(Flags* out) {
 }
 
 namespace {
+// Readers are on every hot path (helper threads, progress engine), so they take no
+// lock: the current set is published through one atomic pointer.  A reload builds
+// a fresh set and swaps it in; the old one is left alive for readers still using it.
 std::mutex g_mu;
-Flags* g_flags = nullptr;
+std::atomic<Flags*> g_flags{nullptr};
 }  // namespace
 
 const Flags& flags() {
+  Flags* f = g_flags.load(std::memory_order_acquire);
+  if (f != nullptr) return *f;
   std::lock_guard<std::mutex> l(g_mu);
-  if (g_flags == nullptr) {
-    g_flags = new Flags();
-    loadFlags(g_flags);
+  f = g_flags.load(std::memory_order_acquire);
+  if (f == nullptr) {
+    f = new Flags();
+    loadFlags(f);
+    g_flags.store(f, std::memory_order_release);
   }
-  return *g_flags;
+  return *f;
 }
 
 void reloadFlags() {
   std::lock_guard<std::mutex> l(g_mu);
-  if (g_flags == nullptr) g_flags = new Flags();
-  loadFlags(g_flags);
+  Flags* f = new Flags();
+  loadFlags(f);
+  g_flags.store(f, std::memory_order_release);
 }
 
 const std::vector<FlagDoc>& flagDocs() {
