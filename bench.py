@@ -40,9 +40,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "plain", "nccl-socket", "nccl-plugin"])
     ap.add_argument("--size-mb", type=int, default=256, help="all_reduce bytes per GPU (MiB)")
     ap.add_argument("--nics", type=int, default=4)
-    ap.add_argument("--nthreads", type=int, default=4)
+    ap.add_argument("--nthreads", type=int, default=2)
     ap.add_argument("--nsocks-per-thread", type=int, default=1)
-    ap.add_argument("--chunk-kb", type=int, default=512)
+    ap.add_argument("--chunk-kb", type=int, default=128)
     ap.add_argument("--request-kb", type=int, default=4096)
     ap.add_argument("--unpack-ctas", type=int, default=16)
     ap.add_argument("--no-microbench", action="store_true")

@@ -157,7 +157,10 @@ RxBufMgr* rxBufMgrFor(int dev) {
   if (it != g_mgrs.end()) return it->second.get();
   const Flags& f = flags();
   const bool device_resident = dev >= 0 && f.rx_pool_mode == kRxPoolDevice && gpu::available();
-  auto m = std::make_unique<EmulatedRxBufMgr>(dev, (uint64_t)f.rx_pool_bytes, f.rx_pool_scatter != 0, device_resident);
+  // a device-resident pool is filled by the copy engine one page run at a time, so
+  // its allocator keeps runs contiguous whatever the scatter flag says
+  auto m = std::make_unique<EmulatedRxBufMgr>(dev, (uint64_t)f.rx_pool_bytes, f.rx_pool_scatter != 0 && !device_resident,
+                                              device_resident);
   if (m->init() != kSuccess) return nullptr;
   RxBufMgr* raw = m.get();
   g_mgrs[dev] = std::move(m);

@@ -420,8 +420,11 @@ Result startCudaSend(Comm* comm, Request* r, MemHandle* mh) {
   if (dbg) INFO(kSubNet, "send comm %lx: resources ready", (unsigned long)comm->id);
   if (r->size == 0) return kSuccess;
   if (!stageAlloc(comm, (uint64_t)r->size, &r->stage, &r->stage_bytes)) return kInProgress;
+  // One staging copy per ~2 MiB: enough to let the first chunks leave while the
+  // rest is still being copied, few enough that the per-copy launch cost stays small.
   const int chunk = (int)flags().dynamic_chunk_size;
-  int seg = (r->size + kMaxTxSegments - 1) / kMaxTxSegments;
+  int n_want = std::max(1, std::min(kMaxTxSegments, r->size / (2 << 20)));
+  int seg = (r->size + n_want - 1) / n_want;
   seg = (seg + chunk - 1) / chunk * chunk;
   if (comm->send_dependency != nullptr) {
     TCPXB_CHECK(gpu::streamWaitEvent(comm->stream, comm->send_dependency));

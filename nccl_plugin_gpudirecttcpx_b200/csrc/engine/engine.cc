@@ -1,7 +1,9 @@
 // Hierarchical collective engine; see tcpxb/engine.h for the algorithms.
 #include "tcpxb/engine.h"
 
+#include <sched.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include <time.h>
 
@@ -93,6 +95,7 @@ struct Engine {
   gpu::Event dep_event = nullptr;
   tcpxbEngineStats stats;
   int req_bytes = 4 << 20, inflight = 8, ctas = 16;
+  bool yield_when_idle = false;
 };
 
 int ensureScratch(Engine* e, uint64_t bytes) {
@@ -276,7 +279,12 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
         moved = true;
       }
     }
-    if (!moved) sched_yield();
+    if (!moved) {
+      // a short pause, not a yield: giving up the time slice here lets the request
+      // pipeline run dry while helper threads keep the core
+      if (e->yield_when_idle) sched_yield();
+      else for (int i = 0; i < 64; ++i) __builtin_ia32_pause();
+    }
   }
   // pool pages go back once the kernels that read them have finished
   for (int r = 0; r < R; ++r) {
@@ -350,6 +358,7 @@ void* tcpxb_engine_create(const tcpxbEngineConfig* cfg) {
   if (cfg->max_inflight > 0) e->inflight = std::min(cfg->max_inflight, 12);
   if (cfg->unpack_ctas > 0) e->ctas = cfg->unpack_ctas;
   memset(&e->stats, 0, sizeof e->stats);
+  e->yield_when_idle = getenv("TCPXB_ENGINE_YIELD") != nullptr;
   int ndev = 0;
   netDevices(&ndev);
   e->rails.resize((size_t)std::min(ndev, TCPXB_ENGINE_MAX_RAILS));

@@ -64,6 +64,7 @@ def main():
     ok = ok and status[0] == 0
     bad = [d for d in detail if not d[-1]]
     print(json.dumps({"rank": rank, "world": world, "G": G, "ok": bool(ok), "checks": len(detail), "bad": bad[:6],
+                      "nvls": bool(getattr(eng, "nvls", False)),
                       "device_status": status}), flush=True)
     eng.close()
     dist.barrier()
