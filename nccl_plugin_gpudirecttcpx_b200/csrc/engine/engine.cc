@@ -11,6 +11,8 @@
 #include <deque>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "tcpxb/kernels.h"
 #include "tcpxb/transport.h"
 
@@ -46,6 +48,12 @@ double nowSec() {
   clock_gettime(CLOCK_MONOTONIC, &ts);
   return ts.tv_sec + ts.tv_nsec * 1e-9;
 }
+
+// NVTX range for the lifetime of a scope; costs nothing unless a tool is attached.
+struct Range {
+  explicit Range(const char* name) { nvtxRangePushA(name); }
+  ~Range() { nvtxRangePop(); }
+};
 
 struct Rail {
   ListenComm* listen = nullptr;
@@ -192,6 +200,7 @@ int launchUnpack(Engine* e, Request* req, const RecvSpec& rs, uint64_t region_of
 // req_bytes striped over the rails.  Request k of a direction uses rail k % rails
 // on both ends, so the two sides agree without talking about it.
 int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
+  Range range("tcpxb exchange");
   const int R = (int)e->rails.size();
   const uint64_t rb = (uint64_t)e->req_bytes;
   const uint64_t n_send = (ss.bytes + rb - 1) / rb, n_recv = (rs.bytes + rb - 1) / rb;
@@ -454,6 +463,7 @@ int tcpxb_engine_set_peers(void* engine, void* const* work_ptrs, void* const* ou
 }
 
 int tcpxb_engine_all_reduce(void* engine, const void* in_, void* out_, uint64_t bytes, int dtype, void* stream) {
+  Range range("tcpxb all_reduce");
   Engine* e = static_cast<Engine*>(engine);
   ENG_TRY(checkReady(e));
   if (dtype != TCPXB_BF16 && dtype != TCPXB_F32) return fail("all_reduce needs bf16 or f32%s", "");
@@ -526,6 +536,7 @@ int tcpxb_engine_all_reduce(void* engine, const void* in_, void* out_, uint64_t 
 }
 
 int tcpxb_engine_all_gather(void* engine, const void* in_, void* out_, uint64_t B, void* stream) {
+  Range range("tcpxb all_gather");
   Engine* e = static_cast<Engine*>(engine);
   ENG_TRY(checkReady(e));
   if (B == 0 || B % 16 != 0) return fail("all_gather block must be a multiple of 16 bytes%s", "");
@@ -557,6 +568,7 @@ int tcpxb_engine_all_gather(void* engine, const void* in_, void* out_, uint64_t 
 }
 
 int tcpxb_engine_reduce_scatter(void* engine, const void* in_, void* out_, uint64_t B, int dtype, void* stream) {
+  Range range("tcpxb reduce_scatter");
   Engine* e = static_cast<Engine*>(engine);
   ENG_TRY(checkReady(e));
   if (dtype != TCPXB_BF16 && dtype != TCPXB_F32) return fail("reduce_scatter needs bf16 or f32%s", "");

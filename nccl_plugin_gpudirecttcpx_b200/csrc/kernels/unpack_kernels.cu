@@ -37,7 +37,16 @@
 
 namespace {
 
-constexpr int kWarps = 8;
+#ifndef TCPXB_WARPS
+#define TCPXB_WARPS 8
+#endif
+#ifndef TCPXB_DEPTH_COPY
+#define TCPXB_DEPTH_COPY 6
+#endif
+#ifndef TCPXB_DEPTH_REDUCE
+#define TCPXB_DEPTH_REDUCE 3
+#endif
+constexpr int kWarps = TCPXB_WARPS;
 constexpr int kThreads = kWarps * 32;
 constexpr int kSlot = TCPXB_FRAG_BYTES;
 constexpr uint64_t kDefaultWaitNs = 2000000000ull;
@@ -317,7 +326,8 @@ template <int RED, bool L2RED, int FAN>
 struct Cfg {
   static constexpr bool kAccSlot = (RED != TCPXB_U8) && !L2RED;
   static constexpr int kStride = kAccSlot ? 2 * kSlot : kSlot;
-  static constexpr int kDepth = kAccSlot ? 3 : 6;
+  static constexpr int kDepth = kAccSlot ? TCPXB_DEPTH_REDUCE : TCPXB_DEPTH_COPY;
+  static_assert(kWarps * kDepth * kStride + kWarps * kDepth * 40 <= 227 * 1024, "slot rings must fit one CTA's shared memory");
   static constexpr int kDataBytes = kWarps * kDepth * kStride;
   static constexpr int kSmemBytes = kDataBytes + kWarps * kDepth * (8 + (int)sizeof(SlotInfo));
 };

@@ -169,6 +169,15 @@ def unpack_copy(pool: torch.Tensor, dst: torch.Tensor, descs: torch.Tensor,
                                   dptr, n, _ptr(status), oref, _stream()))
 
 
+def pack(src: torch.Tensor, staging: torch.Tensor, descs: torch.Tensor,
+         status: Optional[torch.Tensor] = None, **opts) -> None:
+    """K4, send-side gather: staging[dst_off : dst_off+len] = src[src_off : src_off+len] per
+    record, e.g. from a strided or paged send buffer into one pinned, device-mapped staging
+    area the sockets read from.  It is the unpack kernel with the roles of pool and
+    destination swapped; contiguous sends use the copy engine instead."""
+    unpack_copy(src, staging, descs, status=status, **opts)
+
+
 def unpack_reduce(pool: torch.Tensor, acc: torch.Tensor, descs: torch.Tensor,
                   out: Optional[torch.Tensor] = None, impl: int = REDUCE_SM,
                   status: Optional[torch.Tensor] = None, **opts) -> None:

@@ -243,3 +243,28 @@ def test_peer_reduce(dtype):
     torch.cuda.synchronize()
     want = sum(s[2 * shard:3 * shard].float() for s in srcs).to(dtype)
     assert torch.equal(out.cpu(), want)
+
+
+def test_pack_gathers_into_pinned_staging():
+    """Send-side gather into pinned, device-mapped host memory (what the sockets would read)."""
+    src = _pool(1 << 20, 21).to(DEV)
+    staging = torch.zeros(64 * 1024, dtype=torch.uint8).pin_memory()
+    n = 16
+    rng = np.random.default_rng(5)
+    src_off = rng.permutation((1 << 20) // 4096)[:n].astype(np.uint64) * 4096
+    descs = U.make_descriptors(src_off, np.full(n, 4096), np.arange(n, dtype=np.uint64) * 4096)
+    st = U.status_buffer()
+    # the staging tensor lives in pinned host memory; the kernel gets its (unified) address
+    lib = U._k()
+    rc = lib.tcpxb_unpack_copy(src.data_ptr(), src.numel(), staging.data_ptr(), staging.numel(),
+                               U.descriptors_to_device(descs).data_ptr(), n, st.data_ptr(), None,
+                               torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    want = U.reference_unpack(src.cpu(), torch.zeros(64 * 1024, dtype=torch.uint8), descs)
+    assert torch.equal(staging, want) and st.tolist()[0] == U.ST_OK
+    # and through the Python wrapper on device buffers
+    dst = torch.zeros(64 * 1024, dtype=torch.uint8, device=DEV)
+    ops.pack(src, dst, U.descriptors_to_device(descs))
+    torch.cuda.synchronize()
+    assert torch.equal(dst.cpu(), want)
