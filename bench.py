@@ -55,6 +55,8 @@ def parse_args():
 def reference_arm():
     reason = ("reference is a CMake C++ library, not a pip-installable package, and needs protobuf, abseil, GTest, "
               "an NCCL source tree, the devmem-TCP kernel API and the RxDM daemon; none exist on this box")
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0  # one line per job, also when launched as N ranks
     marker = ROOT / "baseline" / "reference_install.log"
     if marker.exists():
         reason += f" (install attempt recorded in baseline/{marker.name})"
@@ -75,6 +77,11 @@ def unpack_microbench(torch, peaks, iters=20, warm=4):
     dsts = [torch.randn((64 << 20) // 2, device=dev).to(torch.bfloat16) for _ in range(3)]
     st = U.status_buffer()
 
+    # bring clocks and caches to their loaded state before the first measurement
+    for i in range(40):
+        U.unpack_copy(pool, dsts[i % 3], descs[i % variants], status=st)
+    torch.cuda.synchronize()
+
     def timed(fn):
         for i in range(warm):
             fn(i)
@@ -86,10 +93,19 @@ def unpack_microbench(torch, peaks, iters=20, warm=4):
             ev[i][1].record()
         torch.cuda.synchronize()
         ts = sorted(a.elapsed_time(b) for a, b in ev)
-        return ts[len(ts) // 2] * 1e-3
+        # and the same launches back to back inside one bracket (no event between them)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(iters):
+            fn(i)
+        b.record()
+        torch.cuda.synchronize()
+        return ts[len(ts) // 2] * 1e-3, a.elapsed_time(b) / iters * 1e-3
 
-    t_copy = timed(lambda i: U.unpack_copy(pool, dsts[i % 3], descs[i % variants], status=st))
-    t_red = timed(lambda i: U.unpack_reduce(pool, dsts[i % 3], descs[i % variants], status=st))
+    t_copy, tb_copy = timed(lambda i: U.unpack_copy(pool, dsts[i % 3], descs[i % variants], status=st))
+    t_red, tb_red = timed(lambda i: U.unpack_reduce(pool, dsts[i % 3], descs[i % variants], status=st))
+    flat = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    t_ref, tb_ref = timed(lambda i: dsts[i % 3].view(torch.uint8).copy_(flat))
     hbm = peaks.get("hbm_gbs", 6650.0)
     tag = "of measured" if "hbm_gbs" in peaks else "of fallback"
     out = {
@@ -97,9 +113,13 @@ def unpack_microbench(torch, peaks, iters=20, warm=4):
         "unpack_copy_frac_hbm": 2 * total / t_copy / 1e9 / hbm,
         "unpack_reduce_us": t_red * 1e6, "unpack_reduce_GBps": 3 * total / t_red / 1e9,
         "unpack_reduce_frac_hbm": 3 * total / t_red / 1e9 / hbm, "roofline": tag,
+        "back_to_back": {"unpack_copy_us": tb_copy * 1e6, "unpack_copy_frac_hbm": 2 * total / tb_copy / 1e9 / hbm,
+                         "unpack_reduce_us": tb_red * 1e6, "unpack_reduce_frac_hbm": 3 * total / tb_red / 1e9 / hbm,
+                         "torch_copy_64MiB_us": tb_ref * 1e6, "torch_copy_64MiB_frac_hbm": 2 * (64 << 20) / tb_ref / 1e9 / hbm},
+        "torch_copy_64MiB_us": t_ref * 1e6,
         "status": st.tolist()[0],
     }
-    del pool, descs, dsts
+    del pool, descs, dsts, flat
     torch.cuda.empty_cache()
     return out
 
@@ -251,6 +271,9 @@ def main():
                               "chunk_kb": args.chunk_kb, "request_kb": args.request_kb, "unpack_ctas": args.unpack_ctas},
                 "busbw_GBps": busbw, "net_bytes_per_gpu_per_step": (s1.bytes_received - b0) // max(args.steps, 1),
                 "fragments_per_step": (s1.fragments - f0) // max(args.steps, 1), "max_abs_err": err,
+                "driver_thread_ms_per_step": {k: round((getattr(s1, k) - getattr(s0, k)) * 1e3 / max(args.steps, 1), 3)
+                                              for k in ("t_post_recv", "t_post_send", "t_test_recv", "t_launch",
+                                                        "t_consume", "t_test_send", "t_idle")},
             },
             "e2e": {"value": agg_e2e, "unit": "GB/s", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": 8,
                     "ms_per_step": ms_e2e, "checksum": last_sum},

@@ -216,6 +216,8 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
   MemHandle send_mh{const_cast<uint8_t*>(ss.src), ss.bytes, kPtrCuda, e->cfg.gpu_dev};
   MemHandle recv_mh{rs.dst, rs.bytes, kPtrCuda, e->cfg.gpu_dev};
   const double t0 = nowSec();
+  double tp = t0;
+  auto lap = [&tp](double& acc) { const double n = nowSec(); acc += n - tp; tp = n; };
   while (done_s < n_send || launched_r < n_recv) {
     bool moved = false;
     // post receives (they claim pool pages as control records arrive)
@@ -234,6 +236,7 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
       ++post_r;
       moved = true;
     }
+    lap(e->stats.t_post_recv);
     while (post_s < n_send) {
       const int r = (int)(post_s % R);
       if ((int)sq[r].size() >= e->inflight) break;
@@ -246,6 +249,7 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
       ++post_s;
       moved = true;
     }
+    lap(e->stats.t_post_send);
     for (int r = 0; r < R; ++r) {
       while (!rq[r].empty()) {
         int done = 0, sz = 0;
@@ -258,6 +262,7 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
         // Whichever request is launched last runs last on the stream, so it is the
         // one that publishes completion.
         const bool publish = rs.last && (launched_r + 1 == n_recv);
+        lap(e->stats.t_test_recv);
         ENG_TRY(launchUnpack(e, rq[r].front(), rs, off, want, publish, stream));
         gpu::Event ev = takeEvent(e);
         ENG_NET(gpu::eventRecord(ev, stream));
@@ -268,7 +273,9 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
         ++e->stats.requests;
         e->stats.bytes_received += want;
         moved = true;
+        lap(e->stats.t_launch);
       }
+      lap(e->stats.t_test_recv);
       while (!uq[r].empty()) {
         Result q = gpu::eventQuery(uq[r].front().event);
         if (q == kInProgress) break;
@@ -278,6 +285,7 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
         uq[r].pop_front();
         moved = true;
       }
+      lap(e->stats.t_consume);
       while (!sq[r].empty()) {
         int done = 0, sz = 0;
         ENG_NET(netTest(sq[r].front(), &done, &sz));
@@ -287,12 +295,14 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
         ++done_s;
         moved = true;
       }
+      lap(e->stats.t_test_send);
     }
     if (!moved) {
       // a short pause, not a yield: giving up the time slice here lets the request
       // pipeline run dry while helper threads keep the core
       if (e->yield_when_idle) sched_yield();
       else for (int i = 0; i < 64; ++i) __builtin_ia32_pause();
+      lap(e->stats.t_idle);
     }
   }
   // pool pages go back once the kernels that read them have finished

@@ -51,7 +51,11 @@ typedef struct tcpxbEngineStats {
   uint64_t bytes_sent, bytes_received;   // over the network, this rank
   uint64_t requests, unpack_launches, fragments;
   uint64_t kernel_launches;              // every kernel of this library the engine queued
-  double seconds_net_wait;               // host time spent polling the transport
+  double seconds_net_wait;               // host time spent inside exchanges
+  // where the driving thread spends that time (seconds): posting receives, posting
+  // sends (staging copies included), testing receives, launching unpack kernels,
+  // returning pages, testing sends, and idle spinning
+  double t_post_recv, t_post_send, t_test_recv, t_launch, t_consume, t_test_send, t_idle;
 } tcpxbEngineStats;
 
 // Creates the engine and initialises the transport (flags are read from the

@@ -34,7 +34,9 @@ class EngineStats(ctypes.Structure):
     _fields_ = [("bytes_sent", ctypes.c_uint64), ("bytes_received", ctypes.c_uint64),
                 ("requests", ctypes.c_uint64), ("unpack_launches", ctypes.c_uint64),
                 ("fragments", ctypes.c_uint64), ("kernel_launches", ctypes.c_uint64),
-                ("seconds_net_wait", ctypes.c_double)]
+                ("seconds_net_wait", ctypes.c_double)] + [
+                    (n, ctypes.c_double) for n in ("t_post_recv", "t_post_send", "t_test_recv", "t_launch",
+                                                   "t_consume", "t_test_send", "t_idle")]
 
 
 _lib = None
