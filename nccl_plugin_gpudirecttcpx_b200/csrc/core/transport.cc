@@ -412,12 +412,8 @@ bool stageAlloc(Comm* comm, uint64_t bytes, uint8_t** out, uint64_t* charged) {
 }
 
 Result startCudaSend(Comm* comm, Request* r, MemHandle* mh) {
-  const bool dbg = getenv("TCPXB_DEBUG_CUDA_SEND") != nullptr && comm->api_calls < 4;
-  if (dbg) INFO(kSubNet, "send comm %lx: cuda send enter (prepared %d stream %p stage %p)", (unsigned long)comm->id,
-                (int)comm->cuda_prepared, comm->stream, (void*)comm->tx_stage);
   TCPXB_CHECK(ensureCudaComm(comm, mh != nullptr && mh->gpu_dev >= 0 ? mh->gpu_dev : comm->gpu_dev));
   TCPXB_CHECK(ensureTxStage(comm));
-  if (dbg) INFO(kSubNet, "send comm %lx: resources ready", (unsigned long)comm->id);
   if (r->size == 0) return kSuccess;
   if (!stageAlloc(comm, (uint64_t)r->size, &r->stage, &r->stage_bytes)) return kInProgress;
   // One staging copy per ~2 MiB: enough to let the first chunks leave while the
@@ -436,12 +432,9 @@ Result startCudaSend(Comm* comm, Request* r, MemHandle* mh) {
   for (int i = 0; i < r->n_segs; ++i) {
     const int off = i * seg;
     const int len = std::min(seg, r->size - off);
-    if (dbg) INFO(kSubNet, "send comm %lx: memcpy %d bytes from %p", (unsigned long)comm->id, len, (void*)(r->data + off));
     TCPXB_CHECK(gpu::copyToHostAsync(r->stage + off, r->data + off, (size_t)len, comm->stream));
-    if (dbg) INFO(kSubNet, "send comm %lx: memcpy queued", (unsigned long)comm->id);
     if (r->seg_event[i] == nullptr) TCPXB_CHECK(gpu::eventCreate(&r->seg_event[i]));
     TCPXB_CHECK(gpu::eventRecord(r->seg_event[i], comm->stream));
-    if (dbg) INFO(kSubNet, "send comm %lx: event recorded", (unsigned long)comm->id);
   }
   return kSuccess;
 }
@@ -1042,7 +1035,7 @@ Result netIsend(Comm* comm, void* data, int size, int tag, MemHandle* mh, Reques
   comm->rq.admit();
   *out = r;
   if (comm->api_calls++ < 3)
-    INFO(kSubNet, "send comm %lx: isend #%u of %d bytes (%s memory)", (unsigned long)comm->id, comm->api_calls, size,
+    TRACE(kSubNet, "send comm %lx: isend #%u of %d bytes (%s memory)", (unsigned long)comm->id, comm->api_calls, size,
          r->mem_type == kPtrCuda ? "cuda" : "host");
   Result pr = progress(comm);
   mark(comm, "idle");
@@ -1082,7 +1075,7 @@ Result netIrecv(Comm* comm, int n, void** data, int* sizes, int* tags, MemHandle
   comm->rq.admit();
   *out = r;
   if (comm->api_calls++ < 3)
-    INFO(kSubNet, "recv comm %lx: irecv #%u of up to %d bytes (%s memory)", (unsigned long)comm->id, comm->api_calls, sizes[0],
+    TRACE(kSubNet, "recv comm %lx: irecv #%u of up to %d bytes (%s memory)", (unsigned long)comm->id, comm->api_calls, sizes[0],
          mem_type == kPtrCuda ? "cuda" : "host");
   Result pr = progress(comm);
   mark(comm, "idle");
@@ -1113,7 +1106,7 @@ Result netTest(Request* r, int* done, int* size) {
   }
   *done = 1;
   if (comm->done_calls++ < 3)
-    INFO(kSubNet, "%s comm %lx: request #%u done, %d bytes", comm->passive ? "recv" : "send", (unsigned long)comm->id,
+    TRACE(kSubNet, "%s comm %lx: request #%u done, %d bytes", comm->passive ? "recv" : "send", (unsigned long)comm->id,
          comm->done_calls, r->size);
   if (size != nullptr) *size = r->size;
   r->reported = true;
