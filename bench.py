@@ -104,6 +104,10 @@ def unpack_microbench(torch, peaks, iters=20, warm=4):
 
     t_copy, tb_copy = timed(lambda i: U.unpack_copy(pool, dsts[i % 3], descs[i % variants], status=st))
     t_red, tb_red = timed(lambda i: U.unpack_reduce(pool, dsts[i % 3], descs[i % variants], status=st))
+    # fused reduce + fan-out with the three "peers" emulated by buffers on this GPU (no NVLink in
+    # this number: it shows the kernel's cost of writing four copies of every reduced fragment)
+    peers = [torch.empty((64 << 20) // 2, dtype=torch.bfloat16, device=dev) for _ in range(3)]
+    t_fan, tb_fan = timed(lambda i: U.unpack_reduce_fanout(pool, dsts[i % 3], dsts[i % 3], peers, descs[i % variants], status=st))
     flat = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
     t_ref, tb_ref = timed(lambda i: dsts[i % 3].view(torch.uint8).copy_(flat))
     hbm = peaks.get("hbm_gbs", 6650.0)
@@ -117,9 +121,13 @@ def unpack_microbench(torch, peaks, iters=20, warm=4):
                          "unpack_reduce_us": tb_red * 1e6, "unpack_reduce_frac_hbm": 3 * total / tb_red / 1e9 / hbm,
                          "torch_copy_64MiB_us": tb_ref * 1e6, "torch_copy_64MiB_frac_hbm": 2 * (64 << 20) / tb_ref / 1e9 / hbm},
         "torch_copy_64MiB_us": t_ref * 1e6,
+        "unpack_reduce_fanout3_us": t_fan * 1e6, "unpack_reduce_fanout3_GBps": 6 * total / t_fan / 1e9,
+        "unpack_reduce_fanout3_frac_hbm": 6 * total / t_fan / 1e9 / hbm,
+        "unpack_reduce_fanout3_back_to_back_us": tb_fan * 1e6,
+        "unpack_reduce_fanout3_back_to_back_frac_hbm": 6 * total / tb_fan / 1e9 / hbm,
         "status": st.tolist()[0],
     }
-    del pool, descs, dsts, flat
+    del pool, descs, dsts, flat, peers
     torch.cuda.empty_cache()
     return out
 
