@@ -73,6 +73,7 @@ const IntSpec kInts[] = {
     {kOwn, "VIRTUAL_NICS", &Flags::virtual_nics, 0, 17, "present N devices on one interface (127.0.0.k on lo)"},
     {kOwn, "RX_POOL_BYTES", &Flags::rx_pool_bytes, 1 << 20, (4ll << 30) + 1, "rx page pool per GPU"},
     {kOwn, "RX_POOL_SCATTER", &Flags::rx_pool_scatter, 0, 2, "hand out rx pages in a scattered order"},
+    {kOwn, "RX_POOL_RUN_PAGES", &Flags::rx_pool_run_pages, 1, 1025, "consecutive pages per scattered group of the rx pool"},
     {kOwn, "TX_STAGING_BYTES", &Flags::tx_staging_bytes, 1 << 16, kMax, "pinned staging per send comm for CUDA buffers"},
     {kOwn, "CONNECT_PACING_US", &Flags::connect_pacing_us, 0, kMax, "pause per socket during connection setup"},
     {kOwn, "NIC_SPEED_MBPS", &Flags::nic_speed_mbps, 0, 100000000, "speed reported to NCCL (0 = sysfs, else 10000)"},

@@ -10,19 +10,27 @@
 
 namespace tcpxb {
 
-PageAllocator::PageAllocator(uint32_t n_pages, bool scatter, uint64_t seed)
+PageAllocator::PageAllocator(uint32_t n_pages, bool scatter, uint64_t seed, uint32_t run_pages)
     : total_(n_pages), in_use_(n_pages, 0) {
-  stack_.resize(n_pages);
-  // ascending hand-out order = descending stack
-  for (uint32_t i = 0; i < n_pages; ++i) stack_[i] = n_pages - 1 - i;
-  if (scatter && n_pages > 1) {
+  if (run_pages < 1) run_pages = 1;
+  // order in which pages are handed out: groups of run_pages, ascending inside a group
+  std::vector<uint32_t> groups((n_pages + run_pages - 1) / run_pages);
+  for (uint32_t g = 0; g < groups.size(); ++g) groups[g] = g;
+  if (scatter && groups.size() > 1) {
     // Fisher-Yates with a fixed xorshift stream: reproducible scatter
     uint64_t x = seed ? seed : 1;
-    for (uint32_t i = n_pages - 1; i > 0; --i) {
+    for (uint32_t i = (uint32_t)groups.size() - 1; i > 0; --i) {
       x ^= x << 13; x ^= x >> 7; x ^= x << 17;
       uint32_t j = (uint32_t)(x % (i + 1));
-      std::swap(stack_[i], stack_[j]);
+      std::swap(groups[i], groups[j]);
     }
+  }
+  stack_.reserve(n_pages);
+  // back() is handed out first, so fill from the last page of the last group
+  for (size_t gi = groups.size(); gi > 0; --gi) {
+    const uint32_t first = groups[gi - 1] * run_pages;
+    const uint32_t last = std::min(first + run_pages, n_pages);
+    for (uint32_t p = last; p > first; --p) stack_.push_back(p - 1);
   }
 }
 
@@ -55,9 +63,9 @@ namespace {
 
 class EmulatedRxBufMgr final : public RxBufMgr {
  public:
-  EmulatedRxBufMgr(int dev, uint64_t bytes, bool scatter, bool device_resident)
+  EmulatedRxBufMgr(int dev, uint64_t bytes, bool scatter, bool device_resident, uint32_t run_pages)
       : dev_(dev), bytes_(bytes / kRxPageBytes * kRxPageBytes), device_resident_(device_resident),
-        alloc_((uint32_t)(bytes / kRxPageBytes), scatter) {}
+        alloc_((uint32_t)(bytes / kRxPageBytes), scatter, 0x9e3779b97f4a7c15ull, run_pages) {}
 
   ~EmulatedRxBufMgr() override {
     if (device_resident_) gpu::deviceFree(dev_base_);
@@ -160,15 +168,15 @@ RxBufMgr* rxBufMgrFor(int dev) {
   // a device-resident pool is filled by the copy engine one page run at a time, so
   // its allocator keeps runs contiguous whatever the scatter flag says
   auto m = std::make_unique<EmulatedRxBufMgr>(dev, (uint64_t)f.rx_pool_bytes, f.rx_pool_scatter != 0 && !device_resident,
-                                              device_resident);
+                                              device_resident, (uint32_t)f.rx_pool_run_pages);
   if (m->init() != kSuccess) return nullptr;
   RxBufMgr* raw = m.get();
   g_mgrs[dev] = std::move(m);
   return raw;
 }
 
-RxBufMgr* newHostRxBufMgr(uint64_t bytes, bool scatter) {
-  auto* m = new EmulatedRxBufMgr(-1, bytes, scatter, false);
+RxBufMgr* newHostRxBufMgr(uint64_t bytes, bool scatter, uint32_t run_pages) {
+  auto* m = new EmulatedRxBufMgr(-1, bytes, scatter, false, run_pages);
   if (m->init() != kSuccess) { delete m; return nullptr; }
   return m;
 }

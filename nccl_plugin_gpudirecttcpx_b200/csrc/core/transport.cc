@@ -619,8 +619,15 @@ Result progressRecvRequest(Comm* comm, Request* r) {
   const Flags& f = flags();
   for (;;) {
     if (!comm->have_ctrl) {
+      // An empty control socket costs a system call to discover; callers poll in
+      // tight loops, so after one empty read the next look waits a microsecond.
+      if (comm->ctrl_recv.buffered() < (int)sizeof(CtrlMsg) && comm->ctrl_quiet_until_ns != 0) {
+        if (monotonicNanos() < comm->ctrl_quiet_until_ns) return kSuccess;
+        comm->ctrl_quiet_until_ns = 0;
+      }
       Result pr = comm->ctrl_recv.pop(&comm->ctrl);
       if (pr == kInProgress) {
+        comm->ctrl_quiet_until_ns = monotonicNanos() + 1000;
         if (f.slow_switch[kSlowRxCtrl]) {
           uint64_t ns = 0;
           if (comm->ctrl_stall.shouldWarn(&ns) && f.slow_report[kSlowRxCtrl])

@@ -41,9 +41,10 @@ struct PageRun {
 // Hands out pool pages.  Not thread-safe by itself (RxBufMgr locks around it).
 class PageAllocator {
  public:
-  // `scatter`: pages come out in a pseudo-random order, like a NIC page pool after
-  // some churn; otherwise ascending, so allocations are mostly contiguous.
-  PageAllocator(uint32_t n_pages, bool scatter, uint64_t seed = 0x9e3779b97f4a7c15ull);
+  // `scatter`: groups of `run_pages` consecutive pages come out in a pseudo-random
+  // order, like a NIC page pool after some churn (run_pages = 1 scatters single
+  // pages); otherwise ascending, so allocations are mostly contiguous.
+  PageAllocator(uint32_t n_pages, bool scatter, uint64_t seed = 0x9e3779b97f4a7c15ull, uint32_t run_pages = 1);
   // Appends runs covering exactly n pages; false (and nothing taken) when fewer are free.
   bool alloc(uint32_t n, std::vector<PageRun>* out);
   void release(uint32_t first, uint32_t count);
@@ -86,7 +87,7 @@ class RxBufMgr {
 // a GPU), created on first use with the sizes and modes the flags give.
 RxBufMgr* rxBufMgrFor(int dev);
 // Test hook: a private emulator with explicit geometry (host memory only).
-RxBufMgr* newHostRxBufMgr(uint64_t bytes, bool scatter);
+RxBufMgr* newHostRxBufMgr(uint64_t bytes, bool scatter, uint32_t run_pages = 1);
 
 }  // namespace tcpxb
 #endif  // TCPXB_RX_BUF_MGR_H_

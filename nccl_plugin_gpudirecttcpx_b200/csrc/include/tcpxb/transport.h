@@ -191,6 +191,7 @@ struct Comm {
   // pending control record on the receive side
   bool have_ctrl = false;
   CtrlMsg ctrl;
+  uint64_t ctrl_quiet_until_ns = 0;  // no control-socket read before this time (after an empty read)
   // CUDA resources (lazy)
   int gpu_dev = -1;
   int recv_mode = kRecvModeHost;

@@ -304,6 +304,16 @@ TEST(page_allocator) {
   EXPECT(sr.size() > 128);                       // and really scattered
   for (auto& r : sr) s.release(r.first, r.count);
   EXPECT(s.freePages() == 1024);
+  // groups of 8 pages scattered as units: 256 pages come out as 32 runs of 8
+  PageAllocator g(1024, /*scatter=*/true, 7, /*run_pages=*/8);
+  std::vector<PageRun> gr;
+  EXPECT(g.alloc(256, &gr) && gr.size() <= 32 && gr.size() >= 28);
+  std::set<uint32_t> gp;
+  for (auto& r : gr) { EXPECT(r.first % 8 == 0 && r.count % 8 == 0); for (uint32_t i = 0; i < r.count; ++i) gp.insert(r.first + i); }
+  EXPECT(gp.size() == 256);
+  for (auto& r : gr) g.release(r.first, r.count);
+  std::vector<PageRun> again;
+  EXPECT(g.alloc(5, &again) && again.size() == 1 && again[0].count == 5);  // a partial group stays contiguous
   s.release(sr[0].first, 1);                     // double release is refused
   EXPECT(s.freePages() == 1024);
 }
