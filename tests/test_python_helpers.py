@@ -1,0 +1,59 @@
+"""CPU tests of the Python helpers: flag listing, NCCL environment builder, clocks sampler."""
+import os
+
+from nccl_plugin_gpudirecttcpx_b200 import _build
+
+
+def test_flag_docs_cover_the_reference_surface():
+    _build.build_host()
+    from nccl_plugin_gpudirecttcpx_b200.utils.flags import flag_docs
+    names = {r[0] for r in flag_docs()}
+    for env in ("NCCL_GPUDIRECTTCPX_SOCKET_ENABLE", "NCCL_MIN_ZCOPY_SIZE", "NCCL_NSOCKS_PERTHREAD", "NCCL_SOCKET_NTHREADS",
+                "NCCL_INLINE_THRESHOLD", "NCCL_DYNAMIC_CHUNK_SIZE", "NCCL_THREAD_SPIN_ENABLE", "NCCL_USE_DMA_BUF",
+                "NCCL_GPUDIRECTTCPX_CONNECTION_RETRY", "NCCL_GPUDIRECTTCPX_RECV_SYNC", "NCCL_GPUDIRECTTCPX_FORCE_ACK",
+                "NCCL_GPUDIRECTTCPX_TX_COMPLETION_NANOSLEEP", "NCCL_GPUDIRECTTCPX_TIMEOUT_THRESHOLD_NS",
+                "NCCL_GPUDIRECTTCPX_TIMEOUT_FREQUENCY_NS", "NCCL_GPUDIRECTTCPX_SPINWAIT_CONNECT",
+                "NCCL_GPUDIRECTTCPX_LOG_STATS_TO_STDOUT", "NCCL_GPUDIRECTTCPX_TELEMETRY_ENABLE_TASK_LEVEL_STATS",
+                "NCCL_GPUDIRECTTCPX_TELEMETRY_EXPORTER_PATH", "NCCL_GPUDIRECTTCPX_REPORT_LIFECYCLE",
+                "NCCL_GPUDIRECTTCPX_CUDA_USE_PRIMARY_CTX", "NCCL_GPUDIRECTTCPX_NIC_N_RXQS",
+                "NCCL_GPUDIRECTTCPX_FLOW_STEERING_STRATEGY", "NCCL_GPUDIRECTTCPX_PROGRAM_FLOW_STEERING_WAIT_MICROS",
+                "NCCL_TCPX_RXMEM_IMPORT_USE_GPU_PCI_CLIENT", "NCCL_GPUDIRECTTCPX_SOCKET_IFNAME",
+                "NCCL_GPUDIRECTTCPX_SOCKET_FAMILY", "NCCL_GPUDIRECTTCPX_CTRL_DEV", "NCCL_GPUDIRECTTCPX_PORT_MAPPING",
+                "NCCL_GPUDIRECTTCPX_TX_BINDINGS", "NCCL_GPUDIRECTTCPX_RX_IRQ_BINDINGS", "NCCL_GPUDIRECTTCPX_WORKER_PIN_THREADS",
+                "NCCL_GPUDIRECTTCPX_SCHED_ALG", "NCCL_GPUDIRECTTCPX_SLOWNESS_SWITCH", "NCCL_GPUDIRECTTCPX_UNIX_CLIENT_PREFIX",
+                "NET_COMM_ID", "NCCL_GPUDIRECTTCPX_RECV_MODE", "NCCL_GPUDIRECTTCPX_VIRTUAL_NICS"):
+        assert env in names, env
+    by_name = {r[0]: r for r in flag_docs()}
+    assert by_name["NCCL_DYNAMIC_CHUNK_SIZE"][2] == "131072"   # the documented default, not 0
+    assert by_name["NCCL_GPUDIRECTTCPX_TIMEOUT_THRESHOLD_NS"][2] == "10000000000"
+
+
+def test_plugin_env_variants(monkeypatch):
+    from nccl_plugin_gpudirecttcpx_b200.parallel import plugin_env
+    from nccl_plugin_gpudirecttcpx_b200.utils import native
+    monkeypatch.setattr(native, "load", lambda name, build=True: None)
+    base = plugin_env(nics=3, nthreads=2, nsocks_per_thread=2, chunk_bytes=65536)
+    assert base["NCCL_GPUDIRECTTCPX_VIRTUAL_NICS"] == "3" and base["NCCL_SOCKET_NTHREADS"] == "2"
+    assert base["NCCL_NSOCKS_PERTHREAD"] == "2" and base["NCCL_DYNAMIC_CHUNK_SIZE"] == "65536"
+    assert base["NCCL_NET_PLUGIN"].endswith("libnccl-net.so") and base["NCCL_P2P_DISABLE"] == "1"
+    assert "NCCL_NET_GDR_LEVEL" not in base and "NCCL_GPUDIRECTTCPX_CUDA_BUFFERS" not in base  # host buffers by default
+    unpack = plugin_env(recv_mode="unpack")
+    assert unpack["NCCL_PROTO"] == "Simple" and unpack["NCCL_ALGO"] == "Ring" and unpack["NCCL_NET_GDR_READ"] == "0"
+    assert unpack["NCCL_GPUDIRECTTCPX_RECV_MODE"] == "unpack"
+    sock = plugin_env(builtin_socket=True, nthreads=2)
+    assert sock["NCCL_NET"] == "Socket" and sock["NCCL_NET_PLUGIN"] == "none" and sock["NCCL_SOCKET_NTHREADS"] == "2"
+    assert not any(k.startswith("NCCL_GPUDIRECTTCPX_") for k in sock)
+
+
+def test_clock_sampler_without_nvidia_smi(monkeypatch):
+    import shutil
+    from nccl_plugin_gpudirecttcpx_b200.utils import clocks
+    monkeypatch.setattr(shutil, "which", lambda name: None)
+    s = clocks.ClockSampler(0).start()
+    summary = s.stop()
+    assert summary["samples"] == 0 and summary["reasons"] == [] and summary["sm_mhz"] is None
+    # and the parser on canned lines
+    s.samples = [["0", "1965", "1965", "700.1", "Not Active", "Not Active", "Not Active", "Active"],
+                 ["0", "1800", "1965", "990.0", "Not Active", "Not Active", "Not Active", "Not Active"]]
+    out = s.summary()
+    assert out["sm_mhz"] == 1882.5 and out["sm_max_mhz"] == 1965 and out["reasons"] == ["sw_power_cap"]
