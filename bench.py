@@ -39,8 +39,8 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "plain", "nccl-socket", "nccl-plugin"])
     ap.add_argument("--size-mb", type=int, default=256, help="all_reduce bytes per GPU (MiB)")
-    ap.add_argument("--nics", type=int, default=4)
-    ap.add_argument("--nthreads", type=int, default=2)
+    ap.add_argument("--nics", type=int, default=0, help="virtual NICs = rails per rank (0 = from the core count)")
+    ap.add_argument("--nthreads", type=int, default=0, help="helper threads (= sockets) per comm (0 = from the core count)")
     ap.add_argument("--nsocks-per-thread", type=int, default=1)
     ap.add_argument("--chunk-kb", type=int, default=128)
     ap.add_argument("--request-kb", type=int, default=4096)
@@ -164,6 +164,15 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+    # Socket helpers are CPU work and all ranks share the box: aim at about one helper
+    # thread per core (measured: 4 cores per rank run best with 2 rails x 1 thread,
+    # 8 with 4 x 1, 16 with 4 x 2).
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 16)
+    per_dir = max(1, min(8, cores // max(world, 1) // 2))
+    if args.nics <= 0:
+        args.nics = min(4, per_dir)
+    if args.nthreads <= 0:
+        args.nthreads = max(1, per_dir // args.nics)
     default_transport_env(nics=args.nics, nthreads=args.nthreads, nsocks_per_thread=args.nsocks_per_thread,
                           chunk_bytes=args.chunk_kb << 10, pool_mb=1024)
     G = max(1, world // 2)
@@ -275,7 +284,7 @@ def main():
                 "model": "all_reduce through the hierarchical engine", "global_batch": None, "seq_len": None,
                 "bytes_per_gpu": nbytes, "parallelism": f"{nodes} emulated nodes x {G} GPU(s)" + (" (single GPU is its own peer)" if world == 1 else ""),
                 "l2_policy": "inputs larger than L2: in+out = %d MiB per GPU" % (2 * args.size_mb),
-                "transport": {"nics": args.nics, "threads": args.nthreads, "socks_per_thread": args.nsocks_per_thread,
+                "transport": {"cpu_cores": cores, "nics": args.nics, "threads": args.nthreads, "socks_per_thread": args.nsocks_per_thread,
                               "chunk_kb": args.chunk_kb, "request_kb": args.request_kb, "unpack_ctas": args.unpack_ctas},
                 "busbw_GBps": busbw, "net_bytes_per_gpu_per_step": (s1.bytes_received - b0) // max(args.steps, 1),
                 "fragments_per_step": (s1.fragments - f0) // max(args.steps, 1), "max_abs_err": err,
