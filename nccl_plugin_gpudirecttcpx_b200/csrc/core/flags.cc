@@ -99,6 +99,7 @@ const StrSpec kStrs[] = {
     {"", "NET_COMM_ID", &Flags::net_comm_id, "subnet hint for interface auto-selection"},
     {kOwn, "RX_POOL_MODE", &Flags::rx_pool_mode_name, "host (pinned, device-mapped) or device (copy-engine placement)"},
     {kOwn, "RECV_MODE", &Flags::recv_mode_name, "host (plugin unpacks) or unpack (NCCL's kernels unpack)"},
+    {kOwn, "RX_BUF_MGR", &Flags::rx_buf_mgr_name, "emulated (in process) or daemon (tcpxb_rxdm under UNIX_CLIENT_PREFIX)"},
 };
 
 std::string envName(const char* prefix, const char* name) { return std::string(prefix) + name; }
@@ -166,6 +167,9 @@ void loadFlags(Flags* out) {
   if (!strcasecmp(out->recv_mode_name.c_str(), "unpack")) out->recv_mode = kRecvModeUnpack;
   else if (!out->recv_mode_name.empty() && strcasecmp(out->recv_mode_name.c_str(), "host"))
     WARN("unknown receive mode '%s'; using host", out->recv_mode_name.c_str());
+  out->rx_buf_mgr_daemon = !strcasecmp(out->rx_buf_mgr_name.c_str(), "daemon");
+  if (!out->rx_buf_mgr_daemon && !out->rx_buf_mgr_name.empty() && strcasecmp(out->rx_buf_mgr_name.c_str(), "emulated"))
+    WARN("unknown rx buffer manager '%s'; using the in-process one", out->rx_buf_mgr_name.c_str());
   parseSlownessList(out->slowness_switch.c_str(), out->slow_switch);
   parseSlownessList(out->slowness_report.c_str(), out->slow_report);
   if (out->inline_threshold > out->dynamic_chunk_size) out->inline_threshold = out->dynamic_chunk_size;

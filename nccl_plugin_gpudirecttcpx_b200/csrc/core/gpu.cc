@@ -44,6 +44,8 @@ Result hostAllocMapped(size_t bytes, void** host_ptr, void** dev_ptr) {
   return kSuccess;
 }
 void hostFreeMapped(void* p) { free(p); }
+Result hostRegisterMapped(void* host_ptr, size_t, void** dev_ptr) { *dev_ptr = host_ptr; return kSuccess; }
+void hostUnregister(void*) {}
 Result deviceAlloc(size_t, void**) { return none(); }
 void deviceFree(void*) {}
 Result streamCreate(Stream*) { return none(); }
@@ -147,6 +149,18 @@ void hostFreeMapped(void* p) {
   if (p == nullptr) return;
   if (!available()) { free(p); return; }
   if (cudaFreeHost(p) != cudaSuccess) (void)cudaGetLastError();
+}
+
+Result hostRegisterMapped(void* host_ptr, size_t bytes, void** dev_ptr) {
+  if (!available()) { *dev_ptr = host_ptr; return kSuccess; }
+  Result r = CU(cudaHostRegister(host_ptr, bytes, cudaHostRegisterMapped | cudaHostRegisterPortable));
+  if (r != kSuccess) return r;
+  return CU(cudaHostGetDevicePointer(dev_ptr, host_ptr, 0));
+}
+
+void hostUnregister(void* host_ptr) {
+  if (host_ptr == nullptr || !available()) return;
+  if (cudaHostUnregister(host_ptr) != cudaSuccess) (void)cudaGetLastError();
 }
 
 Result deviceAlloc(size_t bytes, void** ptr) { return CU(cudaMalloc(ptr, bytes)); }

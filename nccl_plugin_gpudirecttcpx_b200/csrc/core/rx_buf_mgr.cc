@@ -5,8 +5,11 @@
 #include <memory>
 #include <unistd.h>
 
+#include <sys/mman.h>
+
 #include "tcpxb/flags.h"
 #include "tcpxb/gpu.h"
+#include "tcpxb/rxdm.h"
 
 namespace tcpxb {
 
@@ -154,8 +157,128 @@ class EmulatedRxBufMgr final : public RxBufMgr {
   std::vector<int> apps_;
 };
 
+// Pool, rules and registry live in the tcpxb_rxdm daemon; this process maps the pool
+// it is handed (memfd over SCM_RIGHTS), registers it with CUDA and allocates pages
+// from it locally, as the NIC + kernel would on a devmem-TCP host.
+class DaemonRxBufMgr final : public RxBufMgr {
+ public:
+  DaemonRxBufMgr(int dev, std::string prefix) : dev_(dev), prefix_(std::move(prefix)) {}
+  ~DaemonRxBufMgr() override {
+    if (host_base_ != nullptr) {
+      gpu::hostUnregister(host_base_);
+      munmap(host_base_, bytes_);
+    }
+    if (pool_fd_ >= 0) close(pool_fd_);
+  }
+
+  Result init() {
+    pci_ = dev_ >= 0 ? gpu::pciBusId(dev_) : std::string("host");
+    if (pci_.empty()) pci_ = "gpu" + std::to_string(dev_);
+    RxdmMessage q, rep;
+    memset(&q, 0, sizeof q);
+    q.magic = kRxdmMagic;
+    q.type = kRxdmGetGpuMetadata;
+    snprintf(q.gpu.gpu_pci, sizeof q.gpu.gpu_pci, "%s", pci_.c_str());
+    TCPXB_CHECK(rxdmCall(prefix_, "get_gpu_metadata", q, &rep, nullptr));
+    bytes_ = rep.reply.a / kRxPageBytes * kRxPageBytes;
+    q.type = kRxdmGetGpuFd;
+    TCPXB_CHECK(rxdmCall(prefix_, "get_gpu_fd", q, &rep, &pool_fd_));
+    if (pool_fd_ < 0 || bytes_ == 0) { WARN("rx buffer manager sent no pool for %s", pci_.c_str()); return kRemoteError; }
+    void* p = mmap(nullptr, bytes_, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_POPULATE, pool_fd_, 0);
+    if (p == MAP_FAILED) { WARN("mapping the rx pool failed: %s", strerror(errno)); return kSystemError; }
+    host_base_ = static_cast<uint8_t*>(p);
+    void* d = nullptr;
+    TCPXB_CHECK(gpu::hostRegisterMapped(host_base_, bytes_, &d));
+    dev_base_ = static_cast<uint8_t*>(d);
+    const Flags& f = flags();
+    alloc_ = std::make_unique<PageAllocator>((uint32_t)(bytes_ / kRxPageBytes), f.rx_pool_scatter != 0, 0x9e3779b97f4a7c15ull,
+                                             (uint32_t)f.rx_pool_run_pages);
+    INFO(kSubInit | kSubNet, "rx pool for %s imported from %s: %lu MiB, host %p device %p", pci_.c_str(), prefix_.c_str(),
+         (unsigned long)(bytes_ >> 20), (void*)host_base_, (void*)dev_base_);
+    return kSuccess;
+  }
+
+  uint8_t* hostBase() override { return host_base_; }
+  uint8_t* devBase() override { return dev_base_; }
+  uint64_t bytes() const override { return bytes_; }
+  bool deviceResident() const override { return false; }
+  bool allocPages(uint32_t n, std::vector<PageRun>* out) override {
+    std::lock_guard<std::mutex> l(mu_);
+    return alloc_->alloc(n, out);
+  }
+  void releasePages(const PageRun* runs, size_t n) override {
+    std::lock_guard<std::mutex> l(mu_);
+    for (size_t i = 0; i < n; ++i) alloc_->release(runs[i].first, runs[i].count);
+  }
+  uint32_t freePages() override {
+    std::lock_guard<std::mutex> l(mu_);
+    return alloc_->freePages();
+  }
+
+  Result installFlowRule(int fd, const std::string& gpu_pci) override {
+    FlowRule r;
+    memset(&r.local, 0, sizeof r.local);
+    memset(&r.peer, 0, sizeof r.peer);
+    socklen_t ll = sizeof r.local, pl = sizeof r.peer;
+    if (getsockname(fd, &r.local.sa, &ll) != 0 || getpeername(fd, &r.peer.sa, &pl) != 0) return kSystemError;
+    r.gpu_pci = gpu_pci.empty() ? pci_ : gpu_pci;
+    r.fd = fd;
+    RxdmMessage rep;
+    TCPXB_CHECK(rxdmCall(prefix_, "rx_rule_manager", rxdmMakeRule(kRxdmFlowRule, r.local, r.peer, r.gpu_pci), &rep, nullptr));
+    std::lock_guard<std::mutex> l(mu_);
+    rules_.push_back(r);
+    return kSuccess;
+  }
+  Result removeFlowRule(int fd) override {
+    FlowRule found;
+    bool have = false;
+    {
+      std::lock_guard<std::mutex> l(mu_);
+      for (size_t i = 0; i < rules_.size(); ++i)
+        if (rules_[i].fd == fd) { found = rules_[i]; rules_.erase(rules_.begin() + (long)i); have = true; break; }
+    }
+    if (!have) return kSuccess;
+    RxdmMessage rep;
+    return rxdmCall(prefix_, "rx_rule_uninstall", rxdmMakeRule(kRxdmFlowRuleUninstall, found.local, found.peer, found.gpu_pci),
+                    &rep, nullptr);
+  }
+  Result registerApplication(int pid) override {
+    RxdmMessage m, rep;
+    memset(&m, 0, sizeof m);
+    m.magic = kRxdmMagic;
+    m.type = kRxdmAppRegister;
+    m.app.register_client = 1;
+    m.app.pid = pid;
+    // the registration is the connection: the daemon drops the entry when it closes
+    TCPXB_CHECK(keepalive_.connectTo(prefix_ + "/rxdm_application_registry"));
+    TCPXB_CHECK(keepalive_.send(m));
+    Result r = keepalive_.recv(&rep, nullptr);
+    return (r == kSuccess && rep.reply.status == 0) ? kSuccess : kRemoteError;
+  }
+  Result deregisterApplication(int /*pid*/) override {
+    keepalive_.closeNow();
+    return kSuccess;
+  }
+  std::vector<FlowRule> flowRules() override {
+    std::lock_guard<std::mutex> l(mu_);
+    return rules_;
+  }
+
+ private:
+  int dev_;
+  std::string prefix_, pci_;
+  std::mutex mu_;
+  std::unique_ptr<PageAllocator> alloc_;
+  uint8_t* host_base_ = nullptr;
+  uint8_t* dev_base_ = nullptr;
+  uint64_t bytes_ = 0;
+  int pool_fd_ = -1;
+  std::vector<FlowRule> rules_;
+  UnixSocketConnection keepalive_;
+};
+
 std::mutex g_mu;
-std::map<int, std::unique_ptr<EmulatedRxBufMgr>> g_mgrs;
+std::map<int, std::unique_ptr<RxBufMgr>> g_mgrs;
 
 }  // namespace
 
@@ -164,6 +287,13 @@ RxBufMgr* rxBufMgrFor(int dev) {
   auto it = g_mgrs.find(dev);
   if (it != g_mgrs.end()) return it->second.get();
   const Flags& f = flags();
+  if (f.rx_buf_mgr_daemon) {
+    auto m = std::make_unique<DaemonRxBufMgr>(dev, f.unix_client_prefix);
+    if (m->init() != kSuccess) return nullptr;
+    RxBufMgr* raw = m.get();
+    g_mgrs[dev] = std::move(m);
+    return raw;
+  }
   const bool device_resident = dev >= 0 && f.rx_pool_mode == kRxPoolDevice && gpu::available();
   // a device-resident pool is filled by the copy engine one page run at a time, so
   // its allocator keeps runs contiguous whatever the scatter flag says

@@ -91,10 +91,12 @@ struct Flags {
   int64_t poll_block_us = 200;         // helper threads block in poll() this long when every socket would block
   std::string rx_pool_mode_name;       // RX_POOL_MODE: host | device
   std::string recv_mode_name;          // RECV_MODE: host | unpack
+  std::string rx_buf_mgr_name;         // RX_BUF_MGR: emulated (in process) | daemon (tcpxb_rxdm over UNIX sockets)
   // --- derived
   int sched_alg = kSchedRR;
   int rx_pool_mode = kRxPoolHostMapped;
   int recv_mode = kRecvModeHost;
+  bool rx_buf_mgr_daemon = false;
   bool slow_switch[kSlowKinds] = {false, false, false};
   bool slow_report[kSlowKinds] = {false, false, false};
 };

@@ -35,6 +35,10 @@ int numaNode(int dev);          // sysfs, else dev < count/2 ? 0 : 1
 // this is page-aligned host memory and *dev_ptr == *host_ptr.
 Result hostAllocMapped(size_t bytes, void** host_ptr, void** dev_ptr);
 void hostFreeMapped(void* host_ptr);
+// Makes existing page-aligned host memory (e.g. a shared mapping) pinned and visible
+// to the GPU; *dev_ptr is the address the GPU uses.  Without CUDA: *dev_ptr = host_ptr.
+Result hostRegisterMapped(void* host_ptr, size_t bytes, void** dev_ptr);
+void hostUnregister(void* host_ptr);
 Result deviceAlloc(size_t bytes, void** ptr);
 void deviceFree(void* ptr);
 

@@ -1,0 +1,211 @@
+// Receive-datapath manager daemon: owns the rx page pools and the flow-steering and
+// application tables, and serves them to plugin processes over AF_UNIX sockets.
+//
+//   tcpxb_rxdm --prefix /tmp/tcpxb --pool-mb 1024 [--max-rules 65536]
+//
+// It stands in for the external daemon the reference depends on (reference:
+// README.md:14-16 names it; its clients are src/rx_buf_mgr_client/*).  One pool per
+// GPU PCI address, created on first request as a memfd; the plugin maps it and
+// registers it with CUDA.  A client that registers keeps its connection open; when
+// the connection closes the client is deregistered and its flow rules are dropped,
+// which is how a crashed job is cleaned up.
+#include <poll.h>
+#include <signal.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/mman.h>
+#include <sys/socket.h>
+#include <sys/stat.h>
+#include <sys/un.h>
+#include <unistd.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "tcpxb/rxdm.h"
+
+using namespace tcpxb;
+
+namespace {
+
+volatile sig_atomic_t g_stop = 0;
+void onSignal(int) { g_stop = 1; }
+
+struct Rule { RxdmFlowRule r; int owner_fd; };
+struct Pool { int fd; uint64_t size; };
+
+struct State {
+  std::string prefix;
+  uint64_t pool_bytes = 1ull << 30;
+  size_t max_rules = 65536;
+  std::vector<Rule> rules;
+  std::map<int, int> apps;  // connection fd -> pid
+  std::map<std::string, Pool> pools;
+};
+
+int listenOn(const std::string& path) {
+  unlink(path.c_str());
+  int fd = socket(AF_UNIX, SOCK_STREAM, 0);
+  if (fd < 0) return -1;
+  struct sockaddr_un addr;
+  memset(&addr, 0, sizeof addr);
+  addr.sun_family = AF_UNIX;
+  snprintf(addr.sun_path, sizeof addr.sun_path, "%s", path.c_str());
+  if (bind(fd, (struct sockaddr*)&addr, sizeof addr) != 0 || listen(fd, 128) != 0) {
+    close(fd);
+    return -1;
+  }
+  return fd;
+}
+
+RxdmMessage reply(int status, const char* text, uint64_t a = 0, uint64_t b = 0, uint64_t c = 0) {
+  RxdmMessage m;
+  memset(&m, 0, sizeof m);
+  m.magic = kRxdmMagic;
+  m.type = kRxdmReply;
+  m.reply.status = status;
+  snprintf(m.reply.text, sizeof m.reply.text, "%s", text);
+  m.reply.a = a; m.reply.b = b; m.reply.c = c;
+  return m;
+}
+
+Pool* poolFor(State* st, const std::string& pci) {
+  auto it = st->pools.find(pci);
+  if (it != st->pools.end()) return &it->second;
+  std::string name = "tcpxb-rxpool-" + pci;
+  int fd = memfd_create(name.c_str(), 0);
+  if (fd < 0) return nullptr;
+  if (ftruncate(fd, (off_t)st->pool_bytes) != 0) { close(fd); return nullptr; }
+  st->pools[pci] = Pool{fd, st->pool_bytes};
+  fprintf(stderr, "[rxdm] pool for GPU %s: %lu MiB\n", pci.c_str(), (unsigned long)(st->pool_bytes >> 20));
+  return &st->pools[pci];
+}
+
+bool sameRule(const RxdmFlowRule& a, const RxdmFlowRule& b) {
+  return strcmp(a.src_ip, b.src_ip) == 0 && a.src_port == b.src_port && strcmp(a.dst_ip, b.dst_ip) == 0 &&
+         a.dst_port == b.dst_port;
+}
+
+// Handles one request on a fresh connection; returns true when the connection
+// must stay open (an application registration).
+bool serve(State* st, UnixSocketConnection* c, const std::string& service) {
+  RxdmMessage m;
+  int passed = -1;
+  if (c->recv(&m, &passed, 2000) != kSuccess) return false;
+  if (passed >= 0) close(passed);
+  switch (m.type) {
+    case kRxdmFlowRule: {
+      if (st->rules.size() >= st->max_rules) { c->send(reply(8, "resource exhausted")); return false; }
+      m.rule.src_ip[sizeof m.rule.src_ip - 1] = 0;
+      m.rule.dst_ip[sizeof m.rule.dst_ip - 1] = 0;
+      m.rule.gpu_pci[sizeof m.rule.gpu_pci - 1] = 0;
+      st->rules.push_back(Rule{m.rule, -1});
+      c->send(reply(0, "Ok."));
+      return false;
+    }
+    case kRxdmFlowRuleUninstall: {
+      for (size_t i = 0; i < st->rules.size(); ++i)
+        if (sameRule(st->rules[i].r, m.rule)) { st->rules.erase(st->rules.begin() + (long)i); c->send(reply(0, "Ok.")); return false; }
+      c->send(reply(5, "no such rule"));
+      return false;
+    }
+    case kRxdmGetGpuFd:
+    case kRxdmGetGpuMetadata: {
+      m.gpu.gpu_pci[sizeof m.gpu.gpu_pci - 1] = 0;
+      Pool* p = poolFor(st, m.gpu.gpu_pci);
+      if (p == nullptr) { c->send(reply(13, "pool creation failed")); return false; }
+      if (m.type == kRxdmGetGpuFd) c->send(reply(0, "Ok.", p->size, 4096), p->fd);
+      else c->send(reply(0, "Ok.", p->size, 4096));
+      return false;
+    }
+    case kRxdmAppRegister: {
+      if (m.app.register_client) {
+        st->apps[c->fd()] = m.app.pid;
+        c->send(reply(0, "Ok."));
+        return true;  // keep-alive connection
+      }
+      for (auto it = st->apps.begin(); it != st->apps.end();)
+        it = (it->second == m.app.pid) ? st->apps.erase(it) : std::next(it);
+      c->send(reply(0, "Ok."));
+      return false;
+    }
+    case kRxdmStatus:
+      c->send(reply(0, "Ok.", st->rules.size(), st->apps.size(), st->pools.size()));
+      return false;
+    default:
+      fprintf(stderr, "[rxdm] unknown request %u on %s\n", m.type, service.c_str());
+      c->send(reply(3, "unknown request"));
+      return false;
+  }
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  State st;
+  st.prefix = "/tmp";
+  for (int i = 1; i + 1 < argc; i += 2) {
+    std::string a = argv[i];
+    if (a == "--prefix") st.prefix = argv[i + 1];
+    else if (a == "--pool-mb") st.pool_bytes = strtoull(argv[i + 1], nullptr, 0) << 20;
+    else if (a == "--max-rules") st.max_rules = strtoull(argv[i + 1], nullptr, 0);
+    else { fprintf(stderr, "unknown argument %s\n", a.c_str()); return 2; }
+  }
+  mkdir(st.prefix.c_str(), 0755);
+  signal(SIGINT, onSignal);
+  signal(SIGTERM, onSignal);
+  signal(SIGPIPE, SIG_IGN);
+  // fixed services; the per-GPU ones share a wildcard socket each: the client names the GPU in the request
+  const std::vector<std::string> services = {"rx_rule_manager", "rx_rule_uninstall", "get_gpu_fd", "get_gpu_metadata",
+                                             "rxdm_application_registry", "rxdm_status"};
+  std::vector<int> lfds;
+  for (const auto& s : services) {
+    int fd = listenOn(st.prefix + "/" + s);
+    if (fd < 0) { fprintf(stderr, "[rxdm] cannot listen on %s/%s\n", st.prefix.c_str(), s.c_str()); return 1; }
+    lfds.push_back(fd);
+  }
+  fprintf(stderr, "[rxdm] serving under %s\n", st.prefix.c_str());
+  printf("ready\n");
+  fflush(stdout);
+  std::vector<UnixSocketConnection*> keep;
+  while (!g_stop) {
+    std::vector<struct pollfd> pfds;
+    for (int fd : lfds) pfds.push_back({fd, POLLIN, 0});
+    for (auto* k : keep) pfds.push_back({k->fd(), POLLIN, 0});
+    int pr = poll(pfds.data(), (nfds_t)pfds.size(), 500);
+    if (pr <= 0) continue;
+    for (size_t i = 0; i < lfds.size(); ++i) {
+      if (!(pfds[i].revents & POLLIN)) continue;
+      int cfd = accept(lfds[i], nullptr, nullptr);
+      if (cfd < 0) continue;
+      auto* c = new UnixSocketConnection(cfd);
+      if (serve(&st, c, services[i])) keep.push_back(c);
+      else delete c;
+    }
+    for (size_t k = 0; k < keep.size();) {
+      const struct pollfd& p = pfds[lfds.size() + k];
+      if (p.revents & (POLLIN | POLLHUP | POLLERR)) {
+        char b;
+        ssize_t n = recv(keep[k]->fd(), &b, 1, MSG_DONTWAIT);
+        if (n == 0 || (n < 0 && errno != EAGAIN)) {
+          auto it = st.apps.find(keep[k]->fd());
+          if (it != st.apps.end()) {
+            fprintf(stderr, "[rxdm] application %d went away\n", it->second);
+            st.apps.erase(it);
+          }
+          delete keep[k];
+          keep.erase(keep.begin() + (long)k);
+          pfds.erase(pfds.begin() + (long)(lfds.size() + k));
+          continue;
+        }
+      }
+      ++k;
+    }
+  }
+  for (auto* k : keep) delete k;
+  for (size_t i = 0; i < lfds.size(); ++i) { close(lfds[i]); unlink((st.prefix + "/" + services[i]).c_str()); }
+  for (auto& p : st.pools) close(p.second.fd);
+  return 0;
+}

@@ -26,6 +26,7 @@
 #include "tcpxb/flags.h"
 #include "tcpxb/flow_mapper.h"
 #include "tcpxb/rx_buf_mgr.h"
+#include "tcpxb/rxdm.h"
 #include "tcpxb/socket_utils.h"
 #include "tcpxb/stage_ring.h"
 #include "tcpxb/telemetry.h"
@@ -337,6 +338,73 @@ TEST(rx_buf_mgr_host_pool) {
   close(sv[0]);
   close(sv[1]);
   delete m;
+}
+
+// Needs a running tcpxb_rxdm; the Python test-suite starts one and names its
+// directory in TCPXB_TEST_RXDM_PREFIX.  Without it the test is a no-op.
+TEST(rxdm_daemon_roundtrip) {
+  const char* prefix = getenv("TCPXB_TEST_RXDM_PREFIX");
+  if (prefix == nullptr) { printf("  (no daemon: skipped)\n"); return; }
+  setenv("NCCL_GPUDIRECTTCPX_RX_BUF_MGR", "daemon", 1);
+  setenv("NCCL_GPUDIRECTTCPX_UNIX_CLIENT_PREFIX", prefix, 1);
+  reloadFlags();
+  auto status = [&](uint64_t* rules, uint64_t* apps, uint64_t* pools) {
+    RxdmMessage q, rep;
+    memset(&q, 0, sizeof q);
+    q.magic = kRxdmMagic;
+    q.type = kRxdmStatus;
+    EXPECT(rxdmCall(prefix, "rxdm_status", q, &rep, nullptr) == kSuccess);
+    *rules = rep.reply.a; *apps = rep.reply.b; *pools = rep.reply.c;
+  };
+  uint64_t rules = 9, apps = 9, pools = 9;
+  status(&rules, &apps, &pools);
+  EXPECT(rules == 0 && apps == 0);
+  RxBufMgr* m = rxBufMgrFor(-1);  // imports the "host" pool: memfd over SCM_RIGHTS, mapped here
+  EXPECT(m != nullptr);
+  if (m == nullptr) return;
+  EXPECT(m->bytes() == (8u << 20) && m->hostBase() != nullptr && m->freePages() == 2048);
+  std::vector<PageRun> runs;
+  EXPECT(m->allocPages(4, &runs));
+  memset(m->hostBase() + (uint64_t)runs[0].first * kRxPageBytes, 0x5a, kRxPageBytes);
+  // a second mapping of the same pool sees the bytes: the pool really is shared
+  RxdmMessage q, rep;
+  memset(&q, 0, sizeof q);
+  q.magic = kRxdmMagic;
+  q.type = kRxdmGetGpuFd;
+  snprintf(q.gpu.gpu_pci, sizeof q.gpu.gpu_pci, "host");
+  int fd = -1;
+  EXPECT(rxdmCall(prefix, "get_gpu_fd", q, &rep, &fd) == kSuccess && fd >= 0 && rep.reply.a == (8u << 20));
+  if (fd >= 0) {
+    uint8_t probe = 0;
+    EXPECT(pread(fd, &probe, 1, (off_t)runs[0].first * kRxPageBytes + 100) == 1 && probe == 0x5a);
+    close(fd);
+  }
+  m->releasePages(runs.data(), runs.size());
+  // flow-steering rule for a real TCP connection, then its removal
+  std::vector<NetIf> lo = findInterfaces("lo", AF_INET, nullptr);
+  SocketAddress a = lo[0].addr;
+  setAddressPort(&a, 0);
+  int lfd = -1, cfd = -1, sfd = -1;
+  EXPECT(createListenSocket(&lfd, &a) == kSuccess);
+  EXPECT(connectAddress(&cfd, a, nullptr) == kSuccess);
+  EXPECT(acceptSocket(lfd, &sfd, 2000) == kSuccess);
+  EXPECT(m->installFlowRule(sfd, "0000:1b:00.0") == kSuccess && m->flowRules().size() == 1);
+  status(&rules, &apps, &pools);
+  EXPECT(rules == 1 && pools == 1);
+  EXPECT(m->removeFlowRule(sfd) == kSuccess && m->flowRules().empty());
+  status(&rules, &apps, &pools);
+  EXPECT(rules == 0);
+  // lifecycle: registered while the connection lives
+  EXPECT(m->registerApplication(4242) == kSuccess);
+  status(&rules, &apps, &pools);
+  EXPECT(apps == 1);
+  EXPECT(m->deregisterApplication(4242) == kSuccess);
+  for (int i = 0; i < 100 && apps != 0; ++i) { usleep(20000); status(&rules, &apps, &pools); }
+  EXPECT(apps == 0);
+  close(cfd); close(sfd); close(lfd);
+  unsetenv("NCCL_GPUDIRECTTCPX_RX_BUF_MGR");
+  unsetenv("NCCL_GPUDIRECTTCPX_UNIX_CLIENT_PREFIX");
+  reloadFlags();
 }
 
 TEST(dev_queue_fifo) {

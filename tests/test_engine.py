@@ -61,3 +61,30 @@ def test_plain_mode_matches_fused():
         assert torch.equal(out, (x.float() * 2).to(torch.bfloat16))
     finally:
         e.close()
+
+
+def test_engine_with_pool_from_the_rx_buffer_manager_daemon(tmp_path):
+    """Same path, but the rx page pool comes from the tcpxb_rxdm daemon over a UNIX socket."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    from nccl_plugin_gpudirecttcpx_b200 import _build
+    _build.build_host()
+    prefix = tmp_path / "rxdm"
+    daemon = subprocess.Popen([str(_build.OUT / "tcpxb_rxdm"), "--prefix", str(prefix), "--pool-mb", "64"],
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        assert daemon.stdout.readline().strip() == "ready"
+        env = dict(os.environ, NCCL_GPUDIRECTTCPX_RX_BUF_MGR="daemon", NCCL_GPUDIRECTTCPX_UNIX_CLIENT_PREFIX=str(prefix),
+                   NCCL_GPUDIRECTTCPX_REPORT_LIFECYCLE="1")
+        r = subprocess.run([sys.executable, str(Path(__file__).parent / "rxdm_engine_worker.py")], env=env,
+                           capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0 and "rxdm engine ok" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+    finally:
+        daemon.terminate()
+        try:
+            daemon.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            daemon.kill()
+    err = daemon.stderr.read()
+    assert "pool for GPU" in err

@@ -130,3 +130,23 @@ def test_fault_paths_surface_as_errors(host_lib):
     r = subprocess.run([str(LIB / "tcpxb_fault_tests")], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "8 test(s), 0 failure(s)" in r.stdout
+
+
+def test_rx_buffer_manager_daemon(host_lib, tmp_path):
+    """The out-of-process rx buffer manager: pool fd over SCM_RIGHTS, flow rules, lifecycle registry."""
+    prefix = tmp_path / "rxdm"
+    daemon = subprocess.Popen([str(LIB / "tcpxb_rxdm"), "--prefix", str(prefix), "--pool-mb", "8"],
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        assert daemon.stdout.readline().strip() == "ready"
+        env = dict(os.environ, TCPXB_TEST_RXDM_PREFIX=str(prefix))
+        r = subprocess.run([str(LIB / "tcpxb_unit_tests"), "rxdm_daemon"], capture_output=True, text=True, timeout=60, env=env)
+        assert r.returncode == 0, r.stdout + r.stderr
+        assert "ok rxdm_daemon_roundtrip" in r.stdout and "skipped" not in r.stdout
+    finally:
+        daemon.terminate()
+        try:
+            daemon.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            daemon.kill()
+    assert "application 4242 went away" in daemon.stderr.read()
