@@ -79,8 +79,46 @@ Result exchangeStateConnector(int fd, int mine, int* theirs) {
   return socketSend(fd, &mine, sizeof mine, 10000);
 }
 
+// Receive-queue bookkeeping per device: which NAPI ids the accepted sockets landed
+// on, to show how evenly flows spread over the NIC's receive queues
+// (reference: src/connect.cc:474-486, NIC_N_RXQS).
+struct NapiRecord {
+  std::mutex mu;
+  std::map<int, size_t> count;
+};
+NapiRecord g_napi[kMaxIfs];
+
+// Where the kernel last processed this socket (diagnostics only; loopback has no
+// NAPI id and reports 0).  Reference: src/connect.cc:314-336.
+void logSocketLocality(Comm* comm, int index, int fd, bool is_ctrl) {
+  int cpu = -1, napi = -1;
+  socklen_t len = sizeof cpu;
+#ifdef SO_INCOMING_CPU
+  if (getsockopt(fd, SOL_SOCKET, SO_INCOMING_CPU, &cpu, &len) != 0) cpu = -1;
+#endif
+#ifdef SO_INCOMING_NAPI_ID
+  len = sizeof napi;
+  if (getsockopt(fd, SOL_SOCKET, SO_INCOMING_NAPI_ID, &napi, &len) != 0) napi = -1;
+#endif
+  if (comm->passive && !is_ctrl && napi > 0 && comm->dev >= 0 && comm->dev < kMaxIfs) {
+    NapiRecord& rec = g_napi[comm->dev];
+    std::lock_guard<std::mutex> l(rec.mu);
+    const size_t n = ++rec.count[napi];
+    if (rec.count.size() > (size_t)flags().nic_n_rxqs)
+      INFO(kSubNet, "device %d: %zu distinct NAPI ids seen, more than NIC_N_RXQS=%ld", comm->dev, rec.count.size(),
+           (long)flags().nic_n_rxqs);
+    TRACE(kSubNet, "device %d: NAPI id %d now carries %zu flows", comm->dev, napi, n);
+  }
+  if (is_ctrl && !flags().ctrl_sockcond.empty())
+    INFO(kSubNet, "comm %lx ctrl socket: incoming cpu %d napi %d (CTRL_SOCKCOND=%s: checked, not enforced)",
+         (unsigned long)comm->id, cpu, napi, flags().ctrl_sockcond.c_str());
+  TRACE(kSubNet, "comm %lx %s socket %d: incoming cpu %d napi %d", (unsigned long)comm->id, is_ctrl ? "ctrl" : "data", index, cpu,
+        napi);
+}
+
 void attachSocket(Comm* comm, int index, int fd) {
   SocketCtx& s = comm->sock[index];
+  logSocketLocality(comm, index, fd, false);
   s.fd = fd;
   s.flow = flowString(fd, comm->passive);
   s.stats.flow_id = flowIdOf(s.flow);
@@ -89,6 +127,7 @@ void attachSocket(Comm* comm, int index, int fd) {
 }
 
 void attachCtrl(Comm* comm, int fd) {
+  logSocketLocality(comm, -1, fd, true);
   comm->ctrl_fd = fd;
   comm->ctrl_flow = flowString(fd, comm->passive);
   comm->ctrl_stats.flow_id = flowIdOf(comm->ctrl_flow);
@@ -232,6 +271,14 @@ bool finishAsync(AsyncSetup* st, Comm** out, Result* res) {
 
 }  // namespace
 
+std::string handleToString(const Handle& h) {
+  char buf[256];
+  snprintf(buf, sizeof buf, "data %s ctrl %s%s ports %d+%d socks %d threads %d", addressToString(h.connect_addr).c_str(),
+           addressToString(h.ctrl_addr).c_str(), h.redirect_ctrl ? " (redirected)" : "", h.port_start, h.port_count,
+           h.num_socks, h.num_threads);
+  return buf;
+}
+
 void chooseSocksThreads(int dev, int* nsocks, int* nthreads) {
   const Flags& f = flags();
   int threads = (int)f.nthreads, per_thread = (int)f.nsocks_per_thread;
@@ -339,8 +386,7 @@ Result netListen(int dev, void* opaque, ListenComm** out) {
   h->port_start = addressPort(h->connect_addr);
   h->port_count = 1;
   h->connect_args = nullptr;
-  TRACE(kSubNet, "listening on %s (ctrl %s), %d sockets x %d threads", addressToString(h->connect_addr).c_str(),
-        addressToString(h->ctrl_addr).c_str(), l->num_socks, l->num_threads);
+  TRACE(kSubNet, "listening: %s", handleToString(*h).c_str());
   *out = l.release();
   return kSuccess;
 }

@@ -82,6 +82,8 @@ struct Handle {
 };
 static_assert(sizeof(Handle) <= kHandleMaxSize, "handle must fit NCCL's handle buffer");
 
+std::string handleToString(const Handle& h);
+
 enum ConnState : int { kConnOk = 0, kConnPending = 1, kConnFailed = 2 };
 
 struct Comm;
