@@ -108,6 +108,18 @@ def unpack_microbench(torch, peaks, iters=20, warm=4):
     # this number: it shows the kernel's cost of writing four copies of every reduced fragment)
     peers = [torch.empty((64 << 20) // 2, dtype=torch.bfloat16, device=dev) for _ in range(3)]
     t_fan, tb_fan = timed(lambda i: U.unpack_reduce_fanout(pool, dsts[i % 3], dsts[i % 3], peers, descs[i % variants], status=st))
+    # the same result without fusion: unpack to a bounce buffer, add in a second pass, three copies
+    bounce = torch.empty((64 << 20) // 2, dtype=torch.bfloat16, device=dev)
+    n_el = total // 2 // 8 * 8
+
+    def unfused(i):
+        acc = dsts[i % 3]
+        U.unpack_copy(pool, bounce, descs[i % variants], status=st)
+        U.peer_reduce(acc[:n_el], [acc, bounce], 0)
+        for p in peers:
+            p.copy_(acc)
+
+    t_unf, tb_unf = timed(unfused)
     flat = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
     t_ref, tb_ref = timed(lambda i: dsts[i % 3].view(torch.uint8).copy_(flat))
     hbm = peaks.get("hbm_gbs", 6650.0)
@@ -125,9 +137,11 @@ def unpack_microbench(torch, peaks, iters=20, warm=4):
         "unpack_reduce_fanout3_frac_hbm": 6 * total / t_fan / 1e9 / hbm,
         "unpack_reduce_fanout3_back_to_back_us": tb_fan * 1e6,
         "unpack_reduce_fanout3_back_to_back_frac_hbm": 6 * total / tb_fan / 1e9 / hbm,
+        "unfused_unpack_add_3copies_us": t_unf * 1e6, "unfused_back_to_back_us": tb_unf * 1e6,
+        "fusion_speedup_back_to_back": tb_unf / tb_fan,
         "status": st.tolist()[0],
     }
-    del pool, descs, dsts, flat, peers
+    del pool, descs, dsts, flat, peers, bounce
     torch.cuda.empty_cache()
     return out
 
