@@ -75,6 +75,7 @@ const IntSpec kInts[] = {
     {kOwn, "RX_POOL_SCATTER", &Flags::rx_pool_scatter, 0, 2, "hand out rx pages in a scattered order"},
     {kOwn, "RX_POOL_RUN_PAGES", &Flags::rx_pool_run_pages, 1, 1025, "consecutive pages per scattered group of the rx pool"},
     {kOwn, "TX_STAGING_BYTES", &Flags::tx_staging_bytes, 1 << 16, kMax, "pinned staging per send comm for CUDA buffers"},
+    {kOwn, "CONNECT_REFUSED_RETRIES", &Flags::connect_refused_retries, 0, 10000000, "retries, 1 ms apart, while the peer refuses the connection"},
     {kOwn, "CONNECT_PACING_US", &Flags::connect_pacing_us, 0, kMax, "pause per socket during connection setup"},
     {kOwn, "NIC_SPEED_MBPS", &Flags::nic_speed_mbps, 0, 100000000, "speed reported to NCCL (0 = sysfs, else 10000)"},
     {kOwn, "CUDA_BUFFERS", &Flags::cuda_buffers, 0, 2, "host receive mode also takes CUDA pointers (plugin-side copies and kernels)"},

@@ -1,5 +1,7 @@
 #include "tcpxb/socket_utils.h"
 
+#include "tcpxb/flags.h"
+
 #include <algorithm>
 #include <arpa/inet.h>
 #include <fcntl.h>
@@ -281,7 +283,7 @@ Result connectAddress(int* fd_out, const SocketAddress& remote, const SocketAddr
     }
     const int err = errno;
     close(fd);
-    if (err == ECONNREFUSED && ++refused < kRetryRefused) { usleep(1000); continue; }
+    if (err == ECONNREFUSED && ++refused < (int)flags().connect_refused_retries) { usleep(1000); continue; }
     if (err == ETIMEDOUT && ++timedout < kRetryTimedOut) continue;
     if (err == EINTR) continue;
     WARN("connect to %s failed: %s", addressToString(remote).c_str(), strerror(err));

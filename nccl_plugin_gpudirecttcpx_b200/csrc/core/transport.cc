@@ -1100,7 +1100,27 @@ Result netTest(Request* r, int* done, int* size) {
   if (r == nullptr || done == nullptr) return kInvalidArgument;
   *done = 0;
   Comm* comm = r->comm;
-  TCPXB_CHECK(progress(comm));
+  // Callers poll every outstanding request in turn (NCCL keeps up to eight per
+  // comm).  Only the poll of the oldest request still unreported runs the progress
+  // engine; the others just look whether they have finished.  Completion is in
+  // order, so nothing a younger request could learn is missed.
+  bool drives = true;
+  {
+    const uint32_t n = comm->rq.inFlight();
+    const uint32_t base = comm->rq.frontIndex(kReqFinished);
+    for (uint32_t k = 0; k < n; ++k) {
+      Request* q = &comm->rq.slot(base + k);
+      if (q->reported) continue;
+      drives = (q == r);
+      break;
+    }
+  }
+  if (drives) {
+    TCPXB_CHECK(progress(comm));
+  } else {
+    const int err = comm->error.load(std::memory_order_acquire);
+    if (err != kSuccess) return (Result)err;
+  }
   // finished = the request has left the transmitting stage
   bool finished = false;
   const uint32_t nfin = comm->rq.count(kReqFinished);

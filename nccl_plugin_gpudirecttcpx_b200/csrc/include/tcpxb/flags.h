@@ -85,6 +85,7 @@ struct Flags {
   int64_t rx_pool_scatter = 1;         // RX_POOL_SCATTER: hand out pages in a scattered order
   int64_t rx_pool_run_pages = 8;       // RX_POOL_RUN_PAGES: consecutive pages per scattered group
   int64_t tx_staging_bytes = 32ll << 20;  // TX_STAGING_BYTES per send comm with CUDA buffers
+  int64_t connect_refused_retries = 20000;  // CONNECT_REFUSED_RETRIES x 1 ms before a refused connect fails
   int64_t connect_pacing_us = 0;       // CONNECT_PACING_US per socket (the reference sleeps 100 ms)
   int64_t nic_speed_mbps = 0;          // NIC_SPEED_MBPS override for getProperties (0 = sysfs, else 10000)
   int64_t cuda_buffers = 0;            // CUDA_BUFFERS: accept CUDA pointers in host receive mode (see transport.h)

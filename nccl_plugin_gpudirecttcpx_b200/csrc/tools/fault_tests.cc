@@ -252,6 +252,8 @@ TEST(silent_sender_trips_the_detectors) {
 }
 
 TEST(connect_to_dead_listener_fails_cleanly) {
+  setenv("NCCL_GPUDIRECTTCPX_CONNECT_REFUSED_RETRIES", "300", 1);  // 0.3 s instead of 20 s
+  EXPECT(netInit(nullptr) == kSuccess);
   char handle[kHandleMaxSize];
   ListenComm* l = nullptr;
   EXPECT(netListen(0, handle, &l) == kSuccess);
@@ -261,6 +263,8 @@ TEST(connect_to_dead_listener_fails_cleanly) {
   const uint64_t deadline = monotonicNanos() + 40ull * 1000000000ull;
   while (s == nullptr && r == kSuccess && monotonicNanos() < deadline) r = netConnect(0, handle, &s);
   EXPECT(s == nullptr && r != kSuccess);
+  unsetenv("NCCL_GPUDIRECTTCPX_CONNECT_REFUSED_RETRIES");
+  EXPECT(netInit(nullptr) == kSuccess);
 }
 
 }  // namespace
