@@ -157,7 +157,7 @@ int tcpxb_checksum(const void* buf, uint64_t bytes, uint64_t* out, void* partial
 // forbidden or dangerous: the transport's progress loop on NCCL's proxy thread
 // (a cudaMalloc there synchronises the device and can deadlock against a
 // collective kernel that is waiting for that same thread), completion callbacks,
-// and processes that were handed a fixed memory budget and may not grow it.
+// and processes that were handed a fixed amount of device memory and may not grow it.
 // The reference has nothing like it (it owns no kernel at all).
 //
 //  * The array takes TCPXB_CHECKSUM_NOALLOC_SCRATCH_BYTES on every GPU that loads

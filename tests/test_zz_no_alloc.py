@@ -3,7 +3,7 @@
 Some callers of this library may not allocate device memory: the transport's
 progress loop runs on NCCL's proxy thread, where a cudaMalloc would synchronise
 the device and can deadlock against a collective that is waiting for that very
-thread, and embedders may run under a fixed memory budget.  For them
+thread, and embedders may run with a fixed amount of device memory.  For them
 `tcpxb_checksum_noalloc` keeps its scratch in an array inside the library.  This
 test checks it against the ordinary entry point (caller-provided scratch), twice in
 a row because every call reuses the same array, and checks the size limit.
