@@ -20,21 +20,44 @@ const char* lastError() { return g_err; }
 
 #ifdef TCPXB_NO_CUDA
 
-bool compiledWithCuda() { return false; }
-bool available() { return false; }
-int deviceCount() { return 0; }
-static Result none() {
+// Without CUDA there are two behaviours.  By default every call reports "no CUDA".
+// With TCPXB_FAKE_GPU=1 in the environment the calls act on host memory instead: one
+// "device" whose memory is the process's own, copies that are memcpy, streams that
+// run everything at once and events that are always complete.  That lets the
+// CUDA-buffer send path, the page pool, the scatter lists and the device-handle
+// protocol run, and be checked by the sanitizers, on machines with no GPU.
+namespace {
+bool fake() {
+  static const bool on = [] {
+    const char* v = getenv("TCPXB_FAKE_GPU");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  return on;
+}
+Result none() {
   snprintf(g_err, sizeof g_err, "built without CUDA");
   return kUnhandledCudaError;
 }
-Result currentDevice(int*) { return none(); }
-Result setDevice(int) { return none(); }
-Result pointerInfo(const void*, int* device, bool* is_device) {
-  *device = -1;
-  *is_device = false;
+int g_fake_stream_tag, g_fake_event_tag;
+}  // namespace
+
+bool compiledWithCuda() { return false; }
+bool devicePointersPossible() { return fake(); }
+bool available() { return fake(); }
+int deviceCount() { return fake() ? 1 : 0; }
+Result currentDevice(int* dev) {
+  if (!fake()) return none();
+  *dev = 0;
   return kSuccess;
 }
-std::string pciBusId(int) { return ""; }
+Result setDevice(int dev) { return fake() && dev == 0 ? kSuccess : none(); }
+Result pointerInfo(const void*, int* device, bool* is_device) {
+  // every pointer a caller declares as device memory is taken at its word
+  *device = fake() ? 0 : -1;
+  *is_device = fake();
+  return kSuccess;
+}
+std::string pciBusId(int) { return fake() ? "0000:00:00.0" : ""; }
 int numaNode(int) { return 0; }
 Result hostAllocMapped(size_t bytes, void** host_ptr, void** dev_ptr) {
   void* p = nullptr;
@@ -46,21 +69,44 @@ Result hostAllocMapped(size_t bytes, void** host_ptr, void** dev_ptr) {
 void hostFreeMapped(void* p) { free(p); }
 Result hostRegisterMapped(void* host_ptr, size_t, void** dev_ptr) { *dev_ptr = host_ptr; return kSuccess; }
 void hostUnregister(void*) {}
-Result deviceAlloc(size_t, void**) { return none(); }
-void deviceFree(void*) {}
-Result streamCreate(Stream*) { return none(); }
+Result deviceAlloc(size_t bytes, void** ptr) {
+  if (!fake()) return none();
+  void* p = nullptr;
+  if (posix_memalign(&p, 256, bytes ? bytes : 256) != 0) return kSystemError;
+  *ptr = p;
+  return kSuccess;
+}
+void deviceFree(void* p) { free(p); }
+Result streamCreate(Stream* s) {
+  if (!fake()) return none();
+  *s = &g_fake_stream_tag;
+  return kSuccess;
+}
 void streamDestroy(Stream) {}
-Result eventCreate(Event*) { return none(); }
+Result eventCreate(Event* e) {
+  if (!fake()) return none();
+  *e = &g_fake_event_tag;
+  return kSuccess;
+}
 void eventDestroy(Event) {}
-Result eventRecord(Event, Stream) { return none(); }
-Result eventQuery(Event) { return none(); }
-Result streamSynchronize(Stream) { return none(); }
-Result streamWaitEvent(Stream, Event) { return none(); }
-Result eventSynchronize(Event) { return none(); }
-Result copyDeviceToDeviceAsync(void*, const void*, size_t, Stream) { return none(); }
-Result copyToHostAsync(void*, const void*, size_t, Stream) { return none(); }
-Result copyToDeviceAsync(void*, const void*, size_t, Stream) { return none(); }
-Result memsetAsync(void*, int, size_t, Stream) { return none(); }
+Result eventRecord(Event, Stream) { return fake() ? kSuccess : none(); }
+Result eventQuery(Event) { return fake() ? kSuccess : none(); }
+Result streamSynchronize(Stream) { return fake() ? kSuccess : none(); }
+Result streamWaitEvent(Stream, Event) { return fake() ? kSuccess : none(); }
+Result eventSynchronize(Event) { return fake() ? kSuccess : none(); }
+static Result fakeCopy(void* dst, const void* src, size_t bytes) {
+  if (!fake()) return none();
+  memmove(dst, src, bytes);
+  return kSuccess;
+}
+Result copyDeviceToDeviceAsync(void* d, const void* s, size_t n, Stream) { return fakeCopy(d, s, n); }
+Result copyToHostAsync(void* d, const void* s, size_t n, Stream) { return fakeCopy(d, s, n); }
+Result copyToDeviceAsync(void* d, const void* s, size_t n, Stream) { return fakeCopy(d, s, n); }
+Result memsetAsync(void* p, int value, size_t n, Stream) {
+  if (!fake()) return none();
+  memset(p, value, n);
+  return kSuccess;
+}
 
 #else  // CUDA build
 
@@ -88,6 +134,7 @@ int probeCount() {
 }  // namespace
 
 bool compiledWithCuda() { return true; }
+bool devicePointersPossible() { return true; }
 int deviceCount() { return probeCount(); }
 bool available() { return probeCount() > 0; }
 

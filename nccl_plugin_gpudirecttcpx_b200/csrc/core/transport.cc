@@ -67,13 +67,13 @@ void watchdogRegister(Comm* c) {
   std::thread([secs] {
     for (;;) {
       sleep((unsigned)secs);
-      std::lock_guard<std::mutex> l(g_wd_mu);
+      std::lock_guard<std::mutex> guard(g_wd_mu);
       const uint64_t now = monotonicNanos();
-      for (Comm* c : g_wd_comms) {
-        const char* w = c->where.load();
-        const uint64_t t = c->where_ns.load();
+      for (Comm* wc : g_wd_comms) {
+        const char* w = wc->where.load();
+        const uint64_t t = wc->where_ns.load();
         if (strcmp(w, "idle") != 0 && now - t > (uint64_t)secs * 1000000000ull)
-          WARN("watchdog: %s comm %lx has been at '%s' for %lu ms", c->passive ? "recv" : "send", (unsigned long)c->id, w,
+          WARN("watchdog: %s comm %lx has been at '%s' for %lu ms", wc->passive ? "recv" : "send", (unsigned long)wc->id, w,
                (unsigned long)((now - t) / 1000000));
       }
     }
@@ -526,7 +526,8 @@ Result describePages(Comm* comm, Request* r, Task* t) {
     }
     for (uint32_t p = 0; p < run.count && left > 0; ++p) {
       if (r->slot.filled >= (uint64_t)kUnpackMaxSlicePages) {
-        WARN("receive of %d bytes needs more than %d page fragments", r->size, kUnpackMaxSlicePages);
+        WARN("receive of %d bytes into device memory needs more than the %d page records of a scatter-list slot "
+             "(%d bytes at most per receive)", r->size, kUnpackMaxSlicePages, kUnpackMaxSlicePages * (int)kRxPageBytes);
         return kInternalError;
       }
       const uint32_t len = (uint32_t)std::min<int>(left, (int)kRxPageBytes);
@@ -544,8 +545,21 @@ Result describePages(Comm* comm, Request* r, Task* t) {
 
 Result launchUnpack(Comm* comm, Request* r) {
 #ifdef TCPXB_NO_CUDA
-  (void)comm; (void)r;
-  return kInvalidUsage;
+  // stand-in device: apply the scatter list on the host, with the kernel's checks
+  if (!gpu::available()) return kInvalidUsage;
+  for (uint64_t i = 0; i < r->slot.filled; ++i) {
+    const LoadMeta& m = r->slot.mem[i];
+    if ((uint64_t)m.src_off + m.len > comm->rxmgr->bytes() || m.dst_off + m.len > (uint64_t)r->size) {
+      comm->unpack_status_host[0] = 1;
+      comm->unpack_status_host[1] = (uint32_t)i;
+      break;
+    }
+    memcpy(r->data + m.dst_off, comm->rxmgr->hostBase() + m.src_off, m.len);
+  }
+  if (r->unpack_event == nullptr) TCPXB_CHECK(gpu::eventCreate(&r->unpack_event));
+  TCPXB_CHECK(gpu::eventRecord(r->unpack_event, comm->stream));
+  r->unpack_launched = true;
+  return kSuccess;
 #else
   mark(comm, "launchUnpack:kernel");
   if (r->slot.filled > 0) {
@@ -929,14 +943,14 @@ Result netGetProperties(int dev, NetProperties* p) {
   // CUDA pointers are advertised in unpack mode (the consumer's kernel unpacks, the
   // plugin makes no CUDA call on the data path) and, on request, in host mode,
   // where the plugin itself queues copies and kernels from the caller's thread.
-  const bool cuda_ptrs = gpu::compiledWithCuda() && (flags().recv_mode == kRecvModeUnpack || flags().cuda_buffers != 0);
+  const bool cuda_ptrs = gpu::devicePointersPossible() && (flags().recv_mode == kRecvModeUnpack || flags().cuda_buffers != 0);
   p->ptr_support = kPtrHost | (cuda_ptrs ? kPtrCuda : 0);
   p->speed_mbps = d->speed_mbps;
   p->port = 0;
   p->latency = 0;
   p->max_comms = 65536;
   p->max_recvs = 1;
-  const bool unpack = flags().recv_mode == kRecvModeUnpack && gpu::compiledWithCuda();
+  const bool unpack = flags().recv_mode == kRecvModeUnpack && gpu::devicePointersPossible();
   p->device_type = unpack ? 1 : 0;
   p->device_version = unpack ? kUnpackVersion : 0;
   return kSuccess;

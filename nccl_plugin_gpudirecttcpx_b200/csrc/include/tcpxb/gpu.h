@@ -7,6 +7,10 @@
 // runs on machines with no GPU and no driver; and when the core is compiled with
 // TCPXB_NO_CUDA every call reports "no CUDA" and pinned allocations fall back to
 // page-aligned host memory, which keeps the buffer-manager logic testable on CPUs.
+// A TCPXB_NO_CUDA build started with TCPXB_FAKE_GPU=1 goes one step further: it
+// presents one stand-in device whose memory is host memory (copies are memcpy,
+// events are always complete), so that the paths that take CUDA pointers can be
+// driven end to end, under the sanitizers, without a GPU.
 #ifndef TCPXB_GPU_H_
 #define TCPXB_GPU_H_
 
@@ -20,6 +24,10 @@ namespace tcpxb {
 namespace gpu {
 
 bool compiledWithCuda();
+// True when a pointer handed to the transport may be device memory: always in a
+// CUDA build (the runtime is not touched to answer), only with the stand-in device
+// otherwise.
+bool devicePointersPossible();
 // True when the CUDA runtime initialises and reports at least one device.
 bool available();
 int deviceCount();

@@ -3,6 +3,16 @@
 //
 //   tcpxb_loopback --plugin <libnccl-net.so | libtcpxb_host.so> [--v7]
 //                  [--sizes 1024,65536,4194304,67108864] [--inflight 8] [--iters 4]
+//                  [--ptr host|cuda]
+//
+// `--ptr cuda` registers the buffers as device memory.  It is meant for the host-only
+// library started with TCPXB_FAKE_GPU=1, whose stand-in device is host memory: the
+// sender then goes through the staging ring and the receiver through the page pool
+// and the scatter lists.  When the plugin hands out an unpack device handle
+// (NCCL_GPUDIRECTTCPX_RECV_MODE=unpack) the receiver also plays the part of NCCL's
+// unpack consumer: for each finished receive it advances the handle's head, reads
+// that slot's count and records from the mapped block, copies the fragments out of
+// the bounce buffer and only then calls irecvConsumed.
 //
 // The parent is the receiver, the forked child the sender.  One comm is opened per
 // device the plugin reports (set NCCL_GPUDIRECTTCPX_VIRTUAL_NICS=2 to get two
@@ -13,6 +23,7 @@
 // The reference has no such tool: its only tests are two unit tests of the stats
 // code (reference: src/stats/tracepoint_test.cc, src/stats/stats_buffer_test.cc).
 #include <dlfcn.h>
+#include <signal.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -43,7 +54,15 @@ struct Api {
   ncclResult_t (*closeSend)(void*);
   ncclResult_t (*closeRecv)(void*);
   ncclResult_t (*closeListen)(void*);
+  ncclResult_t (*irecvConsumed)(void*, int, void*);
 };
+
+// What a consumer of the unpack device handle sees (NCCL's device-side layout).
+constexpr int kQueueDepth = 16;
+constexpr int kSlotRecords = 2048;
+struct Record { uint32_t src_off, len; uint64_t dst_off; };
+struct MetaBlock { Record mem[kQueueDepth][kSlotRecords]; uint64_t cnt[kQueueDepth]; };
+struct DeviceHandle { MetaBlock* meta; uint8_t* bounce_buf; uint64_t head; };
 
 int (*flow_counters)(void*, tcpxbFlowCounters*, int) = nullptr;
 int (*stats_text)(void*, char*, int) = nullptr;
@@ -92,19 +111,36 @@ bool loadApi(const char* path, bool v7, Api* api) {
     auto* t = (ncclNet_v7_t*)dlsym(h, "ncclNetPlugin_v7");
     if (t == nullptr) return false;
     *api = {t->name, t->init, t->devices, t->listen, t->connect, t->accept, nullptr, t->regMr, t->deregMr,
-            t->isend, t->irecv, t->test, t->closeSend, t->closeRecv, t->closeListen};
+            t->isend, t->irecv, t->test, t->closeSend, t->closeRecv, t->closeListen, t->irecvConsumed};
   } else {
     auto* t = (ncclNet_v8_t*)dlsym(h, "ncclNetPlugin_v8");
     if (t == nullptr) return false;
     *api = {t->name, t->init, t->devices, t->listen, t->connect, t->accept, t->regMr, nullptr, t->deregMr,
-            t->isend, t->irecv, t->test, t->closeSend, t->closeRecv, t->closeListen};
+            t->isend, t->irecv, t->test, t->closeSend, t->closeRecv, t->closeListen, t->irecvConsumed};
   }
   return true;
 }
 
-ncclResult_t regMr(const Api& api, void* comm, void* data, size_t size, void** mh) {
-  if (api.regMr8) return api.regMr8(comm, data, size, NCCL_PTR_HOST, mh);
-  return api.regMr7(comm, data, (int)size, NCCL_PTR_HOST, mh);
+ncclResult_t regMr(const Api& api, void* comm, void* data, size_t size, int type, void** mh) {
+  if (api.regMr8) return api.regMr8(comm, data, size, type, mh);
+  return api.regMr7(comm, data, (int)size, type, mh);
+}
+
+// One step of the unpack consumer: returns false on a malformed slot.
+bool consumeSlot(DeviceHandle* h, uint8_t* dst, size_t size) {
+  h->head += 1;  // starts at all-ones: the first slot is 0
+  const uint64_t slot = h->head % kQueueDepth;
+  const uint64_t cnt = __atomic_load_n(&h->meta->cnt[slot], __ATOMIC_ACQUIRE);
+  if (cnt > (uint64_t)kSlotRecords) { fprintf(stderr, "slot %lu holds %lu records\n", (unsigned long)slot, (unsigned long)cnt); return false; }
+  uint64_t covered = 0;
+  for (uint64_t i = 0; i < cnt; ++i) {
+    const Record& m = h->meta->mem[slot][i];
+    if (m.dst_off + m.len > size) { fprintf(stderr, "record %lu leaves the buffer\n", (unsigned long)i); return false; }
+    memcpy(dst + m.dst_off, h->bounce_buf + m.src_off, m.len);
+    covered += m.len;
+  }
+  if (covered != size) { fprintf(stderr, "records cover %lu of %zu bytes\n", (unsigned long)covered, size); return false; }
+  return true;
 }
 
 void printFlows(const char* side, int ci, void* comm) {
@@ -129,6 +165,7 @@ struct Options {
   int inflight = 8;
   int iters = 4;
   uint64_t seed = 42;
+  int ptr_type = NCCL_PTR_HOST;
 };
 
 int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
@@ -140,12 +177,23 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
   if (ndev < 1) { fprintf(stderr, "no devices\n"); return 1; }
   const int ncomm = ndev;
   std::vector<void*> comms(ncomm, nullptr), listens(ncomm, nullptr);
+  std::vector<DeviceHandle*> unpack(ncomm, nullptr);
   if (receiver) {
     std::vector<char> handles((size_t)ncomm * NCCL_NET_HANDLE_MAXSIZE, 0);
     for (int c = 0; c < ncomm; ++c) CHECK(api.listen(c, &handles[(size_t)c * NCCL_NET_HANDLE_MAXSIZE], &listens[c]));
     if (write(wfd, handles.data(), handles.size()) != (ssize_t)handles.size()) return 1;
     for (int c = 0; c < ncomm; ++c)
-      while (comms[c] == nullptr) { ncclNetDeviceHandle_v8_t* dh = nullptr; CHECK(api.accept(listens[c], &comms[c], &dh)); }
+      while (comms[c] == nullptr) {
+        ncclNetDeviceHandle_v8_t* dh = nullptr;
+        CHECK(api.accept(listens[c], &comms[c], &dh));
+        if (comms[c] == nullptr || dh == nullptr || dh->netDeviceType != NCCL_NET_DEVICE_UNPACK) continue;
+        if (opt.ptr_type != NCCL_PTR_CUDA || getenv("TCPXB_FAKE_GPU") == nullptr) {
+          fprintf(stderr, "the plugin offers an unpack handle; this tool can only consume it with --ptr cuda on the stand-in device\n");
+          return 1;
+        }
+        if (dh->size != sizeof(DeviceHandle)) { fprintf(stderr, "device handle of %zu bytes\n", dh->size); return 1; }
+        unpack[c] = static_cast<DeviceHandle*>(dh->handle);
+      }
   } else {
     std::vector<char> handles((size_t)ncomm * NCCL_NET_HANDLE_MAXSIZE, 0);
     size_t got = 0;
@@ -169,7 +217,7 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
     std::vector<std::vector<uint8_t>> bufs(nbuf, std::vector<uint8_t>(size ? size : 1));
     std::vector<uint8_t> expect(size ? size : 1);
     std::vector<void*> mh(nbuf, nullptr);
-    for (int b = 0; b < nbuf; ++b) CHECK(regMr(api, comms[b / opt.inflight], bufs[b].data(), size, &mh[b]));
+    for (int b = 0; b < nbuf; ++b) CHECK(regMr(api, comms[b / opt.inflight], bufs[b].data(), size, opt.ptr_type, &mh[b]));
     // both sides start a size together: receiver -> sender token, sender waits
     char tok = 'g';
     if (receiver) { if (write(wfd, &tok, 1) != 1) return 1; }
@@ -204,6 +252,12 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
           int d = 0, sz = -1;
           CHECK(api.test(reqs[b], &d, &sz));
           if (!d) continue;
+          if (receiver && unpack[b / opt.inflight] != nullptr) {
+            // requests of one comm finish in posting order, which is the FIFO order of the slots
+            if (sz > 0 && !consumeSlot(unpack[b / opt.inflight], bufs[b].data(), (size_t)sz)) return 1;
+            else if (sz == 0) unpack[b / opt.inflight]->head += 1;
+            CHECK(api.irecvConsumed(comms[b / opt.inflight], 1, reqs[b]));
+          }
           done[b] = 1;
           ++finished;
           got_size[b] = sz;
@@ -252,6 +306,7 @@ int main(int argc, char** argv) {
     else if (a == "--inflight") opt.inflight = atoi(next());
     else if (a == "--iters") opt.iters = atoi(next());
     else if (a == "--seed") opt.seed = strtoull(next(), nullptr, 0);
+    else if (a == "--ptr") opt.ptr_type = std::string(next()) == "cuda" ? NCCL_PTR_CUDA : NCCL_PTR_HOST;
     else if (a == "--sizes") {
       opt.sizes.clear();
       std::string s = next();
@@ -281,6 +336,7 @@ int main(int argc, char** argv) {
   close(to_child[0]);
   close(to_parent[1]);
   int rc = runSide(true, opt, to_parent[0], to_child[1]);
+  if (rc != 0) kill(pid, SIGTERM);  // the sender may be waiting for a receiver that gave up
   int status = 0;
   waitpid(pid, &status, 0);
   if (!WIFEXITED(status) || WEXITSTATUS(status) != 0) rc = 1;

@@ -124,6 +124,61 @@ def test_loopback_under_sanitizer(san):
     assert "WARNING: ThreadSanitizer" not in r.stderr and "ERROR: AddressSanitizer" not in r.stderr
 
 
+STANDIN_VARIANTS = [
+    # plugin-side unpack: staging ring on the sender, page pool + scatter list + host unpack on the receiver
+    dict(NCCL_GPUDIRECTTCPX_CUDA_BUFFERS=1),
+    dict(NCCL_GPUDIRECTTCPX_CUDA_BUFFERS=1, NCCL_GPUDIRECTTCPX_RX_POOL_SCATTER=1, NCCL_GPUDIRECTTCPX_RX_POOL_BYTES=32 << 20),
+    dict(NCCL_GPUDIRECTTCPX_CUDA_BUFFERS=1, NCCL_GPUDIRECTTCPX_RX_POOL_MODE="device"),
+    # consumer-side unpack: the tool plays NCCL's unpack kernel against the device handle
+    dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack"),
+    dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_GPUDIRECTTCPX_RX_POOL_SCATTER=1, NCCL_GPUDIRECTTCPX_RX_POOL_BYTES=32 << 20),
+    dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_GPUDIRECTTCPX_RX_POOL_MODE="device", args=["--v7"]),
+]
+
+
+@pytest.mark.parametrize("variant", STANDIN_VARIANTS)
+def test_device_pointer_paths_on_standin_device(host_lib, variant):
+    """The paths that take CUDA pointers, run on the host-only build's stand-in device
+    (device memory = host memory): staged sends, page pool, scatter lists, the unpack
+    device-handle protocol {meta, bounce_buf, head} and irecvConsumed, byte-exact."""
+    variant = dict(variant)
+    args = variant.pop("args", []) + ["--ptr", "cuda", "--sizes", "0,1,1000,4097,300000,4194304,8388608", "--inflight", "8", "--iters", "2"]
+    r = _loopback(host_lib, args, TCPXB_FAKE_GPU=1, **variant)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "loopback PASSED" in r.stdout
+    rows, _ = _parse(r.stdout)
+    assert len(rows) == 7 and all(row["byte_exact"] for row in rows)
+
+
+def test_standin_device_oversize_receive_is_an_error(host_lib):
+    """A device-memory receive that needs more page records than a scatter-list slot holds
+    fails with an error from test(), and the tool ends instead of hanging."""
+    r = _loopback(host_lib, ["--ptr", "cuda", "--sizes", str(16 << 20), "--inflight", "1", "--iters", "1"], timeout=120,
+                  TCPXB_FAKE_GPU=1, NCCL_GPUDIRECTTCPX_CUDA_BUFFERS=1)
+    assert r.returncode != 0
+    assert "page records of a scatter-list slot" in r.stderr
+
+
+def test_host_build_rejects_device_pointers_without_standin(host_lib):
+    r = _loopback(host_lib, ["--ptr", "cuda", "--sizes", "1024", "--iters", "1"], timeout=120, NCCL_GPUDIRECTTCPX_CUDA_BUFFERS=1)
+    assert r.returncode != 0
+    assert "is not device memory" in r.stderr
+
+
+@pytest.mark.parametrize("san", ["address", "thread"])
+@pytest.mark.parametrize("mode", ["host", "unpack"])
+def test_standin_device_under_sanitizer(san, mode):
+    lib = _build.build_host(sanitize=san)
+    env = {"ASAN_OPTIONS": "detect_leaks=0", "TSAN_OPTIONS": "halt_on_error=1 second_deadlock_stack=1", "TCPXB_FAKE_GPU": "1",
+           "NCCL_GPUDIRECTTCPX_RX_POOL_SCATTER": "1", "NCCL_GPUDIRECTTCPX_RX_POOL_BYTES": str(64 << 20)}
+    env.update({"NCCL_GPUDIRECTTCPX_RECV_MODE": "unpack"} if mode == "unpack" else {"NCCL_GPUDIRECTTCPX_CUDA_BUFFERS": "1"})
+    r = _loopback(lib, ["--ptr", "cuda", "--sizes", "0,1000,65536,2000000", "--inflight", "8", "--iters", "2"],
+                  exe=f"tcpxb_loopback_{san}", timeout=600, **env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
+    assert "loopback PASSED" in r.stdout
+    assert "WARNING: ThreadSanitizer" not in r.stderr and "ERROR: AddressSanitizer" not in r.stderr
+
+
 def test_fault_paths_surface_as_errors(host_lib):
     """Closed peer, socket shutdown in mid-message, forged control records, oversize message,
     full request ring, silent sender: error codes or retries, never a hang."""
