@@ -1117,7 +1117,8 @@ Result netTest(Request* r, int* done, int* size) {
   // Callers poll every outstanding request in turn (NCCL keeps up to eight per
   // comm).  Only the poll of the oldest request still unreported runs the progress
   // engine; the others just look whether they have finished.  Completion is in
-  // order, so nothing a younger request could learn is missed.
+  // order, so nothing a younger request could learn is missed.  A caller that keeps
+  // polling a younger request alone still gets progress: every 32nd such poll drives.
   bool drives = true;
   {
     const uint32_t n = comm->rq.inFlight();
@@ -1129,7 +1130,9 @@ Result netTest(Request* r, int* done, int* size) {
       break;
     }
   }
+  if (!drives && ++comm->polls_not_driving >= 32) drives = true;
   if (drives) {
+    comm->polls_not_driving = 0;
     TCPXB_CHECK(progress(comm));
   } else {
     const int err = comm->error.load(std::memory_order_acquire);

@@ -210,6 +210,7 @@ struct Comm {
   std::atomic<const char*> where{"idle"};  // last checkpoint the API thread passed (watchdog)
   std::atomic<uint64_t> where_ns{0};
   bool want_device_handle = false;
+  uint32_t polls_not_driving = 0;  // test() calls since the progress engine last ran
   // telemetry
   std::unique_ptr<EventLog> events;
   std::unique_ptr<Exporter> exporter;

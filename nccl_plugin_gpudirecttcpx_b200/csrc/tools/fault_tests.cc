@@ -7,6 +7,10 @@
 // (reference: src/sock/tcpx.h:186-281 exits on cmsg anomalies; a helper thread that
 // hits a socket error just returns, src/net_tcpx.cc:329,350, and the proxy then
 // polls forever).  Here they must surface as error codes from test().
+//
+// The device-memory cases run on the host-only library's stand-in device
+// (TCPXB_FAKE_GPU=1, set by main): a consumer that falls behind, frees slots out of
+// order or sits on the pool's pages must see "try again" or an error, never a hang.
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -19,6 +23,7 @@
 #include <string>
 #include <vector>
 
+#include "tcpxb/dev_queue.h"
 #include "tcpxb/transport.h"
 
 using namespace tcpxb;
@@ -151,6 +156,28 @@ TEST(request_ring_full_returns_no_request) {
   closePair(&p);
 }
 
+TEST(polling_only_a_younger_request_still_progresses) {
+  // test() runs the progress engine from the oldest unreported request; a caller that
+  // never polls that one must not starve.
+  Pair p;
+  EXPECT(makePair(&p));
+  std::vector<uint8_t> src0(1 << 20, 1), src1(1 << 20, 2), dst0(1 << 20), dst1(1 << 20);
+  Request *rs0 = nullptr, *rs1 = nullptr, *rr0 = nullptr, *rr1 = nullptr;
+  void* d0 = dst0.data();
+  void* d1 = dst1.data();
+  int sz = 1 << 20, tag = 0;
+  EXPECT(netIrecv(p.r, 1, &d0, &sz, &tag, nullptr, &rr0) == kSuccess && rr0 != nullptr);
+  EXPECT(netIrecv(p.r, 1, &d1, &sz, &tag, nullptr, &rr1) == kSuccess && rr1 != nullptr);
+  EXPECT(netIsend(p.s, src0.data(), sz, 0, nullptr, &rs0) == kSuccess && rs0 != nullptr);
+  EXPECT(netIsend(p.s, src1.data(), sz, 0, nullptr, &rs1) == kSuccess && rs1 != nullptr);
+  int done = 0, got = 0;
+  EXPECT(pollBounded(rr1, &done, &got, rs1) == kSuccess && done && got == sz && dst1 == src1);
+  EXPECT(pollBounded(rs1, &done, &got) == kSuccess && done);
+  EXPECT(pollBounded(rr0, &done, &got, rs0) == kSuccess && done && dst0 == src0);
+  EXPECT(pollBounded(rs0, &done, &got) == kSuccess && done);
+  closePair(&p);
+}
+
 TEST(peer_closed_gives_error_not_hang) {
   Pair p;
   EXPECT(makePair(&p));
@@ -267,9 +294,114 @@ TEST(connect_to_dead_listener_fails_cleanly) {
   EXPECT(netInit(nullptr) == kSuccess);
 }
 
+// ---- device-memory receives on the stand-in device
+void unpackModeOn(const char* pool_bytes) {
+  setenv("NCCL_GPUDIRECTTCPX_RECV_MODE", "unpack", 1);
+  setenv("NCCL_GPUDIRECTTCPX_RX_POOL_BYTES", pool_bytes, 1);  // the first device receive sizes the pool for the process
+  EXPECT(netInit(nullptr) == kSuccess);
+}
+void unpackModeOff() {
+  unsetenv("NCCL_GPUDIRECTTCPX_RECV_MODE");
+  unsetenv("NCCL_GPUDIRECTTCPX_RX_POOL_BYTES");
+  EXPECT(netInit(nullptr) == kSuccess);
+}
+
+struct DevXfer {
+  std::vector<uint8_t> src, dst;
+  MemHandle *smh = nullptr, *rmh = nullptr;
+  Request *rs = nullptr, *rr = nullptr;
+};
+
+// Registers both buffers as device memory and posts the receive, then the send.
+bool postDevXfer(Pair* p, DevXfer* x, int size, int tag, uint8_t fill) {
+  x->src.assign((size_t)size, fill);
+  x->dst.assign((size_t)size, 0);
+  if (netRegMr(p->s, x->src.data(), x->src.size(), kPtrCuda, &x->smh) != kSuccess) return false;
+  if (netRegMr(p->r, x->dst.data(), x->dst.size(), kPtrCuda, &x->rmh) != kSuccess) return false;
+  void* data = x->dst.data();
+  int sz = size;
+  if (netIrecv(p->r, 1, &data, &sz, &tag, &x->rmh, &x->rr) != kSuccess || x->rr == nullptr) return false;
+  return netIsend(p->s, x->src.data(), size, tag, x->smh, &x->rs) == kSuccess && x->rs != nullptr;
+}
+
+// The consumer's part: copy the fragments out of the pool.  Records arrive in the order
+// the chunks finished, so only bounds and total coverage are checked here; the byte
+// comparison by the caller catches overlaps and holes.
+bool applyScatterList(Request* rr, std::vector<uint8_t>* dst) {
+  ScatterList sl;
+  if (netRequestScatterList(rr, &sl) != kSuccess) return false;
+  uint64_t covered = 0;
+  for (uint64_t i = 0; i < sl.count; ++i) {
+    const LoadMeta& m = sl.host[i];
+    if (m.dst_off + m.len > dst->size() || (uint64_t)m.src_off + m.len > sl.pool_bytes) return false;
+    memcpy(dst->data() + m.dst_off, static_cast<const uint8_t*>(sl.pool_dev) + m.src_off, m.len);
+    covered += m.len;
+  }
+  return covered == dst->size();
+}
+
+TEST(device_consumer_behind_gets_try_again) {
+  unpackModeOn("8388608");
+  Pair p;
+  EXPECT(makePair(&p));
+  std::vector<DevXfer> x(kUnpackQueueDepth);
+  int done = 0, got = 0;
+  for (int i = 0; i < kUnpackQueueDepth; ++i) {
+    EXPECT(postDevXfer(&p, &x[i], 20000, i, (uint8_t)(i + 1)));
+    EXPECT(pollBounded(x[i].rr, &done, &got, x[i].rs) == kSuccess && done && got == 20000);
+    EXPECT(pollBounded(x[i].rs, &done, &got) == kSuccess && done);
+  }
+  // every scatter-list slot now waits for its consumer: a further receive is "try again", not an error
+  std::vector<uint8_t> extra(20000);
+  MemHandle* emh = nullptr;
+  EXPECT(netRegMr(p.r, extra.data(), extra.size(), kPtrCuda, &emh) == kSuccess);
+  void* data = extra.data();
+  int sz = 20000, tag = 99;
+  Request* rr = nullptr;
+  EXPECT(netIrecv(p.r, 1, &data, &sz, &tag, &emh, &rr) == kSuccess && rr == nullptr);
+  // slots are freed oldest first; freeing a younger one is refused and changes nothing
+  EXPECT(netIrecvConsumed(p.r, 1, x[1].rr) == kInvalidUsage);
+  EXPECT(applyScatterList(x[0].rr, &x[0].dst) && x[0].dst == x[0].src);
+  EXPECT(netIrecvConsumed(p.r, 1, x[0].rr) == kSuccess);
+  EXPECT(netIrecv(p.r, 1, &data, &sz, &tag, &emh, &rr) == kSuccess && rr != nullptr);  // room again
+  for (int i = 1; i < kUnpackQueueDepth; ++i) {
+    EXPECT(applyScatterList(x[i].rr, &x[i].dst) && x[i].dst == x[i].src);
+    EXPECT(netIrecvConsumed(p.r, 1, x[i].rr) == kSuccess);
+  }
+  closePair(&p);
+  unpackModeOff();
+}
+
+TEST(device_pool_exhaustion_is_backpressure) {
+  unpackModeOn("8388608");  // an 8 MiB pool (already created by the previous device test, same size)
+  Pair p;
+  EXPECT(makePair(&p));
+  // four 4 MiB messages want twice the pool; the consumer holds on to what it has received
+  std::vector<DevXfer> x(4);
+  for (int i = 0; i < 4; ++i) EXPECT(postDevXfer(&p, &x[i], 4 << 20, i, (uint8_t)(0x40 + i)));
+  int done = 0, got = 0;
+  EXPECT(pollBounded(x[0].rr, &done, &got, x[0].rs) == kSuccess && done);
+  EXPECT(pollBounded(x[1].rr, &done, &got, x[1].rs) == kSuccess && done);
+  // the third cannot finish while the first two keep the pages: still in progress after a while, no error
+  const uint64_t until = monotonicNanos() + 200000000ull;
+  while (monotonicNanos() < until) {
+    EXPECT(netTest(x[2].rr, &done, &got) == kSuccess && !done);
+    if (!g_ok) break;
+  }
+  for (int i = 0; i < 4; ++i) {
+    if (i >= 2) EXPECT(pollBounded(x[i].rr, &done, &got, x[i].rs) == kSuccess && done && got == (4 << 20));
+    EXPECT(applyScatterList(x[i].rr, &x[i].dst) && x[i].dst == x[i].src);
+    EXPECT(netIrecvConsumed(p.r, 1, x[i].rr) == kSuccess);  // returns the pages; the next message can land
+  }
+  for (int i = 0; i < 4; ++i) EXPECT(pollBounded(x[i].rs, &done, &got) == kSuccess && done);
+  closePair(&p);
+  unpackModeOff();
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
+  setenv("TCPXB_FAKE_GPU", "1", 0);
   setenv("NCCL_GPUDIRECTTCPX_SOCKET_IFNAME", "lo", 0);
   setenv("NCCL_SOCKET_NTHREADS", "2", 0);
   setenv("NCCL_NSOCKS_PERTHREAD", "2", 0);
@@ -279,6 +411,7 @@ int main(int argc, char** argv) {
   for (const Test& t : tests()) {
     if (*filter && strstr(t.name, filter) == nullptr) continue;
     g_ok = true;
+    g_seen.clear();  // request addresses are reused from one test to the next
     t.fn();
     printf("%s %s\n", g_ok ? "ok" : "FAIL", t.name);
     fflush(stdout);

@@ -181,10 +181,22 @@ def test_standin_device_under_sanitizer(san, mode):
 
 def test_fault_paths_surface_as_errors(host_lib):
     """Closed peer, socket shutdown in mid-message, forged control records, oversize message,
-    full request ring, silent sender: error codes or retries, never a hang."""
+    full request ring, silent sender, a caller that polls only a younger request, and on the
+    stand-in device a consumer that falls behind, frees slots out of order or holds the pool's
+    pages: error codes, "try again" or back-pressure, never a hang."""
     r = subprocess.run([str(LIB / "tcpxb_fault_tests")], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert "8 test(s), 0 failure(s)" in r.stdout
+    assert "11 test(s), 0 failure(s)" in r.stdout
+
+
+@pytest.mark.parametrize("san", ["address", "thread"])
+def test_fault_paths_under_sanitizer(san):
+    _build.build_host(sanitize=san)
+    env = dict(os.environ, ASAN_OPTIONS="detect_leaks=0", TSAN_OPTIONS="halt_on_error=1 second_deadlock_stack=1")
+    r = subprocess.run([str(LIB / f"tcpxb_fault_tests_{san}")], capture_output=True, text=True, timeout=900, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
+    assert "0 failure(s)" in r.stdout
+    assert "WARNING: ThreadSanitizer" not in r.stderr and "ERROR: AddressSanitizer" not in r.stderr
 
 
 def test_rx_buffer_manager_daemon(host_lib, tmp_path):
