@@ -3,7 +3,10 @@
 //
 //   tcpxb_loopback --plugin <libnccl-net.so | libtcpxb_host.so> [--v7]
 //                  [--sizes 1024,65536,4194304,67108864] [--inflight 8] [--iters 4]
-//                  [--ptr host|cuda]
+//                  [--ptr host|cuda] [--yield]
+//
+// `--yield` makes the polling loop call sched_yield() after a pass that neither posted
+// nor finished anything, as NCCL's proxy thread does; without it the loop spins.
 //
 // `--ptr cuda` registers the buffers as device memory.  It is meant for the host-only
 // library started with TCPXB_FAKE_GPU=1, whose stand-in device is host memory: the
@@ -23,10 +26,12 @@
 // The reference has no such tool: its only tests are two unit tests of the stats
 // code (reference: src/stats/tracepoint_test.cc, src/stats/stats_buffer_test.cc).
 #include <dlfcn.h>
+#include <sched.h>
 #include <signal.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/resource.h>
 #include <sys/wait.h>
 #include <time.h>
 #include <unistd.h>
@@ -75,6 +80,14 @@ int (*stats_text)(void*, char*, int) = nullptr;
       return 1;                                                              \
     }                                                                        \
   } while (0)
+
+// user and system CPU seconds of the whole process (all threads) so far
+void cpuSec(double* user, double* sys) {
+  struct rusage ru;
+  getrusage(RUSAGE_SELF, &ru);
+  *user = ru.ru_utime.tv_sec + ru.ru_utime.tv_usec * 1e-6;
+  *sys = ru.ru_stime.tv_sec + ru.ru_stime.tv_usec * 1e-6;
+}
 
 double nowSec() {
   struct timespec ts;
@@ -166,6 +179,7 @@ struct Options {
   int iters = 4;
   uint64_t seed = 42;
   int ptr_type = NCCL_PTR_HOST;
+  bool yield_when_idle = false;
 };
 
 int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
@@ -222,16 +236,18 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
     char tok = 'g';
     if (receiver) { if (write(wfd, &tok, 1) != 1) return 1; }
     else if (read(rfd, &tok, 1) != 1) return 1;
-    double dt = 0;
+    double dt = 0, cpu_user = 0, cpu_sys = 0;
     for (int it = 0; it < opt.iters && rc == 0; ++it) {
       std::vector<void*> reqs(nbuf, nullptr);
       if (!receiver)
         for (int b = 0; b < nbuf; ++b) fillPayload(bufs[b].data(), size, keyOf(opt.seed, b / opt.inflight, (int)si, it, b % opt.inflight));
       else
         for (int b = 0; b < nbuf; ++b) memset(bufs[b].data(), 0xEE, size);
-      int posted = 0, finished = 0;
+      int posted = 0, finished = 0, posted_prev = 0;
       std::vector<char> done(nbuf, 0);
       std::vector<int> got_size(nbuf, -1);
+      double u0, s0, u1, s1;
+      cpuSec(&u0, &s0);
       const double t0 = nowSec();  // payload generation and checking stay outside the clock
       while (finished < nbuf) {
         // post in tag order per comm; a null request means "try again"
@@ -247,6 +263,8 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
           }
           if (reqs[b] != nullptr) ++posted;
         }
+        const int finished_before = finished, posted_before = posted_prev;
+        posted_prev = posted;
         for (int b = 0; b < posted; ++b) {
           if (done[b]) continue;
           int d = 0, sz = -1;
@@ -262,8 +280,13 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
           ++finished;
           got_size[b] = sz;
         }
+        // NCCL's proxy thread gives up its core when a pass over its operations moved nothing
+        if (opt.yield_when_idle && finished == finished_before && posted == posted_before) sched_yield();
       }
       dt += nowSec() - t0;
+      cpuSec(&u1, &s1);
+      cpu_user += u1 - u0;
+      cpu_sys += s1 - s0;
       for (int b = 0; b < nbuf; ++b) {
         if (got_size[b] != (int)size) { fprintf(stderr, "size mismatch: test reported %d, expected %zu\n", got_size[b], size); rc = 1; }
         if (!receiver) continue;
@@ -275,10 +298,11 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
       }
     }
     const double bytes = (double)size * nbuf * opt.iters;
-    if (receiver)
-      printf("{\"tool\": \"loopback\", \"side\": \"recv\", \"size\": %zu, \"messages\": %d, \"inflight\": %d, \"comms\": %d, "
-             "\"seconds\": %.6f, \"GBps\": %.3f, \"byte_exact\": %s}\n",
-             size, nbuf * opt.iters, opt.inflight, ncomm, dt, bytes / dt / 1e9, rc == 0 ? "true" : "false");
+    // the receiver's line is the result; the sender's carries its CPU seconds for the same transfers
+    printf("{\"tool\": \"%s\", \"side\": \"%s\", \"size\": %zu, \"messages\": %d, \"inflight\": %d, \"comms\": %d, "
+           "\"seconds\": %.6f, \"GBps\": %.3f, \"cpu_user_s\": %.4f, \"cpu_sys_s\": %.4f, \"byte_exact\": %s}\n",
+           receiver ? "loopback" : "loopback-sender", receiver ? "recv" : "send", size, nbuf * opt.iters, opt.inflight, ncomm, dt,
+           bytes / dt / 1e9, cpu_user, cpu_sys, rc == 0 ? "true" : "false");
     for (int b = 0; b < nbuf; ++b) CHECK(api.deregMr(comms[b / opt.inflight], mh[b]));
   }
   for (int c = 0; c < ncomm; ++c) printFlows(receiver ? "recv" : "send", c, comms[c]);
@@ -306,6 +330,7 @@ int main(int argc, char** argv) {
     else if (a == "--inflight") opt.inflight = atoi(next());
     else if (a == "--iters") opt.iters = atoi(next());
     else if (a == "--seed") opt.seed = strtoull(next(), nullptr, 0);
+    else if (a == "--yield") opt.yield_when_idle = true;
     else if (a == "--ptr") opt.ptr_type = std::string(next()) == "cuda" ? NCCL_PTR_CUDA : NCCL_PTR_HOST;
     else if (a == "--sizes") {
       opt.sizes.clear();

@@ -44,7 +44,7 @@ def test_unit_tests_binary(host_lib):
 
 
 def _parse(stdout):
-    rows = [json.loads(l) for l in stdout.splitlines() if l.startswith('{"tool"')]
+    rows = [json.loads(l) for l in stdout.splitlines() if l.startswith('{"tool": "loopback",')]
     flows = [l.split() for l in stdout.splitlines() if l.startswith("FLOW ")]
     return rows, flows
 
