@@ -8,7 +8,8 @@ and g++.  Outputs land in `nccl_plugin_gpudirecttcpx_b200/_lib/`:
 
   libtcpxb_kernels.so   device kernels behind a C ABI (needs nvcc)
   libnccl-net.so        the NCCL net plugin: host core + kernels + engine (needs nvcc)
-  libtcpxb_host.so      host core only, no CUDA (g++ only; used by CPU tests)
+  libtcpxb_host.so      host core + engine with no CUDA: device calls go to a stand-in
+                        device in host memory (g++ only; used by CPU tests)
   tcpxb_loopback        stand-alone driver of the ncclNet table (g++ only)
 
 Objects are rebuilt only when a source or header is newer than the object.
@@ -86,7 +87,8 @@ def build_host(verbose: bool = False, sanitize: str | None = None) -> Path:
     flags = CXX_FLAGS + ["-DTCPXB_NO_CUDA=1"]
     if sanitize:
         flags = flags + [f"-fsanitize={sanitize}", "-fno-omit-frame-pointer", "-O1"]
-    srcs = _sources("core", ".cc") + _sources("plugin", ".cc")
+    # kernels/*.cc is the CPU statement of the kernel ABI for the stand-in device
+    srcs = _sources("core", ".cc") + _sources("plugin", ".cc") + _sources("engine", ".cc") + _sources("kernels", ".cc")
     objs = _compile(srcs, tag, ["g++"], flags, hdr, verbose)
     suffix = "" if not sanitize else f"_{sanitize}"
     lib = OUT / f"libtcpxb_host{suffix}.so"

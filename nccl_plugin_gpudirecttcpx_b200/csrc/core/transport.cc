@@ -12,9 +12,7 @@
 
 #include <algorithm>
 
-#ifndef TCPXB_NO_CUDA
 #include "tcpxb/kernels.h"
-#endif
 
 #ifndef SO_EE_ORIGIN_ZEROCOPY
 #define SO_EE_ORIGIN_ZEROCOPY 5
@@ -544,23 +542,7 @@ Result describePages(Comm* comm, Request* r, Task* t) {
 }
 
 Result launchUnpack(Comm* comm, Request* r) {
-#ifdef TCPXB_NO_CUDA
-  // stand-in device: apply the scatter list on the host, with the kernel's checks
-  if (!gpu::available()) return kInvalidUsage;
-  for (uint64_t i = 0; i < r->slot.filled; ++i) {
-    const LoadMeta& m = r->slot.mem[i];
-    if ((uint64_t)m.src_off + m.len > comm->rxmgr->bytes() || m.dst_off + m.len > (uint64_t)r->size) {
-      comm->unpack_status_host[0] = 1;
-      comm->unpack_status_host[1] = (uint32_t)i;
-      break;
-    }
-    memcpy(r->data + m.dst_off, comm->rxmgr->hostBase() + m.src_off, m.len);
-  }
-  if (r->unpack_event == nullptr) TCPXB_CHECK(gpu::eventCreate(&r->unpack_event));
-  TCPXB_CHECK(gpu::eventRecord(r->unpack_event, comm->stream));
-  r->unpack_launched = true;
-  return kSuccess;
-#else
+  // In the host-only build this is the stand-in device's unpack, done at once on this thread.
   mark(comm, "launchUnpack:kernel");
   if (r->slot.filled > 0) {
     int rc = tcpxb_unpack_copy(comm->rxmgr->devBase(), comm->rxmgr->bytes(), r->data, (uint64_t)r->size,
@@ -573,7 +555,6 @@ Result launchUnpack(Comm* comm, Request* r) {
   TCPXB_CHECK(gpu::eventRecord(r->unpack_event, comm->stream));
   r->unpack_launched = true;
   return kSuccess;
-#endif
 }
 
 // ------------------------------------------------------------- progress engine
@@ -991,12 +972,10 @@ Result netPrepareCuda(Comm* comm, int gpu_dev) {
       for (auto& e : r.seg_event) if (e == nullptr) TCPXB_CHECK(gpu::eventCreate(&e));
     }
   }
-#ifndef TCPXB_NO_CUDA
   if (comm->passive && tcpxb_kernels_preload() != 0) {
     WARN("kernel preload failed: %s", tcpxb_kernel_last_error());
     return kUnhandledCudaError;
   }
-#endif
   comm->cuda_prepared = true;
   return kSuccess;
 }

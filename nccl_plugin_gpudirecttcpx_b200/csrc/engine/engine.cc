@@ -11,7 +11,9 @@
 #include <deque>
 #include <vector>
 
+#ifndef TCPXB_NO_CUDA
 #include <nvtx3/nvToolsExt.h>
+#endif
 
 #include "tcpxb/kernels.h"
 #include "tcpxb/transport.h"
@@ -50,10 +52,17 @@ double nowSec() {
 }
 
 // NVTX range for the lifetime of a scope; costs nothing unless a tool is attached.
+#ifndef TCPXB_NO_CUDA
 struct Range {
   explicit Range(const char* name) { nvtxRangePushA(name); }
   ~Range() { nvtxRangePop(); }
 };
+#else
+struct Range {
+  explicit Range(const char*) {}
+  ~Range() {}
+};
+#endif
 
 struct Rail {
   ListenComm* listen = nullptr;

@@ -21,9 +21,12 @@
 #include <atomic>
 #include <functional>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "tcpxb/dev_queue.h"
+#include "tcpxb/engine.h"
+#include "tcpxb/kernels.h"
 #include "tcpxb/transport.h"
 
 using namespace tcpxb;
@@ -396,6 +399,94 @@ TEST(device_pool_exhaustion_is_backpressure) {
   for (int i = 0; i < 4; ++i) EXPECT(pollBounded(x[i].rs, &done, &got) == kSuccess && done);
   closePair(&p);
   unpackModeOff();
+}
+
+// ---- the collective engine on the stand-in device
+void* makeEngine(int rank, int world) {
+  tcpxbEngineConfig cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.rank = rank;
+  cfg.world = world;
+  cfg.gpus_per_node = 1;
+  cfg.request_bytes = 256 << 10;
+  cfg.max_inflight = 4;
+  return tcpxb_engine_create(&cfg);
+}
+
+float bf16Value(uint16_t h) {
+  uint32_t u = (uint32_t)h << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+TEST(engine_twin_collectives_on_standin_device) {
+  void* e = makeEngine(0, 1);
+  EXPECT(e != nullptr);
+  if (e == nullptr) return;
+  std::vector<char> handles((size_t)tcpxb_engine_rails(e) * TCPXB_ENGINE_HANDLE_BYTES);
+  EXPECT(tcpxb_engine_listen(e, handles.data()) == 0);
+  EXPECT(tcpxb_engine_connect(e, handles.data()) == 0);  // the single rank is its own peer
+  const size_t n = 700000 / 4 * 4;  // 2.8 MB of f32: several requests per rail
+  std::vector<float> x(n), y(n, -1.f);
+  for (size_t i = 0; i < n; ++i) x[i] = (float)(i % 1013) * 0.25f - 100.f;
+  EXPECT(tcpxb_engine_all_reduce(e, x.data(), y.data(), n * 4, TCPXB_F32, nullptr) == 0);
+  bool same = true;
+  for (size_t i = 0; i < n; ++i) same = same && y[i] == 2.f * x[i];
+  EXPECT(same);
+  // bf16: doubling is exact, so the result is known bit for bit
+  std::vector<uint16_t> hx(n), hy(n, 0);
+  for (size_t i = 0; i < n; ++i) hx[i] = (uint16_t)(0x3f80 + (i % 64));  // 1.0 .. 1.49
+  EXPECT(tcpxb_engine_all_reduce(e, hx.data(), hy.data(), n * 2, TCPXB_BF16, nullptr) == 0);
+  same = true;
+  for (size_t i = 0; i < n; ++i) same = same && bf16Value(hy[i]) == 2.f * bf16Value(hx[i]);
+  EXPECT(same);
+  // all_gather: both blocks hold the twin's data; reduce_scatter: twice the block
+  std::vector<float> g(2 * n, -1.f), rs(n, -1.f);
+  EXPECT(tcpxb_engine_all_gather(e, x.data(), g.data(), n * 4, nullptr) == 0);
+  EXPECT(memcmp(g.data(), x.data(), n * 4) == 0 && memcmp(g.data() + n, x.data(), n * 4) == 0);
+  EXPECT(tcpxb_engine_reduce_scatter(e, x.data(), rs.data(), n * 4, TCPXB_F32, nullptr) == 0);
+  same = true;
+  for (size_t i = 0; i < n; ++i) same = same && rs[i] == 2.f * x[i];
+  EXPECT(same);
+  // argument errors are messages, not crashes
+  EXPECT(tcpxb_engine_all_reduce(e, x.data(), y.data(), 24, TCPXB_F32, nullptr) != 0);
+  EXPECT(strstr(tcpxb_engine_last_error(), "multiple of") != nullptr);
+  EXPECT(tcpxb_engine_all_reduce(e, x.data(), y.data(), n * 4, TCPXB_U8, nullptr) != 0);
+  uint32_t st[4] = {9, 9, 9, 9};
+  EXPECT(tcpxb_engine_device_status(e, st) == 0 && st[0] == 0);
+  tcpxbEngineStats es;
+  EXPECT(tcpxb_engine_stats(e, &es) == 0 && es.requests > 0 && es.fragments >= es.requests && es.bytes_received == es.bytes_sent);
+  tcpxb_engine_destroy(e);
+}
+
+TEST(two_engines_in_one_process_all_reduce) {
+  // two ranks as two threads: the transport's shared state (flags, page pool of the one
+  // stand-in device, helper threads) is used from both at once
+  void* e[2] = {makeEngine(0, 2), makeEngine(1, 2)};
+  EXPECT(e[0] != nullptr && e[1] != nullptr);
+  if (e[0] == nullptr || e[1] == nullptr) return;
+  const size_t hb = (size_t)tcpxb_engine_rails(e[0]) * TCPXB_ENGINE_HANDLE_BYTES;
+  std::vector<char> h0(hb), h1(hb);
+  EXPECT(tcpxb_engine_listen(e[0], h0.data()) == 0 && tcpxb_engine_listen(e[1], h1.data()) == 0);
+  const size_t n = 400000;
+  std::vector<float> x[2] = {std::vector<float>(n), std::vector<float>(n)}, y[2] = {std::vector<float>(n), std::vector<float>(n)};
+  for (size_t i = 0; i < n; ++i) { x[0][i] = (float)(i % 977); x[1][i] = 0.5f * (float)(i % 31); }
+  std::atomic<int> failures{0};
+  auto rank = [&](int r) {
+    if (tcpxb_engine_connect(e[r], r == 0 ? h1.data() : h0.data()) != 0) { ++failures; return; }
+    for (int rep = 0; rep < 3; ++rep)
+      if (tcpxb_engine_all_reduce(e[r], x[r].data(), y[r].data(), n * 4, TCPXB_F32, nullptr) != 0) ++failures;
+  };
+  std::thread t0(rank, 0), t1(rank, 1);
+  t0.join();
+  t1.join();
+  EXPECT(failures.load() == 0);
+  bool same = true;
+  for (size_t i = 0; i < n; ++i) same = same && y[0][i] == x[0][i] + x[1][i] && y[1][i] == y[0][i];
+  EXPECT(same);
+  tcpxb_engine_destroy(e[0]);
+  tcpxb_engine_destroy(e[1]);
 }
 
 }  // namespace

@@ -42,27 +42,31 @@ class EngineStats(ctypes.Structure):
 _lib = None
 
 
+def bind_engine_api(lib):
+    """Declares the engine's C entry points on a loaded library and returns it."""
+    vp, u64, ci = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int
+    lib.tcpxb_engine_create.restype = vp
+    lib.tcpxb_engine_create.argtypes = [ctypes.POINTER(_Config)]
+    lib.tcpxb_engine_destroy.argtypes = [vp]
+    lib.tcpxb_engine_rails.argtypes = [vp]
+    lib.tcpxb_engine_listen.argtypes = [vp, vp]
+    lib.tcpxb_engine_connect.argtypes = [vp, vp]
+    lib.tcpxb_engine_set_peers.argtypes = [vp, vp, vp, vp, vp, u64]
+    lib.tcpxb_engine_all_reduce.argtypes = [vp, vp, vp, u64, ci, vp]
+    lib.tcpxb_engine_all_gather.argtypes = [vp, vp, vp, u64, vp]
+    lib.tcpxb_engine_reduce_scatter.argtypes = [vp, vp, vp, u64, ci, vp]
+    lib.tcpxb_engine_send_next.argtypes = [vp, vp, u64, vp]
+    lib.tcpxb_engine_recv_prev.argtypes = [vp, vp, u64, vp]
+    lib.tcpxb_engine_stats.argtypes = [vp, ctypes.POINTER(EngineStats)]
+    lib.tcpxb_engine_device_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint32 * 4)]
+    lib.tcpxb_engine_last_error.restype = ctypes.c_char_p
+    return lib
+
+
 def _e():
     global _lib
     if _lib is None:
-        lib = native.load("libnccl-net.so")
-        vp, u64, ci = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int
-        lib.tcpxb_engine_create.restype = vp
-        lib.tcpxb_engine_create.argtypes = [ctypes.POINTER(_Config)]
-        lib.tcpxb_engine_destroy.argtypes = [vp]
-        lib.tcpxb_engine_rails.argtypes = [vp]
-        lib.tcpxb_engine_listen.argtypes = [vp, vp]
-        lib.tcpxb_engine_connect.argtypes = [vp, vp]
-        lib.tcpxb_engine_set_peers.argtypes = [vp, vp, vp, vp, vp, u64]
-        lib.tcpxb_engine_all_reduce.argtypes = [vp, vp, vp, u64, ci, vp]
-        lib.tcpxb_engine_all_gather.argtypes = [vp, vp, vp, u64, vp]
-        lib.tcpxb_engine_reduce_scatter.argtypes = [vp, vp, vp, u64, ci, vp]
-        lib.tcpxb_engine_send_next.argtypes = [vp, vp, u64, vp]
-        lib.tcpxb_engine_recv_prev.argtypes = [vp, vp, u64, vp]
-        lib.tcpxb_engine_stats.argtypes = [vp, ctypes.POINTER(EngineStats)]
-        lib.tcpxb_engine_device_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint32 * 4)]
-        lib.tcpxb_engine_last_error.restype = ctypes.c_char_p
-        _lib = lib
+        _lib = bind_engine_api(native.load("libnccl-net.so"))
     return _lib
 
 
@@ -89,6 +93,7 @@ class HierarchicalEngine:
                  max_inflight: int = 8, unpack_ctas: int = 16, reduce_impl: int = 0, use_nvls: bool = False,
                  plain_mode: bool = False, device: Optional[torch.device] = None):
         import torch.distributed as dist
+        self._api = self._load_api()
         self._dist = dist if dist.is_available() and dist.is_initialized() else None
         self.rank = self._dist.get_rank() if self._dist else 0
         self.world = self._dist.get_world_size() if self._dist else 1
@@ -97,10 +102,10 @@ class HierarchicalEngine:
         self.nodes = max(2, self.world // self.G) if self.world > 1 else 2
         cfg = _Config(self.rank, self.world, self.G, self.device.index or 0, request_bytes, max_inflight, unpack_ctas,
                       reduce_impl, int(use_nvls), int(plain_mode))
-        self._h = _e().tcpxb_engine_create(ctypes.byref(cfg))
+        self._h = self._api.tcpxb_engine_create(ctypes.byref(cfg))
         if not self._h:
-            raise RuntimeError("engine create failed: " + _e().tcpxb_engine_last_error().decode())
-        self.rails = _e().tcpxb_engine_rails(self._h)
+            raise RuntimeError("engine create failed: " + self._api.tcpxb_engine_last_error().decode())
+        self.rails = self._api.tcpxb_engine_rails(self._h)
         self._connect()
         self.work = self.out = None
         self._keep = []
@@ -110,13 +115,20 @@ class HierarchicalEngine:
             self._setup_symmetric(buffer_bytes, use_nvls)
 
     # ------------------------------------------------------------------ set-up
+    def _load_api(self):
+        """The native library with the engine's entry points (the plugin, built for sm_100a)."""
+        return _e()
+
+    def _synchronize(self) -> None:
+        torch.cuda.synchronize(self.device)
+
     def _check(self, rc: int) -> None:
         if rc != 0:
-            raise RuntimeError("engine call failed: " + _e().tcpxb_engine_last_error().decode())
+            raise RuntimeError("engine call failed: " + self._api.tcpxb_engine_last_error().decode())
 
     def _connect(self) -> None:
         mine = ctypes.create_string_buffer(self.rails * HANDLE_BYTES)
-        self._check(_e().tcpxb_engine_listen(self._h, mine))
+        self._check(self._api.tcpxb_engine_listen(self._h, mine))
         if self.world == 1:
             nxt = mine.raw
         else:
@@ -125,7 +137,7 @@ class HierarchicalEngine:
             node, local = divmod(self.rank, self.G)
             nxt = allh[((node + 1) % (self.world // self.G)) * self.G + local]
         buf = ctypes.create_string_buffer(nxt, len(nxt))
-        self._check(_e().tcpxb_engine_connect(self._h, buf))
+        self._check(self._api.tcpxb_engine_connect(self._h, buf))
 
     def _setup_symmetric(self, buffer_bytes: int, use_nvls: bool) -> None:
         import torch.distributed._symmetric_memory as symm
@@ -144,7 +156,7 @@ class HierarchicalEngine:
             t.zero_()
             hdl = symm.rendezvous(t, group=group)
             bufs[name] = (t, hdl)
-        torch.cuda.synchronize()
+        self._synchronize()
         dist.barrier(group)
         self._keep = bufs
         self.work = bufs["work"][0]
@@ -154,7 +166,7 @@ class HierarchicalEngine:
         if use_nvls:
             mc = int(getattr(bufs["out"][1], "multicast_ptr", 0) or 0)
         self.nvls = bool(mc)
-        self._check(_e().tcpxb_engine_set_peers(self._h, arr(bufs["work"][1].buffer_ptrs), arr(bufs["out"][1].buffer_ptrs),
+        self._check(self._api.tcpxb_engine_set_peers(self._h, arr(bufs["work"][1].buffer_ptrs), arr(bufs["out"][1].buffer_ptrs),
                                                 arr(bufs["flags"][1].buffer_ptrs), mc or None, self.buffer_bytes))
 
     # -------------------------------------------------------------- collectives
@@ -169,12 +181,12 @@ class HierarchicalEngine:
         if self.G == 1:
             if out is None:
                 out = torch.empty_like(x)
-            self._check(_e().tcpxb_engine_all_reduce(self._h, x.data_ptr(), out.data_ptr(), nbytes, code, self._stream()))
+            self._check(self._api.tcpxb_engine_all_reduce(self._h, x.data_ptr(), out.data_ptr(), nbytes, code, self._stream()))
             return out
         w = self.work.view(torch.uint8)[:nbytes].view(x.dtype)
         if x.data_ptr() != w.data_ptr():
             w.copy_(x.reshape(-1))
-        self._check(_e().tcpxb_engine_all_reduce(self._h, self.work.data_ptr(), self.out.data_ptr(), nbytes, code, self._stream()))
+        self._check(self._api.tcpxb_engine_all_reduce(self._h, self.work.data_ptr(), self.out.data_ptr(), nbytes, code, self._stream()))
         res = self.out.view(torch.uint8)[:nbytes].view(x.dtype).view(x.shape)
         if out is not None:
             out.copy_(res)
@@ -190,9 +202,9 @@ class HierarchicalEngine:
         blocks = self.nodes * self.G
         if self.G == 1:
             out = torch.empty(blocks * x.numel(), dtype=x.dtype, device=x.device)
-            self._check(_e().tcpxb_engine_all_gather(self._h, x.data_ptr(), out.data_ptr(), nbytes, self._stream()))
+            self._check(self._api.tcpxb_engine_all_gather(self._h, x.data_ptr(), out.data_ptr(), nbytes, self._stream()))
             return out
-        self._check(_e().tcpxb_engine_all_gather(self._h, x.data_ptr(), self.out.data_ptr(), nbytes, self._stream()))
+        self._check(self._api.tcpxb_engine_all_gather(self._h, x.data_ptr(), self.out.data_ptr(), nbytes, self._stream()))
         return self.out.view(torch.uint8)[:nbytes * blocks].view(x.dtype)
 
     def reduce_scatter(self, x: torch.Tensor) -> torch.Tensor:
@@ -206,30 +218,30 @@ class HierarchicalEngine:
             if x.data_ptr() != w.data_ptr():
                 w.copy_(x.reshape(-1))
             src = self.work
-        self._check(_e().tcpxb_engine_reduce_scatter(self._h, src.data_ptr(), out.data_ptr(), nbytes, DTYPE_CODE[x.dtype], self._stream()))
+        self._check(self._api.tcpxb_engine_reduce_scatter(self._h, src.data_ptr(), out.data_ptr(), nbytes, DTYPE_CODE[x.dtype], self._stream()))
         return out
 
     def send_next(self, x: torch.Tensor) -> None:
-        self._check(_e().tcpxb_engine_send_next(self._h, x.data_ptr(), x.numel() * x.element_size(), self._stream()))
+        self._check(self._api.tcpxb_engine_send_next(self._h, x.data_ptr(), x.numel() * x.element_size(), self._stream()))
 
     def recv_prev(self, x: torch.Tensor) -> None:
-        self._check(_e().tcpxb_engine_recv_prev(self._h, x.data_ptr(), x.numel() * x.element_size(), self._stream()))
+        self._check(self._api.tcpxb_engine_recv_prev(self._h, x.data_ptr(), x.numel() * x.element_size(), self._stream()))
 
     # -------------------------------------------------------------------- misc
     def stats(self) -> EngineStats:
         s = EngineStats()
-        _e().tcpxb_engine_stats(self._h, ctypes.byref(s))
+        self._api.tcpxb_engine_stats(self._h, ctypes.byref(s))
         return s
 
     def device_status(self):
         w = (ctypes.c_uint32 * 4)()
-        _e().tcpxb_engine_device_status(self._h, ctypes.byref(w))
+        self._api.tcpxb_engine_device_status(self._h, ctypes.byref(w))
         return list(w)
 
     def close(self) -> None:
         if self._h:
-            torch.cuda.synchronize(self.device)
-            _e().tcpxb_engine_destroy(self._h)
+            self._synchronize()
+            self._api.tcpxb_engine_destroy(self._h)
             self._h = None
 
     def __del__(self):

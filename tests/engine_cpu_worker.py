@@ -1,0 +1,115 @@
+"""Worker for the CPU engine tests: gloo ranks, the engine on the stand-in device.
+
+Ranks form `world / G` emulated nodes of G "GPUs".  Every rank rebuilds every rank's
+seeded input and checks its results against a plain PyTorch fp32 sum.  Modes
+(TCPXB_TEST_MODE): `collectives` (default) and `rank_leaves`, in which the last rank
+exits between two steps and the others must get an error, not a hang.
+"""
+import faulthandler
+import json
+import os
+import sys
+import time
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    faulthandler.dump_traceback_later(int(os.environ.get("TCPXB_TEST_DUMP_AFTER", "150")), exit=True)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    G = int(os.environ.get("TCPXB_TEST_GPUS_PER_NODE", "1"))
+    mode = os.environ.get("TCPXB_TEST_MODE", "collectives")
+    if world > 1:
+        dist.init_process_group("gloo")
+    from nccl_plugin_gpudirecttcpx_b200.parallel.engine import default_transport_env
+    from standin_engine import StandinEngine
+    default_transport_env(nics=2, nthreads=2, nsocks_per_thread=1, pool_mb=64, chunk_bytes=128 * 1024)
+    numels = [int(s) for s in os.environ.get("TCPXB_TEST_NUMELS", "3072,786432").split(",")]
+    buf_bytes = max(numels) * 4 * 2
+    eng = StandinEngine(gpus_per_node=G, buffer_bytes=buf_bytes if G > 1 else 0, request_bytes=256 << 10,
+                        plain_mode=bool(int(os.environ.get("TCPXB_TEST_PLAIN", "0"))),
+                        reduce_impl=int(os.environ.get("TCPXB_TEST_REDUCE_IMPL", "0")))
+    ranks = world if world > 1 else 2  # a single rank is its own twin
+
+    if mode == "rank_leaves":
+        x = torch.ones(98304, dtype=torch.float32)  # a multiple of every layout's unit
+        y = eng.all_reduce(x)
+        first_ok = bool(torch.all(y == ranks).item())
+        dist.barrier()  # a step boundary: nothing is in flight
+        if rank == world - 1:
+            print(json.dumps({"rank": rank, "left": True, "first_ok": first_ok}), flush=True)
+            os._exit(0)  # no clean shutdown: the process is simply gone
+        time.sleep(0.5)
+        t0 = time.time()
+        outcome = "completed"
+        try:
+            eng.all_reduce(x)
+            if eng.device_status()[0] != 0:
+                outcome = "device_status"
+        except RuntimeError as e:
+            outcome = "error: " + str(e)[:120]
+        print(json.dumps({"rank": rank, "left": False, "first_ok": first_ok, "outcome": outcome,
+                          "seconds": round(time.time() - t0, 2), "device_status": eng.device_status()}), flush=True)
+        os._exit(0)
+
+    ok = True
+    detail = []
+    for dtype in (torch.bfloat16, torch.float32):
+        for n in numels:
+            ins = [torch.randn(n, generator=torch.Generator().manual_seed(100 * r + n % 911)).to(dtype) for r in range(world)]
+            if world == 1:
+                ins = ins * 2
+            want = torch.stack([t.float() for t in ins]).sum(0)
+            tol = 0.04 * ranks if dtype == torch.bfloat16 else 1e-4 * ranks
+            for rep in range(2):  # twice: buffers and flag epochs are reused
+                y = eng.all_reduce(ins[rank].clone())
+                err = (y.float() - want).abs().max().item()
+                good = err <= tol
+                ok = ok and good
+                detail.append(("all_reduce", str(dtype), n, rep, err, good))
+            if n % ranks == 0:
+                per = n // ranks
+                g = eng.all_gather(ins[rank][:per].clone())
+                wantg = torch.cat([t[:per] for t in ins])
+                good = torch.equal(g.clone(), wantg)
+                ok = ok and good
+                detail.append(("all_gather", str(dtype), n, 0, 0.0, good))
+                src = ins[rank].clone() if world > 1 else ins[0][:per].clone()
+                r = eng.reduce_scatter(src)
+                wantr = want[rank * per:(rank + 1) * per] if world > 1 else 2 * ins[0][:per].float()
+                err = (r.float() - wantr).abs().max().item()
+                good = err <= tol
+                ok = ok and good
+                detail.append(("reduce_scatter", str(dtype), n, 0, err, good))
+    if world > 1 and G == 1:
+        # point to point around the ring of nodes
+        msg = torch.full((100000,), float(rank), dtype=torch.float32)
+        got = torch.empty_like(msg)
+        if rank % 2 == 0:
+            eng.send_next(msg); eng.recv_prev(got)
+        else:
+            eng.recv_prev(got); eng.send_next(msg)
+        good = bool(torch.all(got == float((rank - 1) % world)).item())
+        ok = ok and good
+        detail.append(("send_recv", "f32", 100000, 0, 0.0, good))
+    status = eng.device_status()
+    ok = ok and status[0] == 0
+    st = eng.stats()
+    bad = [d for d in detail if not d[-1]]
+    print(json.dumps({"rank": rank, "world": world, "G": G, "ok": bool(ok), "checks": len(detail), "bad": bad[:6],
+                      "device_status": status, "unpack_launches": st.unpack_launches, "fragments": st.fragments}), flush=True)
+    eng.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()
