@@ -105,6 +105,20 @@ const StrSpec kStrs[] = {
 
 std::string envName(const char* prefix, const char* name) { return std::string(prefix) + name; }
 
+// Variables of the plugin's own family are also read under the stand-alone prefix
+// NET_TCPX_ (reference: src/adapter/native/param.h:35), for programs that use the
+// transport without NCCL; the NCCL-style name wins when both are set.
+const char* lookup(const char* prefix, const char* name, std::string* used) {
+  *used = envName(prefix, name);
+  const char* v = getenv(used->c_str());
+  if ((v == nullptr || *v == 0) && strcmp(prefix, kOwn) == 0) {
+    const std::string alt = envName("NET_TCPX_", name);
+    const char* a = getenv(alt.c_str());
+    if (a != nullptr && *a != 0) { *used = alt; return a; }
+  }
+  return v;
+}
+
 }  // namespace
 
 bool parseSlownessList(const char* value, bool out[kSlowKinds]) {
@@ -131,8 +145,8 @@ bool parseSlownessList(const char* value, bool out[kSlowKinds]) {
 void loadFlags(Flags* out) {
   *out = Flags();
   for (const IntSpec& s : kInts) {
-    const std::string env = envName(s.prefix, s.name);
-    const char* v = getenv(env.c_str());
+    std::string env;
+    const char* v = lookup(s.prefix, s.name, &env);
     if (v != nullptr && *v != 0) {
       char* end = nullptr;
       errno = 0;
@@ -149,8 +163,8 @@ void loadFlags(Flags* out) {
     INFO(kSubEnv, "%s = %lld", env.c_str(), (long long)(out->*s.field));
   }
   for (const StrSpec& s : kStrs) {
-    const std::string env = envName(s.prefix, s.name);
-    const char* v = getenv(env.c_str());
+    std::string env;
+    const char* v = lookup(s.prefix, s.name, &env);
     if (v != nullptr && *v != 0) out->*s.field = v;
     if (!(out->*s.field).empty()) INFO(kSubEnv, "%s = %s", env.c_str(), (out->*s.field).c_str());
   }

@@ -245,6 +245,19 @@ TEST(flags_defaults_and_ranges) {
                         "NCCL_GPUDIRECTTCPX_SCHED_ALG", "NCCL_GPUDIRECTTCPX_SLOWNESS_SWITCH",
                         "NCCL_GPUDIRECTTCPX_SLOWNESS_REPORT", "NCCL_GPUDIRECTTCPX_TELEMETRY_SAMPLING_FACTOR"})
     unsetenv(e);
+  // the stand-alone prefix is an alias of the plugin's own family; the NCCL-style name wins
+  setenv("NET_TCPX_CONNECTION_RETRY", "7", 1);
+  setenv("NET_TCPX_SCHED_ALG", "KATY", 1);
+  loadFlags(&f);
+  EXPECT(f.connection_retry == 7 && f.sched_alg == kSchedKaty);
+  setenv("NCCL_GPUDIRECTTCPX_CONNECTION_RETRY", "5", 1);
+  loadFlags(&f);
+  EXPECT(f.connection_retry == 5);
+  setenv("NET_TCPX_DYNAMIC_CHUNK_SIZE", "4096", 1);  // not in that family: no alias
+  loadFlags(&f);
+  EXPECT(f.dynamic_chunk_size == 128 * 1024);
+  for (const char* e : {"NET_TCPX_CONNECTION_RETRY", "NET_TCPX_SCHED_ALG", "NCCL_GPUDIRECTTCPX_CONNECTION_RETRY", "NET_TCPX_DYNAMIC_CHUNK_SIZE"})
+    unsetenv(e);
   bool sw[kSlowKinds];
   EXPECT(!parseSlownessList("SENDRECV,bogus", sw) && sw[kSlowSendRecv] && !sw[kSlowTxComp]);
   EXPECT(flagDocs().size() > 50);
