@@ -37,8 +37,10 @@ PageAllocator::PageAllocator(uint32_t n_pages, bool scatter, uint64_t seed, uint
   }
 }
 
-bool PageAllocator::alloc(uint32_t n, std::vector<PageRun>* out) {
+bool PageAllocator::alloc(uint32_t n, std::vector<PageRun>* out, bool from_reservation) {
   if (n > stack_.size()) return false;
+  if (from_reservation) reserved_ -= std::min(n, reserved_);
+  else if (stack_.size() - n < reserved_) return false;  // would eat into somebody's promise
   for (uint32_t i = 0; i < n; ++i) {
     const uint32_t page = stack_.back();
     stack_.pop_back();
@@ -48,6 +50,14 @@ bool PageAllocator::alloc(uint32_t n, std::vector<PageRun>* out) {
   }
   return true;
 }
+
+bool PageAllocator::reserve(uint32_t n) {
+  if (stack_.size() < (size_t)reserved_ + n) return false;
+  reserved_ += n;
+  return true;
+}
+
+void PageAllocator::unreserve(uint32_t n) { reserved_ -= std::min(n, reserved_); }
 
 void PageAllocator::release(uint32_t first, uint32_t count) {
   // pushed in descending order so the run comes out ascending (contiguous) again
@@ -97,10 +107,19 @@ class EmulatedRxBufMgr final : public RxBufMgr {
   uint64_t bytes() const override { return bytes_; }
   bool deviceResident() const override { return device_resident_; }
 
-  bool allocPages(uint32_t n, std::vector<PageRun>* out) override {
+  bool allocPages(uint32_t n, std::vector<PageRun>* out, bool from_reservation) override {
     std::lock_guard<std::mutex> l(mu_);
-    return alloc_.alloc(n, out);
+    return alloc_.alloc(n, out, from_reservation);
   }
+  bool reservePages(uint32_t n) override {
+    std::lock_guard<std::mutex> l(mu_);
+    return alloc_.reserve(n);
+  }
+  void unreservePages(uint32_t n) override {
+    std::lock_guard<std::mutex> l(mu_);
+    alloc_.unreserve(n);
+  }
+  uint32_t totalPages() override { return alloc_.totalPages(); }
   void releasePages(const PageRun* runs, size_t n) override {
     std::lock_guard<std::mutex> l(mu_);
     for (size_t i = 0; i < n; ++i) alloc_.release(runs[i].first, runs[i].count);
@@ -202,10 +221,19 @@ class DaemonRxBufMgr final : public RxBufMgr {
   uint8_t* devBase() override { return dev_base_; }
   uint64_t bytes() const override { return bytes_; }
   bool deviceResident() const override { return false; }
-  bool allocPages(uint32_t n, std::vector<PageRun>* out) override {
+  bool allocPages(uint32_t n, std::vector<PageRun>* out, bool from_reservation) override {
     std::lock_guard<std::mutex> l(mu_);
-    return alloc_->alloc(n, out);
+    return alloc_->alloc(n, out, from_reservation);
   }
+  bool reservePages(uint32_t n) override {
+    std::lock_guard<std::mutex> l(mu_);
+    return alloc_->reserve(n);
+  }
+  void unreservePages(uint32_t n) override {
+    std::lock_guard<std::mutex> l(mu_);
+    alloc_->unreserve(n);
+  }
+  uint32_t totalPages() override { return alloc_->totalPages(); }
   void releasePages(const PageRun* runs, size_t n) override {
     std::lock_guard<std::mutex> l(mu_);
     for (size_t i = 0; i < n; ++i) alloc_->release(runs[i].first, runs[i].count);

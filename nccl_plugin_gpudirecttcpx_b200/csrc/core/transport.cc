@@ -399,6 +399,8 @@ Result ensureTxStage(Comm* comm) {
 bool stageAlloc(Comm* comm, uint64_t bytes, uint8_t** out, uint64_t* charged) {
   const uint64_t cap = comm->tx_stage_bytes;
   if (bytes > cap) return false;
+  // an empty ring restarts at offset 0, so a request as large as the ring always fits eventually
+  if (comm->tx_head == comm->tx_tail) comm->tx_head = comm->tx_tail = 0;
   uint64_t head = comm->tx_head;
   uint64_t pos = head % cap;
   uint64_t skip = (pos + bytes > cap) ? cap - pos : 0;  // do not wrap inside a request
@@ -413,6 +415,11 @@ Result startCudaSend(Comm* comm, Request* r, MemHandle* mh) {
   TCPXB_CHECK(ensureCudaComm(comm, mh != nullptr && mh->gpu_dev >= 0 ? mh->gpu_dev : comm->gpu_dev));
   TCPXB_CHECK(ensureTxStage(comm));
   if (r->size == 0) return kSuccess;
+  if ((uint64_t)r->size > comm->tx_stage_bytes) {
+    WARN("send of %d bytes from device memory is larger than the staging ring (%lu bytes); raise NCCL_GPUDIRECTTCPX_TX_STAGING_BYTES",
+         r->size, (unsigned long)comm->tx_stage_bytes);
+    return kInvalidArgument;
+  }
   if (!stageAlloc(comm, (uint64_t)r->size, &r->stage, &r->stage_bytes)) return kInProgress;
   // One staging copy per ~2 MiB: enough to let the first chunks leave while the
   // rest is still being copied, few enough that the per-copy launch cost stays small.
@@ -484,7 +491,10 @@ bool fillRecvTask(Comm* comm, Request* r, int sock_idx, int chunk, int msg_offse
   t.iov_pos = 0;
   if (r->mem_type == kPtrCuda) {
     const uint32_t n_pages = ((uint32_t)chunk + kRxPageBytes - 1) / kRxPageBytes;
-    if (!comm->rxmgr->allocPages(n_pages, &t.pages)) return false;
+    // a sender whose chunks differ from the first one may outrun the promise; the rest is taken as it comes
+    const bool promised = r->pages_reserved >= n_pages;
+    if (!comm->rxmgr->allocPages(n_pages, &t.pages, promised)) return false;
+    if (promised) r->pages_reserved -= n_pages;
     uint8_t* base = comm->rxmgr->hostBase();
     int left = chunk;
     for (const PageRun& run : t.pages) {
@@ -659,12 +669,35 @@ Result progressRecvRequest(Comm* comm, Request* r) {
       }
     }
     const CtrlMsg& c = comm->ctrl;
+    if (r->mem_type == kPtrCuda && !r->pages_promised && r->size > 0) {
+      // The first record tells the message's size and the sender's chunk size.  Every
+      // page the message will need is promised now, or none: a message that waited for
+      // pages while holding some could block, and be blocked by, another connection's.
+      uint32_t need = 1;
+      if (c.type != kCtrlInline) {
+        const uint32_t chunk = c.size > 0 ? c.size : 1;
+        const uint32_t per = (chunk + kRxPageBytes - 1) / kRxPageBytes;
+        const uint32_t rem = (uint32_t)r->size % chunk;
+        need = (uint32_t)r->size / chunk * per + (rem + kRxPageBytes - 1) / kRxPageBytes;
+      }
+      if (need > comm->rxmgr->totalPages()) {
+        WARN("message of %d bytes needs %u rx pages but the pool has %u; raise NCCL_GPUDIRECTTCPX_RX_POOL_BYTES", r->size, need,
+             comm->rxmgr->totalPages());
+        return kInvalidUsage;
+      }
+      if (!comm->rxmgr->reservePages(need)) return kSuccess;  // pool busy: retry, holding nothing
+      r->pages_promised = true;
+      r->pages_reserved = need;
+    }
     if (c.type == kCtrlInline) {
       if (r->size > 0) {
         uint8_t* dst = r->data;
         if (r->mem_type == kPtrCuda) {
           // land in one pool page; the unpack path then treats it like any fragment
-          if (r->pages.empty() && !comm->rxmgr->allocPages(1, &r->pages)) return kSuccess;
+          if (r->pages.empty()) {
+            if (!comm->rxmgr->allocPages(1, &r->pages, r->pages_reserved >= 1)) return kSuccess;
+            if (r->pages_reserved >= 1) --r->pages_reserved;
+          }
           dst = comm->rxmgr->hostBase() + (uint64_t)r->pages[0].first * kRxPageBytes;
         }
         if (r->inline_off < r->size) r->inline_off += comm->ctrl_recv.drain(dst + r->inline_off, r->size - r->inline_off);
@@ -698,6 +731,7 @@ Result progressRecvRequest(Comm* comm, Request* r) {
     r->offset += (int)c.size;
     comm->have_ctrl = false;
     if (r->offset == r->size) {
+      if (r->pages_reserved > 0) { comm->rxmgr->unreservePages(r->pages_reserved); r->pages_reserved = 0; }
       traceReq(comm, r, kReqTransmitting);
       comm->rq.advance(kReqActive);
       return kSuccess;
@@ -1218,6 +1252,8 @@ void freeComm(Comm* comm) {
     Request& r = comm->rq.slot(i);
     if (comm->rxmgr != nullptr && !r.pages.empty()) comm->rxmgr->releasePages(r.pages.data(), r.pages.size());
     r.pages.clear();
+    if (comm->rxmgr != nullptr && r.pages_reserved > 0) comm->rxmgr->unreservePages(r.pages_reserved);
+    r.pages_reserved = 0;
     for (auto& e : r.seg_event) { gpu::eventDestroy(e); e = nullptr; }
     gpu::eventDestroy(r.unpack_event);
     r.unpack_event = nullptr;

@@ -45,14 +45,23 @@ class PageAllocator {
   // order, like a NIC page pool after some churn (run_pages = 1 scatters single
   // pages); otherwise ascending, so allocations are mostly contiguous.
   PageAllocator(uint32_t n_pages, bool scatter, uint64_t seed = 0x9e3779b97f4a7c15ull, uint32_t run_pages = 1);
-  // Appends runs covering exactly n pages; false (and nothing taken) when fewer are free.
-  bool alloc(uint32_t n, std::vector<PageRun>* out);
+  // Appends runs covering exactly n pages; false (and nothing taken) when fewer are
+  // free.  Pages promised to reservations are not free for anybody else;
+  // `from_reservation` draws on such a promise (the caller tracks how much it holds).
+  bool alloc(uint32_t n, std::vector<PageRun>* out, bool from_reservation = false);
   void release(uint32_t first, uint32_t count);
+  // All-or-nothing promise of n pages.  A message that reserves everything it needs
+  // before it takes its first page can never wait while holding pages, so messages of
+  // several connections that share one pool cannot block one another for good.
+  bool reserve(uint32_t n);
+  void unreserve(uint32_t n);
   uint32_t freePages() const { return (uint32_t)stack_.size(); }
+  uint32_t reservedPages() const { return reserved_; }
   uint32_t totalPages() const { return total_; }
 
  private:
   uint32_t total_;
+  uint32_t reserved_ = 0;
   std::vector<uint32_t> stack_;     // free pages; back() is handed out next
   std::vector<uint8_t> in_use_;     // double-release guard
 };
@@ -72,9 +81,12 @@ class RxBufMgr {
   virtual uint8_t* devBase() = 0;
   virtual uint64_t bytes() const = 0;
   virtual bool deviceResident() const = 0;
-  virtual bool allocPages(uint32_t n, std::vector<PageRun>* out) = 0;
+  virtual bool allocPages(uint32_t n, std::vector<PageRun>* out, bool from_reservation = false) = 0;
   virtual void releasePages(const PageRun* runs, size_t n) = 0;
+  virtual bool reservePages(uint32_t n) = 0;     // see PageAllocator::reserve
+  virtual void unreservePages(uint32_t n) = 0;
   virtual uint32_t freePages() = 0;
+  virtual uint32_t totalPages() = 0;
   // Service hooks with the reference's call points.
   virtual Result installFlowRule(int fd, const std::string& gpu_pci) = 0;
   virtual Result removeFlowRule(int fd) = 0;

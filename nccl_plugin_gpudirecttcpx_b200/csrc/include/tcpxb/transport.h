@@ -137,6 +137,8 @@ struct Request {
   // CUDA receive
   UnpackSlot slot;
   std::vector<PageRun> pages;
+  bool pages_promised = false;    // the pool promised every page this message needs
+  uint32_t pages_reserved = 0;    // what is left of that promise
   bool unpack_launched = false;
   gpu::Event unpack_event = nullptr;
   uint64_t posted_ns = 0, last_stall_report_ns = 0;

@@ -401,6 +401,34 @@ TEST(device_pool_exhaustion_is_backpressure) {
   unpackModeOff();
 }
 
+TEST(device_send_and_the_staging_ring) {
+  setenv("NCCL_GPUDIRECTTCPX_TX_STAGING_BYTES", "1048576", 1);
+  unpackModeOn("8388608");
+  Pair p;
+  EXPECT(makePair(&p));
+  int done = 0, got = 0;
+  // a message larger than the ring can never be staged: refused at once, with a reason
+  std::vector<uint8_t> big(2 << 20, 1);
+  MemHandle* bmh = nullptr;
+  Request* rs = nullptr;
+  EXPECT(netRegMr(p.s, big.data(), big.size(), kPtrCuda, &bmh) == kSuccess);
+  EXPECT(netIsend(p.s, big.data(), (int)big.size(), 0, bmh, &rs) == kInvalidArgument && rs == nullptr);
+  // messages as large as the ring go through one after the other, also after the ring's
+  // write position has moved off zero
+  const int sizes[] = {300001, 1048576, 4096, 1048576, 1048576};
+  for (int i = 0; i < 5; ++i) {
+    DevXfer x;
+    EXPECT(postDevXfer(&p, &x, sizes[i], i, (uint8_t)(0x10 + i)));
+    EXPECT(pollBounded(x.rr, &done, &got, x.rs) == kSuccess && done && got == sizes[i]);
+    EXPECT(applyScatterList(x.rr, &x.dst) && x.dst == x.src);
+    EXPECT(netIrecvConsumed(p.r, 1, x.rr) == kSuccess);
+    EXPECT(pollBounded(x.rs, &done, &got) == kSuccess && done);
+  }
+  closePair(&p);
+  unsetenv("NCCL_GPUDIRECTTCPX_TX_STAGING_BYTES");
+  unpackModeOff();
+}
+
 // ---- the collective engine on the stand-in device
 void* makeEngine(int rank, int world) {
   tcpxbEngineConfig cfg;

@@ -308,6 +308,18 @@ TEST(page_allocator) {
   EXPECT(a.freePages() == 64);
   more.clear();
   EXPECT(a.alloc(32, &more) && more.size() == 1 && more[0].first == 0);  // a released run comes back contiguous
+  // promises: all or nothing, and nobody else may eat into them
+  PageAllocator pr(100, /*scatter=*/false);
+  std::vector<PageRun> held, other;
+  EXPECT(pr.reserve(60) && pr.reservedPages() == 60);
+  EXPECT(!pr.reserve(41) && pr.reservedPages() == 60);      // 40 are left to promise
+  EXPECT(!pr.alloc(41, &other) && other.empty());            // an unpromised taker sees only those 40
+  EXPECT(pr.alloc(40, &other) && pr.freePages() == 60);
+  EXPECT(pr.alloc(25, &held, /*from_reservation=*/true) && pr.reservedPages() == 35 && pr.freePages() == 35);
+  pr.unreserve(35);                                          // the message turned out smaller
+  EXPECT(pr.reservedPages() == 0 && pr.reserve(35));
+  pr.unreserve(1000);                                        // never below zero
+  EXPECT(pr.reservedPages() == 0);
   PageAllocator s(1024, /*scatter=*/true);
   std::vector<PageRun> sr;
   EXPECT(s.alloc(256, &sr));

@@ -133,6 +133,10 @@ STANDIN_VARIANTS = [
     dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack"),
     dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_GPUDIRECTTCPX_RX_POOL_SCATTER=1, NCCL_GPUDIRECTTCPX_RX_POOL_BYTES=32 << 20),
     dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_GPUDIRECTTCPX_RX_POOL_MODE="device", args=["--v7"]),
+    # two connections share a pool that holds exactly one of the largest messages: whoever gets the
+    # pool's promise goes first, nobody waits while holding pages
+    dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_GPUDIRECTTCPX_RX_POOL_BYTES=8 << 20),
+    dict(NCCL_GPUDIRECTTCPX_CUDA_BUFFERS=1, NCCL_GPUDIRECTTCPX_RX_POOL_BYTES=8 << 20, NCCL_GPUDIRECTTCPX_TX_STAGING_BYTES=8 << 20),
 ]
 
 
@@ -157,6 +161,13 @@ def test_standin_device_oversize_receive_is_an_error(host_lib):
                   TCPXB_FAKE_GPU=1, NCCL_GPUDIRECTTCPX_CUDA_BUFFERS=1)
     assert r.returncode != 0
     assert "page records of a scatter-list slot" in r.stderr
+
+
+def test_standin_device_pool_smaller_than_a_message_is_an_error(host_lib):
+    r = _loopback(host_lib, ["--ptr", "cuda", "--sizes", str(4 << 20), "--inflight", "2", "--iters", "1"], timeout=120,
+                  TCPXB_FAKE_GPU=1, NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_GPUDIRECTTCPX_RX_POOL_BYTES=1 << 20)
+    assert r.returncode != 0
+    assert "rx pages but the pool has" in r.stderr
 
 
 def test_host_build_rejects_device_pointers_without_standin(host_lib):
@@ -186,7 +197,7 @@ def test_fault_paths_surface_as_errors(host_lib):
     pages: error codes, "try again" or back-pressure, never a hang."""
     r = subprocess.run([str(LIB / "tcpxb_fault_tests")], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert "13 test(s), 0 failure(s)" in r.stdout
+    assert "14 test(s), 0 failure(s)" in r.stdout
 
 
 @pytest.mark.parametrize("san", ["address", "thread"])
