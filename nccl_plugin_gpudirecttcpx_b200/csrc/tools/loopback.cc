@@ -325,6 +325,11 @@ int main(int argc, char** argv) {
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
     auto next = [&]() -> const char* { return i + 1 < argc ? argv[++i] : ""; };
+    if (a == "--help" || a == "-h") {
+      printf("usage: tcpxb_loopback --plugin LIB [--v7] [--sizes a,b,...] [--inflight 1..16] [--iters N] [--seed S]\n"
+             "                      [--ptr host|cuda] [--yield]\n");
+      return 0;
+    }
     if (a == "--plugin") opt.plugin = next();
     else if (a == "--v7") opt.v7 = true;
     else if (a == "--inflight") opt.inflight = atoi(next());

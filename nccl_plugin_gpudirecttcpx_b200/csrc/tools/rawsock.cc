@@ -115,13 +115,19 @@ int sender(const Options& o, int port_pipe, int go_pipe) {
 
 int main(int argc, char** argv) {
   Options o;
-  for (int i = 1; i + 1 < argc; i += 2) {
+  for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
-    if (a == "--streams") o.streams = atoi(argv[i + 1]);
-    else if (a == "--mb-per-stream") o.mb = atol(argv[i + 1]);
-    else if (a == "--block-kb") o.block_kb = atoi(argv[i + 1]);
-    else if (a == "--nics") o.nics = atoi(argv[i + 1]);
-    else { fprintf(stderr, "unknown argument %s\n", a.c_str()); return 2; }
+    if (a == "--help" || a == "-h") {
+      printf("usage: tcpxb_rawsock [--streams 8] [--mb-per-stream 2048] [--block-kb 512] [--nics 4]\n");
+      return 0;
+    }
+    if (i + 1 >= argc) { fprintf(stderr, "%s needs a value (see --help)\n", a.c_str()); return 2; }
+    const char* v = argv[++i];
+    if (a == "--streams") o.streams = atoi(v);
+    else if (a == "--mb-per-stream") o.mb = atol(v);
+    else if (a == "--block-kb") o.block_kb = atoi(v);
+    else if (a == "--nics") o.nics = atoi(v);
+    else { fprintf(stderr, "unknown argument %s (see --help)\n", a.c_str()); return 2; }
   }
   if (o.streams < 1 || o.streams > 256 || o.nics < 1) return 2;
   int ports[2], go[2];

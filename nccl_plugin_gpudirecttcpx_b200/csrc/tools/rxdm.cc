@@ -146,12 +146,19 @@ bool serve(State* st, UnixSocketConnection* c, const std::string& service) {
 int main(int argc, char** argv) {
   State st;
   st.prefix = "/tmp";
-  for (int i = 1; i + 1 < argc; i += 2) {
+  for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
-    if (a == "--prefix") st.prefix = argv[i + 1];
-    else if (a == "--pool-mb") st.pool_bytes = strtoull(argv[i + 1], nullptr, 0) << 20;
-    else if (a == "--max-rules") st.max_rules = strtoull(argv[i + 1], nullptr, 0);
-    else { fprintf(stderr, "unknown argument %s\n", a.c_str()); return 2; }
+    if (a == "--help" || a == "-h") {
+      printf("usage: tcpxb_rxdm [--prefix DIR] [--pool-mb N] [--max-rules N]\n"
+             "Serves the rx buffer manager's UNIX sockets under DIR (default /tmp) until SIGINT or SIGTERM.\n");
+      return 0;
+    }
+    if (i + 1 >= argc) { fprintf(stderr, "%s needs a value (see --help)\n", a.c_str()); return 2; }
+    const char* v = argv[++i];
+    if (a == "--prefix") st.prefix = v;
+    else if (a == "--pool-mb") st.pool_bytes = strtoull(v, nullptr, 0) << 20;
+    else if (a == "--max-rules") st.max_rules = strtoull(v, nullptr, 0);
+    else { fprintf(stderr, "unknown argument %s (see --help)\n", a.c_str()); return 2; }
   }
   mkdir(st.prefix.c_str(), 0755);
   signal(SIGINT, onSignal);
