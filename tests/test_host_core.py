@@ -228,3 +228,27 @@ def test_rx_buffer_manager_daemon(host_lib, tmp_path):
         except subprocess.TimeoutExpired:
             daemon.kill()
     assert "application 4242 went away" in daemon.stderr.read()
+
+
+@pytest.mark.parametrize("mode", ["unpack", "host"])
+def test_daemon_pool_carries_device_receives_on_standin_device(host_lib, tmp_path, mode):
+    """Receives into device memory land in the pool that the daemon owns and hands over as a file
+    descriptor."""
+    prefix = tmp_path / "rxdm"
+    daemon = subprocess.Popen([str(LIB / "tcpxb_rxdm"), "--prefix", str(prefix), "--pool-mb", "32"],
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        assert daemon.stdout.readline().strip() == "ready"
+        env = dict(TCPXB_FAKE_GPU=1, NCCL_GPUDIRECTTCPX_RX_BUF_MGR="daemon", NCCL_GPUDIRECTTCPX_UNIX_CLIENT_PREFIX=str(prefix))
+        env.update({"NCCL_GPUDIRECTTCPX_RECV_MODE": "unpack"} if mode == "unpack" else {"NCCL_GPUDIRECTTCPX_CUDA_BUFFERS": 1})
+        r = _loopback(host_lib, ["--ptr", "cuda", "--sizes", "0,1000,300000,4194304", "--inflight", "8", "--iters", "2"], **env)
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+        assert "loopback PASSED" in r.stdout
+    finally:
+        daemon.terminate()
+        try:
+            daemon.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            daemon.kill()
+    log = daemon.stderr.read()
+    assert "pool for GPU 0000:00:00.0: 32 MiB" in log, log[-2000:]  # the pool came from the daemon
