@@ -1,6 +1,7 @@
 """Lists every environment variable the transport understands (name, kind, default, meaning).
 
-    python -m nccl_plugin_gpudirecttcpx_b200.utils.flags          # table on stdout
+    python -m nccl_plugin_gpudirecttcpx_b200.utils.flags              # table on stdout
+    python -m nccl_plugin_gpudirecttcpx_b200.utils.flags --markdown   # the table of docs/environment.md
 """
 from __future__ import annotations
 
@@ -26,7 +27,18 @@ def flag_docs() -> List[Tuple[str, str, str, str]]:
     return out
 
 
+def markdown_table() -> str:
+    lines = ["| variable | kind | default | meaning |", "|---|---|---|---|"]
+    for env, kind, dflt, doc in flag_docs():
+        lines.append(f"| `{env}` | {kind} | {('`' + dflt + '`') if dflt else '-'} | {doc} |")
+    return "\n".join(lines) + "\n"
+
+
 if __name__ == "__main__":
+    import sys
+    if "--markdown" in sys.argv[1:]:
+        sys.stdout.write(markdown_table())
+        sys.exit(0)
     rows = flag_docs()
     width = max(len(r[0]) for r in rows)
     for env, kind, dflt, doc in rows:

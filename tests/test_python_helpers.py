@@ -57,3 +57,12 @@ def test_clock_sampler_without_nvidia_smi(monkeypatch):
                  ["0", "1800", "1965", "990.0", "Not Active", "Not Active", "Not Active", "Not Active"]]
     out = s.summary()
     assert out["sm_mhz"] == 1882.5 and out["sm_max_mhz"] == 1965 and out["reasons"] == ["sw_power_cap"]
+
+
+def test_environment_doc_matches_the_flag_registry():
+    """docs/environment.md carries the table the native registry generates."""
+    from pathlib import Path
+    from nccl_plugin_gpudirecttcpx_b200.utils.flags import markdown_table
+    text = (Path(__file__).resolve().parent.parent / "docs" / "environment.md").read_text()
+    table = text.split("<!-- table:begin -->\n")[1].split("<!-- table:end -->")[0]
+    assert table == markdown_table()
