@@ -3,7 +3,12 @@
 //
 //   tcpxb_loopback --plugin <libnccl-net.so | libtcpxb_host.so> [--v7]
 //                  [--sizes 1024,65536,4194304,67108864] [--inflight 8] [--iters 4]
-//                  [--ptr host|cuda] [--yield]
+//                  [--ptr host|cuda] [--yield] [--random-sizes]
+//
+// `--random-sizes`: each listed size is the capacity of the posted receives; every message
+// carries a seeded random number of bytes between 0 and that capacity (both sides derive
+// it from the key), as under NCCL, which posts the largest size a step may bring.  The
+// receiver checks the size test() reports and that nothing beyond it was written.
 //
 // `--yield` makes the polling loop call sched_yield() after a pass that neither posted
 // nor finished anything, as NCCL's proxy thread does; without it the loop spins.
@@ -114,6 +119,19 @@ uint64_t keyOf(uint64_t seed, int comm, int size_idx, int iter, int tag) {
   return ((((seed * 131 + (uint64_t)comm) * 131 + (uint64_t)size_idx) * 131 + (uint64_t)iter) * 131) + (uint64_t)tag;
 }
 
+// Bytes message `key` really carries when sizes are random: 0..cap, with the edges likely.
+size_t actualSize(bool random, size_t cap, uint64_t key) {
+  if (!random || cap == 0) return cap;
+  uint64_t x = key * 0xd6e8feb86659fd93ull + 0x9e3779b97f4a7c15ull;
+  x ^= x >> 32; x *= 0xd6e8feb86659fd93ull; x ^= x >> 32;
+  switch (x & 7) {
+    case 0: return 0;
+    case 1: return cap;
+    case 2: return cap > 1 ? cap - 1 : cap;
+    default: return (size_t)((x >> 8) % (cap + 1));
+  }
+}
+
 bool loadApi(const char* path, bool v7, Api* api) {
   void* h = dlopen(path, RTLD_NOW | RTLD_LOCAL);
   if (h == nullptr) { fprintf(stderr, "dlopen(%s): %s\n", path, dlerror()); return false; }
@@ -180,6 +198,7 @@ struct Options {
   uint64_t seed = 42;
   int ptr_type = NCCL_PTR_HOST;
   bool yield_when_idle = false;
+  bool random_sizes = false;
 };
 
 int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
@@ -236,7 +255,7 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
     char tok = 'g';
     if (receiver) { if (write(wfd, &tok, 1) != 1) return 1; }
     else if (read(rfd, &tok, 1) != 1) return 1;
-    double dt = 0, cpu_user = 0, cpu_sys = 0;
+    double dt = 0, cpu_user = 0, cpu_sys = 0, bytes = 0;
     for (int it = 0; it < opt.iters && rc == 0; ++it) {
       std::vector<void*> reqs(nbuf, nullptr);
       if (!receiver)
@@ -259,7 +278,8 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
             int sz = (int)size, tag = b % opt.inflight;
             CHECK(api.irecv(comm, 1, &data, &sz, &tag, &mh[b], &reqs[b]));
           } else {
-            CHECK(api.isend(comm, bufs[b].data(), (int)size, b % opt.inflight, mh[b], &reqs[b]));
+            const size_t act = actualSize(opt.random_sizes, size, keyOf(opt.seed, b / opt.inflight, (int)si, it, b % opt.inflight));
+            CHECK(api.isend(comm, bufs[b].data(), (int)act, b % opt.inflight, mh[b], &reqs[b]));
           }
           if (reqs[b] != nullptr) ++posted;
         }
@@ -288,16 +308,20 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
       cpu_user += u1 - u0;
       cpu_sys += s1 - s0;
       for (int b = 0; b < nbuf; ++b) {
-        if (got_size[b] != (int)size) { fprintf(stderr, "size mismatch: test reported %d, expected %zu\n", got_size[b], size); rc = 1; }
+        const uint64_t key = keyOf(opt.seed, b / opt.inflight, (int)si, it, b % opt.inflight);
+        const size_t act = actualSize(opt.random_sizes, size, key);
+        bytes += (double)act;
+        if (got_size[b] != (int)act) { fprintf(stderr, "size mismatch: test reported %d, expected %zu\n", got_size[b], act); rc = 1; }
         if (!receiver) continue;
-        fillPayload(expect.data(), size, keyOf(opt.seed, b / opt.inflight, (int)si, it, b % opt.inflight));
-        if (memcmp(expect.data(), bufs[b].data(), size) != 0) {
-          fprintf(stderr, "payload mismatch: size %zu iter %d comm %d tag %d\n", size, it, b / opt.inflight, b % opt.inflight);
+        fillPayload(expect.data(), size, key);
+        if (memcmp(expect.data(), bufs[b].data(), act) != 0) {
+          fprintf(stderr, "payload mismatch: size %zu of %zu iter %d comm %d tag %d\n", act, size, it, b / opt.inflight, b % opt.inflight);
           rc = 1;
         }
+        for (size_t k = act; k < size; ++k)
+          if (bufs[b][k] != 0xEE) { fprintf(stderr, "byte %zu beyond the message's %zu bytes was written\n", k, act); rc = 1; break; }
       }
     }
-    const double bytes = (double)size * nbuf * opt.iters;
     // the receiver's line is the result; the sender's carries its CPU seconds for the same transfers
     printf("{\"tool\": \"%s\", \"side\": \"%s\", \"size\": %zu, \"messages\": %d, \"inflight\": %d, \"comms\": %d, "
            "\"seconds\": %.6f, \"GBps\": %.3f, \"cpu_user_s\": %.4f, \"cpu_sys_s\": %.4f, \"byte_exact\": %s}\n",
@@ -327,7 +351,7 @@ int main(int argc, char** argv) {
     auto next = [&]() -> const char* { return i + 1 < argc ? argv[++i] : ""; };
     if (a == "--help" || a == "-h") {
       printf("usage: tcpxb_loopback --plugin LIB [--v7] [--sizes a,b,...] [--inflight 1..16] [--iters N] [--seed S]\n"
-             "                      [--ptr host|cuda] [--yield]\n");
+             "                      [--ptr host|cuda] [--yield] [--random-sizes]\n");
       return 0;
     }
     if (a == "--plugin") opt.plugin = next();
@@ -336,6 +360,7 @@ int main(int argc, char** argv) {
     else if (a == "--iters") opt.iters = atoi(next());
     else if (a == "--seed") opt.seed = strtoull(next(), nullptr, 0);
     else if (a == "--yield") opt.yield_when_idle = true;
+    else if (a == "--random-sizes") opt.random_sizes = true;
     else if (a == "--ptr") opt.ptr_type = std::string(next()) == "cuda" ? NCCL_PTR_CUDA : NCCL_PTR_HOST;
     else if (a == "--sizes") {
       opt.sizes.clear();

@@ -74,6 +74,8 @@ def test_api_loopback_byte_exact_with_flow_stats(host_lib):
 
 @pytest.mark.parametrize("variant", [
     dict(args=["--v7"]),
+    dict(args=["--random-sizes"]),                                   # receives posted larger than what arrives
+    dict(args=["--random-sizes"], NCCL_INLINE_THRESHOLD=2048),
     dict(NCCL_GPUDIRECTTCPX_SCHED_ALG="KATY"),
     dict(NCCL_INLINE_THRESHOLD=2048),
     dict(NCCL_GPUDIRECTTCPX_RECV_SYNC=1),
@@ -133,6 +135,8 @@ STANDIN_VARIANTS = [
     dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack"),
     dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_GPUDIRECTTCPX_RX_POOL_SCATTER=1, NCCL_GPUDIRECTTCPX_RX_POOL_BYTES=32 << 20),
     dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_GPUDIRECTTCPX_RX_POOL_MODE="device", args=["--v7"]),
+    dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", args=["--random-sizes"]),
+    dict(NCCL_GPUDIRECTTCPX_CUDA_BUFFERS=1, NCCL_INLINE_THRESHOLD=2048, args=["--random-sizes"]),
     # two connections share a pool that holds exactly one of the largest messages: whoever gets the
     # pool's promise goes first, nobody waits while holding pages
     dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_GPUDIRECTTCPX_RX_POOL_BYTES=8 << 20),
