@@ -212,10 +212,14 @@ const Flags& flags() {
 }
 
 void reloadFlags() {
+  // Readers hold plain references with no count, so a replaced table is never freed:
+  // it is parked here, reachable until the process ends.  Reloads happen at init only.
+  static std::vector<Flags*>* retired = new std::vector<Flags*>();
   std::lock_guard<std::mutex> l(g_mu);
   Flags* f = new Flags();
   loadFlags(f);
-  g_flags.store(f, std::memory_order_release);
+  Flags* old = g_flags.exchange(f, std::memory_order_acq_rel);
+  if (old != nullptr) retired->push_back(old);
 }
 
 const std::vector<FlagDoc>& flagDocs() {

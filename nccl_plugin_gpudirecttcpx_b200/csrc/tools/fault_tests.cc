@@ -281,6 +281,47 @@ TEST(silent_sender_trips_the_detectors) {
   EXPECT(netInit(nullptr) == kSuccess);
 }
 
+TEST(close_with_transfers_in_flight) {
+  // NCCL's abort path closes comms whatever state they are in: helper threads must
+  // stop, nothing may be touched afterwards, and the other side sees an error.
+  Pair p;
+  EXPECT(makePair(&p));
+  std::vector<uint8_t> src(32 << 20, 7), dst(32 << 20);
+  std::vector<Request*> rs(4, nullptr);
+  Request* rr = nullptr;
+  void* data = dst.data();
+  int sz = (int)dst.size(), tag = 0;
+  EXPECT(netIrecv(p.r, 1, &data, &sz, &tag, nullptr, &rr) == kSuccess && rr != nullptr);
+  for (auto& q : rs) EXPECT(netIsend(p.s, src.data(), (int)src.size(), 0, nullptr, &q) == kSuccess && q != nullptr);
+  int done = 0, got = 0;
+  EXPECT(netTest(rs[0], &done, &got) == kSuccess);  // some bytes are moving, nothing is complete on the wire yet
+  const uint64_t t0 = monotonicNanos();
+  EXPECT(netClose(p.s) == kSuccess);                // three and a half messages never leave
+  p.s = nullptr;
+  EXPECT(monotonicNanos() - t0 < 3000000000ull);
+  // the first message may or may not have made it; the second receive can only fail
+  Result a = pollBounded(rr, &done, &got);
+  EXPECT(a == kRemoteError || a == kSystemError || (a == kSuccess && done));
+  if (a == kSuccess) {
+    Request* rr2 = nullptr;
+    Result b = netIrecv(p.r, 1, &data, &sz, &tag, nullptr, &rr2);
+    if (b == kSuccess && rr2 != nullptr) b = pollBounded(rr2, &done, &got);
+    EXPECT(b == kRemoteError || b == kSystemError);
+  }
+  closePair(&p);
+}
+
+TEST(close_listen_with_nobody_connecting) {
+  char handle[kHandleMaxSize];
+  ListenComm* l = nullptr;
+  EXPECT(netListen(0, handle, &l) == kSuccess);
+  Comm* r = nullptr;
+  for (int i = 0; i < 3; ++i) EXPECT(netAccept(l, &r) == kSuccess && r == nullptr);  // an accept is pending in the background
+  const uint64_t t0 = monotonicNanos();
+  EXPECT(netCloseListen(l) == kSuccess);  // must not wait for a peer that never comes
+  EXPECT(monotonicNanos() - t0 < 3000000000ull);
+}
+
 TEST(connect_to_dead_listener_fails_cleanly) {
   setenv("NCCL_GPUDIRECTTCPX_CONNECT_REFUSED_RETRIES", "300", 1);  // 0.3 s instead of 20 s
   EXPECT(netInit(nullptr) == kSuccess);
@@ -313,6 +354,10 @@ struct DevXfer {
   std::vector<uint8_t> src, dst;
   MemHandle *smh = nullptr, *rmh = nullptr;
   Request *rs = nullptr, *rr = nullptr;
+  ~DevXfer() {  // registrations do not refer to the comm, so they may outlive it
+    netDeregMr(nullptr, smh);
+    netDeregMr(nullptr, rmh);
+  }
 };
 
 // Registers both buffers as device memory and posts the receive, then the send.
@@ -372,6 +417,7 @@ TEST(device_consumer_behind_gets_try_again) {
     EXPECT(netIrecvConsumed(p.r, 1, x[i].rr) == kSuccess);
   }
   closePair(&p);
+  netDeregMr(nullptr, emh);
   unpackModeOff();
 }
 
@@ -413,6 +459,7 @@ TEST(device_send_and_the_staging_ring) {
   Request* rs = nullptr;
   EXPECT(netRegMr(p.s, big.data(), big.size(), kPtrCuda, &bmh) == kSuccess);
   EXPECT(netIsend(p.s, big.data(), (int)big.size(), 0, bmh, &rs) == kInvalidArgument && rs == nullptr);
+  netDeregMr(nullptr, bmh);
   // messages as large as the ring go through one after the other, also after the ring's
   // write position has moved off zero
   const int sizes[] = {300001, 1048576, 4096, 1048576, 1048576};

@@ -118,7 +118,7 @@ def test_telemetry_files(host_lib, tmp_path):
 @pytest.mark.parametrize("san", ["address", "thread"])
 def test_loopback_under_sanitizer(san):
     lib = _build.build_host(sanitize=san)
-    env = {"ASAN_OPTIONS": "detect_leaks=0", "TSAN_OPTIONS": "halt_on_error=1 second_deadlock_stack=1"}
+    env = {"ASAN_OPTIONS": "detect_leaks=1", "TSAN_OPTIONS": "halt_on_error=1 second_deadlock_stack=1"}
     r = _loopback(lib, ["--sizes", "0,1000,65536,2000000", "--inflight", "8", "--iters", "2"],
                   exe=f"tcpxb_loopback_{san}", timeout=600, **env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
@@ -184,7 +184,7 @@ def test_host_build_rejects_device_pointers_without_standin(host_lib):
 @pytest.mark.parametrize("mode", ["host", "unpack"])
 def test_standin_device_under_sanitizer(san, mode):
     lib = _build.build_host(sanitize=san)
-    env = {"ASAN_OPTIONS": "detect_leaks=0", "TSAN_OPTIONS": "halt_on_error=1 second_deadlock_stack=1", "TCPXB_FAKE_GPU": "1",
+    env = {"ASAN_OPTIONS": "detect_leaks=1", "TSAN_OPTIONS": "halt_on_error=1 second_deadlock_stack=1", "TCPXB_FAKE_GPU": "1",
            "NCCL_GPUDIRECTTCPX_RX_POOL_SCATTER": "1", "NCCL_GPUDIRECTTCPX_RX_POOL_BYTES": str(64 << 20)}
     env.update({"NCCL_GPUDIRECTTCPX_RECV_MODE": "unpack"} if mode == "unpack" else {"NCCL_GPUDIRECTTCPX_CUDA_BUFFERS": "1"})
     r = _loopback(lib, ["--ptr", "cuda", "--sizes", "0,1000,65536,2000000", "--inflight", "8", "--iters", "2"],
@@ -201,13 +201,13 @@ def test_fault_paths_surface_as_errors(host_lib):
     pages: error codes, "try again" or back-pressure, never a hang."""
     r = subprocess.run([str(LIB / "tcpxb_fault_tests")], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert "14 test(s), 0 failure(s)" in r.stdout
+    assert "16 test(s), 0 failure(s)" in r.stdout
 
 
 @pytest.mark.parametrize("san", ["address", "thread"])
 def test_fault_paths_under_sanitizer(san):
     _build.build_host(sanitize=san)
-    env = dict(os.environ, ASAN_OPTIONS="detect_leaks=0", TSAN_OPTIONS="halt_on_error=1 second_deadlock_stack=1")
+    env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1", TSAN_OPTIONS="halt_on_error=1 second_deadlock_stack=1")
     r = subprocess.run([str(LIB / f"tcpxb_fault_tests_{san}")], capture_output=True, text=True, timeout=900, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
     assert "0 failure(s)" in r.stdout
