@@ -115,7 +115,7 @@ def test_telemetry_files(host_lib, tmp_path):
     assert all(l.startswith("per_flow_stats[") for l in stats[0].read_text().splitlines())
 
 
-@pytest.mark.parametrize("san", ["address", "thread"])
+@pytest.mark.parametrize("san", ["address", "thread", "undefined"])
 def test_loopback_under_sanitizer(san):
     lib = _build.build_host(sanitize=san)
     env = {"ASAN_OPTIONS": "detect_leaks=1", "TSAN_OPTIONS": "halt_on_error=1 second_deadlock_stack=1"}
@@ -124,6 +124,7 @@ def test_loopback_under_sanitizer(san):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
     assert "loopback PASSED" in r.stdout
     assert "WARNING: ThreadSanitizer" not in r.stderr and "ERROR: AddressSanitizer" not in r.stderr
+    assert "runtime error:" not in r.stderr
 
 
 STANDIN_VARIANTS = [
@@ -192,6 +193,7 @@ def test_standin_device_under_sanitizer(san, mode):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
     assert "loopback PASSED" in r.stdout
     assert "WARNING: ThreadSanitizer" not in r.stderr and "ERROR: AddressSanitizer" not in r.stderr
+    assert "runtime error:" not in r.stderr
 
 
 def test_fault_paths_surface_as_errors(host_lib):
@@ -204,7 +206,7 @@ def test_fault_paths_surface_as_errors(host_lib):
     assert "16 test(s), 0 failure(s)" in r.stdout
 
 
-@pytest.mark.parametrize("san", ["address", "thread"])
+@pytest.mark.parametrize("san", ["address", "thread", "undefined"])
 def test_fault_paths_under_sanitizer(san):
     _build.build_host(sanitize=san)
     env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1", TSAN_OPTIONS="halt_on_error=1 second_deadlock_stack=1")
@@ -212,6 +214,7 @@ def test_fault_paths_under_sanitizer(san):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
     assert "0 failure(s)" in r.stdout
     assert "WARNING: ThreadSanitizer" not in r.stderr and "ERROR: AddressSanitizer" not in r.stderr
+    assert "runtime error:" not in r.stderr
 
 
 def test_rx_buffer_manager_daemon(host_lib, tmp_path):
