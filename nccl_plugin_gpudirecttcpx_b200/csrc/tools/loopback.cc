@@ -3,7 +3,7 @@
 //
 //   tcpxb_loopback --plugin <libnccl-net.so | libtcpxb_host.so> [--v7]
 //                  [--sizes 1024,65536,4194304,67108864] [--inflight 8] [--iters 4]
-//                  [--ptr host|cuda] [--yield] [--random-sizes]
+//                  [--ptr host|cuda] [--yield] [--random-sizes] [--thread-times]
 //
 // `--random-sizes`: each listed size is the capacity of the posted receives; every message
 // carries a seeded random number of bytes between 0 and that capacity (both sides derive
@@ -30,6 +30,7 @@
 // each side prints per-flow byte counters and one JSON line per size.
 // The reference has no such tool: its only tests are two unit tests of the stats
 // code (reference: src/stats/tracepoint_test.cc, src/stats/stats_buffer_test.cc).
+#include <dirent.h>
 #include <dlfcn.h>
 #include <sched.h>
 #include <signal.h>
@@ -189,6 +190,32 @@ void printFlows(const char* side, int ci, void* comm) {
   }
 }
 
+// CPU seconds of every thread of this process, by thread name (helper threads are named
+// tcpxb-tx<i> / tcpxb-rx<i>), from /proc: shows where a core-starved box spends its time.
+void printThreadTimes(const char* side) {
+  DIR* d = opendir("/proc/self/task");
+  if (d == nullptr) return;
+  const double tick = 1.0 / (double)sysconf(_SC_CLK_TCK);
+  while (struct dirent* e = readdir(d)) {
+    if (e->d_name[0] == '.') continue;
+    std::string path = std::string("/proc/self/task/") + e->d_name + "/stat";
+    FILE* f = fopen(path.c_str(), "r");
+    if (f == nullptr) continue;
+    char line[1024];
+    if (fgets(line, sizeof line, f) != nullptr) {
+      char* open = strchr(line, '(');
+      char* close = strrchr(line, ')');
+      unsigned long ut = 0, st = 0;
+      if (open && close && sscanf(close + 2, "%*c %*d %*d %*d %*d %*d %*u %*u %*u %*u %*u %lu %lu", &ut, &st) == 2) {
+        *close = 0;
+        printf("THREAD %s %s user %.3f sys %.3f\n", side, open + 1, (double)ut * tick, (double)st * tick);
+      }
+    }
+    fclose(f);
+  }
+  closedir(d);
+}
+
 struct Options {
   std::string plugin;
   bool v7 = false;
@@ -199,6 +226,7 @@ struct Options {
   int ptr_type = NCCL_PTR_HOST;
   bool yield_when_idle = false;
   bool random_sizes = false;
+  bool thread_times = false;
 };
 
 int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
@@ -330,6 +358,7 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
     for (int b = 0; b < nbuf; ++b) CHECK(api.deregMr(comms[b / opt.inflight], mh[b]));
   }
   for (int c = 0; c < ncomm; ++c) printFlows(receiver ? "recv" : "send", c, comms[c]);
+  if (opt.thread_times) printThreadTimes(receiver ? "recv" : "send");
   fflush(stdout);
   // the sender closes after the receiver confirmed it has everything
   char tok = 'c';
@@ -351,7 +380,7 @@ int main(int argc, char** argv) {
     auto next = [&]() -> const char* { return i + 1 < argc ? argv[++i] : ""; };
     if (a == "--help" || a == "-h") {
       printf("usage: tcpxb_loopback --plugin LIB [--v7] [--sizes a,b,...] [--inflight 1..16] [--iters N] [--seed S]\n"
-             "                      [--ptr host|cuda] [--yield] [--random-sizes]\n");
+             "                      [--ptr host|cuda] [--yield] [--random-sizes] [--thread-times]\n");
       return 0;
     }
     if (a == "--plugin") opt.plugin = next();
@@ -361,6 +390,7 @@ int main(int argc, char** argv) {
     else if (a == "--seed") opt.seed = strtoull(next(), nullptr, 0);
     else if (a == "--yield") opt.yield_when_idle = true;
     else if (a == "--random-sizes") opt.random_sizes = true;
+    else if (a == "--thread-times") opt.thread_times = true;
     else if (a == "--ptr") opt.ptr_type = std::string(next()) == "cuda" ? NCCL_PTR_CUDA : NCCL_PTR_HOST;
     else if (a == "--sizes") {
       opt.sizes.clear();
