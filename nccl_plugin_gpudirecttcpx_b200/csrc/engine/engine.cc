@@ -170,7 +170,11 @@ int launchUnpack(Engine* e, Request* req, const RecvSpec& rs, uint64_t region_of
     // Baseline: unpack to a bounce buffer, add in a second pass, copy to the peers.
     ENG_TRY(ensureScratch(e, e->scratch_bytes));
     uint8_t* bounce = e->scratch + e->scratch_bytes - (uint64_t)e->req_bytes;
-    ENG_K(tcpxb_unpack_copy(sl.pool_dev, sl.pool_bytes, acc ? bounce : dst, len, descs, count, e->status_dev, &opts, stream));
+    // the unpack kernel must not publish completion here: the add and the peer copies come after it
+    tcpxbUnpackOpts copy_opts;
+    memset(&copy_opts, 0, sizeof copy_opts);
+    copy_opts.max_ctas = opts.max_ctas;
+    ENG_K(tcpxb_unpack_copy(sl.pool_dev, sl.pool_bytes, acc ? bounce : dst, len, descs, count, e->status_dev, &copy_opts, stream));
     if (acc) {
       void* srcs[2] = {const_cast<uint8_t*>(acc), bounce};
       ENG_K(tcpxb_peer_reduce(dst, srcs, 2, 0, len & ~15ull, rs.dtype, stream));

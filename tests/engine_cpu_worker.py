@@ -69,10 +69,17 @@ def main():
             tol = 0.04 * ranks if dtype == torch.bfloat16 else 1e-4 * ranks
             for rep in range(2):  # twice: buffers and flag epochs are reused
                 y = eng.all_reduce(ins[rank].clone())
-                err = (y.float() - want).abs().max().item()
+                diff = (y.float() - want).abs()
+                err = diff.max().item()
                 good = err <= tol
                 ok = ok and good
-                detail.append(("all_reduce", str(dtype), n, rep, err, good))
+                where = ""
+                if not good:  # which elements, and do they heal once every rank is past the step
+                    badix = (diff > tol).nonzero().flatten()
+                    time.sleep(1.0)
+                    later = ((y.float() - want).abs() > tol).sum().item()
+                    where = f"{badix.numel()} bad in [{badix[0].item()}, {badix[-1].item()}], {later} still bad a second later"
+                detail.append(("all_reduce", str(dtype), n, rep, err, good, where) if where else ("all_reduce", str(dtype), n, rep, err, good))
             if n % ranks == 0:
                 per = n // ranks
                 g = eng.all_gather(ins[rank][:per].clone())
@@ -101,7 +108,7 @@ def main():
     status = eng.device_status()
     ok = ok and status[0] == 0
     st = eng.stats()
-    bad = [d for d in detail if not d[-1]]
+    bad = [d for d in detail if not d[5]]
     print(json.dumps({"rank": rank, "world": world, "G": G, "ok": bool(ok), "checks": len(detail), "bad": bad[:6],
                       "device_status": status, "unpack_launches": st.unpack_launches, "fragments": st.fragments}), flush=True)
     eng.close()
