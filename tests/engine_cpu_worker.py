@@ -31,7 +31,7 @@ def main():
     from standin_engine import StandinEngine
     default_transport_env(nics=2, nthreads=2, nsocks_per_thread=1, pool_mb=64, chunk_bytes=128 * 1024)
     numels = [int(s) for s in os.environ.get("TCPXB_TEST_NUMELS", "3072,786432").split(",")]
-    buf_bytes = max(numels) * 4 * 2
+    buf_bytes = max(numels) * 4  # the largest case in fp32
     eng = StandinEngine(gpus_per_node=G, buffer_bytes=buf_bytes if G > 1 else 0, request_bytes=256 << 10,
                         plain_mode=bool(int(os.environ.get("TCPXB_TEST_PLAIN", "0"))),
                         reduce_impl=int(os.environ.get("TCPXB_TEST_REDUCE_IMPL", "0")))

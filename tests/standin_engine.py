@@ -60,7 +60,8 @@ class StandinEngine(HierarchicalEngine):
         n_el = (buffer_bytes + 3) // 4
         self.buffer_bytes = n_el * 4
         counts = {"work": n_el, "out": n_el, "flags": 64}
-        path = lambda r, name: f"/dev/shm/tcpxb_{tag[0]}_{r}_{name}"
+        shm_dir = os.environ.get("TCPXB_TEST_SHM_DIR", "/dev/shm")
+        path = lambda r, name: f"{shm_dir}/tcpxb_{tag[0]}_{r}_{name}"
         mine = {name: _shared_int32(path(self.rank, name), c, create=True) for name, c in counts.items()}
         for t in mine.values():
             t.zero_()
