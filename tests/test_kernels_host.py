@@ -163,3 +163,42 @@ def test_peer_reduce_and_checksum(k):
     got = ctypes.c_uint64(0)
     assert k.tcpxb_checksum_noalloc(buf.data_ptr(), buf.numel(), ctypes.byref(got), None) == 0
     assert got.value == want_sum
+
+
+def test_streaming_ready_counter(k):
+    """Records are consumed as a producer publishes them; a counter that stops short runs the
+    bounded wait out and the rest is reported, not waited for."""
+    import threading
+    import time
+    total = 4096 * 32
+    pool, descs = _case(total, 33)
+    want = reference_unpack(pool, torch.zeros(total, dtype=torch.uint8), descs)
+    counter = torch.zeros(1, dtype=torch.int32)
+    opts = Opts()
+    opts.ready_count = counter.data_ptr()
+    opts.wait_ns = 2_000_000_000
+    status = torch.zeros(4, dtype=torch.int32)
+    dst = torch.zeros(total, dtype=torch.uint8)
+    p, n = _dptr(descs)
+
+    def producer():
+        for i in range(1, n + 1):
+            if i % 8 == 0:
+                time.sleep(0.001)
+            counter[0] = i
+
+    t = threading.Thread(target=producer)
+    t.start()
+    rc = k.tcpxb_unpack_copy(pool.data_ptr(), pool.numel(), dst.data_ptr(), total, p, n, status.data_ptr(), ctypes.byref(opts), None)
+    t.join()
+    assert rc == 0 and status[0].item() == 0 and torch.equal(dst, want)
+    # the producer stops after 10 records
+    counter[0] = 10
+    opts.wait_ns = 50_000_000
+    dst.zero_()
+    t0 = time.time()
+    assert k.tcpxb_unpack_copy(pool.data_ptr(), pool.numel(), dst.data_ptr(), total, p, n, status.data_ptr(), ctypes.byref(opts), None) == 0
+    assert time.time() - t0 < 1.0
+    assert status.tolist()[:3] == [3, 10, n - 10]  # TCPXB_ST_TIMEOUT from record 10 on
+    partial = reference_unpack(pool, torch.zeros(total, dtype=torch.uint8), descs[:10])
+    assert torch.equal(dst, partial)
