@@ -236,6 +236,26 @@ TEST(forged_control_record_is_rejected) {
   closePair(&p);
 }
 
+TEST(truncated_control_record_then_close) {
+  // half a record arrives, then the peer's control socket goes away: an error, not a wait for the rest
+  Pair p;
+  EXPECT(makePair(&p));
+  std::vector<uint8_t> dst(4096);
+  Request* rr = nullptr;
+  void* data = dst.data();
+  int sz = 4096, tag = 0;
+  EXPECT(netIrecv(p.r, 1, &data, &sz, &tag, nullptr, &rr) == kSuccess && rr != nullptr);
+  CtrlMsg half = {kCtrlNormal, 0, 4096, 0, 4096};
+  EXPECT(send(p.s->ctrl_fd, &half, 7, 0) == 7);
+  int done = 0, got = 0;
+  const uint64_t until = monotonicNanos() + 50000000ull;  // 50 ms: the fragment alone completes nothing
+  while (monotonicNanos() < until) EXPECT(netTest(rr, &done, &got) == kSuccess && !done);
+  shutdown(p.s->ctrl_fd, SHUT_RDWR);
+  Result r = pollBounded(rr, &done, &got);
+  EXPECT(r == kRemoteError || r == kSystemError);
+  closePair(&p);
+}
+
 TEST(message_larger_than_posted_receive) {
   Pair p;
   EXPECT(makePair(&p));
