@@ -263,6 +263,59 @@ TEST(flags_defaults_and_ranges) {
   EXPECT(flagDocs().size() > 50);
 }
 
+TEST(page_allocator_random_walk) {
+  // thousands of random allocations, promises and releases: a page is never out twice,
+  // the counts always add up, and a promise can always be drawn
+  for (int variant = 0; variant < 3; ++variant) {
+    const uint32_t total = 777;
+    PageAllocator a(total, variant > 0, 12345 + (uint64_t)variant, variant == 2 ? 8 : 1);
+    std::vector<std::vector<PageRun>> held;
+    std::vector<uint8_t> out(total, 0);
+    uint32_t in_use = 0, promised = 0;
+    uint64_t x = 88172645463325252ull + (uint64_t)variant;
+    auto rnd = [&x]() { x ^= x << 13; x ^= x >> 7; x ^= x << 17; return x; };
+    bool ok = true;
+    for (int step = 0; step < 20000 && ok; ++step) {
+      const uint32_t op = (uint32_t)(rnd() % 4);
+      if (op == 0 || op == 1) {  // allocate, sometimes out of a promise
+        const uint32_t n = 1 + (uint32_t)(rnd() % 40);
+        const bool from_promise = op == 1 && promised >= n;
+        std::vector<PageRun> runs;
+        const bool got = a.alloc(n, &runs, from_promise);
+        const bool should = from_promise ? true : (total - in_use - promised >= n);
+        ok = ok && got == should;
+        if (got) {
+          uint32_t count = 0;
+          for (const PageRun& r : runs)
+            for (uint32_t i = 0; i < r.count; ++i) { ok = ok && r.first + i < total && !out[r.first + i]; out[r.first + i] = 1; ++count; }
+          ok = ok && count == n;
+          in_use += n;
+          if (from_promise) promised -= n;
+          held.push_back(runs);
+        } else {
+          ok = ok && runs.empty();
+        }
+      } else if (op == 2) {  // promise
+        const uint32_t n = 1 + (uint32_t)(rnd() % 60);
+        const bool got = a.reserve(n);
+        ok = ok && got == (total - in_use - promised >= n);
+        if (got) promised += n;
+      } else if (!held.empty()) {  // release one allocation, now and then also give a promise back
+        const size_t k = (size_t)(rnd() % held.size());
+        for (const PageRun& r : held[k]) {
+          a.release(r.first, r.count);
+          for (uint32_t i = 0; i < r.count; ++i) out[r.first + i] = 0;
+          in_use -= r.count;
+        }
+        held.erase(held.begin() + (long)k);
+        if (promised > 0 && rnd() % 3 == 0) { const uint32_t back = 1 + (uint32_t)(rnd() % promised); a.unreserve(back); promised -= back; }
+      }
+      ok = ok && a.freePages() == total - in_use && a.reservedPages() == promised;
+    }
+    EXPECT(ok);
+  }
+}
+
 // ---------------------------------------------------------------- interface lists
 TEST(interface_list_syntax) {
   IfList l = parseIfList("eth,ib0");
