@@ -207,6 +207,17 @@ def test_fault_paths_surface_as_errors(host_lib):
 
 
 @pytest.mark.parametrize("san", ["address", "thread", "undefined"])
+def test_unit_tests_under_sanitizer(san):
+    _build.build_host(sanitize=san)
+    env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1", TSAN_OPTIONS="halt_on_error=1 second_deadlock_stack=1")
+    r = subprocess.run([str(LIB / f"tcpxb_unit_tests_{san}")], capture_output=True, text=True, timeout=900, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
+    assert "0 failure(s)" in r.stdout
+    assert "WARNING: ThreadSanitizer" not in r.stderr and "ERROR: AddressSanitizer" not in r.stderr
+    assert "runtime error:" not in r.stderr
+
+
+@pytest.mark.parametrize("san", ["address", "thread", "undefined"])
 def test_fault_paths_under_sanitizer(san):
     _build.build_host(sanitize=san)
     env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1", TSAN_OPTIONS="halt_on_error=1 second_deadlock_stack=1")
