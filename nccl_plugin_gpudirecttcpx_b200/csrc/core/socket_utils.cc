@@ -173,9 +173,10 @@ std::vector<NetIf> scan(const IfList& list, int family, const SocketAddress* sub
     if (family != AF_UNSPEC && fam != family) continue;
     if (!(ifa->ifa_flags & IFF_UP)) continue;
     if (fam == AF_INET6) {
-      // link-local v6 needs a scope id per socket; the loopback ::1 duplicates 127.0.0.1
+      // link-local v6 needs a scope id per socket; ::1 duplicates 127.0.0.1 unless v6 was asked for
       const struct sockaddr_in6* s6 = (const struct sockaddr_in6*)ifa->ifa_addr;
-      if (IN6_IS_ADDR_LINKLOCAL(&s6->sin6_addr) || IN6_IS_ADDR_LOOPBACK(&s6->sin6_addr)) continue;
+      if (IN6_IS_ADDR_LINKLOCAL(&s6->sin6_addr)) continue;
+      if (IN6_IS_ADDR_LOOPBACK(&s6->sin6_addr) && family != AF_INET6) continue;
     }
     if (subnet_hint ? !sameSubnet(ifa, *subnet_hint) : !matchIfList(list, ifa->ifa_name)) continue;
     bool dup = false;

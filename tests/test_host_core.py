@@ -92,6 +92,22 @@ def test_api_loopback_variants(host_lib, variant):
     assert "loopback PASSED" in r.stdout
 
 
+def _has_v6_loopback():
+    try:
+        return any(l.split()[-1] == "lo" for l in open("/proc/net/if_inet6"))
+    except OSError:
+        return False
+
+
+@pytest.mark.skipif(not _has_v6_loopback(), reason="no IPv6 loopback address on this machine")
+def test_api_loopback_over_ipv6(host_lib):
+    r = _loopback(host_lib, ["--sizes", "0,1000,300000,4194304", "--iters", "2"], NCCL_GPUDIRECTTCPX_SOCKET_FAMILY="AF_INET6",
+                  NCCL_DEBUG="INFO")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "loopback PASSED" in r.stdout
+    assert "connected to ::1<" in r.stdout + r.stderr
+
+
 def test_plugin_disabled_by_env(host_lib):
     r = _loopback(host_lib, ["--sizes", "1024", "--iters", "1"], NCCL_GPUDIRECTTCPX_SOCKET_ENABLE=0)
     assert r.returncode != 0  # init fails so that NCCL would fall back
