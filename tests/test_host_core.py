@@ -83,6 +83,10 @@ def test_api_loopback_byte_exact_with_flow_stats(host_lib):
     dict(NCCL_DYNAMIC_CHUNK_SIZE=4096, NCCL_THREAD_SPIN_ENABLE=1),
     dict(NCCL_SOCKET_NTHREADS=1, NCCL_NSOCKS_PERTHREAD=1, NCCL_GPUDIRECTTCPX_FORCE_ACK=1),
     dict(NCCL_SOCKET_NTHREADS=8, NCCL_NSOCKS_PERTHREAD=1, NCCL_GPUDIRECTTCPX_SLOWNESS_SWITCH="ALL"),
+    dict(NCCL_GPUDIRECTTCPX_CTRL_DEV="lo"),                          # control sockets on a named interface
+    dict(NCCL_GPUDIRECTTCPX_TX_BINDINGS="lo#0:0-1;lo#1:0-1", NCCL_GPUDIRECTTCPX_RX_BINDINGS="lo#0:0-1;lo#1:0-1",
+         NCCL_GPUDIRECTTCPX_WORKER_PIN_THREADS=1, NCCL_GPUDIRECTTCPX_REPORT_LIFECYCLE=1),
+    dict(NCCL_GPUDIRECTTCPX_SPINWAIT_CONNECT=0),
 ])
 def test_api_loopback_variants(host_lib, variant):
     variant = dict(variant)
