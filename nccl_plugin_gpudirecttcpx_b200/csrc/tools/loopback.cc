@@ -208,7 +208,16 @@ void printThreadTimes(const char* side) {
       unsigned long ut = 0, st = 0;
       if (open && close && sscanf(close + 2, "%*c %*d %*d %*d %*d %*d %*u %*u %*u %*u %*u %lu %lu", &ut, &st) == 2) {
         *close = 0;
-        printf("THREAD %s %s user %.3f sys %.3f\n", side, open + 1, (double)ut * tick, (double)st * tick);
+        // the cores the thread may run on (shows whether the TX/RX_BINDINGS took effect)
+        char cpus[128] = "?";
+        std::string spath = std::string("/proc/self/task/") + e->d_name + "/status";
+        if (FILE* sf = fopen(spath.c_str(), "r")) {
+          char sl[256];
+          while (fgets(sl, sizeof sl, sf) != nullptr)
+            if (sscanf(sl, "Cpus_allowed_list: %127s", cpus) == 1) break;
+          fclose(sf);
+        }
+        printf("THREAD %s %s user %.3f sys %.3f cpus %s\n", side, open + 1, (double)ut * tick, (double)st * tick, cpus);
       }
     }
     fclose(f);

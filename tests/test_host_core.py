@@ -112,6 +112,25 @@ def test_api_loopback_over_ipv6(host_lib):
     assert "connected to ::1<" in r.stdout + r.stderr
 
 
+@pytest.mark.skipif(len(os.sched_getaffinity(0)) < 2 or 0 not in os.sched_getaffinity(0) or 1 not in os.sched_getaffinity(0),
+                    reason="needs cores 0 and 1")
+def test_core_bindings_pin_the_helper_threads(host_lib):
+    """TX/RX_BINDINGS restrict the helper threads to the listed cores; WORKER_PIN_THREADS gives each one core."""
+    r = _loopback(host_lib, ["--sizes", "1000000", "--iters", "2", "--thread-times"], NCCL_GPUDIRECTTCPX_VIRTUAL_NICS=1,
+                  NCCL_GPUDIRECTTCPX_TX_BINDINGS="lo:0-1", NCCL_GPUDIRECTTCPX_RX_BINDINGS="lo:1")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    rows = [l.split() for l in r.stdout.splitlines() if l.startswith("THREAD ")]
+    tx = [w for w in rows if w[2].startswith("tcpxb-tx")]
+    rx = [w for w in rows if w[2].startswith("tcpxb-rx")]
+    assert len(tx) == 2 and len(rx) == 2  # NCCL_SOCKET_NTHREADS=2 in this file's environment
+    assert all(w[-1] == "0-1" for w in tx) and all(w[-1] == "1" for w in rx)
+    r = _loopback(host_lib, ["--sizes", "1000000", "--iters", "2", "--thread-times"], NCCL_GPUDIRECTTCPX_VIRTUAL_NICS=1,
+                  NCCL_GPUDIRECTTCPX_TX_BINDINGS="lo:0-1", NCCL_GPUDIRECTTCPX_WORKER_PIN_THREADS=1)
+    assert r.returncode == 0
+    tx = [l.split() for l in r.stdout.splitlines() if l.startswith("THREAD send tcpxb-tx")]
+    assert sorted(w[-1] for w in tx) == ["0", "1"]
+
+
 def test_plugin_disabled_by_env(host_lib):
     r = _loopback(host_lib, ["--sizes", "1024", "--iters", "1"], NCCL_GPUDIRECTTCPX_SOCKET_ENABLE=0)
     assert r.returncode != 0  # init fails so that NCCL would fall back
