@@ -9,6 +9,7 @@
 // the stall detector on an injected clock, flag parsing and range fallback,
 // interface-list syntax, the page allocator and the scatter-list ring.
 #include <stdio.h>
+#include <sys/time.h>
 #include <stdlib.h>
 #include <string.h>
 #include <sys/socket.h>
@@ -574,6 +575,34 @@ TEST(tracepoints_and_exporter) {
   // the collector removes only exporter_*.log files that are old enough
   EXPECT(LogGarbageCollector::sweepOnce(dir, 1) == 0);
   EXPECT(LogGarbageCollector::sweepOnce(dir, 0) == 0);
+  // two hours old: an exporter log goes, a file of another name stays
+  const std::string old_log = std::string(dir) + "/exporter_1_old.log", other = std::string(dir) + "/notes.log";
+  for (const std::string& pth : {old_log, other}) {
+    FILE* of = fopen(pth.c_str(), "w");
+    EXPECT(of != nullptr);
+    if (of != nullptr) fclose(of);
+    struct timeval tv[2];
+    gettimeofday(&tv[0], nullptr);
+    tv[0].tv_sec -= 7200;
+    tv[1] = tv[0];
+    EXPECT(utimes(pth.c_str(), tv) == 0);
+  }
+  EXPECT(LogGarbageCollector::sweepOnce(dir, 60) == 1);
+  EXPECT(access(old_log.c_str(), F_OK) != 0 && access(other.c_str(), F_OK) == 0);
+  {
+    // the background collector does the same on its period
+    FILE* of = fopen(old_log.c_str(), "w");
+    if (of != nullptr) fclose(of);
+    struct timeval tv[2];
+    gettimeofday(&tv[0], nullptr);
+    tv[0].tv_sec -= 7200;
+    tv[1] = tv[0];
+    utimes(old_log.c_str(), tv);
+    LogGarbageCollector gc(dir, 60, 1, -1);
+    const uint64_t until = monotonicNanos() + 3000000000ull;
+    while (access(old_log.c_str(), F_OK) == 0 && monotonicNanos() < until) usleep(10000);
+    EXPECT(access(old_log.c_str(), F_OK) != 0);
+  }
   setTraceConfig(TraceConfig());
   std::string cmd = std::string("rm -r ") + dir;
   EXPECT(system(cmd.c_str()) == 0);
