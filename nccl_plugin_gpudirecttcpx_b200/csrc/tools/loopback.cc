@@ -66,6 +66,11 @@ struct Api {
   ncclResult_t (*closeRecv)(void*);
   ncclResult_t (*closeListen)(void*);
   ncclResult_t (*irecvConsumed)(void*, int, void*);
+  ncclResult_t (*props8)(int, ncclNetProperties_v8_t*);
+  ncclResult_t (*props7)(int, ncclNetProperties_v7_t*);
+  ncclResult_t (*iflush)(void*, int, void**, int*, void**, void**);
+  ncclResult_t (*getDeviceMr)(void*, void*, void**);
+  void* regMrDmaBuf;
 };
 
 // What a consumer of the unpack device handle sees (NCCL's device-side layout).
@@ -143,12 +148,14 @@ bool loadApi(const char* path, bool v7, Api* api) {
     auto* t = (ncclNet_v7_t*)dlsym(h, "ncclNetPlugin_v7");
     if (t == nullptr) return false;
     *api = {t->name, t->init, t->devices, t->listen, t->connect, t->accept, nullptr, t->regMr, t->deregMr,
-            t->isend, t->irecv, t->test, t->closeSend, t->closeRecv, t->closeListen, t->irecvConsumed};
+            t->isend, t->irecv, t->test, t->closeSend, t->closeRecv, t->closeListen, t->irecvConsumed,
+            nullptr, t->getProperties, t->iflush, t->getDeviceMr, (void*)t->regMrDmaBuf};
   } else {
     auto* t = (ncclNet_v8_t*)dlsym(h, "ncclNetPlugin_v8");
     if (t == nullptr) return false;
     *api = {t->name, t->init, t->devices, t->listen, t->connect, t->accept, t->regMr, nullptr, t->deregMr,
-            t->isend, t->irecv, t->test, t->closeSend, t->closeRecv, t->closeListen, t->irecvConsumed};
+            t->isend, t->irecv, t->test, t->closeSend, t->closeRecv, t->closeListen, t->irecvConsumed,
+            t->getProperties, nullptr, t->iflush, t->getDeviceMr, (void*)t->regMrDmaBuf};
   }
   return true;
 }
@@ -245,6 +252,27 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
   int ndev = 0;
   CHECK(api.devices(&ndev));
   if (ndev < 1) { fprintf(stderr, "no devices\n"); return 1; }
+  if (receiver) {
+    // what NCCL learns about each device
+    for (int d = 0; d < ndev; ++d) {
+      if (api.props8 != nullptr) {
+        ncclNetProperties_v8_t p;
+        memset(&p, 0, sizeof p);
+        CHECK(api.props8(d, &p));
+        printf("PROPS dev %d name %s pci %s guid %lu ptr %d regIsGlobal %d speed %d port %d latency %.1f maxComms %d maxRecvs %d devType %d devVersion %d\n",
+               d, p.name, p.pciPath ? p.pciPath : "-", (unsigned long)p.guid, p.ptrSupport, p.regIsGlobal, p.speed, p.port, p.latency,
+               p.maxComms, p.maxRecvs, (int)p.netDeviceType, p.netDeviceVersion);
+      } else {
+        ncclNetProperties_v7_t p;
+        memset(&p, 0, sizeof p);
+        CHECK(api.props7(d, &p));
+        printf("PROPS dev %d name %s pci %s guid %lu ptr %d speed %d port %d latency %.1f maxComms %d maxRecvs %d devType %d devVersion %d\n",
+               d, p.name, p.pciPath ? p.pciPath : "-", (unsigned long)p.guid, p.ptrSupport, p.speed, p.port, p.latency, p.maxComms,
+               p.maxRecvs, (int)p.netDeviceType, p.netDeviceVersion);
+      }
+    }
+    printf("TABLE regMrDmaBuf %s\n", api.regMrDmaBuf == nullptr ? "null" : "set");
+  }
   const int ncomm = ndev;
   std::vector<void*> comms(ncomm, nullptr), listens(ncomm, nullptr);
   std::vector<DeviceHandle*> unpack(ncomm, nullptr);

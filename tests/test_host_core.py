@@ -131,6 +131,34 @@ def test_core_bindings_pin_the_helper_threads(host_lib):
     assert sorted(w[-1] for w in tx) == ["0", "1"]
 
 
+def _props(stdout):
+    rows = []
+    for l in stdout.splitlines():
+        if l.startswith("PROPS "):
+            w = l.split()[1:]
+            rows.append(dict(zip(w[0::2], w[1::2])))
+    return rows
+
+
+def test_device_properties_as_nccl_sees_them(host_lib):
+    """Values of getProperties through both table versions (reference: src/net_tcpx.cc:705-744):
+    host pointers only by default, 65536 comms, one receive per irecv, 10000 Mb/s when sysfs has no speed;
+    CUDA pointers and the unpack device type (version 7) in unpack mode; regMrDmaBuf stays null."""
+    r = _loopback(host_lib, ["--sizes", "1000", "--iters", "1"])
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    p = _props(r.stdout)
+    assert [d["name"] for d in p] == ["lo#0", "lo#1"] and [d["guid"] for d in p] == ["0", "1"]
+    for d in p:
+        assert d["ptr"] == "1" and d["maxComms"] == "65536" and d["maxRecvs"] == "1" and d["speed"] == "10000"
+        assert d["devType"] == "0" and d["latency"] == "0.0" and d["port"] == "0" and d["regIsGlobal"] == "0"
+    assert "TABLE regMrDmaBuf null" in r.stdout
+    r = _loopback(host_lib, ["--v7", "--ptr", "cuda", "--sizes", "1000", "--iters", "1"], TCPXB_FAKE_GPU=1,
+                  NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_GPUDIRECTTCPX_NIC_SPEED_MBPS=200000)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    for d in _props(r.stdout):
+        assert d["ptr"] == "3" and d["devType"] == "1" and d["devVersion"] == "7" and d["speed"] == "200000"
+
+
 def test_plugin_disabled_by_env(host_lib):
     r = _loopback(host_lib, ["--sizes", "1024", "--iters", "1"], NCCL_GPUDIRECTTCPX_SOCKET_ENABLE=0)
     assert r.returncode != 0  # init fails so that NCCL would fall back
