@@ -316,6 +316,12 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
     std::vector<uint8_t> expect(size ? size : 1);
     std::vector<void*> mh(nbuf, nullptr);
     for (int b = 0; b < nbuf; ++b) CHECK(regMr(api, comms[b / opt.inflight], bufs[b].data(), size, opt.ptr_type, &mh[b]));
+    if (receiver && opt.ptr_type == NCCL_PTR_CUDA && nbuf > 0 && api.getDeviceMr != nullptr) {
+      // the consumer's kernels index the user buffer directly: the device view of a registration is its base
+      void* dptr = nullptr;
+      CHECK(api.getDeviceMr(comms[0], mh[0], &dptr));
+      if (dptr != bufs[0].data()) { fprintf(stderr, "getDeviceMr returned %p for a buffer at %p\n", dptr, (void*)bufs[0].data()); return 1; }
+    }
     // both sides start a size together: receiver -> sender token, sender waits
     char tok = 'g';
     if (receiver) { if (write(wfd, &tok, 1) != 1) return 1; }
@@ -360,6 +366,14 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
             if (sz > 0 && !consumeSlot(unpack[b / opt.inflight], bufs[b].data(), (size_t)sz)) return 1;
             else if (sz == 0) unpack[b / opt.inflight]->head += 1;
             CHECK(api.irecvConsumed(comms[b / opt.inflight], 1, reqs[b]));
+          }
+          if (receiver && api.iflush != nullptr) {
+            // data is visible when test() reports done, so a flush has nothing to wait for
+            void* fdata = bufs[b].data();
+            int fsz = sz;
+            void* freq = reinterpret_cast<void*>(1);
+            CHECK(api.iflush(comms[b / opt.inflight], 1, &fdata, &fsz, &mh[b], &freq));
+            if (freq != nullptr) { fprintf(stderr, "iflush returned a request\n"); return 1; }
           }
           done[b] = 1;
           ++finished;
