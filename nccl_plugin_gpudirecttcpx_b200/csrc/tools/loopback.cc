@@ -4,6 +4,7 @@
 //   tcpxb_loopback --plugin <libnccl-net.so | libtcpxb_host.so> [--v7]
 //                  [--sizes 1024,65536,4194304,67108864] [--inflight 8] [--iters 4]
 //                  [--ptr host|cuda] [--yield] [--random-sizes] [--thread-times]
+//                  [--comms-per-dev N]
 //
 // `--random-sizes`: each listed size is the capacity of the posted receives; every message
 // carries a seeded random number of bytes between 0 and that capacity (both sides derive
@@ -22,8 +23,8 @@
 // that slot's count and records from the mapped block, copies the fragments out of
 // the bounce buffer and only then calls irecvConsumed.
 //
-// The parent is the receiver, the forked child the sender.  One comm is opened per
-// device the plugin reports (set NCCL_GPUDIRECTTCPX_VIRTUAL_NICS=2 to get two
+// The parent is the receiver, the forked child the sender.  One comm (or
+// --comms-per-dev of them) is opened per device the plugin reports (set NCCL_GPUDIRECTTCPX_VIRTUAL_NICS=2 to get two
 // "NICs" on lo); every comm moves `inflight` messages per iteration with tags
 // 0..inflight-1.  Payload bytes are a pure function of (seed, comm, iteration,
 // tag), so the receiver regenerates and compares them byte for byte.  At the end
@@ -243,6 +244,7 @@ struct Options {
   bool yield_when_idle = false;
   bool random_sizes = false;
   bool thread_times = false;
+  int comms_per_dev = 1;
 };
 
 int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
@@ -273,12 +275,12 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
     }
     printf("TABLE regMrDmaBuf %s\n", api.regMrDmaBuf == nullptr ? "null" : "set");
   }
-  const int ncomm = ndev;
+  const int ncomm = ndev * opt.comms_per_dev;  // comm c lives on device c % ndev, like NCCL's channels
   std::vector<void*> comms(ncomm, nullptr), listens(ncomm, nullptr);
   std::vector<DeviceHandle*> unpack(ncomm, nullptr);
   if (receiver) {
     std::vector<char> handles((size_t)ncomm * NCCL_NET_HANDLE_MAXSIZE, 0);
-    for (int c = 0; c < ncomm; ++c) CHECK(api.listen(c, &handles[(size_t)c * NCCL_NET_HANDLE_MAXSIZE], &listens[c]));
+    for (int c = 0; c < ncomm; ++c) CHECK(api.listen(c % ndev, &handles[(size_t)c * NCCL_NET_HANDLE_MAXSIZE], &listens[c]));
     if (write(wfd, handles.data(), handles.size()) != (ssize_t)handles.size()) return 1;
     for (int c = 0; c < ncomm; ++c)
       while (comms[c] == nullptr) {
@@ -303,7 +305,7 @@ int runSide(bool receiver, const Options& opt, int rfd, int wfd) {
     for (int c = 0; c < ncomm; ++c)
       while (comms[c] == nullptr) {
         ncclNetDeviceHandle_v8_t* dh = nullptr;
-        CHECK(api.connect(c, &handles[(size_t)c * NCCL_NET_HANDLE_MAXSIZE], &comms[c], &dh));
+        CHECK(api.connect(c % ndev, &handles[(size_t)c * NCCL_NET_HANDLE_MAXSIZE], &comms[c], &dh));
       }
   }
   printf("%s: %s, %d comm(s) up\n", receiver ? "receiver" : "sender", api.name, ncomm);
@@ -431,7 +433,8 @@ int main(int argc, char** argv) {
     auto next = [&]() -> const char* { return i + 1 < argc ? argv[++i] : ""; };
     if (a == "--help" || a == "-h") {
       printf("usage: tcpxb_loopback --plugin LIB [--v7] [--sizes a,b,...] [--inflight 1..16] [--iters N] [--seed S]\n"
-             "                      [--ptr host|cuda] [--yield] [--random-sizes] [--thread-times]\n");
+             "                      [--ptr host|cuda] [--yield] [--random-sizes] [--thread-times]\n"
+             "                      [--comms-per-dev N]\n");
       return 0;
     }
     if (a == "--plugin") opt.plugin = next();
@@ -442,6 +445,7 @@ int main(int argc, char** argv) {
     else if (a == "--yield") opt.yield_when_idle = true;
     else if (a == "--random-sizes") opt.random_sizes = true;
     else if (a == "--thread-times") opt.thread_times = true;
+    else if (a == "--comms-per-dev") opt.comms_per_dev = atoi(next());
     else if (a == "--ptr") opt.ptr_type = std::string(next()) == "cuda" ? NCCL_PTR_CUDA : NCCL_PTR_HOST;
     else if (a == "--sizes") {
       opt.sizes.clear();
@@ -457,6 +461,7 @@ int main(int argc, char** argv) {
   }
   if (opt.plugin.empty()) { fprintf(stderr, "--plugin is required\n"); return 2; }
   if (opt.inflight < 1 || opt.inflight > 16) { fprintf(stderr, "--inflight must be 1..16\n"); return 2; }
+  if (opt.comms_per_dev < 1 || opt.comms_per_dev > 64) { fprintf(stderr, "--comms-per-dev must be 1..64\n"); return 2; }
   int to_child[2], to_parent[2];
   if (pipe(to_child) != 0 || pipe(to_parent) != 0) return 1;
   fflush(stdout);

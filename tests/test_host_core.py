@@ -87,6 +87,7 @@ def test_api_loopback_byte_exact_with_flow_stats(host_lib):
     dict(NCCL_GPUDIRECTTCPX_TX_BINDINGS="lo#0:0-1;lo#1:0-1", NCCL_GPUDIRECTTCPX_RX_BINDINGS="lo#0:0-1;lo#1:0-1",
          NCCL_GPUDIRECTTCPX_WORKER_PIN_THREADS=1, NCCL_GPUDIRECTTCPX_REPORT_LIFECYCLE=1),
     dict(NCCL_GPUDIRECTTCPX_SPINWAIT_CONNECT=0),
+    dict(args=["--comms-per-dev", "8", "--random-sizes"], NCCL_SOCKET_NTHREADS=2, NCCL_NSOCKS_PERTHREAD=1),  # 16 connections, as NCCL's channels
 ])
 def test_api_loopback_variants(host_lib, variant):
     variant = dict(variant)
@@ -205,6 +206,9 @@ STANDIN_VARIANTS = [
     dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_GPUDIRECTTCPX_RX_POOL_MODE="device", args=["--v7"]),
     dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", args=["--random-sizes"]),
     dict(NCCL_GPUDIRECTTCPX_CUDA_BUFFERS=1, NCCL_INLINE_THRESHOLD=2048, args=["--random-sizes"]),
+    # 16 connections share a 16 MiB pool: at most four of the largest messages fit at a time
+    dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_GPUDIRECTTCPX_RX_POOL_BYTES=16 << 20, NCCL_SOCKET_NTHREADS=2,
+         NCCL_NSOCKS_PERTHREAD=1, args=["--comms-per-dev", "8", "--random-sizes"]),
     # two connections share a pool that holds exactly one of the largest messages: whoever gets the
     # pool's promise goes first, nobody waits while holding pages
     dict(NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_GPUDIRECTTCPX_RX_POOL_BYTES=8 << 20),
