@@ -66,3 +66,30 @@ def test_environment_doc_matches_the_flag_registry():
     text = (Path(__file__).resolve().parent.parent / "docs" / "environment.md").read_text()
     table = text.split("<!-- table:begin -->\n")[1].split("<!-- table:end -->")[0]
     assert table == markdown_table()
+
+
+def test_clock_sampler_against_a_fake_nvidia_smi(tmp_path, monkeypatch):
+    """The sampler only ever runs a read-only query, and digests what the tool prints."""
+    import os
+    import stat
+    import time
+    from nccl_plugin_gpudirecttcpx_b200.utils import clocks
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text(
+        "#!/bin/sh\n"
+        f"echo \"$@\" > {tmp_path}/argv\n"
+        "i=0\n"
+        "while true; do\n"
+        "  if [ $i -lt 2 ]; then echo '3, 1965, 1965, 640.00, Not Active, Not Active, Not Active, Not Active';\n"
+        "  else echo '3, 1410, 1965, 999.10, Not Active, Not Active, Not Active, Active'; fi\n"
+        "  i=$((i+1)); sleep 0.05\n"
+        "done\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", f"{tmp_path}:{os.environ['PATH']}")
+    s = clocks.ClockSampler(3, period_ms=50).start()
+    time.sleep(0.5)
+    out = s.stop()
+    argv = (tmp_path / "argv").read_text().split()
+    assert "--id=3" in argv and any(a.startswith("--query-gpu=") for a in argv) and "-lms" in argv
+    assert not any(a in ("-lgc", "-rgc", "-ac", "-rac", "-pm", "-pl", "-r", "--gpu-reset", "-c", "-e", "-mig") for a in argv)
+    assert out["samples"] >= 4 and out["sm_max_mhz"] == 1965 and out["sm_mhz"] == 1410 and out["reasons"] == ["sw_power_cap"]
