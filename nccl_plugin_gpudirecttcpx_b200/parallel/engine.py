@@ -173,20 +173,44 @@ class HierarchicalEngine:
     def _stream(self) -> int:
         return torch.cuda.current_stream(self.device).cuda_stream
 
+    def _all_reduce_unit(self) -> int:
+        """Byte granularity of the native all_reduce: every GPU's shard (and, on a ring of
+        more than two nodes, every piece of it) is a whole number of 16-byte vectors."""
+        return self.G * (self.nodes if self.nodes > 2 else 1) * 16
+
     def all_reduce(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Sum over all ranks.  G == 1: any contiguous CUDA tensors.  G > 1: `x` is staged
-        into the symmetric work buffer and the result is a view of the symmetric output."""
+        """Sum over all ranks, any number of elements (sizes that are not a multiple of the
+        native granularity are zero-padded on the way in and trimmed on the way out).
+        G == 1: any contiguous tensors.  G > 1: `x` is staged into the symmetric work buffer
+        and the result is a view of the symmetric output."""
         nbytes = x.numel() * x.element_size()
         code = DTYPE_CODE[x.dtype]
+        unit = self._all_reduce_unit()
+        padded = (nbytes + unit - 1) // unit * unit
         if self.G == 1:
+            if padded != nbytes:
+                xin = torch.zeros(padded // x.element_size(), dtype=x.dtype, device=x.device)
+                xin[:x.numel()].copy_(x.reshape(-1))
+                res = torch.empty_like(xin)
+                self._check(self._api.tcpxb_engine_all_reduce(self._h, xin.data_ptr(), res.data_ptr(), padded, code, self._stream()))
+                res = res[:x.numel()].view(x.shape)
+                if out is not None:
+                    out.copy_(res)
+                    return out
+                return res
             if out is None:
                 out = torch.empty_like(x)
             self._check(self._api.tcpxb_engine_all_reduce(self._h, x.data_ptr(), out.data_ptr(), nbytes, code, self._stream()))
             return out
-        w = self.work.view(torch.uint8)[:nbytes].view(x.dtype)
+        if padded > self.buffer_bytes:
+            raise ValueError(f"all_reduce of {nbytes} bytes does not fit the {self.buffer_bytes}-byte symmetric buffers")
+        wb = self.work.view(torch.uint8)
+        w = wb[:nbytes].view(x.dtype)
         if x.data_ptr() != w.data_ptr():
             w.copy_(x.reshape(-1))
-        self._check(self._api.tcpxb_engine_all_reduce(self._h, self.work.data_ptr(), self.out.data_ptr(), nbytes, code, self._stream()))
+        if padded != nbytes:
+            wb[nbytes:padded].zero_()
+        self._check(self._api.tcpxb_engine_all_reduce(self._h, self.work.data_ptr(), self.out.data_ptr(), padded, code, self._stream()))
         res = self.out.view(torch.uint8)[:nbytes].view(x.dtype).view(x.shape)
         if out is not None:
             out.copy_(res)

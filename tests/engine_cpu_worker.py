@@ -31,7 +31,7 @@ def main():
     from standin_engine import StandinEngine
     default_transport_env(nics=2, nthreads=2, nsocks_per_thread=1, pool_mb=64, chunk_bytes=128 * 1024)
     numels = [int(s) for s in os.environ.get("TCPXB_TEST_NUMELS", "3072,786432").split(",")]
-    buf_bytes = max(numels) * 4  # the largest case in fp32
+    buf_bytes = max(max(numels), 1000003 + 64) * 4  # the largest case in fp32, padding included
     eng = StandinEngine(gpus_per_node=G, buffer_bytes=buf_bytes if G > 1 else 0, request_bytes=256 << 10,
                         plain_mode=bool(int(os.environ.get("TCPXB_TEST_PLAIN", "0"))),
                         reduce_impl=int(os.environ.get("TCPXB_TEST_REDUCE_IMPL", "0")))
@@ -94,6 +94,15 @@ def main():
                 good = err <= tol
                 ok = ok and good
                 detail.append(("reduce_scatter", str(dtype), n, 0, err, good))
+    # sizes that are no multiple of the native granularity are padded inside the binding
+    for n in (1, 1000003):
+        xs = [torch.randn(n, generator=torch.Generator().manual_seed(7 * r + n)).float() for r in range(world)]
+        if world == 1:
+            xs = xs * 2
+        y = eng.all_reduce(xs[rank].clone())
+        good = tuple(y.shape) == (n,) and torch.allclose(y, torch.stack(xs).sum(0), atol=1e-4 * ranks)
+        ok = ok and good
+        detail.append(("all_reduce_odd", "f32", n, 0, 0.0, good))
     if world > 1 and G == 1:
         # point to point around the ring of nodes
         msg = torch.full((100000,), float(rank), dtype=torch.float32)

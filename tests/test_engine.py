@@ -28,6 +28,19 @@ def test_twin_all_reduce_doubles(engine, dtype, numel):
     assert engine.device_status()[0] == 0
 
 
+@pytest.mark.parametrize("numel", [1, 7, (1 << 20) + 3])
+def test_twin_all_reduce_of_any_size(engine, numel):
+    """Sizes below the 16-byte granularity of the native call are padded inside the binding."""
+    x = torch.randn(numel, device="cuda", generator=torch.Generator("cuda").manual_seed(numel)).to(torch.bfloat16)
+    out = engine.all_reduce(x)
+    torch.cuda.synchronize()
+    assert out.shape == x.shape and torch.equal(out, (x.float() * 2).to(torch.bfloat16))
+    given = torch.empty_like(x)
+    assert engine.all_reduce(x, given) is given
+    torch.cuda.synchronize()
+    assert torch.equal(given, out)
+
+
 def test_twin_all_gather_and_reduce_scatter(engine):
     x = torch.randn(3 << 18, device="cuda").to(torch.bfloat16)
     g = engine.all_gather(x)
