@@ -222,22 +222,44 @@ class HierarchicalEngine:
         return self.work.view(torch.uint8)[:numel * dtype.itemsize].view(dtype)
 
     def all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        """Concatenation of every rank's `x` in rank order.  Blocks whose byte size is not a
+        multiple of 16 travel padded and are compacted on return."""
         nbytes = x.numel() * x.element_size()
         blocks = self.nodes * self.G
+        if nbytes % 16 != 0:
+            padded = (nbytes + 15) // 16 * 16
+            xin = torch.zeros(padded, dtype=torch.uint8, device=x.device)
+            xin[:nbytes].copy_(x.reshape(-1).view(torch.uint8))
+            g = self.all_gather(xin)
+            return g.view(blocks, padded)[:, :nbytes].contiguous().view(-1).view(x.dtype)
         if self.G == 1:
             out = torch.empty(blocks * x.numel(), dtype=x.dtype, device=x.device)
             self._check(self._api.tcpxb_engine_all_gather(self._h, x.data_ptr(), out.data_ptr(), nbytes, self._stream()))
             return out
+        if nbytes * blocks > self.buffer_bytes:
+            raise ValueError(f"all_gather of {blocks} x {nbytes} bytes does not fit the {self.buffer_bytes}-byte symmetric buffers")
         self._check(self._api.tcpxb_engine_all_gather(self._h, x.data_ptr(), self.out.data_ptr(), nbytes, self._stream()))
         return self.out.view(torch.uint8)[:nbytes * blocks].view(x.dtype)
 
     def reduce_scatter(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum over all ranks of `x`, of which this rank keeps its 1/world part (`x.numel()`
+        must divide by the number of ranks).  Parts whose byte size is not a multiple of 16
+        travel padded."""
         blocks = self.nodes * self.G if self.world > 1 else 1
+        if x.numel() % blocks != 0:
+            raise ValueError(f"reduce_scatter input of {x.numel()} elements does not divide into {blocks} parts")
         per = x.numel() // blocks
         nbytes = per * x.element_size()
+        if nbytes % 16 != 0:
+            per_padded = (nbytes + 15) // 16 * 16 // x.element_size()
+            xin = torch.zeros(blocks, per_padded, dtype=x.dtype, device=x.device)
+            xin[:, :per].copy_(x.reshape(blocks, per))
+            return self.reduce_scatter(xin.view(-1))[:per].clone()
         out = torch.empty(per, dtype=x.dtype, device=x.device)
         src = x
         if self.G > 1:
+            if x.numel() * x.element_size() > self.buffer_bytes:
+                raise ValueError(f"reduce_scatter input of {x.numel() * x.element_size()} bytes does not fit the symmetric buffers")
             w = self.work.view(torch.uint8)[:x.numel() * x.element_size()].view(x.dtype)
             if x.data_ptr() != w.data_ptr():
                 w.copy_(x.reshape(-1))

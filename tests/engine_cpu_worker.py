@@ -103,6 +103,24 @@ def main():
         good = tuple(y.shape) == (n,) and torch.allclose(y, torch.stack(xs).sum(0), atol=1e-4 * ranks)
         ok = ok and good
         detail.append(("all_reduce_odd", "f32", n, 0, 0.0, good))
+    # all_gather and reduce_scatter blocks that are no multiple of 16 bytes
+    per = 1001
+    xs = [torch.randn(per * ranks, generator=torch.Generator().manual_seed(11 * r + 5)).float() for r in range(world)]
+    if world == 1:
+        xs = xs * 2
+    g = eng.all_gather(xs[rank][:per].clone())
+    good = torch.equal(g.clone(), torch.cat([t[:per] for t in xs]))
+    ok = ok and good
+    detail.append(("all_gather_odd", "f32", per, 0, 0.0, good))
+    if world > 1:
+        r = eng.reduce_scatter(xs[rank].clone())
+        wantr = torch.stack(xs).sum(0)[rank * per:(rank + 1) * per]
+    else:
+        r = eng.reduce_scatter(xs[0][:per].clone())
+        wantr = 2 * xs[0][:per]
+    good = tuple(r.shape) == (per,) and torch.allclose(r, wantr, atol=1e-4 * ranks)
+    ok = ok and good
+    detail.append(("reduce_scatter_odd", "f32", per, 0, 0.0, good))
     if world > 1 and G == 1:
         # point to point around the ring of nodes
         msg = torch.full((100000,), float(rank), dtype=torch.float32)

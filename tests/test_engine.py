@@ -41,6 +41,16 @@ def test_twin_all_reduce_of_any_size(engine, numel):
     assert torch.equal(given, out)
 
 
+def test_twin_all_gather_and_reduce_scatter_of_any_size(engine):
+    x = torch.randn(1001, device="cuda")  # 4004 bytes: no multiple of 16
+    g = engine.all_gather(x)
+    torch.cuda.synchronize()
+    assert g.shape == (2002,) and torch.equal(g[:1001], x) and torch.equal(g[1001:], x)
+    r = engine.reduce_scatter(x)
+    torch.cuda.synchronize()
+    assert r.shape == (1001,) and torch.equal(r, 2 * x)
+
+
 def test_twin_all_gather_and_reduce_scatter(engine):
     x = torch.randn(3 << 18, device="cuda").to(torch.bfloat16)
     g = engine.all_gather(x)
