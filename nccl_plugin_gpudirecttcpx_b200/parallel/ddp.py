@@ -7,7 +7,11 @@ Ranks are split into emulated nodes with NCCL_HOSTID, so NCCL keeps NVLink insid
 node and sends the inter-node part of every gradient all_reduce through the net
 transport: this plugin (`plugin`: host buffers; `unpack`: NCCL's kernels unpack from
 the rx page pool) or NCCL's own socket transport (`socket`, the baseline, with the
-same thread / socket / chunk settings).  Model, optimizer and bucketing are stock
+same thread / socket / chunk settings).  `engine` keeps NCCL for set-up only and
+reduces every gradient bucket through the hierarchical engine (fused unpack + reduce +
+NVLink fan-out kernels) from a DDP communication hook; the hook hands buckets to a
+worker thread with its own stream, so backward keeps running while a bucket is on the
+wire.  Model, optimizer and bucketing are stock
 PyTorch: Llama-style decoder, AdamW, DistributedDataParallel with 25 MB buckets
 overlapped with backward.  Synthetic uniform token ids, random-init weights.
 Rank 0 prints one JSON line with the device-timed step time (max over ranks).
@@ -22,7 +26,9 @@ import sys
 
 def parse_args(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--transport", default="plugin", choices=["plugin", "unpack", "socket", "nvlink"])
+    ap.add_argument("--transport", default="plugin", choices=["plugin", "unpack", "socket", "nvlink", "engine"])
+    ap.add_argument("--engine-class", default="nccl_plugin_gpudirecttcpx_b200.parallel.engine:HierarchicalEngine",
+                    help="module:Class of the engine behind --transport engine")
     ap.add_argument("--gpus-per-node", type=int, default=4)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
@@ -41,8 +47,8 @@ def setup_env(args, rank: int) -> None:
     if args.backend != "nccl":
         return
     from .plugin_env import plugin_env
-    if args.transport == "nvlink":
-        return  # one real node: NCCL's own intra-node transports, no emulation
+    if args.transport in ("nvlink", "engine"):
+        return  # one real node for NCCL: its own intra-node transports, no emulation
     env = plugin_env(nics=args.nics, nthreads=args.nthreads, builtin_socket=(args.transport == "socket"),
                      recv_mode="unpack" if args.transport == "unpack" else "host")
     # nodes are told apart by host id, so P2P and SHM stay on inside a node
@@ -50,6 +56,84 @@ def setup_env(args, rank: int) -> None:
     env.pop("NCCL_SHM_DISABLE", None)
     env["NCCL_HOSTID"] = f"tcpxb-node-{rank // args.gpus_per_node}"
     os.environ.update(env)
+
+
+class EngineBucketReducer:
+    """Averages DDP's gradient buckets through the hierarchical engine.
+
+    The engine's calls block their caller until the network part is done, so they run on
+    a worker thread with its own stream: the hook only records where the bucket became
+    ready and returns a future, backward goes on, and the future completes (carrying the
+    worker stream's event on CUDA) when the averaged bucket is in place."""
+
+    def __init__(self, engine, ranks: int, device):
+        import queue
+        import threading
+        import torch
+        self.engine, self.ranks, self.device = engine, ranks, device
+        self.cuda = device.type == "cuda"
+        self.stream = torch.cuda.Stream(device=device) if self.cuda else None
+        self.buckets = 0
+        self._q = queue.Queue()
+        self._thread = threading.Thread(target=self._work, name="tcpxb-ddp", daemon=True)
+        self._thread.start()
+
+    def hook(self, _state, bucket):
+        import torch
+        buf = bucket.buffer()
+        fut = torch.futures.Future(devices=[self.device]) if self.cuda else torch.futures.Future()
+        ready = None
+        if self.cuda:
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream(self.device))
+        self._q.put((buf, ready, fut))
+        return fut
+
+    def _reduce(self, buf):
+        res = self.engine.all_reduce(buf)   # a fresh tensor, or a view of the symmetric output
+        buf.copy_(res.view_as(buf))
+        buf.div_(self.ranks)
+        self.buckets += 1
+
+    def _work(self):
+        import torch
+        if self.cuda:
+            torch.cuda.set_device(self.device)
+        while True:
+            item = self._q.get()
+            if item is None:
+                return
+            buf, ready, fut = item
+            try:
+                if self.cuda:
+                    with torch.cuda.stream(self.stream):
+                        self.stream.wait_event(ready)
+                        self._reduce(buf)
+                        fut.set_result(buf)   # records this stream's event for whoever waits
+                else:
+                    self._reduce(buf)
+                    fut.set_result(buf)
+            except Exception as e:  # the training thread gets the error from the future
+                fut.set_exception(e)
+
+    def close(self):
+        self._q.put(None)
+        self._thread.join(timeout=30)
+        self.engine.close()
+
+
+def make_engine_reducer(args, dev, world: int, model):
+    """Engine sized for the largest bucket DDP can form: the cap plus one whole parameter."""
+    import importlib
+    from .engine import default_transport_env
+    mod, _, cls = args.engine_class.partition(":")
+    engine_cls = getattr(importlib.import_module(mod), cls)
+    default_transport_env(nics=args.nics, nthreads=args.nthreads)
+    G = args.gpus_per_node if world > 1 else 1
+    largest = max(p.numel() * p.element_size() for p in model.parameters())
+    buffer_bytes = ((args.bucket_mb << 20) + largest + (1 << 20) - 1) >> 20 << 20
+    eng = engine_cls(gpus_per_node=G, buffer_bytes=buffer_bytes if G > 1 else 0, device=dev)
+    return EngineBucketReducer(eng, world if world > 1 else 2, dev)
 
 
 def main(argv=None) -> int:
@@ -78,6 +162,10 @@ def main(argv=None) -> int:
     dtype = torch.bfloat16 if use_cuda else torch.float32
     model = LlamaDecoder(cfg).to(device=dev, dtype=dtype)
     ddp = DDP(model, device_ids=[local] if use_cuda else None, bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
+    reducer = None
+    if args.transport == "engine":
+        reducer = make_engine_reducer(args, dev, world, model)
+        ddp.register_comm_hook(None, reducer.hook)
     opt = torch.optim.AdamW(ddp.parameters(), lr=1e-4, weight_decay=0.1, fused=use_cuda)
     seq = min(args.seq_len, 64) if args.tiny else args.seq_len
     gen = torch.Generator(device=dev).manual_seed(99 + rank)
@@ -126,7 +214,12 @@ def main(argv=None) -> int:
             "grad_bytes_per_step": n_params * (2 if use_cuda else 4), "bucket_mb": args.bucket_mb,
             "micro_batch": args.micro_batch, "seq_len": seq, "loss_first": losses[0], "loss_last": losses[-1],
             "replicas_in_sync": in_sync, "dtype": str(dtype), "data": "synthetic uniform token ids, random init",
+            "engine_buckets": reducer.buckets if reducer else None,
         }), flush=True)
+    if reducer is not None:
+        if use_cuda:
+            torch.cuda.synchronize()
+        reducer.close()
     dist.barrier()
     dist.destroy_process_group()
     return 0 if in_sync else 1

@@ -30,6 +30,21 @@ def test_ddp_harness_two_cpu_ranks():
     assert rows[0]["loss_last"] < rows[0]["loss_first"] + 1.0
 
 
+@pytest.mark.parametrize("nproc,gpn", [(2, 1), (4, 2)])
+def test_ddp_buckets_through_the_engine_on_cpu_ranks(nproc, gpn):
+    """Gradient buckets averaged by the hierarchical engine (communication hook + worker thread) on the
+    stand-in device give the same training trajectory as gloo's own all_reduce."""
+    common = ["--backend", "gloo", "--tiny", "--steps", "3", "--warmup", "2", "--micro-batch", "2", "--bucket-mb", "1"]
+    env = {"PYTHONPATH": str(ROOT) + os.pathsep + str(ROOT / "tests"), "TCPXB_FAKE_GPU": "1", "OMP_NUM_THREADS": "1"}
+    r, rows = _launch(nproc, common + ["--transport", "engine", "--engine-class", "standin_engine:StandinEngine",
+                                       "--gpus-per-node", str(gpn), "--nics", "2", "--nthreads", "2"], env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert len(rows) == 1 and rows[0]["replicas_in_sync"] and rows[0]["engine_buckets"] >= 5
+    ref_r, ref = _launch(nproc, common, env={"OMP_NUM_THREADS": "1"})
+    assert ref_r.returncode == 0 and len(ref) == 1
+    assert abs(rows[0]["loss_last"] - ref[0]["loss_last"]) < 1e-3 and rows[0]["loss_first"] == ref[0]["loss_first"]
+
+
 def test_llama_shapes_and_param_count():
     from nccl_plugin_gpudirecttcpx_b200.models import LlamaConfig, LlamaDecoder
     cfg = LlamaConfig.tiny()
@@ -54,3 +69,11 @@ def test_ddp_step_over_the_plugin(transport):
                               "--warmup", "2", "--nics", "2", "--nthreads", "2"])
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert len(rows) == 1 and rows[0]["replicas_in_sync"]
+
+
+@pytest.mark.gpu
+def test_ddp_buckets_through_the_engine_one_gpu():
+    """One GPU as its own network peer: every bucket goes through the transport and the fused kernels."""
+    r, rows = _launch(1, ["--transport", "engine", "--tiny", "--steps", "3", "--warmup", "2", "--nics", "2", "--nthreads", "2"])
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert len(rows) == 1 and rows[0]["replicas_in_sync"] and rows[0]["engine_buckets"] > 0
