@@ -146,19 +146,36 @@ bool serve(State* st, UnixSocketConnection* c, const std::string& service) {
 int main(int argc, char** argv) {
   State st;
   st.prefix = "/tmp";
+  bool status_only = false;
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
     if (a == "--help" || a == "-h") {
       printf("usage: tcpxb_rxdm [--prefix DIR] [--pool-mb N] [--max-rules N]\n"
-             "Serves the rx buffer manager's UNIX sockets under DIR (default /tmp) until SIGINT or SIGTERM.\n");
+             "       tcpxb_rxdm --status [--prefix DIR]\n"
+             "Serves the rx buffer manager's UNIX sockets under DIR (default /tmp) until SIGINT or SIGTERM;\n"
+             "with --status asks a running daemon under DIR for its counters and prints one JSON line.\n");
       return 0;
     }
+    if (a == "--status") { status_only = true; continue; }
     if (i + 1 >= argc) { fprintf(stderr, "%s needs a value (see --help)\n", a.c_str()); return 2; }
     const char* v = argv[++i];
     if (a == "--prefix") st.prefix = v;
     else if (a == "--pool-mb") st.pool_bytes = strtoull(v, nullptr, 0) << 20;
     else if (a == "--max-rules") st.max_rules = strtoull(v, nullptr, 0);
     else { fprintf(stderr, "unknown argument %s (see --help)\n", a.c_str()); return 2; }
+  }
+  if (status_only) {
+    RxdmMessage req, rep;
+    memset(&req, 0, sizeof req);
+    req.magic = kRxdmMagic;
+    req.type = kRxdmStatus;
+    if (rxdmCall(st.prefix, "rxdm_status", req, &rep, nullptr) != kSuccess) {
+      fprintf(stderr, "no daemon answers under %s\n", st.prefix.c_str());
+      return 1;
+    }
+    printf("{\"tool\": \"rxdm\", \"prefix\": \"%s\", \"flow_rules\": %lu, \"applications\": %lu, \"pools\": %lu}\n", st.prefix.c_str(),
+           (unsigned long)rep.reply.a, (unsigned long)rep.reply.b, (unsigned long)rep.reply.c);
+    return 0;
   }
   mkdir(st.prefix.c_str(), 0755);
   signal(SIGINT, onSignal);

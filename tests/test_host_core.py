@@ -333,6 +333,11 @@ def test_daemon_pool_carries_device_receives_on_standin_device(host_lib, tmp_pat
         r = _loopback(host_lib, ["--ptr", "cuda", "--sizes", "0,1000,300000,4194304", "--inflight", "8", "--iters", "2"], **env)
         assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
         assert "loopback PASSED" in r.stdout
+        # the daemon's own view afterwards: every rule withdrawn, every application gone, the pool still there
+        q = subprocess.run([str(LIB / "tcpxb_rxdm"), "--status", "--prefix", str(prefix)], capture_output=True, text=True, timeout=20)
+        assert q.returncode == 0, q.stderr
+        st = json.loads(q.stdout)
+        assert st["flow_rules"] == 0 and st["applications"] == 0 and st["pools"] == 1
     finally:
         daemon.terminate()
         try:
