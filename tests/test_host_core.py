@@ -181,6 +181,16 @@ def test_telemetry_files(host_lib, tmp_path):
     states = {l.split()[3] for l in text}
     assert {"ACTIVE", "COMPLETING", "INACTIVE", "POSTED", "TRANSMITTING"} <= states
     assert all(l.startswith("per_flow_stats[") for l in stats[0].read_text().splitlines())
+    # the offline reader turns the lines into time spent per state; every life is whole
+    from nccl_plugin_gpudirecttcpx_b200.utils.trace import summarize
+    rows = summarize([str(p) for p in logs])
+    steps = {(r["kind"], r["side"], r["from"], r["to"]): r for r in rows}
+    for side in ("send", "recv"):
+        for a, b in (("POSTED", "ACTIVE"), ("ACTIVE", "TRANSMITTING"), ("TRANSMITTING", "INACTIVE"), ("INACTIVE", "FREE")):
+            assert steps[("request", side, a, b)]["count"] == 2 * 2 * 8 * 2  # sizes x iterations x in flight x comms
+        for a, b in (("ACTIVE", "COMPLETING"), ("COMPLETING", "INACTIVE"), ("INACTIVE", "FREE")):
+            assert steps[("task", side, a, b)]["count"] > 0
+    assert len(rows) == 14 and all(r["p50_us"] <= r["p99_us"] <= r["max_us"] for r in rows)
 
 
 @pytest.mark.parametrize("san", ["address", "thread", "undefined"])
