@@ -160,6 +160,17 @@ def test_device_properties_as_nccl_sees_them(host_lib):
         assert d["ptr"] == "3" and d["devType"] == "1" and d["devVersion"] == "7" and d["speed"] == "200000"
 
 
+@pytest.mark.parametrize("threads,per,want", [(16, 3, "8 sockets, 8 threads"), (3, 4, "6 sockets, 3 threads"), (20, 3, "8 sockets, 4 threads"),
+                                              (0, 0, "1 sockets, 1 threads"), (-2, -2, "4 sockets, 4 threads")])
+def test_socket_and_thread_counts_are_clamped(host_lib, threads, per, want):
+    """At most 8 sockets and 16 helper threads per connection (reference: src/macro.h:36-37); the automatic
+    choice for an interface without a PCI device (loopback, veth) is 4 x 1."""
+    r = _loopback(host_lib, ["--sizes", "300000", "--iters", "1"], NCCL_SOCKET_NTHREADS=threads, NCCL_NSOCKS_PERTHREAD=per,
+                  NCCL_DEBUG="INFO", NCCL_GPUDIRECTTCPX_VIRTUAL_NICS=1)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert f"connected to 127.0.0.1<" in r.stdout + r.stderr and want in r.stdout + r.stderr
+
+
 def test_plugin_disabled_by_env(host_lib):
     r = _loopback(host_lib, ["--sizes", "1024", "--iters", "1"], NCCL_GPUDIRECTTCPX_SOCKET_ENABLE=0)
     assert r.returncode != 0  # init fails so that NCCL would fall back
