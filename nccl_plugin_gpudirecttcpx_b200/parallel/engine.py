@@ -198,6 +198,13 @@ class HierarchicalEngine:
                     out.copy_(res)
                     return out
                 return res
+            if out is not None and out.data_ptr() == x.data_ptr():
+                # in place: later requests are still being sent from `x` while earlier ones are summed,
+                # so the result goes to a scratch tensor first
+                tmp = torch.empty_like(x)
+                self._check(self._api.tcpxb_engine_all_reduce(self._h, x.data_ptr(), tmp.data_ptr(), nbytes, code, self._stream()))
+                out.copy_(tmp)
+                return out
             if out is None:
                 out = torch.empty_like(x)
             self._check(self._api.tcpxb_engine_all_reduce(self._h, x.data_ptr(), out.data_ptr(), nbytes, code, self._stream()))

@@ -103,6 +103,16 @@ def main():
         good = tuple(y.shape) == (n,) and torch.allclose(y, torch.stack(xs).sum(0), atol=1e-4 * ranks)
         ok = ok and good
         detail.append(("all_reduce_odd", "f32", n, 0, 0.0, good))
+    if G == 1:
+        # in place (out is the input tensor)
+        xs = [torch.randn(600000, generator=torch.Generator().manual_seed(3 * r + 1)).float() for r in range(world)]
+        if world == 1:
+            xs = xs * 2
+        mine = xs[rank].clone()
+        y = eng.all_reduce(mine, mine)
+        good = y is mine and torch.allclose(mine, torch.stack(xs).sum(0), atol=1e-4 * ranks)
+        ok = ok and good
+        detail.append(("all_reduce_in_place", "f32", 600000, 0, 0.0, good))
     # all_gather and reduce_scatter blocks that are no multiple of 16 bytes
     per = 1001
     xs = [torch.randn(per * ranks, generator=torch.Generator().manual_seed(11 * r + 5)).float() for r in range(world)]
