@@ -496,6 +496,9 @@ int tcpxb_engine_all_reduce(void* engine, const void* in_, void* out_, uint64_t 
   uint8_t* out = static_cast<uint8_t*>(out_);
   if (e->G > 1 && (in != e->work[e->local] || out != e->out[e->local] || bytes > e->buffer_bytes))
     return fail("with several GPUs per node, in/out must be the registered work/output buffers%s", "");
+  // two nodes swap shards request by request: a request summed into `out` would overwrite
+  // input that a later request has yet to send
+  if (e->G == 1 && e->nodes == 2 && in == out) return fail("all_reduce between two nodes needs an output separate from its input%s", "");
   ++e->epoch;
   const uint64_t shard = bytes / (uint64_t)e->G;
   const uint64_t shard_off = shard * (uint64_t)e->local;

@@ -77,7 +77,8 @@ int tcpxb_engine_set_peers(void* engine, void* const* work_ptrs, void* const* ou
                            uint32_t* const* flag_ptrs, void* mc_out, uint64_t buffer_bytes);
 
 // Collectives.  With gpus_per_node > 1, `in` must be this rank's work buffer and
-// `out` its output buffer as registered with tcpxb_engine_set_peers.
+// `out` its output buffer as registered with tcpxb_engine_set_peers.  With one GPU per
+// node and two nodes, all_reduce needs `out` != `in`.
 int tcpxb_engine_all_reduce(void* engine, const void* in, void* out, uint64_t bytes, int dtype, void* stream);
 // all_gather: `in` holds bytes_per_rank; out receives world x bytes_per_rank in rank order.
 int tcpxb_engine_all_gather(void* engine, const void* in, void* out, uint64_t bytes_per_rank, void* stream);
