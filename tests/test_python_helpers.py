@@ -45,6 +45,20 @@ def test_plugin_env_variants(monkeypatch):
     assert not any(k.startswith("NCCL_GPUDIRECTTCPX_") for k in sock)
 
 
+def test_socket_settings_follow_the_cores_per_rank(monkeypatch):
+    import importlib
+    pe = importlib.import_module("nccl_plugin_gpudirecttcpx_b200.parallel.plugin_env")  # the package re-exports the function
+    assert pe.socket_settings_for(32, 8) == {"nthreads": 2, "chunk_bytes": 128 * 1024}   # 4 cores per rank
+    assert pe.socket_settings_for(24, 4) == {"nthreads": 4, "chunk_bytes": 512 * 1024}   # 6 cores per rank
+    assert pe.socket_settings_for(2, 8)["nthreads"] == 2
+    monkeypatch.setattr(os, "sched_getaffinity", lambda pid: set(range(32)))
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "8")
+    env = pe.plugin_env(nthreads=0, chunk_bytes=0, builtin_socket=True)
+    assert env["NCCL_SOCKET_NTHREADS"] == "2" and env["NCCL_DYNAMIC_CHUNK_SIZE"] == str(128 * 1024)
+    env = pe.plugin_env(nthreads=3, chunk_bytes=0, builtin_socket=True)
+    assert env["NCCL_SOCKET_NTHREADS"] == "3" and env["NCCL_DYNAMIC_CHUNK_SIZE"] == str(128 * 1024)
+
+
 def test_clock_sampler_without_nvidia_smi(monkeypatch):
     import shutil
     from nccl_plugin_gpudirecttcpx_b200.utils import clocks
