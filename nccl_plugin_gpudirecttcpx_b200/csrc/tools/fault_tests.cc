@@ -586,6 +586,31 @@ TEST(two_engines_in_one_process_all_reduce) {
   tcpxb_engine_destroy(e[1]);
 }
 
+TEST(engine_peer_gone_between_steps_is_an_error) {
+  void* e[2] = {makeEngine(0, 2), makeEngine(1, 2)};
+  EXPECT(e[0] != nullptr && e[1] != nullptr);
+  if (e[0] == nullptr || e[1] == nullptr) return;
+  const size_t hb = (size_t)tcpxb_engine_rails(e[0]) * TCPXB_ENGINE_HANDLE_BYTES;
+  std::vector<char> h0(hb), h1(hb);
+  EXPECT(tcpxb_engine_listen(e[0], h0.data()) == 0 && tcpxb_engine_listen(e[1], h1.data()) == 0);
+  const size_t n = 200000;
+  std::vector<float> x(n, 1.f), y0(n), y1(n);
+  std::atomic<int> failures{0};
+  std::thread t1([&] {
+    if (tcpxb_engine_connect(e[1], h0.data()) != 0 || tcpxb_engine_all_reduce(e[1], x.data(), y1.data(), n * 4, TCPXB_F32, nullptr) != 0) ++failures;
+  });
+  if (tcpxb_engine_connect(e[0], h1.data()) != 0 || tcpxb_engine_all_reduce(e[0], x.data(), y0.data(), n * 4, TCPXB_F32, nullptr) != 0) ++failures;
+  t1.join();
+  EXPECT(failures.load() == 0 && y0[0] == 2.f && y1[n - 1] == 2.f);
+  // rank 1 leaves at the step boundary; rank 0's next step must come back with an error
+  tcpxb_engine_destroy(e[1]);
+  const uint64_t t0 = monotonicNanos();
+  EXPECT(tcpxb_engine_all_reduce(e[0], x.data(), y0.data(), n * 4, TCPXB_F32, nullptr) != 0);
+  EXPECT(monotonicNanos() - t0 < 10000000000ull);
+  EXPECT(strlen(tcpxb_engine_last_error()) > 0);
+  tcpxb_engine_destroy(e[0]);
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {

@@ -295,7 +295,7 @@ def test_fault_paths_surface_as_errors(host_lib):
     pages: error codes, "try again" or back-pressure, never a hang."""
     r = subprocess.run([str(LIB / "tcpxb_fault_tests")], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert "17 test(s), 0 failure(s)" in r.stdout
+    assert "18 test(s), 0 failure(s)" in r.stdout
 
 
 @pytest.mark.parametrize("san", ["address", "thread", "undefined"])
