@@ -30,7 +30,8 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-METRIC = "net-path all_reduce aggregate GB/s (bf16, 2 emulated nodes over loopback sockets)"
+METRIC = ("net-path all_reduce GB/s, whole-job aggregate (bf16, 2 emulated nodes over loopback sockets; "
+          "bus GB/s in config.busbw_GBps, unpack+reduce % roofline in unpack_microbench)")
 
 
 def parse_args():
