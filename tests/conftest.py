@@ -29,3 +29,11 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip_gpu)
         if "multigpu" in item.keywords and ngpu < 2:
             item.add_marker(skip_multi)
+
+
+def free_port() -> int:
+    """A TCP port nobody listens on right now (for the rendezvous of child ranks)."""
+    import socket
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]

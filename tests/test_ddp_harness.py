@@ -9,12 +9,14 @@ from pathlib import Path
 import pytest
 import torch
 
+from conftest import free_port
+
 ROOT = Path(__file__).resolve().parent.parent
 
 
 def _launch(nproc, extra, env=None, timeout=240):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-           "--master-addr", "127.0.0.1", "--master-port", "29541", "-m", "nccl_plugin_gpudirecttcpx_b200.parallel.ddp"] + extra
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()), "-m", "nccl_plugin_gpudirecttcpx_b200.parallel.ddp"] + extra
     e = dict(os.environ)
     e["PYTHONPATH"] = str(ROOT) + os.pathsep + e.get("PYTHONPATH", "")
     e.update(env or {})

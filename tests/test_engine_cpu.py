@@ -12,10 +12,12 @@ from pathlib import Path
 
 import pytest
 
+from conftest import free_port
+
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def _run(nproc, gpus_per_node, port, timeout=420, **envkw):
+def _run(nproc, gpus_per_node, timeout=420, **envkw):
     env = dict(os.environ)
     env.update({"TCPXB_TEST_GPUS_PER_NODE": str(gpus_per_node), "OMP_NUM_THREADS": "1", "TCPXB_FAKE_GPU": "1"})
     env.update({k: str(v) for k, v in envkw.items()})
@@ -24,7 +26,7 @@ def _run(nproc, gpus_per_node, port, timeout=420, **envkw):
         cmd = [sys.executable, worker]
     else:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-               "--master-addr", "127.0.0.1", "--master-port", str(port), worker]
+               "--master-addr", "127.0.0.1", "--master-port", str(free_port()), worker]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
     rows = []
     for line in r.stdout.splitlines():
@@ -38,7 +40,7 @@ def _run(nproc, gpus_per_node, port, timeout=420, **envkw):
 def test_collectives_match_fp32_sums(nproc, gpn):
     """all_reduce (twice per size), all_gather, reduce_scatter in bf16 and fp32, plus send/recv
     around the ring: twin, two nodes, a three-node ring, and hierarchies of 2 x 2, 3 x 2, 2 x 3."""
-    r, rows = _run(nproc, gpn, 29610 + nproc * 10 + gpn)
+    r, rows = _run(nproc, gpn)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert len(rows) == nproc and all(row["ok"] and row["device_status"][0] == 0 for row in rows)
     assert all(row["unpack_launches"] > 0 and row["fragments"] >= row["unpack_launches"] for row in rows)
@@ -48,7 +50,7 @@ def test_collectives_match_fp32_sums(nproc, gpn):
                                    dict(NCCL_GPUDIRECTTCPX_RX_POOL_SCATTER=1, NCCL_GPUDIRECTTCPX_RX_POOL_BYTES=8 << 20)])
 def test_engine_variants(envkw):
     """The unfused baseline, the add-at-destination reduce, and a small scattered page pool."""
-    r, rows = _run(4, 2, 29690, **envkw)
+    r, rows = _run(4, 2, **envkw)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert len(rows) == 4 and all(row["ok"] for row in rows)
 
@@ -58,7 +60,7 @@ def test_a_rank_that_leaves_is_an_error_for_the_others(nproc, gpn):
     """The last rank exits at a step boundary.  Its network neighbours get an error from the
     transport at once; its node-mates' bounded flag waits run out and set the device status.
     Nobody hangs, and the step before the exit was correct everywhere."""
-    r, rows = _run(nproc, gpn, 29750 + nproc * 10 + gpn, timeout=180, TCPXB_TEST_MODE="rank_leaves")
+    r, rows = _run(nproc, gpn, timeout=180, TCPXB_TEST_MODE="rank_leaves")
     assert len(rows) == nproc, r.stdout[-3000:] + r.stderr[-3000:]
     assert all(row["first_ok"] for row in rows)
     left = [row for row in rows if row["left"]]
