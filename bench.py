@@ -34,6 +34,18 @@ METRIC = ("net-path all_reduce GB/s, whole-job aggregate (bf16, 2 emulated nodes
           "bus GB/s in config.busbw_GBps, unpack+reduce % roofline in unpack_microbench)")
 
 
+def rails_and_threads(cores: int, world: int, nics: int = 0, nthreads: int = 0):
+    """Rails (virtual NICs) and helper threads per connection for `world` ranks sharing `cores`
+    cores; values given by the caller (> 0) are kept.  About one helper thread per core and
+    direction: 4 cores per rank -> 2 x 1, 8 -> 4 x 1, 16 -> 4 x 2."""
+    per_dir = max(1, min(8, cores // max(world, 1) // 2))
+    if nics <= 0:
+        nics = min(4, per_dir)
+    if nthreads <= 0:
+        nthreads = max(1, per_dir // nics)
+    return nics, nthreads
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -185,11 +197,7 @@ def main():
     # thread per core (measured: 4 cores per rank run best with 2 rails x 1 thread,
     # 8 with 4 x 1, 16 with 4 x 2).
     cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 16)
-    per_dir = max(1, min(8, cores // max(world, 1) // 2))
-    if args.nics <= 0:
-        args.nics = min(4, per_dir)
-    if args.nthreads <= 0:
-        args.nthreads = max(1, per_dir // args.nics)
+    args.nics, args.nthreads = rails_and_threads(cores, world, args.nics, args.nthreads)
     default_transport_env(nics=args.nics, nthreads=args.nthreads, nsocks_per_thread=args.nsocks_per_thread,
                           chunk_bytes=args.chunk_kb << 10, pool_mb=1024)
     G = max(1, world // 2)

@@ -107,3 +107,16 @@ def test_clock_sampler_against_a_fake_nvidia_smi(tmp_path, monkeypatch):
     assert "--id=3" in argv and any(a.startswith("--query-gpu=") for a in argv) and "-lms" in argv
     assert not any(a in ("-lgc", "-rgc", "-ac", "-rac", "-pm", "-pl", "-r", "--gpu-reset", "-c", "-e", "-mig") for a in argv)
     assert out["samples"] >= 4 and out["sm_max_mhz"] == 1965 and out["sm_mhz"] == 1410 and out["reasons"] == ["sw_power_cap"]
+
+
+def test_bench_rails_and_threads_follow_the_cores():
+    import sys
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench
+    assert bench.rails_and_threads(16, 1) == (4, 2)     # the one-GPU box
+    assert bench.rails_and_threads(24, 2) == (4, 1)
+    assert bench.rails_and_threads(32, 4) == (4, 1)
+    assert bench.rails_and_threads(32, 8) == (2, 1)     # 4 cores per rank
+    assert bench.rails_and_threads(2, 8) == (1, 1)
+    assert bench.rails_and_threads(32, 8, nics=4) == (4, 1) and bench.rails_and_threads(32, 8, nthreads=3) == (2, 3)
