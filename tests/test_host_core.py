@@ -367,3 +367,48 @@ def test_daemon_pool_carries_device_receives_on_standin_device(host_lib, tmp_pat
             daemon.kill()
     log = daemon.stderr.read()
     assert "pool for GPU 0000:00:00.0: 32 MiB" in log, log[-2000:]  # the pool came from the daemon
+
+
+@pytest.mark.parametrize("san", ["", "address"])
+def test_rx_buffer_manager_daemon_survives_garbage(tmp_path, san):
+    """Random bytes, truncated frames and oversize lengths on every service socket: the daemon drops the
+    connection and keeps serving."""
+    import random
+    import socket
+    import struct
+    prefix = tmp_path / "rxdm"
+    if san:
+        _build.build_host(sanitize=san)
+    else:
+        _build.build_host()
+    daemon = subprocess.Popen([str(LIB / ("tcpxb_rxdm" + ("_" + san if san else ""))), "--prefix", str(prefix), "--pool-mb", "4"],
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                              env=dict(os.environ, ASAN_OPTIONS="detect_leaks=0"))
+    try:
+        assert daemon.stdout.readline().strip() == "ready"
+        rng = random.Random(7)
+        services = ["rx_rule_manager", "rx_rule_uninstall", "get_gpu_fd", "get_gpu_metadata", "rxdm_application_registry", "rxdm_status"]
+        for name in services:
+            for payload in (b"", b"\x00", struct.pack("!H", 65535) + b"x" * 100, struct.pack("!H", 8) + b"12345678",
+                            bytes(rng.randrange(256) for _ in range(600)), struct.pack("!H", 300)):
+                s = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+                s.settimeout(2)
+                s.connect(str(prefix / name))
+                try:
+                    s.sendall(payload)
+                    s.shutdown(socket.SHUT_WR)
+                    s.recv(4096)
+                except OSError:
+                    pass
+                s.close()
+        assert daemon.poll() is None, daemon.stderr.read()
+        q = subprocess.run([str(LIB / "tcpxb_rxdm"), "--status", "--prefix", str(prefix)], capture_output=True, text=True, timeout=20)
+        assert q.returncode == 0, q.stderr
+        assert json.loads(q.stdout)["flow_rules"] == 0
+    finally:
+        daemon.terminate()
+        try:
+            daemon.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            daemon.kill()
+    assert "ERROR: AddressSanitizer" not in daemon.stderr.read()
