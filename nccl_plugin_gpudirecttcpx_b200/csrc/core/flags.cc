@@ -79,6 +79,7 @@ const IntSpec kInts[] = {
     {kOwn, "CONNECT_PACING_US", &Flags::connect_pacing_us, 0, kMax, "pause per socket during connection setup"},
     {kOwn, "NIC_SPEED_MBPS", &Flags::nic_speed_mbps, 0, 100000000, "speed reported to NCCL (0 = sysfs, else 10000)"},
     {kOwn, "CUDA_BUFFERS", &Flags::cuda_buffers, 0, 2, "host receive mode also takes CUDA pointers (plugin-side copies and kernels)"},
+    {kOwn, "ADAPTIVE_CHUNK", &Flags::adaptive_chunk, 0, 2, "cut a message into about one chunk per socket (0 = always NCCL_DYNAMIC_CHUNK_SIZE)"},
     {kOwn, "POLL_BLOCK_US", &Flags::poll_block_us, 0, 1000000, "helper threads block in poll() this long when idle on EAGAIN"},
 };
 

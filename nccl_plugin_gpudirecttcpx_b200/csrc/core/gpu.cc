@@ -38,8 +38,20 @@ Result none() {
   snprintf(g_err, sizeof g_err, "built without CUDA");
   return kUnhandledCudaError;
 }
+// TCPXB_FAKE_GPU=2: the stand-in device's copies and kernels move no data, as if a
+// copy engine and SMs did the work for free.  Results are then meaningless; the
+// setting exists to time the host side of the data path on a machine with no GPU.
+bool fakeMovesData() {
+  static const bool moves = [] {
+    const char* v = getenv("TCPXB_FAKE_GPU");
+    return !(v != nullptr && v[0] == '2');
+  }();
+  return moves;
+}
 int g_fake_stream_tag, g_fake_event_tag;
 }  // namespace
+
+bool standinMovesData() { return fakeMovesData(); }
 
 bool compiledWithCuda() { return false; }
 bool devicePointersPossible() { return fake(); }
@@ -96,7 +108,7 @@ Result streamWaitEvent(Stream, Event) { return fake() ? kSuccess : none(); }
 Result eventSynchronize(Event) { return fake() ? kSuccess : none(); }
 static Result fakeCopy(void* dst, const void* src, size_t bytes) {
   if (!fake()) return none();
-  memmove(dst, src, bytes);
+  if (fakeMovesData()) memmove(dst, src, bytes);
   return kSuccess;
 }
 Result copyDeviceToDeviceAsync(void* d, const void* s, size_t n, Stream) { return fakeCopy(d, s, n); }
@@ -134,6 +146,7 @@ int probeCount() {
 }  // namespace
 
 bool compiledWithCuda() { return true; }
+bool standinMovesData() { return true; }
 bool devicePointersPossible() { return true; }
 int deviceCount() { return probeCount(); }
 bool available() { return probeCount() > 0; }

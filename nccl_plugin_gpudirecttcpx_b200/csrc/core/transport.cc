@@ -187,6 +187,17 @@ int readZerocopyCompletions(SocketCtx* s) {
   }
 }
 
+// Tells the thread that drives this comm (if it sleeps between polls) that a task
+// changed state.  One system call at most per sleep of that thread.
+inline void notifyDriver(Comm* comm) {
+  Notifier* n = comm->notifier;
+  if (n != nullptr && n->armed.load(std::memory_order_acquire) != 0 && n->armed.exchange(0, std::memory_order_acq_rel) != 0) {
+    const uint64_t one = 1;
+    ssize_t rc = write(n->event_fd, &one, sizeof one);
+    (void)rc;
+  }
+}
+
 // ------------------------------------------------------------------ helper thread
 // Moves bytes for the oldest active task of socket `s`.  Returns 1 when the task
 // finished its I/O, 0 when the socket would block, -1 on error.
@@ -264,7 +275,7 @@ void helperMain(Comm* comm, int tid) {
   const bool slow_txc = f.slow_switch[kSlowTxComp];
   int idle_rounds = 0;
   while (!comm->stop.load(std::memory_order_acquire)) {
-    bool moved = false, blocked = false;
+    bool moved = false, blocked = false, finished = false;
     struct pollfd pfds[kMaxSockets];
     int npfd = 0;
     for (int idx = tid; idx < comm->num_socks; idx += comm->num_threads) {
@@ -272,7 +283,7 @@ void helperMain(Comm* comm, int tid) {
       while (s->tasks.has(kTaskActive)) {
         Task* t = &s->tasks.front(kTaskActive);
         int rc = progressTask(comm, s, t);
-        if (rc < 0) return;
+        if (rc < 0) { notifyDriver(comm); return; }
         if (rc == 0) {
           blocked = true;
           pfds[npfd].fd = s->fd;
@@ -288,7 +299,7 @@ void helperMain(Comm* comm, int tid) {
       // completion stage: zero-copy sends wait for the kernel's notification
       if (s->zc_done != s->zc_next) {
         int c = readZerocopyCompletions(s);
-        if (c < 0) { setError(comm, kSystemError); return; }
+        if (c < 0) { setError(comm, kSystemError); notifyDriver(comm); return; }
         if (c > 0) { s->zc_done += (uint32_t)c; s->stats.tx_completion_cnt.fetch_add((uint64_t)c); s->stall.reset(); moved = true; }
         else if (slow_txc) {
           uint64_t ns = 0;
@@ -317,8 +328,10 @@ void helperMain(Comm* comm, int tid) {
         traceTask(comm, t, kTaskInactive);
         s->tasks.advance(kTaskCompleting);
         moved = true;
+        finished = true;
       }
     }
+    if (finished) notifyDriver(comm);
     if (moved) { idle_rounds = 0; continue; }
     if (spin) continue;
     if (blocked) {
@@ -330,22 +343,33 @@ void helperMain(Comm* comm, int tid) {
     }
     if (++idle_rounds < 64) continue;  // short spin: the next chunk usually follows at once
     std::unique_lock<std::mutex> l(me.mu);
+    me.sleeping.store(true, std::memory_order_seq_cst);
     me.cv.wait_for(l, std::chrono::milliseconds(50), [&] {
-      return me.kicks.load(std::memory_order_acquire) != me.seen || comm->stop.load(std::memory_order_acquire);
+      return me.kicks.load(std::memory_order_seq_cst) != me.seen || comm->stop.load(std::memory_order_acquire);
     });
+    me.sleeping.store(false, std::memory_order_release);
     me.seen = me.kicks.load(std::memory_order_acquire);
     idle_rounds = 0;
   }
 }
 
-void kick(Comm* comm, int sock_idx) {
-  HelperThread& h = comm->helpers[sock_idx % comm->num_threads];
-  h.kicks.fetch_add(1, std::memory_order_release);
-  if (!flags().thread_spin) {
-    // Taking the lock after the increment closes the window in which a helper has
-    // evaluated its wait predicate but is not yet blocked.
-    { std::lock_guard<std::mutex> l(h.mu); }
-    h.cv.notify_one();
+// A new task for socket `sock_idx`: its helper is woken once per progress round
+// (flushKicks), however many tasks the round queued for it.
+void kick(Comm* comm, int sock_idx) { comm->kick_mask |= 1u << (sock_idx % comm->num_threads); }
+
+void flushKicks(Comm* comm) {
+  uint32_t mask = comm->kick_mask;
+  comm->kick_mask = 0;
+  for (int t = 0; mask != 0; ++t, mask >>= 1) {
+    if ((mask & 1u) == 0) continue;
+    HelperThread& h = comm->helpers[t];
+    h.kicks.fetch_add(1, std::memory_order_seq_cst);
+    if (!flags().thread_spin && h.sleeping.load(std::memory_order_seq_cst)) {
+      // Taking the lock after the increment closes the window in which a helper has
+      // evaluated its wait predicate but is not yet blocked.
+      { std::lock_guard<std::mutex> l(h.mu); }
+      h.cv.notify_one();
+    }
   }
 }
 
@@ -423,7 +447,7 @@ Result startCudaSend(Comm* comm, Request* r, MemHandle* mh) {
   if (!stageAlloc(comm, (uint64_t)r->size, &r->stage, &r->stage_bytes)) return kInProgress;
   // One staging copy per ~2 MiB: enough to let the first chunks leave while the
   // rest is still being copied, few enough that the per-copy launch cost stays small.
-  const int chunk = (int)flags().dynamic_chunk_size;
+  const int chunk = chunkBytesFor(r->size, comm->num_socks);
   int n_want = std::max(1, std::min(kMaxTxSegments, r->size / (2 << 20)));
   int seg = (r->size + n_want - 1) / n_want;
   seg = (seg + chunk - 1) / chunk * chunk;
@@ -568,6 +592,27 @@ Result launchUnpack(Comm* comm, Request* r) {
 }
 
 // ------------------------------------------------------------- progress engine
+}  // namespace
+
+// Striping quantum of one message.  The fixed quantum (NCCL_DYNAMIC_CHUNK_SIZE) cuts a
+// 4 MiB message into 32 chunks even when the comm has a single socket, and every
+// chunk costs a control record, a task hand-off and a completion.  With
+// ADAPTIVE_CHUNK (default) a message is cut into about one chunk per socket instead:
+// the quantum grows to size / sockets, rounded up to a whole rx page, but never
+// beyond kMaxAdaptiveChunk, so that large messages still pipeline through the task rings.
+int chunkBytesFor(int message_bytes, int num_socks) {
+  const Flags& f = flags();
+  int64_t chunk = f.dynamic_chunk_size;
+  if (f.adaptive_chunk != 0 && num_socks > 0) {
+    int64_t per_sock = ((int64_t)message_bytes + num_socks - 1) / num_socks;
+    per_sock = (per_sock + kRxPageBytes - 1) / kRxPageBytes * kRxPageBytes;
+    chunk = std::max(chunk, std::min<int64_t>(per_sock, std::max<int64_t>(kMaxAdaptiveChunk, chunk)));
+  }
+  return (int)std::min<int64_t>(chunk, INT32_MAX);
+}
+
+namespace {
+
 Result progressSendRequest(Comm* comm, Request* r) {
   const Flags& f = flags();
   if (r->size <= f.inline_threshold || r->size == 0) {
@@ -596,7 +641,7 @@ Result progressSendRequest(Comm* comm, Request* r) {
     comm->rq.advance(kReqActive);
     return kSuccess;
   }
-  const int chunk_size = (int)f.dynamic_chunk_size;
+  const int chunk_size = chunkBytesFor(r->size, comm->num_socks);
   while (r->offset < r->size && comm->mapper->hasFlow()) {
     const int chunk = std::min(chunk_size, r->size - r->offset);
     if (r->mem_type == kPtrCuda && !stagedUpTo(r, r->offset + chunk)) break;
@@ -739,7 +784,7 @@ Result progressRecvRequest(Comm* comm, Request* r) {
   }
 }
 
-Result progress(Comm* comm) {
+Result progressRound(Comm* comm) {
   mark(comm, "progress:enter");
   const int err = comm->error.load(std::memory_order_acquire);
   if (err != kSuccess) return (Result)err;
@@ -767,7 +812,7 @@ Result progress(Comm* comm) {
   while (comm->rq.has(kReqPosted)) {
     Request* r = &comm->rq.front(kReqPosted);
     if (f.recv_sync) {
-      uint32_t idx = comm->rq.frontIndex(kReqPosted);
+      uint32_t idx = (uint32_t)comm->rq.frontIndex(kReqPosted);  // 32 bits on the wire
       if (r->op == kSockRecv) {
         Result sr = socketSend(comm->ctrl_fd, &idx, sizeof idx, 1000);
         if (sr != kSuccess) return sr == kInProgress ? kSystemError : sr;
@@ -791,7 +836,7 @@ Result progress(Comm* comm) {
   }
   while (comm->rq.has(kReqActive)) {
     Request* r = &comm->rq.front(kReqActive);
-    const uint32_t before = comm->rq.frontIndex(kReqActive);
+    const uint64_t before = comm->rq.frontIndex(kReqActive);
     if (r->op == kSockSend) {
       if (!comm->mapper->hasFlow() && r->size > f.inline_threshold && r->size != 0) break;
       TCPXB_CHECK(progressSendRequest(comm, r));
@@ -841,6 +886,12 @@ Result progress(Comm* comm) {
     comm->rq.advance(kReqTransmitting);
   }
   return kSuccess;
+}
+
+Result progress(Comm* comm) {
+  const Result r = progressRound(comm);
+  if (comm->kick_mask != 0) flushKicks(comm);  // helpers learn of this round's new tasks in one go
+  return r;
 }
 
 // Frees finished requests from the head of the ring once the user has seen them
@@ -1135,7 +1186,7 @@ Result netTest(Request* r, int* done, int* size) {
   bool drives = true;
   {
     const uint32_t n = comm->rq.inFlight();
-    const uint32_t base = comm->rq.frontIndex(kReqFinished);
+    const uint64_t base = comm->rq.frontIndex(kReqFinished);
     for (uint32_t k = 0; k < n; ++k) {
       Request* q = &comm->rq.slot(base + k);
       if (q->reported) continue;
@@ -1203,6 +1254,16 @@ Result netIrecvConsumed(Comm* comm, int n, Request* r) {
 }
 
 void netSetSendDependency(Comm* comm, gpu::Event event) { comm->send_dependency = event; }
+
+void netSetNotifier(Comm* comm, Notifier* notifier) {
+  if (comm != nullptr) comm->notifier = notifier;
+}
+
+int netCtrlPollFd(Comm* comm) {
+  if (comm == nullptr || !comm->passive || comm->have_ctrl) return -1;
+  if (comm->ctrl_recv.buffered() >= (int)sizeof(CtrlMsg)) return -1;
+  return comm->ctrl_fd;
+}
 
 Result netRequestScatterList(Request* r, ScatterList* out) {
   if (r == nullptr || out == nullptr || r->op != kSockRecv || r->mem_type != kPtrCuda) return kInvalidArgument;

@@ -1,11 +1,14 @@
 // Hierarchical collective engine; see tcpxb/engine.h for the algorithms.
 #include "tcpxb/engine.h"
 
+#include <poll.h>
 #include <sched.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/eventfd.h>
 #include <time.h>
+#include <unistd.h>
 
 #include <algorithm>
 #include <deque>
@@ -113,7 +116,34 @@ struct Engine {
   tcpxbEngineStats stats;
   int req_bytes = 4 << 20, inflight = 8, ctas = 16;
   bool yield_when_idle = false;
+  // idle policy of the driving thread
+  Notifier notifier;
+  int idle_spin_us = 20, idle_sleep_us = 200;
 };
+
+// Blocks the driving thread until a helper thread finishes a task, a control record
+// arrives, or `timeout_us` passes (GPU events have no descriptor: the timeout bounds
+// how late their completion is noticed).
+void sleepUntilWork(Engine* e, bool want_ctrl, int timeout_us) {
+  struct pollfd pfds[1 + TCPXB_ENGINE_MAX_RAILS];
+  int n = 0;
+  pfds[n++] = {e->notifier.event_fd, POLLIN, 0};
+  if (want_ctrl) {
+    for (Rail& r : e->rails) {
+      const int fd = netCtrlPollFd(r.recv);
+      if (fd >= 0) pfds[n++] = {fd, POLLIN, 0};
+    }
+  }
+  struct timespec ts = {0, (long)timeout_us * 1000};
+  const int rc = ppoll(pfds, (nfds_t)n, &ts, nullptr);
+  e->notifier.armed.store(0, std::memory_order_release);
+  if (rc > 0 && (pfds[0].revents & POLLIN)) {
+    uint64_t v;
+    ssize_t got = read(e->notifier.event_fd, &v, sizeof v);
+    (void)got;
+  }
+  ++e->stats.sleeps;
+}
 
 int ensureScratch(Engine* e, uint64_t bytes) {
   if (e->scratch_bytes >= bytes) return 0;
@@ -231,6 +261,8 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
   const double t0 = nowSec();
   double tp = t0;
   auto lap = [&tp](double& acc) { const double n = nowSec(); acc += n - tp; tp = n; };
+  double idle_since = 0;
+  bool armed = false;
   while (done_s < n_send || launched_r < n_recv) {
     bool moved = false;
     // post receives (they claim pool pages as control records arrive)
@@ -310,14 +342,34 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
       }
       lap(e->stats.t_test_send);
     }
-    if (!moved) {
-      // a short pause, not a yield: giving up the time slice here lets the request
-      // pipeline run dry while helper threads keep the core
+    if (moved) {
+      idle_since = 0;
+      if (armed) { e->notifier.armed.store(0, std::memory_order_release); armed = false; }
+      continue;
+    }
+    // Nothing moved.  Spin briefly (the next event is usually microseconds away when
+    // messages are small), then sleep: on a box where helper threads outnumber the
+    // cores, a spinning driver takes a core away from the threads that move the bytes.
+    if (idle_since == 0) idle_since = tp;
+    const bool may_sleep = e->idle_sleep_us > 0 && e->notifier.event_fd >= 0;
+    if (!may_sleep || (tp - idle_since) * 1e6 < (double)e->idle_spin_us) {
       if (e->yield_when_idle) sched_yield();
       else for (int i = 0; i < 64; ++i) __builtin_ia32_pause();
       lap(e->stats.t_idle);
+    } else if (!armed) {
+      // arm, then look once more: a completion between the last look and the arming is not lost
+      e->notifier.armed.store(1, std::memory_order_seq_cst);
+      armed = true;
+    } else {
+      // kernels or staging copies in flight complete without a wake-up: look again sooner
+      bool gpu_pending = false;
+      for (int r = 0; r < R; ++r) gpu_pending = gpu_pending || !uq[r].empty();
+      sleepUntilWork(e, launched_r < n_recv, gpu_pending ? std::min(e->idle_sleep_us, 50) : e->idle_sleep_us);
+      armed = false;
+      lap(e->stats.t_sleep);
     }
   }
+  if (armed) e->notifier.armed.store(0, std::memory_order_release);
   // pool pages go back once the kernels that read them have finished
   for (int r = 0; r < R; ++r) {
     while (!uq[r].empty()) {
@@ -391,6 +443,9 @@ void* tcpxb_engine_create(const tcpxbEngineConfig* cfg) {
   if (cfg->unpack_ctas > 0) e->ctas = cfg->unpack_ctas;
   memset(&e->stats, 0, sizeof e->stats);
   e->yield_when_idle = getenv("TCPXB_ENGINE_YIELD") != nullptr;
+  if (cfg->idle_spin_us > 0) e->idle_spin_us = cfg->idle_spin_us;
+  if (cfg->idle_sleep_us != 0) e->idle_sleep_us = cfg->idle_sleep_us;
+  e->notifier.event_fd = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
   int ndev = 0;
   netDevices(&ndev);
   e->rails.resize((size_t)std::min(ndev, TCPXB_ENGINE_MAX_RAILS));
@@ -419,6 +474,7 @@ void tcpxb_engine_destroy(void* engine) {
     if (r.recv) netClose(r.recv);
     if (r.listen) netCloseListen(r.listen);
   }
+  if (e->notifier.event_fd >= 0) close(e->notifier.event_fd);
   for (gpu::Event ev : e->event_pool) gpu::eventDestroy(ev);
   gpu::eventDestroy(e->dep_event);
   gpu::deviceFree(e->scratch);
@@ -464,6 +520,8 @@ int tcpxb_engine_connect(void* engine, const void* next_handles) {
   for (Rail& rail : e->rails) {
     ENG_NET(netPrepareCuda(rail.send, e->cfg.gpu_dev));
     ENG_NET(netPrepareCuda(rail.recv, e->cfg.gpu_dev));
+    netSetNotifier(rail.send, &e->notifier);
+    netSetNotifier(rail.recv, &e->notifier);
   }
   e->connected = true;
   return 0;

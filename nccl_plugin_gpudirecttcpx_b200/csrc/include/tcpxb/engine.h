@@ -45,6 +45,10 @@ typedef struct tcpxbEngineConfig {
   int reduce_impl;        // TCPXB_REDUCE_SM or TCPXB_REDUCE_L2
   int use_nvls;           // use the multimem fan-out when a multicast mapping is given
   int plain_mode;         // 1 = baseline: unpack_copy to a bounce buffer, separate add, no fused fan-out
+  // The driving thread of an exchange spins for idle_spin_us without progress, then sleeps
+  // (ppoll on the control sockets and on an eventfd the helper threads write) for at most
+  // idle_sleep_us at a time.  0 = defaults (20 / 200); idle_sleep_us < 0 = never sleep.
+  int idle_spin_us, idle_sleep_us;
 } tcpxbEngineConfig;
 
 typedef struct tcpxbEngineStats {
@@ -54,8 +58,9 @@ typedef struct tcpxbEngineStats {
   double seconds_net_wait;               // host time spent inside exchanges
   // where the driving thread spends that time (seconds): posting receives, posting
   // sends (staging copies included), testing receives, launching unpack kernels,
-  // returning pages, testing sends, and idle spinning
-  double t_post_recv, t_post_send, t_test_recv, t_launch, t_consume, t_test_send, t_idle;
+  // returning pages, testing sends, idle spinning, and asleep waiting for a wake-up
+  double t_post_recv, t_post_send, t_test_recv, t_launch, t_consume, t_test_send, t_idle, t_sleep;
+  uint64_t sleeps;                       // times the driving thread blocked
 } tcpxbEngineStats;
 
 // Creates the engine and initialises the transport (flags are read from the

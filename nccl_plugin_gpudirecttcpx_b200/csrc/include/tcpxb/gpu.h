@@ -24,6 +24,9 @@ namespace tcpxb {
 namespace gpu {
 
 bool compiledWithCuda();
+// False only for the host-only build's stand-in device in its timing mode (TCPXB_FAKE_GPU=2),
+// where copies and kernels are skipped so that only the host side of the data path costs time.
+bool standinMovesData();
 // True when a pointer handed to the transport may be device memory: always in a
 // CUDA build (the runtime is not touched to answer), only with the stand-in device
 // otherwise.

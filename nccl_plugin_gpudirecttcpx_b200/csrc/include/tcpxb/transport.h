@@ -170,7 +170,17 @@ struct HelperThread {
   std::mutex mu;
   std::condition_variable cv;
   std::atomic<uint32_t> kicks{0};
+  std::atomic<bool> sleeping{false};  // blocked (or about to block) on `cv`: a kick must notify
   uint32_t seen = 0;
+};
+
+// Lets the thread that polls test() sleep between polls.  That thread arms the
+// notifier, looks once more for work, and blocks on `event_fd` (an eventfd, usually
+// inside ppoll together with the control sockets); a helper thread that finishes a
+// task, or fails, disarms it and writes the eventfd.  Shared by any number of comms.
+struct Notifier {
+  int event_fd = -1;
+  std::atomic<uint32_t> armed{0};
 };
 
 struct Comm {
@@ -192,6 +202,8 @@ struct Comm {
   std::atomic<bool> stop{false};
   bool threads_started = false;
   int rotate = 0;  // socket the reaping pass starts from
+  uint32_t kick_mask = 0;        // helpers that got new tasks in the current progress round
+  Notifier* notifier = nullptr;  // owned by the caller of netSetNotifier
   // pending control record on the receive side
   bool have_ctrl = false;
   CtrlMsg ctrl;
@@ -268,6 +280,17 @@ Result netIrecvConsumed(Comm* comm, int n, Request* req);
 // Selects the receive mode of comms accepted from now on by this thread's next
 // netAccept (used by the collective engine, which unpacks with its own kernels).
 void netSetAcceptRecvMode(ListenComm* lcomm, int recv_mode);
+
+// Completion wake-ups for a driving thread that sleeps (see Notifier); null detaches.
+// Set it while no request is in flight.
+void netSetNotifier(Comm* comm, Notifier* notifier);
+// The descriptor whose readability means "the peer sent control records this comm
+// has not read yet" (receive side), or -1 when waiting on it would return at once
+// (a record is already buffered) or never (send side).
+int netCtrlPollFd(Comm* comm);
+// Bytes per chunk for a message of `message_bytes` on a comm with `num_socks` data sockets.
+int chunkBytesFor(int message_bytes, int num_socks);
+constexpr int kMaxAdaptiveChunk = 4 << 20;
 
 // The next netIsend of a CUDA buffer on `comm` first makes the comm's copy stream
 // wait for `event` (the kernel that produces the data), then stages the data.

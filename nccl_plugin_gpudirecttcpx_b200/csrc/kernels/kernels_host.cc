@@ -23,6 +23,7 @@
 #include <string.h>
 #include <time.h>
 
+#include "tcpxb/gpu.h"
 #include "tcpxb/kernels.h"
 
 namespace {
@@ -118,7 +119,8 @@ int run(const Job& j) {
   const uint64_t wait_ns = j.opts && j.opts->wait_ns ? j.opts->wait_ns : kDefaultWaitNs;
   const uint64_t t0 = nowNs();
   bool dead = false;
-  for (uint32_t i = 0; i < j.count; ++i) {
+  const uint32_t count = tcpxb::gpu::standinMovesData() ? j.count : 0;  // timing mode: no data is moved
+  for (uint32_t i = 0; i < count; ++i) {
     if (ready != nullptr && !dead) {
       // streaming: record i exists once the producer's counter has passed it
       while (__atomic_load_n(ready, __ATOMIC_ACQUIRE) <= i) {
@@ -241,6 +243,7 @@ int tcpxb_peer_reduce(void* out, void* const* srcs, int nsrcs, uint64_t shard_of
   if (dtype != TCPXB_BF16 && dtype != TCPXB_F32) return fail(TCPXB_K_INVALID, "reduce needs bf16 or f32");
   if ((bytes | shard_off) & 15) return fail(TCPXB_K_INVALID, "shard offset and size must be multiples of 16 bytes");
   uint8_t* o = static_cast<uint8_t*>(out);
+  if (!tcpxb::gpu::standinMovesData()) return TCPXB_K_OK;  // timing mode
   if (dtype == TCPXB_BF16) {
     // one rounding, after all addends are summed in fp32
     for (uint64_t i = 0; i < bytes; i += 2) {

@@ -74,7 +74,7 @@ TEST(ring_cursor_algebra) {
   r.nextFree() = 999;
   r.admit();
   EXPECT(r.at(1, 4) == 999);  // wrapped into slot 0
-  // wrap many times: invariants hold with 32-bit cursor overflow semantics
+  // wrap many times: invariants hold
   for (int i = 0; i < 100000; ++i) {
     while (r.has(1)) r.advance(1);
     while (r.has(2)) r.advance(2);
@@ -82,6 +82,28 @@ TEST(ring_cursor_algebra) {
     EXPECT(r.empty());
     r.nextFree() = i; r.admit();
     if (!g_current_ok) break;
+  }
+}
+
+TEST(ring_cursor_crosses_2_32) {
+  // capacity 6 does not divide 2^32: with 32-bit cursors the slot of index 2^32 would be
+  // slot 0 while index 2^32 - 1 sits in slot 3, and a live item could be overwritten
+  StageRing<uint64_t, 6, 3, false> r;
+  for (uint64_t start : {(uint64_t)UINT32_MAX - 9, (uint64_t)UINT32_MAX * 3 - 2}) {
+    r.reset(start);
+    uint64_t next_in = 0, next_out = 0;
+    for (int round = 0; round < 40; ++round) {
+      while (r.hasFree()) { r.nextFree() = next_in++; r.admit(); }
+      EXPECT(r.inFlight() == 6 && r.count(1) == 6);
+      // every live item is intact: no admitted item landed on another live one
+      for (uint32_t k = 0; k < 6; ++k) EXPECT(r.at(1, k) == next_out + k);
+      for (int k = 0; k < 1 + round % 5; ++k) {
+        EXPECT(r.front(1) == next_out);
+        r.advance(1); r.advance(2); r.advance(3);
+        ++next_out;
+      }
+    }
+    EXPECT(r.slot(r.frontIndex(1)) == next_out);
   }
 }
 

@@ -27,7 +27,7 @@ DTYPE_CODE = {torch.bfloat16: 1, torch.float32: 2}
 class _Config(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in (
         "rank", "world", "gpus_per_node", "gpu_dev", "request_bytes", "max_inflight", "unpack_ctas",
-        "reduce_impl", "use_nvls", "plain_mode")]
+        "reduce_impl", "use_nvls", "plain_mode", "idle_spin_us", "idle_sleep_us")]
 
 
 class EngineStats(ctypes.Structure):
@@ -36,7 +36,8 @@ class EngineStats(ctypes.Structure):
                 ("fragments", ctypes.c_uint64), ("kernel_launches", ctypes.c_uint64),
                 ("seconds_net_wait", ctypes.c_double)] + [
                     (n, ctypes.c_double) for n in ("t_post_recv", "t_post_send", "t_test_recv", "t_launch",
-                                                   "t_consume", "t_test_send", "t_idle")]
+                                                   "t_consume", "t_test_send", "t_idle", "t_sleep")] + [
+                                                       ("sleeps", ctypes.c_uint64)]
 
 
 _lib = None
@@ -91,7 +92,8 @@ class HierarchicalEngine:
 
     def __init__(self, gpus_per_node: int = 1, buffer_bytes: int = 0, request_bytes: int = 4 << 20,
                  max_inflight: int = 8, unpack_ctas: int = 16, reduce_impl: int = 0, use_nvls: bool = False,
-                 plain_mode: bool = False, device: Optional[torch.device] = None):
+                 plain_mode: bool = False, device: Optional[torch.device] = None,
+                 idle_spin_us: int = 0, idle_sleep_us: int = 0):
         import torch.distributed as dist
         self._api = self._load_api()
         self._dist = dist if dist.is_available() and dist.is_initialized() else None
@@ -101,7 +103,7 @@ class HierarchicalEngine:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.nodes = max(2, self.world // self.G) if self.world > 1 else 2
         cfg = _Config(self.rank, self.world, self.G, self.device.index or 0, request_bytes, max_inflight, unpack_ctas,
-                      reduce_impl, int(use_nvls), int(plain_mode))
+                      reduce_impl, int(use_nvls), int(plain_mode), idle_spin_us, idle_sleep_us)
         self._h = self._api.tcpxb_engine_create(ctypes.byref(cfg))
         if not self._h:
             raise RuntimeError("engine create failed: " + self._api.tcpxb_engine_last_error().decode())
