@@ -183,6 +183,21 @@ void loadFlags(Flags* out) {
   if (!strcasecmp(out->recv_mode_name.c_str(), "unpack")) out->recv_mode = kRecvModeUnpack;
   else if (!out->recv_mode_name.empty() && strcasecmp(out->recv_mode_name.c_str(), "host"))
     WARN("unknown receive mode '%s'; using host", out->recv_mode_name.c_str());
+  if (out->recv_mode == kRecvModeUnpack) {
+    // Only the ring primitives of NCCL's Simple protocol copy the payload out of the rx
+    // pool; with any other algorithm or protocol the consumer would never run and the
+    // user's buffers would keep stale data.  Without both settings the plugin does not
+    // offer the unpack device type: it receives into host buffers like any net plugin.
+    const char* proto = getenv("NCCL_PROTO");
+    const char* algo = getenv("NCCL_ALGO");
+    const bool ok = proto != nullptr && !strcasecmp(proto, "Simple") && algo != nullptr && !strcasecmp(algo, "Ring");
+    if (!ok) {
+      WARN("NCCL_GPUDIRECTTCPX_RECV_MODE=unpack needs NCCL_PROTO=Simple and NCCL_ALGO=Ring (found NCCL_PROTO=%s, NCCL_ALGO=%s): "
+           "using host receive mode instead", proto ? proto : "(unset)", algo ? algo : "(unset)");
+      out->recv_mode = kRecvModeHost;
+      out->recv_mode_fell_back = true;
+    }
+  }
   out->rx_buf_mgr_daemon = !strcasecmp(out->rx_buf_mgr_name.c_str(), "daemon");
   if (!out->rx_buf_mgr_daemon && !out->rx_buf_mgr_name.empty() && strcasecmp(out->rx_buf_mgr_name.c_str(), "emulated"))
     WARN("unknown rx buffer manager '%s'; using the in-process one", out->rx_buf_mgr_name.c_str());

@@ -167,6 +167,19 @@ gpu::Event takeEvent(Engine* e) {
   return ev;
 }
 
+// The kernels report into a pinned status block; a non-zero first word means a
+// record was skipped or a bounded wait ran out, and the collective's result is not
+// to be trusted.  Checked whenever the host learns that kernels have finished.
+int checkDeviceStatus(Engine* e) {
+  const uint32_t code = e->status_host[0];
+  if (code == 0) return 0;
+  snprintf(g_err, sizeof g_err, "device status %u (%s) at record %u, %u report(s)", code,
+           code == TCPXB_ST_BOUNDS ? "record out of bounds" : code == TCPXB_ST_ALIGN ? "misaligned reduce record"
+           : code == TCPXB_ST_TIMEOUT ? "a bounded device wait ran out" : "unknown",
+           e->status_host[1], e->status_host[2]);
+  return -1;
+}
+
 // Launches the unpack kernel for one finished receive request.
 int launchUnpack(Engine* e, Request* req, const RecvSpec& rs, uint64_t region_off, uint64_t len, bool publish,
                  void* stream) {
@@ -198,8 +211,13 @@ int launchUnpack(Engine* e, Request* req, const RecvSpec& rs, uint64_t region_of
   }
   if (e->cfg.plain_mode) {
     // Baseline: unpack to a bounce buffer, add in a second pass, copy to the peers.
-    ENG_TRY(ensureScratch(e, e->scratch_bytes));
-    uint8_t* bounce = e->scratch + e->scratch_bytes - (uint64_t)e->req_bytes;
+    // the last req_bytes of the scratch are the bounce buffer of the two-pass reduce
+    uint8_t* bounce = nullptr;
+    if (acc != nullptr) {
+      ENG_TRY(ensureScratch(e, std::max<uint64_t>(e->scratch_bytes, (uint64_t)e->req_bytes)));
+      if (e->scratch == nullptr) return fail("no scratch for the unfused reduce%s", "");
+      bounce = e->scratch + e->scratch_bytes - (uint64_t)e->req_bytes;
+    }
     // the unpack kernel must not publish completion here: the add and the peer copies come after it
     tcpxbUnpackOpts copy_opts;
     memset(&copy_opts, 0, sizeof copy_opts);
@@ -325,6 +343,7 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
         Result q = gpu::eventQuery(uq[r].front().event);
         if (q == kInProgress) break;
         ENG_NET(q);
+        ENG_TRY(checkDeviceStatus(e));
         ENG_NET(netIrecvConsumed(e->rails[r].recv, 1, uq[r].front().req));
         e->event_pool.push_back(uq[r].front().event);
         uq[r].pop_front();
@@ -380,6 +399,7 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
     }
   }
   e->stats.seconds_net_wait += nowSec() - t0;
+  ENG_TRY(checkDeviceStatus(e));  // every unpack kernel of this exchange has finished
   return 0;
 }
 
@@ -388,7 +408,8 @@ int checkReady(Engine* e) {
   if (!e->connected) return fail("engine is not connected%s", "");
   if (e->G > 1 && e->out.empty()) return fail("set_peers was not called%s", "");
   ENG_NET(gpu::setDevice(e->cfg.gpu_dev));
-  return 0;
+  // an earlier call's last kernels (e.g. its final flag wait) may have failed after it returned
+  return checkDeviceStatus(e);
 }
 
 // "Inputs staged" barrier among the local GPUs: block A of the flag pages.

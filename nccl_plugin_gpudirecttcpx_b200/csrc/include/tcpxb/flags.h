@@ -98,6 +98,7 @@ struct Flags {
   int sched_alg = kSchedRR;
   int rx_pool_mode = kRxPoolHostMapped;
   int recv_mode = kRecvModeHost;
+  bool recv_mode_fell_back = false;  // unpack was asked for without NCCL_PROTO=Simple + NCCL_ALGO=Ring
   bool rx_buf_mgr_daemon = false;
   bool slow_switch[kSlowKinds] = {false, false, false};
   bool slow_report[kSlowKinds] = {false, false, false};

@@ -65,13 +65,16 @@ typedef enum tcpxbDeviceStatus {
 typedef struct tcpxbUnpackOpts {
   // Streaming: when non-null the kernel treats descriptor i as published once
   // *ready_count > i (a host-mapped or device counter the producer advances with
-  // release semantics) and waits for it, at most wait_ns nanoseconds in total.
+  // release semantics) and waits for it, at most wait_ns nanoseconds per descriptor
+  // (a producer that keeps advancing never trips the limit, however long the launch).
   const uint32_t* ready_count;
   uint64_t wait_ns;        // 0 = default (2 s)
   // Fan-out completion: when flag_value != 0, after every store of the launch has
   // completed the kernel writes flag_value (release, system scope) to every
-  // non-null peer_flags[i].  `ticket` is one zero-initialised uint32 of
-  // scratch on the launching GPU; the kernel leaves it zero again.
+  // non-null peer_flags[i], unless the launch recorded an error in `status`: then
+  // no flag is written and the peers' own bounded waits run out.  `ticket` is one
+  // zero-initialised uint32 of scratch on the launching GPU (at most 65535 CTAs per
+  // launch); the kernel leaves it zero again.
   uint32_t* peer_flags[TCPXB_MAX_PEERS];
   uint32_t flag_value;
   uint32_t* ticket;
@@ -164,9 +167,11 @@ int tcpxb_checksum(const void* buf, uint64_t bytes, uint64_t* out, void* partial
 //    the library, from load until the process exits.
 //  * Buffers larger than TCPXB_CHECKSUM_NOALLOC_MAX_BYTES are refused with
 //    TCPXB_K_TOO_LARGE and an explanatory message; nothing is launched.
-//  * The first call on each device looks up the array's device address
-//    (cudaGetSymbolAddress with that device current).  Make that first call before
-//    any stream capture begins on the device.
+//  * The array's device address is looked up once per device (cudaGetSymbolAddress
+//    with that device current): by tcpxb_kernels_preload if it ran on the device,
+//    else by the first call there.  Do whichever comes first before any stream
+//    capture begins on the device, and off the path that must not block: the
+//    look-up may load the module.  Later calls only clear the counter and launch.
 //  * All calls on one GPU share the array: the counter it starts from is cleared
 //    on the stream at the head of every call, and the partial sums keep the
 //    previous call's values until overwritten.  Two calls that overlap in time on

@@ -117,20 +117,23 @@ int run(const Job& j) {
   if (v != TCPXB_K_OK) return v;
   const uint32_t* ready = j.opts ? j.opts->ready_count : nullptr;
   const uint64_t wait_ns = j.opts && j.opts->wait_ns ? j.opts->wait_ns : kDefaultWaitNs;
-  const uint64_t t0 = nowNs();
-  bool dead = false;
+  bool errors = false;
   const uint32_t count = tcpxb::gpu::standinMovesData() ? j.count : 0;  // timing mode: no data is moved
   for (uint32_t i = 0; i < count; ++i) {
-    if (ready != nullptr && !dead) {
-      // streaming: record i exists once the producer's counter has passed it
+    if (ready != nullptr) {
+      // streaming: record i exists once the producer's counter has passed it; the limit
+      // is per wait, and after a time-out nothing further is attempted
+      const uint64_t t0 = nowNs();
+      bool timed_out = false;
       while (__atomic_load_n(ready, __ATOMIC_ACQUIRE) <= i) {
-        if (nowNs() - t0 > wait_ns) { dead = true; break; }
+        if (nowNs() - t0 > wait_ns) { timed_out = true; break; }
       }
+      if (timed_out) { report(j.status, TCPXB_ST_TIMEOUT, i); errors = true; break; }
     }
-    if (dead) { report(j.status, TCPXB_ST_TIMEOUT, i); continue; }
     const tcpxbLoadMeta m = j.descs[i];
     if ((uint64_t)m.src_off + m.len > j.pool_bytes || m.dst_off + m.len > j.dst_bytes || m.dst_off + m.len < m.dst_off) {
       report(j.status, TCPXB_ST_BOUNDS, i);
+      errors = true;
       continue;
     }
     const uint8_t* src = j.pool + m.src_off;
@@ -144,6 +147,7 @@ int run(const Job& j) {
     const uint8_t* a = j.acc + m.dst_off;
     if ((((uintptr_t)src | (uintptr_t)d | (uintptr_t)a | m.len) & (es - 1)) != 0) {
       report(j.status, TCPXB_ST_ALIGN, i);
+      errors = true;
       continue;
     }
     if (j.add_into_peers) {
@@ -157,8 +161,9 @@ int run(const Job& j) {
       for (int p = 0; p < j.npeers; ++p) memcpy(static_cast<uint8_t*>(j.peers[p]) + m.dst_off, d, m.len);
     }
   }
-  if (j.opts != nullptr && j.opts->flag_value != 0) {
-    // "every store of this launch has completed": trivially true here
+  if (j.opts != nullptr && j.opts->flag_value != 0 && !errors) {
+    // "every store of this launch has completed": trivially true here.  A launch that
+    // recorded an error publishes nothing; the peers' bounded waits then run out.
     for (int p = 0; p < TCPXB_MAX_PEERS; ++p)
       if (j.opts->peer_flags[p] != nullptr) __atomic_store_n(j.opts->peer_flags[p], j.opts->flag_value, __ATOMIC_RELEASE);
   }

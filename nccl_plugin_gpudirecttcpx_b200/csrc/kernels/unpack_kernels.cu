@@ -25,7 +25,10 @@
 // slot, take a warp-cooperative ld/st path; ragged tails (< 16 B) likewise.
 //
 // Every wait is bounded: on expiry the kernel records TCPXB_ST_TIMEOUT in the
-// status block and drains, it never traps and never spins forever.
+// status block, stops issuing, waits only for the loads already in flight and
+// returns; it never traps and never spins forever.  A launch that recorded any error
+// does not publish its fan-out completion flag: the peers then run into their own
+// bounded flag wait instead of taking partly written output for complete.
 // No load in this file is a cluster-wide one; peers are reached by stores only.
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
@@ -254,7 +257,7 @@ __device__ __forceinline__ void copy_units(const uint8_t* src, const UnpackParam
 // stores, widest unit the common alignment of source and destination allows.
 template <int RED, bool L2RED, int FAN>
 __device__ void warp_generic(const UnpackParams& p, uint32_t src_off, uint64_t dst_off, uint32_t n,
-                             uint32_t desc_index, int lane) {
+                             uint32_t desc_index, int lane, uint32_t* cta_err) {
   if (n == 0) return;
   const uint8_t* src = p.pool + src_off;
   const int fan = (FAN != FAN_NONE);
@@ -285,7 +288,7 @@ __device__ void warp_generic(const UnpackParams& p, uint32_t src_off, uint64_t d
     uintptr_t d = reinterpret_cast<uintptr_t>(p.dst + dst_off);
     uintptr_t a = reinterpret_cast<uintptr_t>(p.acc + dst_off);
     if (((s | d | a | n) & (es - 1)) != 0) {
-      if (lane == 0) report(p.status, TCPXB_ST_ALIGN, desc_index);
+      if (lane == 0) { report(p.status, TCPXB_ST_ALIGN, desc_index); atomicOr(cta_err, 1u); }
       return;
     }
     uint32_t elems = n / es;
@@ -346,11 +349,17 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kDataBytes) + warp * D;
   SlotInfo* infos = reinterpret_cast<SlotInfo*>(smem + C::kDataBytes + kWarps * D * 8) + warp * D;
 
+  __shared__ uint32_t cta_err;  // any warp of this CTA recorded an error
+  if (threadIdx.x == 0) cta_err = 0;
   if (lane == 0) {
     for (int s = 0; s < D; ++s) mbar_init(smem_u32(&bars[s]), 1);
     fence_mbar_init();
   }
-  __syncwarp();
+  __syncthreads();
+  auto record = [&](uint32_t code, uint32_t index) {  // one lane calls this
+    report(p.status, code, index);
+    atomicOr(&cta_err, 1u);
+  };
 
   // Consecutive descriptors go to different SMs first, then to different warps.
   const uint32_t G = gridDim.x * kWarps;
@@ -363,18 +372,20 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
   uint32_t ready_seen = 0;
   uint64_t ready_t0 = 0;
   bool dead = false;  // a bounded wait ran out: stop issuing, drain what is in flight
+  uint32_t issued = 0;  // local iterations whose loads were issued
 
   // Issue the loads of local iteration k into slot k % D.  Warp-uniform.
   auto issue = [&](uint32_t k) {
     const uint32_t slot = k % D;
     const uint32_t idx = gw + k * G;
+    issued = k + 1;
     uint32_t so, ln, dlo, dhi;
     if (p.ready != nullptr) {
       // Streaming: descriptor idx exists once the producer's counter passed it.
       if (lane == 0 && ready_seen <= idx) {
         for (uint32_t spin = 0;; ++spin) {
           ready_seen = ld_acquire_sys(p.ready);
-          if (ready_seen > idx) break;
+          if (ready_seen > idx) { ready_t0 = 0; break; }  // the limit is per wait, not per launch
           if ((spin & 0x3f) == 0x3f) {
             uint64_t now = globaltimer_ns();
             if (ready_t0 == 0) ready_t0 = now;
@@ -386,7 +397,7 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
       ready_seen = __shfl_sync(0xffffffffu, ready_seen, 0);
       uint4 d = make_uint4(0, 0, 0, 0);
       if (ready_seen <= idx) {
-        if (lane == 0) report(p.status, TCPXB_ST_TIMEOUT, idx);
+        if (lane == 0) record(TCPXB_ST_TIMEOUT, idx);
         dead = true;
       } else if (lane == 0) {
         d = ld_volatile_v4(&p.descs[idx]);
@@ -410,7 +421,7 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
     const uint64_t dof = (static_cast<uint64_t>(dhi) << 32) | dlo;
     if (dead) ln = 0;
     if ((uint64_t)so + ln > p.pool_bytes || dof + ln > p.dst_bytes || dof + ln < dof) {
-      if (lane == 0) report(p.status, TCPXB_ST_BOUNDS, idx);
+      if (lane == 0) record(TCPXB_ST_BOUNDS, idx);
       ln = 0;
     }
     uintptr_t al = reinterpret_cast<uintptr_t>(p.pool + so) | reinterpret_cast<uintptr_t>(p.dst + dof);
@@ -437,11 +448,14 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
   for (uint32_t k = 0; k < pro; ++k) issue(k);
 
   for (uint32_t k = 0; k < n; ++k) {
+    // After a time-out only the loads already issued are waited for (at most D of
+    // them, each with a shortened limit): the drain takes about one wait, not n of them.
+    if (dead && k >= issued) break;
     const uint32_t slot = k % D;
     const uint32_t parity = (k / D) & 1;
     const uint32_t bar = smem_u32(&bars[slot]);
-    if (!mbar_wait_bounded(bar, parity, wait_ns)) {
-      if (lane == 0) report(p.status, TCPXB_ST_TIMEOUT, gw + k * G);
+    if (!mbar_wait_bounded(bar, parity, dead ? (wait_ns >> 3) + 1 : wait_ns)) {
+      if (lane == 0 && !dead) record(TCPXB_ST_TIMEOUT, gw + k * G);
       dead = true;
     }
     dead = __any_sync(0xffffffffu, dead);
@@ -499,7 +513,7 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
     if (lane == 0) bulk_commit();
     if (info.len > info.bulk && !dead) {
       warp_generic<RED, L2RED, FAN>(p, info.src_off + info.bulk, info.dst_off + info.bulk,
-                                    info.len - info.bulk, gw + k * G, lane);
+                                    info.len - info.bulk, gw + k * G, lane, &cta_err);
     }
     // Refill the slot of the previous iteration: its store has had one iteration
     // to read shared memory, so this wait rarely blocks.
@@ -513,15 +527,19 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
 
   if (FAN != FAN_NONE && p.flag_value != 0 && p.ticket != nullptr) {
     // Publish completion to the peers once every CTA's stores are done.
+    // The ticket counts CTAs in its low half and CTAs with errors in its high half.
     __syncthreads();
     if (threadIdx.x == 0) {
       __threadfence_system();
-      const uint32_t t = atomicAdd(p.ticket, 1u);
-      if (t == gridDim.x - 1) {
+      const uint32_t mine = 1u + (cta_err ? 0x10000u : 0u);
+      const uint32_t t = atomicAdd(p.ticket, mine) + mine;
+      if ((t & 0xffffu) == gridDim.x) {
         *p.ticket = 0;
         __threadfence_system();
-        for (int r = 0; r < TCPXB_MAX_PEERS; ++r) {
-          if (p.peer_flags[r] != nullptr) st_release_sys(p.peer_flags[r], p.flag_value);
+        if ((t >> 16) == 0) {
+          for (int r = 0; r < TCPXB_MAX_PEERS; ++r) {
+            if (p.peer_flags[r] != nullptr) st_release_sys(p.peer_flags[r], p.flag_value);
+          }
         }
       }
     }
@@ -729,6 +747,22 @@ int launch(const UnpackParams& p, int max_ctas, cudaStream_t stream) {
   return TCPXB_K_OK;
 }
 
+// Device address of the allocation-free checksum's scratch on `dev` (the current
+// device).  In host code `g_csum_static` is only a handle for the runtime, not an
+// address a kernel could use, so the address is resolved once per device and kept.
+int csumStaticScratch(int dev, void** out) {
+  static std::mutex mu;
+  static void* scratch_of_device[kMaxDevices] = {};
+  std::lock_guard<std::mutex> l(mu);
+  if (scratch_of_device[dev] == nullptr) {
+    void* p = nullptr;
+    CUDA_TRY(cudaGetSymbolAddress(&p, g_csum_static));
+    scratch_of_device[dev] = p;
+  }
+  *out = scratch_of_device[dev];
+  return TCPXB_K_OK;
+}
+
 template <int FAN>
 int prepareFan(int dev) {
   int rc = prepareVariant<TCPXB_U8, false, FAN>(dev);
@@ -837,8 +871,15 @@ int tcpxb_kernels_preload(void) {
   memset(&pp, 0, sizeof pp);
   peer_reduce_kernel<TCPXB_BF16><<<1, 256, 0, s>>>(pp);
   peer_reduce_kernel<TCPXB_F32><<<1, 256, 0, s>>>(pp);
-  cudaFuncAttributes a;
-  CUDA_TRY(cudaFuncGetAttributes(&a, checksum_kernel));
+  // The checksum kernel and the address of the allocation-free entry point's scratch:
+  // one launch over zero bytes, its result written into the scratch itself, so that
+  // the first real tcpxb_checksum_noalloc on this device only clears and launches.
+  void* cs = nullptr;
+  rc = csumStaticScratch(dev, &cs);
+  if (rc) return rc;
+  CUDA_TRY(cudaMemsetAsync(cs, 0, 8, s));
+  checksum_kernel<<<1, kCsumThreads, 0, s>>>(nullptr, 0, &static_cast<CsumScratch*>(cs)->partial[kCsumBlocks - 1],
+                                             static_cast<CsumScratch*>(cs));
   CUDA_TRY(cudaGetLastError());
   CUDA_TRY(cudaStreamSynchronize(s));
   CUDA_TRY(cudaStreamDestroy(s));
@@ -1000,31 +1041,20 @@ int tcpxb_checksum(const void* buf, uint64_t bytes, uint64_t* out, void* partial
   return TCPXB_K_OK;
 }
 
-// In host code `g_csum_static` is only a handle for the runtime, not an address a
-// kernel could use, so the device address is resolved once per device.
 int tcpxb_checksum_noalloc(const void* buf, uint64_t bytes, uint64_t* out, void* stream) {
-  static std::mutex mu;
-  static void* scratch_of_device[kMaxDevices] = {};
   if (out == nullptr || (buf == nullptr && bytes != 0))
     return fail(TCPXB_K_INVALID, "null buffer or output");
   if (reinterpret_cast<uintptr_t>(buf) & 3)
     return fail(TCPXB_K_INVALID, "checksum buffer must be 4-byte aligned");
   if (bytes > TCPXB_CHECKSUM_NOALLOC_MAX_BYTES)
     return fail(TCPXB_K_TOO_LARGE,
-                "tcpxb_checksum_noalloc handles at most 16 GiB per call; split the buffer or use tcpxb_checksum%s");
+                "tcpxb_checksum_noalloc handles at most 16 GiB per call; split the buffer or use tcpxb_checksum");
   int dev = 0;
   CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return fail(TCPXB_K_INVALID, "device ordinal out of range");
   void* scratch = nullptr;
-  {
-    std::lock_guard<std::mutex> l(mu);
-    if (scratch_of_device[dev] == nullptr) {
-      void* p = nullptr;
-      CUDA_TRY(cudaGetSymbolAddress(&p, g_csum_static));
-      scratch_of_device[dev] = p;
-    }
-    scratch = scratch_of_device[dev];
-  }
+  const int rc = csumStaticScratch(dev, &scratch);  // a table look-up after tcpxb_kernels_preload or a first call
+  if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // the completion counter must start at zero even if an earlier launch was cut short
   CUDA_TRY(cudaMemsetAsync(scratch, 0, 8, s));

@@ -361,6 +361,8 @@ TEST(connect_to_dead_listener_fails_cleanly) {
 // ---- device-memory receives on the stand-in device
 void unpackModeOn(const char* pool_bytes) {
   setenv("NCCL_GPUDIRECTTCPX_RECV_MODE", "unpack", 1);
+  setenv("NCCL_PROTO", "Simple", 1);  // the consumer of these tests is the test itself
+  setenv("NCCL_ALGO", "Ring", 1);
   setenv("NCCL_GPUDIRECTTCPX_RX_POOL_BYTES", pool_bytes, 1);  // the first device receive sizes the pool for the process
   EXPECT(netInit(nullptr) == kSuccess);
 }

@@ -3,18 +3,31 @@
 // blocks and nothing else.  The transport cannot beat this number; benchmarks
 // report their socket stage as a fraction of it.
 //   tcpxb_rawsock [--streams 8] [--mb-per-stream 2048] [--block-kb 512] [--nics 4]
+//                 [--span-mb 0] [--nonblocking 0] [--scatter-kb 0]
 // Prints one JSON line.  Stream i uses address 127.0.0.(1 + i % nics).
+// The defaults give the friendliest case (one block per thread, reused, so it stays
+// in the core's cache; blocking calls).  The other options take that apart:
+//   --span-mb M      every thread walks through a buffer of M MiB block by block, so that
+//                    with a large M the copies miss the caches, as a transport's do when
+//                    its staging and landing buffers are as large as the data in flight;
+//   --nonblocking 1  MSG_DONTWAIT calls with poll() when the socket would block;
+//   --scatter-kb K   the receiver lands every block with one recvmsg over pieces of K KiB
+//                    at shuffled places of its span (page-pool landing).
 #include <arpa/inet.h>
+#include <errno.h>
 #include <netinet/in.h>
 #include <netinet/tcp.h>
+#include <poll.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 #include <sys/socket.h>
+#include <sys/uio.h>
 #include <sys/wait.h>
 #include <time.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <string>
 #include <thread>
 #include <vector>
@@ -32,7 +45,15 @@ struct Options {
   long mb = 2048;
   int block_kb = 512;
   int nics = 4;
+  long span_mb = 0;
+  int nonblocking = 0;
+  int scatter_kb = 0;
 };
+
+void waitFor(int fd, short events) {
+  struct pollfd p = {fd, events, 0};
+  poll(&p, 1, 100);
+}
 
 int receiver(const Options& o, int port_pipe, int go_pipe) {
   std::vector<int> lfd(o.streams), ports(o.streams);
@@ -57,18 +78,59 @@ int receiver(const Options& o, int port_pipe, int go_pipe) {
   std::vector<std::thread> th;
   for (int i = 0; i < o.streams; ++i)
     th.emplace_back([&, i] {
-      std::vector<char> buf(block);
-      size_t got = 0;
+      const size_t span = std::max(block, (size_t)o.span_mb << 20) / block * block;
+      std::vector<char> buf(span);
+      const int fl = o.nonblocking ? MSG_DONTWAIT : 0;
+      // scattered landing: the pieces of the span in a fixed shuffled order
+      const size_t piece = (size_t)o.scatter_kb << 10;
+      std::vector<uint32_t> order;
+      if (piece > 0) {
+        order.resize(span / piece);
+        for (uint32_t k = 0; k < order.size(); ++k) order[k] = k;
+        uint64_t x = 0x9e3779b97f4a7c15ull + (uint64_t)i;
+        for (size_t k = order.size(); k > 1; --k) {
+          x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+          std::swap(order[k - 1], order[x % k]);
+        }
+      }
+      std::vector<struct iovec> iov;
+      size_t got = 0, pos = 0, next_piece = 0;
       while (got < total) {
-        ssize_t n = recv(fd[i], buf.data(), block, 0);
+        ssize_t n;
+        if (piece > 0) {
+          if (iov.empty()) {
+            for (size_t b = 0; b < block; b += piece) {
+              iov.push_back({buf.data() + (size_t)order[next_piece] * piece, piece});
+              next_piece = (next_piece + 1) % order.size();
+            }
+          }
+          struct msghdr msg;
+          memset(&msg, 0, sizeof msg);
+          msg.msg_iov = iov.data();
+          msg.msg_iovlen = iov.size();
+          n = recvmsg(fd[i], &msg, fl);
+          if (n > 0) {
+            size_t left = (size_t)n, k = 0;
+            while (left > 0 && k < iov.size()) {
+              if (left >= iov[k].iov_len) { left -= iov[k].iov_len; ++k; }
+              else { iov[k].iov_base = (char*)iov[k].iov_base + left; iov[k].iov_len -= left; left = 0; }
+            }
+            iov.erase(iov.begin(), iov.begin() + (long)k);
+          }
+        } else {
+          n = recv(fd[i], buf.data() + pos, block, fl);
+          if (n > 0) pos = (pos + block) % span;
+        }
+        if (n < 0 && (errno == EAGAIN || errno == EWOULDBLOCK)) { waitFor(fd[i], POLLIN); continue; }
         if (n <= 0) break;
         got += (size_t)n;
       }
     });
   for (auto& t : th) t.join();
   const double dt = nowSec() - t0;
-  printf("{\"tool\": \"rawsock\", \"streams\": %d, \"block_kb\": %d, \"mb_per_stream\": %ld, \"seconds\": %.4f, \"GBps\": %.3f}\n",
-         o.streams, o.block_kb, o.mb, dt, (double)total * o.streams / dt / 1e9);
+  printf("{\"tool\": \"rawsock\", \"streams\": %d, \"block_kb\": %d, \"mb_per_stream\": %ld, \"span_mb\": %ld, \"nonblocking\": %d, "
+         "\"scatter_kb\": %d, \"seconds\": %.4f, \"GBps\": %.3f}\n",
+         o.streams, o.block_kb, o.mb, o.span_mb, o.nonblocking, o.scatter_kb, dt, (double)total * o.streams / dt / 1e9);
   return 0;
 }
 
@@ -98,12 +160,18 @@ int sender(const Options& o, int port_pipe, int go_pipe) {
   std::vector<std::thread> th;
   for (int i = 0; i < o.streams; ++i)
     th.emplace_back([&, i] {
-      std::vector<char> buf(block, (char)i);
-      size_t sent = 0;
+      const size_t span = std::max(block, (size_t)o.span_mb << 20) / block * block;
+      std::vector<char> buf(span, (char)i);
+      const int fl = MSG_NOSIGNAL | (o.nonblocking ? MSG_DONTWAIT : 0);
+      size_t sent = 0, pos = 0, in_block = 0;
       while (sent < total) {
-        ssize_t n = send(fd[i], buf.data(), block < total - sent ? block : total - sent, MSG_NOSIGNAL);
+        const size_t want = std::min(block - in_block, total - sent);
+        ssize_t n = send(fd[i], buf.data() + pos + in_block, want, fl);
+        if (n < 0 && (errno == EAGAIN || errno == EWOULDBLOCK)) { waitFor(fd[i], POLLOUT); continue; }
         if (n <= 0) break;
         sent += (size_t)n;
+        in_block += (size_t)n;
+        if (in_block == block) { in_block = 0; pos = (pos + block) % span; }
       }
     });
   for (auto& t : th) t.join();
@@ -118,7 +186,8 @@ int main(int argc, char** argv) {
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
     if (a == "--help" || a == "-h") {
-      printf("usage: tcpxb_rawsock [--streams 8] [--mb-per-stream 2048] [--block-kb 512] [--nics 4]\n");
+      printf("usage: tcpxb_rawsock [--streams 8] [--mb-per-stream 2048] [--block-kb 512] [--nics 4] [--span-mb 0] "
+             "[--nonblocking 0] [--scatter-kb 0]\n");
       return 0;
     }
     if (i + 1 >= argc) { fprintf(stderr, "%s needs a value (see --help)\n", a.c_str()); return 2; }
@@ -127,9 +196,13 @@ int main(int argc, char** argv) {
     else if (a == "--mb-per-stream") o.mb = atol(v);
     else if (a == "--block-kb") o.block_kb = atoi(v);
     else if (a == "--nics") o.nics = atoi(v);
+    else if (a == "--span-mb") o.span_mb = atol(v);
+    else if (a == "--nonblocking") o.nonblocking = atoi(v);
+    else if (a == "--scatter-kb") o.scatter_kb = atoi(v);
     else { fprintf(stderr, "unknown argument %s (see --help)\n", a.c_str()); return 2; }
   }
-  if (o.streams < 1 || o.streams > 256 || o.nics < 1) return 2;
+  if (o.streams < 1 || o.streams > 256 || o.nics < 1 || o.span_mb < 0 || o.scatter_kb < 0) return 2;
+  if (o.scatter_kb > 0 && (o.block_kb % o.scatter_kb) != 0) { fprintf(stderr, "--block-kb must be a multiple of --scatter-kb\n"); return 2; }
   int ports[2], go[2];
   if (pipe(ports) != 0 || pipe(go) != 0) return 1;
   fflush(stdout);

@@ -27,6 +27,9 @@ def _env(**kw):
         "NCCL_NSOCKS_PERTHREAD": "2",   # 4 sockets per comm
     })
     env.update({k: str(v) for k, v in kw.items()})
+    if env.get("NCCL_GPUDIRECTTCPX_RECV_MODE") == "unpack" and "NCCL_PROTO" not in kw:
+        # the settings unpack mode is documented with; without them the plugin falls back to host mode
+        env.update({"NCCL_PROTO": "Simple", "NCCL_ALGO": "Ring"})
     return env
 
 
@@ -158,6 +161,19 @@ def test_device_properties_as_nccl_sees_them(host_lib):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     for d in _props(r.stdout):
         assert d["ptr"] == "3" and d["devType"] == "1" and d["devVersion"] == "7" and d["speed"] == "200000"
+
+
+@pytest.mark.parametrize("proto,algo", [("", ""), ("LL128", "Ring"), ("Simple", "Tree"), ("Simple", "")])
+def test_unpack_mode_is_not_offered_without_simple_ring(host_lib, proto, algo):
+    """Only NCCL's Simple-protocol ring primitives run the unpack consumer.  Asked for unpack mode under any
+    other setting, the plugin warns once and behaves as in host mode (no unpack device type, host pointers),
+    so that results stay correct (reference: src/net_tcpx.cc:739-740 always advertises the unpack type)."""
+    r = _loopback(host_lib, ["--sizes", "1000,300000", "--iters", "1"], TCPXB_FAKE_GPU=1,
+                  NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_PROTO=proto, NCCL_ALGO=algo)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    for d in _props(r.stdout):
+        assert d["devType"] == "0" and d["ptr"] == "1"
+    assert "needs NCCL_PROTO=Simple and NCCL_ALGO=Ring" in r.stdout + r.stderr
 
 
 @pytest.mark.parametrize("threads,per,want", [(16, 3, "8 sockets, 8 threads"), (3, 4, "6 sockets, 3 threads"), (20, 3, "8 sockets, 4 threads"),

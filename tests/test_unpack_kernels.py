@@ -212,6 +212,83 @@ def test_streaming_ready_counter_and_bounded_timeout():
     assert int(torch.ones(4, device=DEV).sum().item()) == 4
 
 
+def test_stalled_ready_counter_drains_in_about_one_wait():
+    """One CTA, 4096 records, a producer that stops after 5: the kernel gives up after one
+    wait (not one wait per remaining record) and reports the time-out once per warp."""
+    n = 4096
+    pool_bytes = 1 << 20
+    total = 4096 * n
+    pool = torch.zeros(pool_bytes, dtype=torch.uint8, device=DEV)
+    descs = U.make_descriptors(np.zeros(n, dtype=np.uint64), np.full(n, 4096), np.arange(n, dtype=np.uint64) * 4096)
+    d = U.descriptors_to_device(descs)
+    ready = torch.tensor([5], dtype=torch.int32, device=DEV)
+    dst = torch.zeros(total, dtype=torch.uint8, device=DEV)
+    st = U.status_buffer()
+    wait_ns = 10_000_000
+    U.unpack_copy(pool, dst, d, status=st, ready_count=ready, wait_ns=wait_ns, max_ctas=1)  # warm: module load
+    torch.cuda.synchronize()
+    st.zero_()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    U.unpack_copy(pool, dst, d, status=st, ready_count=ready, wait_ns=wait_ns, max_ctas=1)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    s = st.tolist()
+    assert s[0] == U.ST_TIMEOUT
+    assert ms < 5 * wait_ns * 1e-6, f"drain took {ms} ms for a {wait_ns * 1e-6} ms limit"
+    assert 1 <= s[2] <= 16  # at most one report per warp of the CTA
+    assert int(torch.ones(4, device=DEV).sum().item()) == 4
+
+
+def test_slow_but_steady_producer_never_trips_the_limit():
+    """The streaming limit is per wait: a launch that lasts many times wait_ns finishes
+    cleanly as long as the producer keeps publishing."""
+    n = 64
+    pool_bytes = 1 << 20
+    pool = _pool(pool_bytes, 31)
+    descs = U.permuted_fragments(4096 * n, pool_bytes, seed=32)
+    d = U.descriptors_to_device(descs)
+    ready_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+    dst = torch.zeros(4096 * n, dtype=torch.uint8, device=DEV)
+    st = U.status_buffer()
+    wait_ns = 40_000_000
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        U.unpack_copy(pool.to(DEV), dst, d, status=st, ready_count=ready_host.data_ptr(), wait_ns=wait_ns, max_ctas=2)
+    import time
+    t0 = time.time()
+    for k in range(1, 9):           # 8 steps of 15 ms: 120 ms in all, three times the limit
+        time.sleep(0.015)
+        ready_host[0] = k * n // 8
+    side.synchronize()
+    assert time.time() - t0 > 2 * wait_ns * 1e-9
+    want = U.reference_unpack(pool, torch.zeros(4096 * n, dtype=torch.uint8), descs)
+    assert st.tolist()[0] == U.ST_OK and torch.equal(dst.cpu(), want)
+
+
+def test_fanout_flag_is_not_published_after_an_error():
+    """A launch that records an error leaves the peers' completion flag alone."""
+    pool_bytes = 1 << 20
+    n = 40
+    pool = _pool(pool_bytes, 33).to(DEV)
+    good = U.permuted_fragments(4096 * n, pool_bytes, seed=34)
+    bad = good.copy()
+    bad[7]["src_off"] = pool_bytes - 8  # runs past the end of the pool
+    dst = torch.zeros(4096 * n, dtype=torch.uint8, device=DEV)
+    peer = torch.zeros(4096 * n, dtype=torch.uint8, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ticket = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for descs, want_flag, want_status in ((bad, 0, U.ST_BOUNDS), (good, 5, U.ST_OK)):
+        st = U.status_buffer()
+        U.unpack_fanout(pool, dst, [peer], U.descriptors_to_device(descs), status=st,
+                        peer_flags=[flag.data_ptr()], flag_value=5, ticket=ticket)
+        torch.cuda.synchronize()
+        assert st.tolist()[0] == want_status
+        assert flag.item() == want_flag
+        assert ticket.item() == 0  # left clean for the next launch either way
+
+
 def test_wait_flags_timeout_returns_status():
     flags = torch.zeros(3, dtype=torch.int32, device=DEV)
     flags[1] = 9

@@ -43,12 +43,19 @@ def test_noalloc_checksum_matches_the_allocating_entry_point(nbytes):
     got = torch.zeros(2, dtype=torch.int64, device="cuda")
     bufs = [torch.randint(0, 256, (nbytes,), dtype=torch.uint8, device="cuda",
                           generator=torch.Generator("cuda").manual_seed(nbytes + i)) for i in range(2)]
+    # one call first: the array's address is looked up once per device, which may load the module
+    assert lib.tcpxb_checksum_noalloc(bufs[0].data_ptr(), 4, got.data_ptr(), stream) == 0
     torch.cuda.synchronize()
     for i, buf in enumerate(bufs):  # two calls in a row share the library's scratch array
         assert lib.tcpxb_checksum(buf.data_ptr(), nbytes, want.data_ptr(), scratch.data_ptr(), stream) == 0
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = lib.tcpxb_checksum_noalloc(buf.data_ptr(), nbytes, got[i:].data_ptr(), stream)
         assert rc == 0, lib.tcpxb_kernel_last_error().decode()
         torch.cuda.synchronize()
+        # the device's free memory is what it was: the call allocated nothing (no other
+        # CUDA work of this process ran in between)
+        assert torch.cuda.mem_get_info()[0] >= free_before
         assert got[i].item() == want.item()  # integer sums: equal, not merely close
         pad = torch.cat([buf, torch.zeros((-nbytes) % 4, dtype=torch.uint8, device="cuda")])
         assert (got[i].item() & 0xFFFFFFFFFFFFFFFF) == int(pad.view(torch.int32).to(torch.int64).bitwise_and(0xFFFFFFFF).sum().item())
