@@ -531,7 +531,9 @@ def main():
     if is_engine:
         launches = int(s1.kernel_launches - s0.kernel_launches)
         drv = {k: round((getattr(s1, k) - getattr(s0, k)) * 1e3 / max(args.steps, 1), 3)
-               for k in ("t_post_recv", "t_post_send", "t_test_recv", "t_launch", "t_consume", "t_test_send", "t_idle", "t_sleep")}
+               for k in ("t_post_recv", "t_post_send", "t_test_recv", "t_launch", "t_consume", "t_test_send", "t_idle", "t_sleep",
+                         "tx_idle", "tx_blocked", "rx_idle", "rx_blocked")}
+        drv["sleeps"] = int((s1.sleeps - s0.sleeps) // max(args.steps, 1))
         net_bytes = (s1.bytes_received - s0.bytes_received) // max(args.steps, 1)
         frags = (s1.fragments - s0.fragments) // max(args.steps, 1)
         eng.close()

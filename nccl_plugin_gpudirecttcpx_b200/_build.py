@@ -11,6 +11,8 @@ and g++.  Outputs land in `nccl_plugin_gpudirecttcpx_b200/_lib/`:
   libtcpxb_host.so      host core + engine with no CUDA: device calls go to a stand-in
                         device in host memory (g++ only; used by CPU tests)
   tcpxb_loopback        stand-alone driver of the ncclNet table (g++ only)
+  tcpxb_rxdm            rx buffer manager daemon (host pools; g++ only)
+  tcpxb_rxdm_gpu        the same daemon linked against the CUDA build: can own device pools
 
 Objects are rebuilt only when a source or header is newer than the object.
 """
@@ -130,6 +132,13 @@ def build_cuda(verbose: bool = False) -> list[Path]:
             _run([nvcc, "-shared", "-o", str(plug)] + [str(o) for o in cobjs + eobjs + kobjs] +
                  ["-cudart", "static", "-Xlinker", "--no-undefined", "-lpthread", "-ldl", "-lrt"])
         outs.append(plug)
+        # the buffer-manager daemon against the CUDA build: the one that can own device pools
+        daemon = OUT / "tcpxb_rxdm_gpu"
+        src = CSRC / "tools" / "rxdm.cc"
+        if _stale(daemon, [src, plug], hdr):
+            _run(["g++"] + CXX_FLAGS + ["-I", _cuda_include(nvcc), str(src), "-o", str(daemon), "-L", str(OUT),
+                                        f"-l:{plug.name}", "-Wl,-rpath,$ORIGIN", "-ldl", "-pthread"])
+        outs.append(daemon)
     return outs
 
 

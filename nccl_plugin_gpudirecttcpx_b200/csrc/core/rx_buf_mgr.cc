@@ -7,6 +7,7 @@
 
 #include <sys/mman.h>
 
+#include "tcpxb/cu_driver.h"
 #include "tcpxb/flags.h"
 #include "tcpxb/gpu.h"
 #include "tcpxb/rxdm.h"
@@ -177,13 +178,20 @@ class EmulatedRxBufMgr final : public RxBufMgr {
 };
 
 // Pool, rules and registry live in the tcpxb_rxdm daemon; this process maps the pool
-// it is handed (memfd over SCM_RIGHTS), registers it with CUDA and allocates pages
-// from it locally, as the NIC + kernel would on a devmem-TCP host.
+// it is handed (a descriptor over SCM_RIGHTS) and allocates pages from it locally, as
+// the NIC + kernel would on a devmem-TCP host.  A host pool is a memfd: mapped and
+// registered with CUDA.  A device pool is a shareable handle of GPU memory the daemon
+// allocated: imported and mapped through the driver's virtual memory API (reference:
+// src/gpu/common.cu:25-65); without a devmem NIC to write into it, payload lands in a
+// pinned mirror of the same size and the copy engine places each page run.
 class DaemonRxBufMgr final : public RxBufMgr {
  public:
   DaemonRxBufMgr(int dev, std::string prefix) : dev_(dev), prefix_(std::move(prefix)) {}
   ~DaemonRxBufMgr() override {
-    if (host_base_ != nullptr) {
+    if (device_pool_) {
+      cu::sharedRelease(&imported_);
+      gpu::hostFreeMapped(host_base_);
+    } else if (host_base_ != nullptr) {
       gpu::hostUnregister(host_base_);
       munmap(host_base_, bytes_);
     }
@@ -200,27 +208,41 @@ class DaemonRxBufMgr final : public RxBufMgr {
     snprintf(q.gpu.gpu_pci, sizeof q.gpu.gpu_pci, "%s", pci_.c_str());
     TCPXB_CHECK(rxdmCall(prefix_, "get_gpu_metadata", q, &rep, nullptr));
     bytes_ = rep.reply.a / kRxPageBytes * kRxPageBytes;
+    device_pool_ = rep.reply.c == (uint64_t)kRxdmPoolDevice;
     q.type = kRxdmGetGpuFd;
     TCPXB_CHECK(rxdmCall(prefix_, "get_gpu_fd", q, &rep, &pool_fd_));
     if (pool_fd_ < 0 || bytes_ == 0) { WARN("rx buffer manager sent no pool for %s", pci_.c_str()); return kRemoteError; }
-    void* p = mmap(nullptr, bytes_, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_POPULATE, pool_fd_, 0);
-    if (p == MAP_FAILED) { WARN("mapping the rx pool failed: %s", strerror(errno)); return kSystemError; }
-    host_base_ = static_cast<uint8_t*>(p);
-    void* d = nullptr;
-    TCPXB_CHECK(gpu::hostRegisterMapped(host_base_, bytes_, &d));
-    dev_base_ = static_cast<uint8_t*>(d);
+    if (bytes_ > (4ull << 30)) { WARN("rx pool of %lu bytes is larger than 4 GiB (record offsets are 32-bit)", (unsigned long)bytes_); return kInvalidUsage; }
+    if (device_pool_) {
+      if (dev_ < 0) { WARN("a device rx pool needs a GPU"); return kInvalidUsage; }
+      TCPXB_CHECK(cu::deviceInit(dev_));
+      TCPXB_CHECK(cu::sharedImport(dev_, pool_fd_, bytes_, &imported_));
+      dev_base_ = static_cast<uint8_t*>(imported_.dptr);
+      void* h = nullptr;
+      void* hd = nullptr;
+      TCPXB_CHECK(gpu::hostAllocMapped(bytes_, &h, &hd));  // landing mirror
+      host_base_ = static_cast<uint8_t*>(h);
+    } else {
+      void* p = mmap(nullptr, bytes_, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_POPULATE, pool_fd_, 0);
+      if (p == MAP_FAILED) { WARN("mapping the rx pool failed: %s", strerror(errno)); return kSystemError; }
+      host_base_ = static_cast<uint8_t*>(p);
+      void* d = nullptr;
+      TCPXB_CHECK(gpu::hostRegisterMapped(host_base_, bytes_, &d));
+      dev_base_ = static_cast<uint8_t*>(d);
+    }
     const Flags& f = flags();
-    alloc_ = std::make_unique<PageAllocator>((uint32_t)(bytes_ / kRxPageBytes), f.rx_pool_scatter != 0, 0x9e3779b97f4a7c15ull,
-                                             (uint32_t)f.rx_pool_run_pages);
-    INFO(kSubInit | kSubNet, "rx pool for %s imported from %s: %lu MiB, host %p device %p", pci_.c_str(), prefix_.c_str(),
-         (unsigned long)(bytes_ >> 20), (void*)host_base_, (void*)dev_base_);
+    // a device pool is filled by the copy engine one page run at a time: keep runs contiguous
+    alloc_ = std::make_unique<PageAllocator>((uint32_t)(bytes_ / kRxPageBytes), f.rx_pool_scatter != 0 && !device_pool_,
+                                             0x9e3779b97f4a7c15ull, (uint32_t)f.rx_pool_run_pages);
+    INFO(kSubInit | kSubNet, "rx pool for %s imported from %s: %lu MiB of %s memory, host %p device %p", pci_.c_str(), prefix_.c_str(),
+         (unsigned long)(bytes_ >> 20), device_pool_ ? "device" : "host", (void*)host_base_, (void*)dev_base_);
     return kSuccess;
   }
 
   uint8_t* hostBase() override { return host_base_; }
   uint8_t* devBase() override { return dev_base_; }
   uint64_t bytes() const override { return bytes_; }
-  bool deviceResident() const override { return false; }
+  bool deviceResident() const override { return device_pool_; }
   bool allocPages(uint32_t n, std::vector<PageRun>* out, bool from_reservation) override {
     std::lock_guard<std::mutex> l(mu_);
     return alloc_->alloc(n, out, from_reservation);
@@ -301,6 +323,8 @@ class DaemonRxBufMgr final : public RxBufMgr {
   uint8_t* dev_base_ = nullptr;
   uint64_t bytes_ = 0;
   int pool_fd_ = -1;
+  bool device_pool_ = false;
+  cu::SharedAllocation imported_;
   std::vector<FlowRule> rules_;
   UnixSocketConnection keepalive_;
 };

@@ -337,17 +337,21 @@ void helperMain(Comm* comm, int tid) {
     if (blocked) {
       // every owned socket with work would block: sleep in the kernel until one is ready
       if (++idle_rounds > 8 && f.poll_block_us > 0) {
+        const uint64_t t0 = monotonicNanos();
         poll(pfds, (nfds_t)npfd, (int)std::max<int64_t>(1, f.poll_block_us / 1000));
+        me.blocked_ns.fetch_add(monotonicNanos() - t0, std::memory_order_relaxed);
       }
       continue;
     }
     if (++idle_rounds < 64) continue;  // short spin: the next chunk usually follows at once
+    const uint64_t idle_t0 = monotonicNanos();
     std::unique_lock<std::mutex> l(me.mu);
     me.sleeping.store(true, std::memory_order_seq_cst);
     me.cv.wait_for(l, std::chrono::milliseconds(50), [&] {
       return me.kicks.load(std::memory_order_seq_cst) != me.seen || comm->stop.load(std::memory_order_acquire);
     });
     me.sleeping.store(false, std::memory_order_release);
+    me.idle_ns.fetch_add(monotonicNanos() - idle_t0, std::memory_order_relaxed);
     me.seen = me.kicks.load(std::memory_order_acquire);
     idle_rounds = 0;
   }
@@ -1273,6 +1277,18 @@ Result netRequestScatterList(Request* r, ScatterList* out) {
   out->pool_dev = r->comm->rxmgr->devBase();
   out->pool_bytes = r->comm->rxmgr->bytes();
   return kSuccess;
+}
+
+void netCommHelperWaits(Comm* comm, uint64_t* idle_ns, uint64_t* blocked_ns) {
+  uint64_t idle = 0, blocked = 0;
+  if (comm != nullptr) {
+    for (int t = 0; t < comm->num_threads; ++t) {
+      idle += comm->helpers[t].idle_ns.load(std::memory_order_relaxed);
+      blocked += comm->helpers[t].blocked_ns.load(std::memory_order_relaxed);
+    }
+  }
+  if (idle_ns != nullptr) *idle_ns = idle;
+  if (blocked_ns != nullptr) *blocked_ns = blocked;
 }
 
 int netCommFlowCounters(Comm* comm, FlowCounters* out, int max) {

@@ -739,7 +739,16 @@ int tcpxb_engine_recv_prev(void* engine, void* buf, uint64_t bytes, void* stream
 
 int tcpxb_engine_stats(void* engine, tcpxbEngineStats* out) {
   if (engine == nullptr || out == nullptr) return -1;
-  *out = static_cast<Engine*>(engine)->stats;
+  Engine* e = static_cast<Engine*>(engine);
+  uint64_t ti = 0, tb = 0, ri = 0, rb = 0;
+  for (Rail& r : e->rails) {
+    uint64_t a = 0, b = 0;
+    netCommHelperWaits(r.send, &a, &b); ti += a; tb += b;
+    netCommHelperWaits(r.recv, &a, &b); ri += a; rb += b;
+  }
+  e->stats.tx_idle = ti * 1e-9; e->stats.tx_blocked = tb * 1e-9;
+  e->stats.rx_idle = ri * 1e-9; e->stats.rx_blocked = rb * 1e-9;
+  *out = e->stats;
   return 0;
 }
 

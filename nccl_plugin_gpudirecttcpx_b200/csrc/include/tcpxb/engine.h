@@ -61,6 +61,9 @@ typedef struct tcpxbEngineStats {
   // returning pages, testing sends, idle spinning, and asleep waiting for a wake-up
   double t_post_recv, t_post_send, t_test_recv, t_launch, t_consume, t_test_send, t_idle, t_sleep;
   uint64_t sleeps;                       // times the driving thread blocked
+  // helper threads of all rails, seconds: sending helpers asleep without a task / in poll()
+  // on a full socket; receiving helpers asleep without a task / in poll() on an empty socket
+  double tx_idle, tx_blocked, rx_idle, rx_blocked;
 } tcpxbEngineStats;
 
 // Creates the engine and initialises the transport (flags are read from the

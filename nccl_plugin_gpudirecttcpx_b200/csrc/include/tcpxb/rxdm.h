@@ -37,6 +37,10 @@ enum RxdmType : uint16_t {
   kRxdmReply = 0x8000,
 };
 
+// What a pool descriptor stands for: a memfd of host memory (map it, register it with
+// CUDA) or a shareable handle of device memory (import and map it through the driver).
+enum RxdmPoolKind : int { kRxdmPoolHost = 0, kRxdmPoolDevice = 1 };
+
 struct RxdmFlowRule {
   char src_ip[46];
   uint16_t src_port;
@@ -61,7 +65,7 @@ struct RxdmMessage {
       int32_t status;     // 0 = ok
       char text[64];      // "Ok." on success, like the reference's raw reply
       uint64_t a, b;      // metadata: size, alignment; status: rules, apps
-      uint64_t c;         // status: pools
+      uint64_t c;         // metadata: RxdmPoolKind; status: pools
     } reply;
   };
 };

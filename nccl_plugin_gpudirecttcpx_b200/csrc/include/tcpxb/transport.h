@@ -171,6 +171,9 @@ struct HelperThread {
   std::condition_variable cv;
   std::atomic<uint32_t> kicks{0};
   std::atomic<bool> sleeping{false};  // blocked (or about to block) on `cv`: a kick must notify
+  // where the thread waits: asleep with no task at all, and inside poll() because
+  // every socket with a task would block (the peer or the kernel is the slower side)
+  std::atomic<uint64_t> idle_ns{0}, blocked_ns{0};
   uint32_t seen = 0;
 };
 
@@ -311,6 +314,9 @@ struct FlowCounters {
   uint64_t flow_id, bytes_posted, bytes_done, tx_cnt, tx_completion_cnt, rx_cnt;
 };
 int netCommFlowCounters(Comm* comm, FlowCounters* out, int max);
+// Sums over the comm's helper threads: time asleep for want of a task, and time in
+// poll() waiting for a socket to become ready.  Tells which side of a slow transfer waits.
+void netCommHelperWaits(Comm* comm, uint64_t* idle_ns, uint64_t* blocked_ns);
 std::vector<std::string> netCommStatsLines(Comm* comm);
 void netResetForTests();
 

@@ -1,12 +1,17 @@
 // Receive-datapath manager daemon: owns the rx page pools and the flow-steering and
 // application tables, and serves them to plugin processes over AF_UNIX sockets.
 //
-//   tcpxb_rxdm --prefix /tmp/tcpxb --pool-mb 1024 [--max-rules 65536]
+//   tcpxb_rxdm --prefix /tmp/tcpxb --pool-mb 1024 [--max-rules 65536] [--device-pool]
 //
 // It stands in for the external daemon the reference depends on (reference:
 // README.md:14-16 names it; its clients are src/rx_buf_mgr_client/*).  One pool per
-// GPU PCI address, created on first request as a memfd; the plugin maps it and
-// registers it with CUDA.  A client that registers keeps its connection open; when
+// GPU PCI address, created on first request.  By default a pool is host memory (a
+// memfd the plugin maps and registers with CUDA).  With --device-pool it is device
+// memory of the GPU the request names, allocated through the driver's virtual memory
+// API and handed out as a shareable file descriptor that the plugin imports and maps
+// (reference: src/gpu/rx_pool.cu:62-124 asks the daemon for exactly this, and
+// src/gpu/common.cu:25-65 imports it); the GPU build of this tool (tcpxb_rxdm_gpu) is
+// the one that can do that on real hardware.  A client that registers keeps its connection open; when
 // the connection closes the client is deregistered and its flow rules are dropped,
 // which is how a crashed job is cleaned up.
 #include <poll.h>
@@ -24,6 +29,8 @@
 #include <string>
 #include <vector>
 
+#include "tcpxb/cu_driver.h"
+#include "tcpxb/gpu.h"
 #include "tcpxb/rxdm.h"
 
 using namespace tcpxb;
@@ -34,12 +41,18 @@ volatile sig_atomic_t g_stop = 0;
 void onSignal(int) { g_stop = 1; }
 
 struct Rule { RxdmFlowRule r; int owner_fd; };
-struct Pool { int fd; uint64_t size; };
+struct Pool {
+  int fd = -1;
+  uint64_t size = 0, align = 4096;
+  int kind = kRxdmPoolHost;
+  cu::SharedAllocation dev;  // device pools: the daemon's own mapping keeps the allocation alive
+};
 
 struct State {
   std::string prefix;
   uint64_t pool_bytes = 1ull << 30;
   size_t max_rules = 65536;
+  bool device_pool = false;
   std::vector<Rule> rules;
   std::map<int, int> apps;  // connection fd -> pid
   std::map<std::string, Pool> pools;
@@ -74,12 +87,30 @@ RxdmMessage reply(int status, const char* text, uint64_t a = 0, uint64_t b = 0, 
 Pool* poolFor(State* st, const std::string& pci) {
   auto it = st->pools.find(pci);
   if (it != st->pools.end()) return &it->second;
-  std::string name = "tcpxb-rxpool-" + pci;
-  int fd = memfd_create(name.c_str(), 0);
-  if (fd < 0) return nullptr;
-  if (ftruncate(fd, (off_t)st->pool_bytes) != 0) { close(fd); return nullptr; }
-  st->pools[pci] = Pool{fd, st->pool_bytes};
-  fprintf(stderr, "[rxdm] pool for GPU %s: %lu MiB\n", pci.c_str(), (unsigned long)(st->pool_bytes >> 20));
+  Pool p;
+  if (st->device_pool) {
+    // the GPU whose PCI address the client named
+    int dev = -1;
+    for (int d = 0; d < gpu::deviceCount(); ++d)
+      if (gpu::pciBusId(d) == pci) dev = d;
+    if (dev < 0) { fprintf(stderr, "[rxdm] no GPU with PCI address %s\n", pci.c_str()); return nullptr; }
+    if (cu::deviceInit(dev) != kSuccess || cu::sharedCreate(dev, st->pool_bytes, &p.dev, &p.fd) != kSuccess) {
+      fprintf(stderr, "[rxdm] device pool on GPU %s failed: %s\n", pci.c_str(), cu::lastError());
+      return nullptr;
+    }
+    p.size = p.dev.bytes;
+    p.align = cu::sharedGranularity(dev);
+    p.kind = kRxdmPoolDevice;
+  } else {
+    std::string name = "tcpxb-rxpool-" + pci;
+    p.fd = memfd_create(name.c_str(), 0);
+    if (p.fd < 0) return nullptr;
+    if (ftruncate(p.fd, (off_t)st->pool_bytes) != 0) { close(p.fd); return nullptr; }
+    p.size = st->pool_bytes;
+  }
+  fprintf(stderr, "[rxdm] pool for GPU %s: %lu MiB of %s memory\n", pci.c_str(), (unsigned long)(p.size >> 20),
+          p.kind == kRxdmPoolDevice ? "device" : "host");
+  st->pools[pci] = p;
   return &st->pools[pci];
 }
 
@@ -116,8 +147,8 @@ bool serve(State* st, UnixSocketConnection* c, const std::string& service) {
       m.gpu.gpu_pci[sizeof m.gpu.gpu_pci - 1] = 0;
       Pool* p = poolFor(st, m.gpu.gpu_pci);
       if (p == nullptr) { c->send(reply(13, "pool creation failed")); return false; }
-      if (m.type == kRxdmGetGpuFd) c->send(reply(0, "Ok.", p->size, 4096), p->fd);
-      else c->send(reply(0, "Ok.", p->size, 4096));
+      if (m.type == kRxdmGetGpuFd) c->send(reply(0, "Ok.", p->size, p->align, (uint64_t)p->kind), p->fd);
+      else c->send(reply(0, "Ok.", p->size, p->align, (uint64_t)p->kind));
       return false;
     }
     case kRxdmAppRegister: {
@@ -150,13 +181,14 @@ int main(int argc, char** argv) {
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
     if (a == "--help" || a == "-h") {
-      printf("usage: tcpxb_rxdm [--prefix DIR] [--pool-mb N] [--max-rules N]\n"
+      printf("usage: tcpxb_rxdm [--prefix DIR] [--pool-mb N] [--max-rules N] [--device-pool]\n"
              "       tcpxb_rxdm --status [--prefix DIR]\n"
              "Serves the rx buffer manager's UNIX sockets under DIR (default /tmp) until SIGINT or SIGTERM;\n"
              "with --status asks a running daemon under DIR for its counters and prints one JSON line.\n");
       return 0;
     }
     if (a == "--status") { status_only = true; continue; }
+    if (a == "--device-pool") { st.device_pool = true; continue; }
     if (i + 1 >= argc) { fprintf(stderr, "%s needs a value (see --help)\n", a.c_str()); return 2; }
     const char* v = argv[++i];
     if (a == "--prefix") st.prefix = v;
@@ -230,6 +262,9 @@ int main(int argc, char** argv) {
   }
   for (auto* k : keep) delete k;
   for (size_t i = 0; i < lfds.size(); ++i) { close(lfds[i]); unlink((st.prefix + "/" + services[i]).c_str()); }
-  for (auto& p : st.pools) close(p.second.fd);
+  for (auto& p : st.pools) {
+    close(p.second.fd);
+    cu::sharedRelease(&p.second.dev);
+  }
   return 0;
 }

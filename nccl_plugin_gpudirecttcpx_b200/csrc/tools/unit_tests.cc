@@ -12,18 +12,23 @@
 #include <sys/time.h>
 #include <stdlib.h>
 #include <string.h>
+#include <linux/errqueue.h>
+#include <netinet/in.h>
 #include <sys/socket.h>
 #include <unistd.h>
 
 #include <atomic>
 #include <functional>
+#include <map>
 #include <set>
 #include <string>
 #include <thread>
 #include <vector>
 
 #include "tcpxb/ctrl_sock.h"
+#include "tcpxb/cu_driver.h"
 #include "tcpxb/dev_queue.h"
+#include "tcpxb/devmem.h"
 #include "tcpxb/flags.h"
 #include "tcpxb/flow_mapper.h"
 #include "tcpxb/rx_buf_mgr.h"
@@ -628,6 +633,337 @@ TEST(tracepoints_and_exporter) {
   setTraceConfig(TraceConfig());
   std::string cmd = std::string("rm -r ") + dir;
   EXPECT(system(cmd.c_str()) == 0);
+}
+
+
+// ------------------------------------------------------------------ devmem-TCP
+// A control buffer as recvmsg(MSG_SOCK_DEVMEM) would fill it.
+struct CmsgBuilder {
+  std::vector<char> buf;
+  struct msghdr msg;
+  size_t used = 0;
+  explicit CmsgBuilder(size_t fragments) : buf(devmem::rxControlBytes(fragments) + 64) { memset(&msg, 0, sizeof msg); }
+  void add(int type, uint64_t off, uint32_t size, uint32_t token, uint32_t dmabuf = 1) {
+    devmem::DmabufCmsg f = {off, size, token, dmabuf, 0};
+    msg.msg_control = buf.data();
+    msg.msg_controllen = used + CMSG_SPACE(sizeof f);
+    struct cmsghdr* cm = reinterpret_cast<struct cmsghdr*>(buf.data() + used);
+    cm->cmsg_level = SOL_SOCKET;
+    cm->cmsg_type = type;
+    cm->cmsg_len = CMSG_LEN(sizeof f);
+    memcpy(CMSG_DATA(cm), &f, sizeof f);
+    used += CMSG_SPACE(sizeof f);
+  }
+};
+
+TEST(devmem_recv_fragments_become_records_and_token_runs) {
+  CmsgBuilder b(8);
+  const uint64_t offs[5] = {81920, 4096, 1 << 20, 12288, 40960};
+  const uint32_t toks[5] = {7, 8, 9, 20, 21};
+  for (int i = 0; i < 5; ++i) b.add(devmem::kSoDevmemDmabuf, offs[i], i == 4 ? 1000 : 4096, toks[i]);
+  LoadMeta rec[16];
+  std::vector<devmem::DmabufToken> runs;
+  devmem::RxSink sink;
+  sink.records = rec; sink.capacity = 16; sink.tokens = &runs; sink.pool_bytes = 8 << 20; sink.dmabuf_id = 1;
+  EXPECT(devmem::parseRecv(&b.msg, 4 * 4096 + 1000, 1 << 16, &sink) == kSuccess);
+  EXPECT(sink.filled == 5);
+  for (int i = 0; i < 5; ++i) {
+    EXPECT(rec[i].src_off == offs[i] && rec[i].len == (i == 4 ? 1000u : 4096u));
+    EXPECT(rec[i].dst_off == (1u << 16) + (uint64_t)i * 4096);
+  }
+  EXPECT(runs.size() == 2 && runs[0].token_start == 7 && runs[0].token_count == 3 && runs[1].token_start == 20 && runs[1].token_count == 2);
+  // a second recvmsg of the same message appends, and its first token extends the last run
+  CmsgBuilder c(2);
+  c.add(devmem::kSoDevmemDmabuf, 8192, 4096, 22);
+  EXPECT(devmem::parseRecv(&c.msg, 4096, (1 << 16) + 4 * 4096 + 1000, &sink) == kSuccess);
+  EXPECT(sink.filled == 6 && runs.size() == 2 && runs[1].token_count == 3);
+}
+
+TEST(devmem_recv_refuses_what_the_scatter_list_cannot_describe) {
+  LoadMeta rec[4];
+  std::vector<devmem::DmabufToken> runs;
+  auto freshSink = [&] {
+    devmem::RxSink s;
+    s.records = rec; s.capacity = 4; s.tokens = &runs; s.pool_bytes = 1 << 20; s.dmabuf_id = 1;
+    runs.clear();
+    return s;
+  };
+  {  // payload in the host linear buffer: the flow missed the devmem queue
+    CmsgBuilder b(3);
+    b.add(devmem::kSoDevmemDmabuf, 0, 4096, 1);
+    b.add(devmem::kSoDevmemLinear, 0, 512, 0);
+    b.add(devmem::kSoDevmemDmabuf, 4096, 4096, 2);
+    devmem::RxSink s = freshSink();
+    EXPECT(devmem::parseRecv(&b.msg, 8192 + 512, 0, &s) == kInternalError);
+    EXPECT(runs.size() == 1 && runs[0].token_count == 2);  // both tokens can still be handed back
+  }
+  {  // an empty linear record is harmless (the kernel emits one for a header-only skb)
+    CmsgBuilder b(2);
+    b.add(devmem::kSoDevmemLinear, 0, 0, 0);
+    b.add(devmem::kSoDevmemDmabuf, 0, 100, 1);
+    devmem::RxSink s = freshSink();
+    EXPECT(devmem::parseRecv(&b.msg, 100, 0, &s) == kSuccess && s.filled == 1);
+  }
+  {  // a fragment longer than a page is cut into page-sized records under one token
+    CmsgBuilder b(1);
+    b.add(devmem::kSoDevmemDmabuf, 65536, 10000, 5);
+    devmem::RxSink s = freshSink();
+    EXPECT(devmem::parseRecv(&b.msg, 10000, 300, &s) == kSuccess && s.filled == 3);
+    EXPECT(rec[0].len == 4096 && rec[1].len == 4096 && rec[2].len == 10000 - 8192);
+    EXPECT(rec[2].src_off == 65536 + 8192 && rec[2].dst_off == 300 + 8192 && runs.size() == 1 && runs[0].token_count == 1);
+  }
+  {  // more fragments than the list holds
+    CmsgBuilder b(6);
+    for (uint32_t i = 0; i < 6; ++i) b.add(devmem::kSoDevmemDmabuf, i * 4096, 4096, i);
+    devmem::RxSink s = freshSink();
+    EXPECT(devmem::parseRecv(&b.msg, 6 * 4096, 0, &s) == kInternalError);
+    EXPECT(runs.size() == 1 && runs[0].token_count == 6);
+  }
+  {  // truncated control buffer, fragments that do not add up, a fragment outside the pool, a foreign dma-buf
+    CmsgBuilder b(1);
+    b.add(devmem::kSoDevmemDmabuf, 0, 4096, 1);
+    devmem::RxSink s = freshSink();
+    b.msg.msg_flags = MSG_CTRUNC;
+    EXPECT(devmem::parseRecv(&b.msg, 4096, 0, &s) == kInternalError);
+    b.msg.msg_flags = 0;
+    s = freshSink();
+    EXPECT(devmem::parseRecv(&b.msg, 5000, 0, &s) == kInternalError);
+    CmsgBuilder o(1);
+    o.add(devmem::kSoDevmemDmabuf, (1 << 20) - 100, 4096, 1);
+    s = freshSink();
+    EXPECT(devmem::parseRecv(&o.msg, 4096, 0, &s) == kInternalError);
+    CmsgBuilder f(1);
+    f.add(devmem::kSoDevmemDmabuf, 0, 4096, 1, /*dmabuf=*/9);
+    s = freshSink();
+    EXPECT(devmem::parseRecv(&f.msg, 4096, 0, &s) == kInternalError);
+    struct msghdr none;
+    memset(&none, 0, sizeof none);
+    s = freshSink();
+    EXPECT(devmem::parseRecv(&none, 4096, 0, &s) == kInternalError);  // bytes without any fragment record
+  }
+  {  // the scatter-list slot of a request holds 2048 records: fragment 2049 is refused
+    std::vector<LoadMeta> big(kUnpackMaxSlicePages);
+    CmsgBuilder b(kUnpackMaxSlicePages + 1);
+    for (uint32_t i = 0; i <= (uint32_t)kUnpackMaxSlicePages; ++i) b.add(devmem::kSoDevmemDmabuf, (uint64_t)i * 2048, 2048, i);
+    devmem::RxSink s;
+    s.records = big.data(); s.capacity = big.size(); s.tokens = &runs; s.pool_bytes = 16 << 20;
+    runs.clear();
+    EXPECT(devmem::parseRecv(&b.msg, (kUnpackMaxSlicePages + 1) * 2048, 0, &s) == kInternalError && s.filled == big.size());
+  }
+}
+
+std::vector<std::pair<int, size_t>> g_dontneed_calls;  // (fd, runs) per setsockopt
+int g_dontneed_fail_at = -1;
+int fakeDontneed(int fd, int level, int optname, const void* val, socklen_t len) {
+  if (level != SOL_SOCKET || optname != devmem::kSoDevmemDontneed || val == nullptr || len % sizeof(devmem::DmabufToken)) { errno = EINVAL; return -1; }
+  if ((int)g_dontneed_calls.size() == g_dontneed_fail_at) { errno = ENOMEM; return -1; }
+  g_dontneed_calls.push_back({fd, len / sizeof(devmem::DmabufToken)});
+  return 0;
+}
+
+TEST(devmem_tokens_go_back_in_batches) {
+  devmem::SocketOps ops = devmem::systemOps();
+  ops.setsockopt = fakeDontneed;
+  std::vector<devmem::DmabufToken> runs;
+  for (uint32_t i = 0; i < 300; ++i) runs.push_back({i * 10, 3});
+  g_dontneed_calls.clear();
+  g_dontneed_fail_at = -1;
+  size_t calls = 0;
+  EXPECT(devmem::recycle(ops, 42, &runs, &calls) == kSuccess && runs.empty() && calls == 3);
+  EXPECT(g_dontneed_calls.size() == 3 && g_dontneed_calls[0].second == 128 && g_dontneed_calls[1].second == 128 && g_dontneed_calls[2].second == 44);
+  EXPECT(g_dontneed_calls[0].first == 42);
+  // a failing call keeps what was not handed back yet
+  for (uint32_t i = 0; i < 200; ++i) runs.push_back({i * 10, 1});
+  g_dontneed_calls.clear();
+  g_dontneed_fail_at = 1;
+  EXPECT(devmem::recycle(ops, 42, &runs, nullptr) == kSystemError && runs.size() == 72 && runs[0].token_start == 1280);
+  g_dontneed_fail_at = -1;
+}
+
+TEST(devmem_send_message_and_completion_accounting) {
+  devmem::TxMessage m;
+  devmem::buildSend(&m, 77, (5ull << 30) + 12345, 262144);
+  EXPECT(m.msg.msg_iovlen == 1 && (uintptr_t)m.iov.iov_base == (5ull << 30) + 12345 && m.iov.iov_len == 262144);
+  struct cmsghdr* cm = CMSG_FIRSTHDR(&m.msg);
+  uint32_t id = 0;
+  memcpy(&id, CMSG_DATA(cm), 4);
+  EXPECT(cm->cmsg_level == SOL_SOCKET && cm->cmsg_type == devmem::kSoDevmemDmabuf && id == 77 && CMSG_NXTHDR(&m.msg, cm) == nullptr);
+  // an error-queue notice as the kernel writes it: inclusive range in ee_info .. ee_data
+  char control[CMSG_SPACE(sizeof(struct sock_extended_err))];
+  memset(control, 0, sizeof control);
+  struct msghdr em;
+  memset(&em, 0, sizeof em);
+  em.msg_control = control;
+  em.msg_controllen = sizeof control;
+  struct cmsghdr* ec = CMSG_FIRSTHDR(&em);
+  ec->cmsg_level = SOL_IP;
+  ec->cmsg_type = IP_RECVERR;
+  ec->cmsg_len = CMSG_LEN(sizeof(struct sock_extended_err));
+  struct sock_extended_err ee;
+  memset(&ee, 0, sizeof ee);
+  ee.ee_origin = 5;  // SO_EE_ORIGIN_ZEROCOPY
+  ee.ee_info = 10;
+  ee.ee_data = 14;
+  memcpy(CMSG_DATA(ec), &ee, sizeof ee);
+  uint32_t lo = 0, hi = 0;
+  EXPECT(devmem::parseZerocopyNotice(&em, &lo, &hi) && lo == 10 && hi == 15);
+  ee.ee_origin = 2;  // an ICMP error, not a completion
+  memcpy(CMSG_DATA(ec), &ee, sizeof ee);
+  EXPECT(!devmem::parseZerocopyNotice(&em, &lo, &hi));
+  // completions: out of order, overlapping, across the 2^32 wrap
+  devmem::TxCompletions tc;
+  for (int i = 0; i < 10; ++i) EXPECT(tc.onSend() == (uint32_t)i);
+  tc.onNotice(3, 6);
+  EXPECT(tc.done() == 0 && !tc.completed(0, 1) && tc.outstanding() == 10);
+  tc.onNotice(0, 3);
+  EXPECT(tc.done() == 6 && tc.completed(0, 6) && !tc.completed(5, 2));
+  tc.onNotice(4, 8);  // overlaps what is done
+  EXPECT(tc.done() == 8 && tc.outstanding() == 2);
+  // across the 2^32 wrap of the per-socket sequence numbers
+  devmem::TxCompletions w(0xfffffffdu);
+  uint32_t ids[6];
+  for (int i = 0; i < 6; ++i) ids[i] = w.onSend();
+  EXPECT(ids[0] == 0xfffffffdu && ids[3] == 0 && ids[5] == 2);
+  w.onNotice(0xffffffffu, 2);            // ids 2^32 - 1, 0, 1: ahead of the frontier
+  EXPECT(!w.completed(ids[0], 1) && w.outstanding() == 6);
+  w.onNotice(0xfffffffdu, 0xffffffffu);  // the two before them
+  EXPECT(w.completed(ids[0], 5) && !w.completed(ids[0], 6) && w.done() == 2 && w.outstanding() == 1);
+}
+
+// A model of a devmem socket for the receive loop: bytes come from a real socket, land in
+// a "pool" at shuffled pages, and are reported as fragment records with tokens.
+struct DevmemModel {
+  std::vector<uint8_t> pool;
+  std::vector<uint32_t> free_pages;
+  std::map<uint32_t, uint32_t> live;  // token -> page
+  uint32_t next_token = 100;
+  std::vector<uint8_t> bounce;
+} *g_model = nullptr;
+
+ssize_t modelRecvmsg(int fd, struct msghdr* msg, int flags) {
+  if (!(flags & devmem::kMsgSockDevmem)) { errno = EINVAL; return -1; }
+  DevmemModel& m = *g_model;
+  const size_t room = msg->msg_controllen / CMSG_SPACE(sizeof(devmem::DmabufCmsg));
+  size_t want = std::min<size_t>(msg->msg_iov[0].iov_len, room * 4096);
+  want = std::min<size_t>(want, m.free_pages.size() * 4096);
+  if (want == 0) { errno = ENOBUFS; return -1; }
+  m.bounce.resize(want);
+  const ssize_t n = recv(fd, m.bounce.data(), want, MSG_DONTWAIT);
+  if (n <= 0) return n;
+  size_t used = 0;
+  char* c = static_cast<char*>(msg->msg_control);
+  for (size_t off = 0; off < (size_t)n; off += 4096) {
+    const uint32_t len = (uint32_t)std::min<size_t>(4096, (size_t)n - off);
+    const uint32_t page = m.free_pages.back();
+    m.free_pages.pop_back();
+    memcpy(m.pool.data() + (size_t)page * 4096, m.bounce.data() + off, len);
+    const uint32_t tok = m.next_token++;
+    m.live[tok] = page;
+    devmem::DmabufCmsg f = {(uint64_t)page * 4096, len, tok, 1, 0};
+    struct cmsghdr* cm = reinterpret_cast<struct cmsghdr*>(c + used);
+    cm->cmsg_level = SOL_SOCKET;
+    cm->cmsg_type = devmem::kSoDevmemDmabuf;
+    cm->cmsg_len = CMSG_LEN(sizeof f);
+    memcpy(CMSG_DATA(cm), &f, sizeof f);
+    used += CMSG_SPACE(sizeof f);
+  }
+  msg->msg_controllen = used;
+  msg->msg_flags = 0;
+  return n;
+}
+int modelSetsockopt(int, int level, int optname, const void* val, socklen_t len) {
+  if (level != SOL_SOCKET || optname != devmem::kSoDevmemDontneed) { errno = EINVAL; return -1; }
+  const devmem::DmabufToken* t = static_cast<const devmem::DmabufToken*>(val);
+  for (size_t i = 0; i < len / sizeof *t; ++i)
+    for (uint32_t k = 0; k < t[i].token_count; ++k) {
+      auto it = g_model->live.find(t[i].token_start + k);
+      if (it == g_model->live.end()) { errno = EINVAL; return -1; }
+      g_model->free_pages.push_back(it->second);
+      g_model->live.erase(it);
+    }
+  return 0;
+}
+
+TEST(devmem_receive_loop_against_a_kernel_model) {
+  int sv[2];
+  EXPECT(socketpair(AF_UNIX, SOCK_STREAM, 0, sv) == 0);
+  DevmemModel model;
+  const uint32_t pages = 512;
+  model.pool.assign((size_t)pages * 4096, 0xEE);
+  for (uint32_t p = 0; p < pages; ++p) model.free_pages.push_back((p * 197) % pages);  // 197 is coprime to 512: a permutation
+  g_model = &model;
+  devmem::SocketOps ops = {modelRecvmsg, nullptr, modelSetsockopt};
+  const size_t total = 1000000;  // not a multiple of the page size
+  std::vector<uint8_t> src(total), dst(total, 0);
+  for (size_t i = 0; i < total; ++i) src[i] = (uint8_t)(i * 2654435761u >> 13);
+  std::thread sender([&] {
+    size_t sent = 0;
+    while (sent < total) {
+      ssize_t n = send(sv[0], src.data() + sent, std::min<size_t>(70000, total - sent), 0);
+      if (n <= 0) break;
+      sent += (size_t)n;
+    }
+  });
+  std::vector<LoadMeta> rec(kUnpackMaxSlicePages);
+  std::vector<devmem::DmabufToken> runs;
+  devmem::RxSink sink;
+  sink.records = rec.data(); sink.capacity = rec.size(); sink.tokens = &runs; sink.pool_bytes = model.pool.size(); sink.dmabuf_id = 1;
+  std::vector<char> control(devmem::rxControlBytes(64));
+  size_t got = 0;
+  bool ok = true;
+  while (got < total && ok) {
+    const ssize_t n = devmem::recvInto(ops, sv[1], total - got, control.data(), control.size(), got, &sink);
+    if (n == -EAGAIN) { usleep(100); continue; }
+    if (n <= 0) { ok = false; break; }
+    got += (size_t)n;
+  }
+  sender.join();
+  EXPECT(ok && got == total);
+  // what a consumer does with the list: copy every record out of the pool
+  uint64_t covered = 0;
+  for (uint64_t i = 0; i < sink.filled; ++i) {
+    memcpy(dst.data() + rec[i].dst_off, model.pool.data() + rec[i].src_off, rec[i].len);
+    covered += rec[i].len;
+  }
+  EXPECT(covered == total && dst == src);
+  EXPECT(runs.size() == 1 && runs[0].token_count == sink.filled);  // one flow: consecutive tokens, one run
+  EXPECT(model.live.size() == sink.filled);
+  EXPECT(devmem::recycle(ops, sv[1], &runs) == kSuccess && model.live.empty() && model.free_pages.size() == pages);
+  g_model = nullptr;
+  close(sv[0]);
+  close(sv[1]);
+}
+
+// ------------------------------------------------- driver-API services (stand-in device)
+TEST(shared_device_allocation_and_dmabuf_export_on_standin_device) {
+  if (!cu::available()) { printf("  skipped: no device (set TCPXB_FAKE_GPU=1)\n"); return; }
+  EXPECT(cu::deviceInit(0) == kSuccess);
+  cu::SharedAllocation owner, client;
+  int fd = -1;
+  EXPECT(cu::sharedCreate(0, 3 << 20, &owner, &fd) == kSuccess && fd >= 0);
+  EXPECT(owner.bytes % cu::sharedGranularity(0) == 0 && owner.bytes >= (3u << 20) && !owner.imported);
+  EXPECT(cu::sharedImport(0, fd, owner.bytes, &client) == kSuccess && client.imported);
+  close(fd);
+  // the two mappings are the same memory
+  memset(owner.dptr, 0x5a, 4096);
+  EXPECT(static_cast<uint8_t*>(client.dptr)[4095] == 0x5a);
+  static_cast<uint8_t*>(client.dptr)[8192] = 0x33;
+  EXPECT(static_cast<uint8_t*>(owner.dptr)[8192] == 0x33);
+  // a dma-buf of a range inside the allocation: a descriptor plus the range's offset
+  int dfd = -1;
+  uint64_t off = 0;
+  EXPECT(cu::exportDmabuf(static_cast<uint8_t*>(client.dptr) + 12288, 65536, &dfd, &off) == kSuccess && dfd >= 0 && off == 12288);
+  if (dfd >= 0) close(dfd);
+  EXPECT(cu::exportDmabuf(static_cast<uint8_t*>(client.dptr) + client.bytes - 100, 4096, &dfd, &off) != kSuccess);  // leaves the allocation
+  int stack_var = 0;
+  EXPECT(cu::exportDmabuf(&stack_var, 4, &dfd, &off) != kSuccess);
+  {
+    cu::ScopedContext ctx(0);
+    EXPECT(ctx.ok());
+  }
+  cu::sharedRelease(&client);
+  cu::sharedRelease(&owner);
+  EXPECT(owner.dptr == nullptr && client.dptr == nullptr);
 }
 
 TEST(result_strings_and_handle_layout) {

@@ -37,7 +37,8 @@ class EngineStats(ctypes.Structure):
                 ("seconds_net_wait", ctypes.c_double)] + [
                     (n, ctypes.c_double) for n in ("t_post_recv", "t_post_send", "t_test_recv", "t_launch",
                                                    "t_consume", "t_test_send", "t_idle", "t_sleep")] + [
-                                                       ("sleeps", ctypes.c_uint64)]
+                                                       ("sleeps", ctypes.c_uint64)] + [
+                                                           (n, ctypes.c_double) for n in ("tx_idle", "tx_blocked", "rx_idle", "rx_blocked")]
 
 
 _lib = None

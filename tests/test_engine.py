@@ -86,16 +86,21 @@ def test_plain_mode_matches_fused():
         e.close()
 
 
-def test_engine_with_pool_from_the_rx_buffer_manager_daemon(tmp_path):
-    """Same path, but the rx page pool comes from the tcpxb_rxdm daemon over a UNIX socket."""
+@pytest.mark.parametrize("pool", ["host", "device"])
+def test_engine_with_pool_from_the_rx_buffer_manager_daemon(tmp_path, pool):
+    """Same path, but the rx page pool comes from the rx buffer manager daemon over a UNIX socket:
+    host memory as a memfd, or GPU memory the daemon allocated with the driver's virtual memory API,
+    exported as a file descriptor and imported here (RX_POOL_MODE=device RX_BUF_MGR=daemon)."""
     import subprocess
     import sys
     from pathlib import Path
     from nccl_plugin_gpudirecttcpx_b200 import _build
     _build.build_host()
     prefix = tmp_path / "rxdm"
-    daemon = subprocess.Popen([str(_build.OUT / "tcpxb_rxdm"), "--prefix", str(prefix), "--pool-mb", "64"],
-                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    cmd = [str(_build.OUT / "tcpxb_rxdm"), "--prefix", str(prefix), "--pool-mb", "64"]
+    if pool == "device":
+        cmd = [str(_build.OUT / "tcpxb_rxdm_gpu"), "--prefix", str(prefix), "--pool-mb", "64", "--device-pool"]
+    daemon = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
     try:
         assert daemon.stdout.readline().strip() == "ready"
         env = dict(os.environ, NCCL_GPUDIRECTTCPX_RX_BUF_MGR="daemon", NCCL_GPUDIRECTTCPX_UNIX_CLIENT_PREFIX=str(prefix),
@@ -110,4 +115,4 @@ def test_engine_with_pool_from_the_rx_buffer_manager_daemon(tmp_path):
         except subprocess.TimeoutExpired:
             daemon.kill()
     err = daemon.stderr.read()
-    assert "pool for GPU" in err
+    assert "pool for GPU" in err and f"of {pool} memory" in err

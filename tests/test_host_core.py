@@ -356,12 +356,17 @@ def test_rx_buffer_manager_daemon(host_lib, tmp_path):
     assert "application 4242 went away" in daemon.stderr.read()
 
 
+@pytest.mark.parametrize("pool", ["host", "device"])
 @pytest.mark.parametrize("mode", ["unpack", "host"])
-def test_daemon_pool_carries_device_receives_on_standin_device(host_lib, tmp_path, mode):
+def test_daemon_pool_carries_device_receives_on_standin_device(host_lib, tmp_path, mode, pool):
     """Receives into device memory land in the pool that the daemon owns and hands over as a file
-    descriptor."""
+    descriptor: a memfd of host memory, or (--device-pool) a shareable handle of device memory that
+    the client imports and maps, with payload placed by the copy engine from a pinned mirror
+    (reference: src/gpu/rx_pool.cu:62-124, src/gpu/common.cu:25-65)."""
     prefix = tmp_path / "rxdm"
-    daemon = subprocess.Popen([str(LIB / "tcpxb_rxdm"), "--prefix", str(prefix), "--pool-mb", "32"],
+    daemon = subprocess.Popen([str(LIB / "tcpxb_rxdm"), "--prefix", str(prefix), "--pool-mb", "32"] +
+                              (["--device-pool"] if pool == "device" else []),
+                              env=dict(os.environ, TCPXB_FAKE_GPU="1"),
                               stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
     try:
         assert daemon.stdout.readline().strip() == "ready"
@@ -382,7 +387,7 @@ def test_daemon_pool_carries_device_receives_on_standin_device(host_lib, tmp_pat
         except subprocess.TimeoutExpired:
             daemon.kill()
     log = daemon.stderr.read()
-    assert "pool for GPU 0000:00:00.0: 32 MiB" in log, log[-2000:]  # the pool came from the daemon
+    assert f"pool for GPU 0000:00:00.0: 32 MiB of {pool} memory" in log, log[-2000:]  # the pool came from the daemon
 
 
 @pytest.mark.parametrize("san", ["", "address"])
