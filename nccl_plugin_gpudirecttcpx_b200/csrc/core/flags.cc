@@ -38,7 +38,7 @@ const IntSpec kInts[] = {
     {kGen, "THREAD_SPIN_ENABLE", &Flags::thread_spin, 0, 2, "helper threads never sleep"},
     {kGen, "SCATTER_COPY_MIN_MESSAGE_SIZE", &Flags::scatter_copy_min, 0, kMax, "accepted for compatibility, unused"},
     {kGen, "STAGING_BUFFER_SIZE", &Flags::staging_buffer_size, 0, kMax, "accepted for compatibility, unused"},
-    {kGen, "USE_DMA_BUF", &Flags::use_dma_buf, 0, 2, "accepted for compatibility"},
+    {kGen, "USE_DMA_BUF", &Flags::use_dma_buf, 0, 2, "devmem datapath: export registered CUDA buffers as dma-bufs for zero-copy transmit"},
     {kOwn, "SOCKET_ENABLE", &Flags::enable, 0, 2, "0 makes init fail so NCCL falls back"},
     {kOwn, "PORT_BEGIN", &Flags::port_begin, -2, 65536, "accepted for compatibility, unused"},
     {kOwn, "PORT_END", &Flags::port_end, -2, 65536, "accepted for compatibility, unused"},
@@ -60,13 +60,13 @@ const IntSpec kInts[] = {
     {kOwn, "TELEMETRY_FILE_LIFE", &Flags::file_life_min, 0, kMax, "remove event logs older than this many minutes (0 = keep)"},
     {kOwn, "TELEMETRY_FILE_REMOVE_FREQUENCY", &Flags::file_remove_frequency_s, 1, kMax, "seconds between garbage-collector passes"},
     {kOwn, "REPORT_LIFECYCLE", &Flags::report_lifecycle, 0, 2, "register the process with the rx buffer manager"},
-    {kOwn, "CUDA_USE_PRIMARY_CTX", &Flags::cuda_use_primary_ctx, 0, 2, "use the device's primary context"},
+    {kOwn, "CUDA_USE_PRIMARY_CTX", &Flags::cuda_use_primary_ctx, 0, 2, "driver-API services use the device's primary context (0: a context of the library's own, for the buffer manager daemon)"},
     {kOwn, "NIC_N_RXQS", &Flags::nic_n_rxqs, 1, 4096, "receive queues per NIC assumed by the queue-balance bookkeeping"},
     {kOwn, "FLOW_STEERING_STRATEGY", &Flags::flow_steering_strategy, 0, 4, "3 = rules through the rx buffer manager"},
     {kOwn, "PROGRAM_FLOW_STEERING_WAIT_MICROS", &Flags::flow_steering_wait_us, 0, kMax, "receiver pause after accept"},
     {"NCCL_TCPX_", "RXMEM_IMPORT_USE_GPU_PCI_CLIENT", &Flags::rxmem_import_use_gpu_pci_client, 0, 2, "accepted for compatibility"},
     {"NCCL_TCPX_", "RXMEM_IMPORT_SKIP_ODDS", &Flags::rxmem_import_skip_odds, 0, 2, "accepted for compatibility"},
-    {kOwn, "REG_DMABUF_USE_INTERNAL_API", &Flags::reg_dmabuf_use_internal_api, 0, 2, "accepted for compatibility"},
+    {kOwn, "REG_DMABUF_USE_INTERNAL_API", &Flags::reg_dmabuf_use_internal_api, 0, 2, "1 asks for the driver's procfs dma-buf interface, which is not offered: the CUDA export call is used"},
     {kOwn, "WORKER_PIN_THREADS", &Flags::worker_pin_threads, 0, 2, "pin every helper thread to one core"},
     {kOwn, "WORKER_SPRAY_COUNT", &Flags::worker_spray_count, 1, 4096, "helper placement: candidates per thread"},
     {kOwn, "WORKER_SPRAY_STRIDE", &Flags::worker_spray_stride, 0, 4096, "helper placement: stride between comms"},
@@ -101,7 +101,7 @@ const StrSpec kStrs[] = {
     {"", "NET_COMM_ID", &Flags::net_comm_id, "subnet hint for interface auto-selection"},
     {kOwn, "RX_POOL_MODE", &Flags::rx_pool_mode_name, "host (pinned, device-mapped) or device (copy-engine placement)"},
     {kOwn, "RECV_MODE", &Flags::recv_mode_name, "host (plugin unpacks) or unpack (NCCL's kernels unpack)"},
-    {kOwn, "RX_BUF_MGR", &Flags::rx_buf_mgr_name, "emulated (in process) or daemon (tcpxb_rxdm under UNIX_CLIENT_PREFIX)"},
+    {kOwn, "RX_BUF_MGR", &Flags::rx_buf_mgr_name, "emulated (in process), daemon (tcpxb_rxdm under UNIX_CLIENT_PREFIX) or devmem (kernel devmem-TCP sockets, pool from the daemon)"},
 };
 
 std::string envName(const char* prefix, const char* name) { return std::string(prefix) + name; }
@@ -198,7 +198,9 @@ void loadFlags(Flags* out) {
       out->recv_mode_fell_back = true;
     }
   }
-  out->rx_buf_mgr_daemon = !strcasecmp(out->rx_buf_mgr_name.c_str(), "daemon");
+  out->rx_buf_mgr_devmem = !strcasecmp(out->rx_buf_mgr_name.c_str(), "devmem");
+  // the devmem datapath takes its pool (bound to the NIC's queues) from the daemon as well
+  out->rx_buf_mgr_daemon = out->rx_buf_mgr_devmem || !strcasecmp(out->rx_buf_mgr_name.c_str(), "daemon");
   if (!out->rx_buf_mgr_daemon && !out->rx_buf_mgr_name.empty() && strcasecmp(out->rx_buf_mgr_name.c_str(), "emulated"))
     WARN("unknown rx buffer manager '%s'; using the in-process one", out->rx_buf_mgr_name.c_str());
   parseSlownessList(out->slowness_switch.c_str(), out->slow_switch);

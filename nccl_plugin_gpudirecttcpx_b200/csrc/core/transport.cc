@@ -12,6 +12,7 @@
 
 #include <algorithm>
 
+#include "tcpxb/cu_driver.h"
 #include "tcpxb/kernels.h"
 
 #ifndef SO_EE_ORIGIN_ZEROCOPY
@@ -1084,12 +1085,24 @@ Result netRegMr(Comm* comm, void* data, size_t size, int type, MemHandle** out) 
     // registration happens during connection set-up, before any collective kernel
     // can be waiting on this thread: the right moment for allocations and loading
     if (comm != nullptr) TCPXB_CHECK(netPrepareCuda(comm, mh->gpu_dev));
+    if (flags().rx_buf_mgr_devmem && flags().use_dma_buf != 0) {
+      // devmem datapath: the NIC reads transmit payload from the buffer itself, through a dma-buf
+      if (flags().reg_dmabuf_use_internal_api != 0)
+        WARN("NCCL_GPUDIRECTTCPX_REG_DMABUF_USE_INTERNAL_API=1 (driver procfs interface) is not offered; using the CUDA export call");
+      Result er = cu::exportDmabuf(data, size, &mh->dmabuf_fd, &mh->dmabuf_offset);
+      if (er != kSuccess) {
+        WARN("regMr: dma-buf export of %p (+%zu) failed: %s", data, size, cu::lastError());
+        delete mh;
+        return er;
+      }
+    }
   }
   *out = mh;
   return kSuccess;
 }
 
 Result netDeregMr(Comm* /*comm*/, MemHandle* mh) {
+  if (mh != nullptr && mh->dmabuf_fd >= 0) close(mh->dmabuf_fd);
   delete mh;
   return kSuccess;
 }

@@ -93,13 +93,14 @@ struct Flags {
   int64_t poll_block_us = 200;         // helper threads block in poll() this long when every socket would block
   std::string rx_pool_mode_name;       // RX_POOL_MODE: host | device
   std::string recv_mode_name;          // RECV_MODE: host | unpack
-  std::string rx_buf_mgr_name;         // RX_BUF_MGR: emulated (in process) | daemon (tcpxb_rxdm over UNIX sockets)
+  std::string rx_buf_mgr_name;         // RX_BUF_MGR: emulated (in process) | daemon (tcpxb_rxdm over UNIX sockets) | devmem (kernel devmem-TCP)
   // --- derived
   int sched_alg = kSchedRR;
   int rx_pool_mode = kRxPoolHostMapped;
   int recv_mode = kRecvModeHost;
   bool recv_mode_fell_back = false;  // unpack was asked for without NCCL_PROTO=Simple + NCCL_ALGO=Ring
   bool rx_buf_mgr_daemon = false;
+  bool rx_buf_mgr_devmem = false;    // devmem-TCP datapath: pool from the daemon, fragments from the kernel
   bool slow_switch[kSlowKinds] = {false, false, false};
   bool slow_report[kSlowKinds] = {false, false, false};
 };

@@ -128,6 +128,13 @@ typedef struct {
 int tcpxb_comm_flow_counters(void* comm, tcpxbFlowCounters* out, int max);
 // Writes the comm's per-flow summary lines, '\n'-separated, into buf; returns the length needed.
 int tcpxb_comm_stats_text(void* comm, char* buf, int len);
+// A dma-buf file descriptor of the device range [ptr, ptr + bytes) (widened to host pages;
+// *offset_out is where ptr sits in it).  0 on success; the caller closes *fd_out.
+int tcpxb_export_dmabuf(const void* ptr, uint64_t bytes, int* fd_out, uint64_t* offset_out);
+// Creates a shareable device allocation on `dev`, exports it as a file descriptor, imports that
+// descriptor again and checks that the two mappings alias (what the buffer manager daemon and a
+// client do across processes).  0 on success.
+int tcpxb_shared_pool_selftest(int dev, uint64_t bytes);
 // Number of documented environment variables; fills env/kind/default/doc of entry i.
 int tcpxb_flag_count(void);
 int tcpxb_flag_doc(int i, const char** env, const char** kind, const char** dflt, const char** doc);

@@ -94,6 +94,11 @@ struct MemHandle {
   size_t size;
   int type;     // kPtrHost / kPtrCuda
   int gpu_dev;  // owning GPU for CUDA memory, else -1
+  // devmem datapath: the buffer exported as a dma-buf for zero-copy transmit
+  // (reference: src/gpu/tx_pool.cu:104-181); -1 when not exported
+  int dmabuf_fd = -1;
+  uint64_t dmabuf_offset = 0;  // of `ptr` inside the exported range
+  uint32_t dmabuf_id = 0;      // id the NIC binding gave the dma-buf (0 = not bound)
 };
 
 // ---- tasks: one chunk on one data socket ------------------------------------------

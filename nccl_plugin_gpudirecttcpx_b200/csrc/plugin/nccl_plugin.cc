@@ -5,11 +5,14 @@
 // and a v8 table (size_t regMr, regIsGlobal property) is added.
 #include <stdio.h>
 #include <string.h>
+#include <unistd.h>
 
 #include <map>
 #include <mutex>
 #include <string>
 
+#include "tcpxb/cu_driver.h"
+#include "tcpxb/gpu.h"
 #include "tcpxb/nccl_net_abi.h"
 #include "tcpxb/transport.h"
 
@@ -226,6 +229,32 @@ int tcpxb_comm_stats_text(void* comm, char* buf, int len) {
   for (const std::string& l : netCommStatsLines(static_cast<Comm*>(comm))) all += l + "\n";
   if (buf != nullptr && len > 0) snprintf(buf, (size_t)len, "%s", all.c_str());
   return (int)all.size() + 1;
+}
+
+int tcpxb_export_dmabuf(const void* ptr, uint64_t bytes, int* fd_out, uint64_t* offset_out) {
+  if (fd_out == nullptr || offset_out == nullptr) return -1;
+  return cu::exportDmabuf(ptr, (size_t)bytes, fd_out, offset_out) == kSuccess ? 0 : -1;
+}
+
+int tcpxb_shared_pool_selftest(int dev, uint64_t bytes) {
+  // owner and client in one process: create, export, import, and check that both mappings are the same memory
+  cu::SharedAllocation owner, client;
+  int fd = -1;
+  if (cu::deviceInit(dev) != kSuccess || cu::sharedCreate(dev, (size_t)bytes, &owner, &fd) != kSuccess) return -1;
+  int rc = -2;
+  if (cu::sharedImport(dev, fd, owner.bytes, &client) == kSuccess) {
+    const uint32_t pattern = 0x5aa5c33c;
+    uint32_t back = 0;
+    void* tail = static_cast<uint8_t*>(owner.dptr) + owner.bytes - sizeof pattern;
+    void* tail_c = static_cast<uint8_t*>(client.dptr) + owner.bytes - sizeof pattern;
+    if (gpu::copyToDeviceAsync(tail, &pattern, sizeof pattern, nullptr) == kSuccess && gpu::streamSynchronize(nullptr) == kSuccess &&
+        gpu::copyToHostAsync(&back, tail_c, sizeof back, nullptr) == kSuccess && gpu::streamSynchronize(nullptr) == kSuccess)
+      rc = back == pattern ? 0 : -3;
+    cu::sharedRelease(&client);
+  }
+  close(fd);
+  cu::sharedRelease(&owner);
+  return rc;
 }
 
 int tcpxb_flag_count(void) { return (int)flagDocs().size(); }
