@@ -97,6 +97,12 @@ void sharedRelease(SharedAllocation* a) {
   *a = SharedAllocation();
 }
 
+Result streamWriteValue32(void*, void* dev_word, uint32_t value) {
+  if (!fake()) return failed("streamWriteValue32", "no device");
+  __atomic_store_n(static_cast<uint32_t*>(dev_word), value, __ATOMIC_RELEASE);  // the stand-in's streams run everything at once
+  return kSuccess;
+}
+
 Result exportDmabuf(const void* ptr, size_t bytes, int* fd_out, uint64_t* offset_out) {
   if (!fake()) return failed("exportDmabuf", "no device");
   std::lock_guard<std::mutex> l(g_mu);
@@ -139,6 +145,7 @@ struct Api {
   CUresult (*MemAddressFree)(CUdeviceptr, size_t) = nullptr;
   CUresult (*MemRelease)(CUmemGenericAllocationHandle) = nullptr;
   CUresult (*MemGetHandleForAddressRange)(void*, CUdeviceptr, size_t, CUmemRangeHandleType, unsigned long long) = nullptr;
+  CUresult (*StreamWriteValue32)(CUstream, CUdeviceptr, cuuint32_t, unsigned int) = nullptr;
 };
 
 template <typename F>
@@ -168,6 +175,7 @@ const Api& api() {
               sym(x.lib, "cuMemAddressFree", &x.MemAddressFree) && sym(x.lib, "cuMemRelease", &x.MemRelease);
     // optional: present from CUDA 11.7 drivers on
     sym(x.lib, "cuMemGetHandleForAddressRange", &x.MemGetHandleForAddressRange);
+    sym(x.lib, "cuStreamWriteValue32_v2", &x.StreamWriteValue32);
     x.ok = ok && x.Init(0) == CUDA_SUCCESS;
     return x;
   }();
@@ -327,6 +335,14 @@ void sharedRelease(SharedAllocation* s) {
   a.MemAddressFree(va, s->bytes);
   a.MemRelease(s->handle);
   *s = SharedAllocation();
+}
+
+Result streamWriteValue32(void* stream, void* dev_word, uint32_t value) {
+  const Api& a = api();
+  if (!a.ok || a.StreamWriteValue32 == nullptr) return kInvalidUsage;
+  // default flags: the write is ordered after the memory effects of the work before it
+  return a.StreamWriteValue32(static_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(dev_word), value, 0) == CUDA_SUCCESS
+             ? kSuccess : kInvalidUsage;
 }
 
 Result exportDmabuf(const void* ptr, size_t bytes, int* fd_out, uint64_t* offset_out) {

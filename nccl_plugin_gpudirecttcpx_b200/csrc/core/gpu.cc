@@ -1,5 +1,8 @@
 #include "tcpxb/gpu.h"
 
+#include "tcpxb/cu_driver.h"
+#include "tcpxb/kernels.h"
+
 #include <ctype.h>
 #include <mutex>
 #include <stdio.h>
@@ -270,6 +273,39 @@ Result memsetAsync(void* d, int v, size_t n, Stream s) {
 }
 
 #endif
+
+
+// ---------------------------------------------------------------- StreamCounter
+StreamCounter::~StreamCounter() { hostFreeMapped(host_); }
+
+Result StreamCounter::init() {
+  if (host_ != nullptr) return kSuccess;
+  void* h = nullptr;
+  void* d = nullptr;
+  TCPXB_CHECK(hostAllocMapped(64, &h, &d));
+  memset(h, 0, 64);
+  host_ = static_cast<uint32_t*>(h);
+  dev_ = static_cast<uint32_t*>(d);
+  return kSuccess;
+}
+
+Result StreamCounter::mark(Stream s, uint32_t* value) {
+  const uint32_t v = issued_ + 1;
+  if (!use_kernel_) {
+    Result r = cu::streamWriteValue32(s, dev_, v);
+    if (r != kSuccess) use_kernel_ = true;  // no stream memory operations here: fall back for good
+  }
+  if (use_kernel_) {
+    uint32_t* flags[1] = {dev_};
+    if (tcpxb_signal_flags(flags, 1, v, s) != 0) {
+      snprintf(g_err, sizeof g_err, "stream counter: %s", tcpxb_kernel_last_error());
+      return kUnhandledCudaError;
+    }
+  }
+  issued_ = v;
+  *value = v;
+  return kSuccess;
+}
 
 }  // namespace gpu
 }  // namespace tcpxb

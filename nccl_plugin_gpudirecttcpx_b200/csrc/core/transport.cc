@@ -387,6 +387,7 @@ Result ensureCudaComm(Comm* comm, int gpu_dev) {
   TCPXB_CHECK(gpu::currentDevice(&cur));
   if (cur != gpu_dev) TCPXB_CHECK(gpu::setDevice(gpu_dev));
   TCPXB_CHECK(gpu::streamCreate(&comm->stream));
+  TCPXB_CHECK(comm->passive ? comm->unpack_marks.init() : comm->stage_marks.init());
   return kSuccess;
 }
 
@@ -418,7 +419,7 @@ Result ensureTxStage(Comm* comm) {
   if (comm->tx_stage != nullptr) return kSuccess;
   void* h = nullptr;
   void* d = nullptr;
-  comm->tx_stage_bytes = (uint64_t)flags().tx_staging_bytes;
+  if (comm->tx_stage_bytes == 0) comm->tx_stage_bytes = (uint64_t)flags().tx_staging_bytes;
   TCPXB_CHECK(gpu::hostAllocMapped(comm->tx_stage_bytes, &h, &d));
   comm->tx_stage = static_cast<uint8_t*>(h);
   return kSuccess;
@@ -467,8 +468,7 @@ Result startCudaSend(Comm* comm, Request* r, MemHandle* mh) {
     const int off = i * seg;
     const int len = std::min(seg, r->size - off);
     TCPXB_CHECK(gpu::copyToHostAsync(r->stage + off, r->data + off, (size_t)len, comm->stream));
-    if (r->seg_event[i] == nullptr) TCPXB_CHECK(gpu::eventCreate(&r->seg_event[i]));
-    TCPXB_CHECK(gpu::eventRecord(r->seg_event[i], comm->stream));
+    TCPXB_CHECK(comm->stage_marks.mark(comm->stream, &r->seg_mark[i]));
   }
   return kSuccess;
 }
@@ -477,8 +477,7 @@ Result startCudaSend(Comm* comm, Request* r, MemHandle* mh) {
 bool stagedUpTo(Request* r, int upto) {
   const int need = (upto + r->seg_bytes - 1) / r->seg_bytes;
   while (r->segs_done < need) {
-    mark(r->comm, "stagedUpTo:eventQuery");
-    if (gpu::eventQuery(r->seg_event[r->segs_done]) != kSuccess) return false;
+    if (!r->comm->stage_marks.reached(r->seg_mark[r->segs_done])) return false;
     ++r->segs_done;
   }
   return true;
@@ -589,9 +588,8 @@ Result launchUnpack(Comm* comm, Request* r) {
                                comm->unpack_status_dev, nullptr, comm->stream);
     if (rc != 0) { WARN("unpack launch failed: %s", tcpxb_kernel_last_error()); return kUnhandledCudaError; }
   }
-  mark(comm, "launchUnpack:event");
-  if (r->unpack_event == nullptr) TCPXB_CHECK(gpu::eventCreate(&r->unpack_event));
-  TCPXB_CHECK(gpu::eventRecord(r->unpack_event, comm->stream));
+  mark(comm, "launchUnpack:mark");
+  TCPXB_CHECK(comm->unpack_marks.mark(comm->stream, &r->unpack_mark));
   r->unpack_launched = true;
   return kSuccess;
 }
@@ -863,20 +861,14 @@ Result progressRound(Comm* comm) {
         std::atomic_thread_fence(std::memory_order_seq_cst);
         if (comm->rxmgr->deviceResident()) {
           if (!r->unpack_launched) {
-            if (r->unpack_event == nullptr) TCPXB_CHECK(gpu::eventCreate(&r->unpack_event));
-            TCPXB_CHECK(gpu::eventRecord(r->unpack_event, comm->stream));
+            TCPXB_CHECK(comm->unpack_marks.mark(comm->stream, &r->unpack_mark));  // behind the page placements
             r->unpack_launched = true;
           }
-          Result q = gpu::eventQuery(r->unpack_event);
-          if (q == kInProgress) break;
-          TCPXB_CHECK(q);
+          if (!comm->unpack_marks.reached(r->unpack_mark)) break;
         }
       } else {
         if (!r->unpack_launched) TCPXB_CHECK(launchUnpack(comm, r));
-        mark(comm, "finish:unpack eventQuery");
-        Result q = gpu::eventQuery(r->unpack_event);
-        if (q == kInProgress) break;
-        TCPXB_CHECK(q);
+        if (!comm->unpack_marks.reached(r->unpack_mark)) break;
         if (comm->unpack_status_host[0] != 0) {
           WARN("unpack kernel reported status %u at record %u", comm->unpack_status_host[0], comm->unpack_status_host[1]);
           return kInternalError;
@@ -950,15 +942,10 @@ Request* claimRequest(Comm* comm) {
   retireRequests(comm);
   if (!comm->rq.hasFree()) return nullptr;
   Request* r = &comm->rq.nextFree();
-  gpu::Event seg[kMaxTxSegments];
-  memcpy(seg, r->seg_event, sizeof seg);
-  gpu::Event ue = r->unpack_event;
   std::vector<PageRun> pages = std::move(r->pages);
   pages.clear();
   *r = Request();
-  memcpy(r->seg_event, seg, sizeof seg);  // events are created once per slot and reused
-  r->unpack_event = ue;
-  r->pages = std::move(pages);
+  r->pages = std::move(pages);  // keeps its capacity from one use of the slot to the next
   r->comm = comm;
   r->posted_ns = monotonicNanos();
   return r;
@@ -1054,14 +1041,6 @@ Result netPrepareCuda(Comm* comm, int gpu_dev) {
   if (gpu_dev < 0 && gpu::currentDevice(&gpu_dev) != kSuccess) return kUnhandledCudaError;
   if (comm->passive) TCPXB_CHECK(ensureCudaRecv(comm, gpu_dev, comm->recv_mode == kRecvModeUnpack && comm->want_device_handle));
   else { TCPXB_CHECK(ensureCudaComm(comm, gpu_dev)); TCPXB_CHECK(ensureTxStage(comm)); }
-  for (uint32_t i = 0; i < kMaxRequests; ++i) {
-    Request& r = comm->rq.slot(i);
-    if (comm->passive) {
-      if (r.unpack_event == nullptr) TCPXB_CHECK(gpu::eventCreate(&r.unpack_event));
-    } else {
-      for (auto& e : r.seg_event) if (e == nullptr) TCPXB_CHECK(gpu::eventCreate(&e));
-    }
-  }
   if (comm->passive && tcpxb_kernels_preload() != 0) {
     WARN("kernel preload failed: %s", tcpxb_kernel_last_error());
     return kUnhandledCudaError;
@@ -1272,6 +1251,13 @@ Result netIrecvConsumed(Comm* comm, int n, Request* r) {
 
 void netSetSendDependency(Comm* comm, gpu::Event event) { comm->send_dependency = event; }
 
+Result netSetTxStagingBytes(Comm* comm, uint64_t bytes) {
+  if (comm == nullptr || comm->passive || bytes < 4096) return kInvalidArgument;
+  if (comm->tx_stage != nullptr) return kInvalidUsage;  // already allocated
+  comm->tx_stage_bytes = bytes;
+  return kSuccess;
+}
+
 void netSetNotifier(Comm* comm, Notifier* notifier) {
   if (comm != nullptr) comm->notifier = notifier;
 }
@@ -1344,9 +1330,6 @@ void freeComm(Comm* comm) {
     r.pages.clear();
     if (comm->rxmgr != nullptr && r.pages_reserved > 0) comm->rxmgr->unreservePages(r.pages_reserved);
     r.pages_reserved = 0;
-    for (auto& e : r.seg_event) { gpu::eventDestroy(e); e = nullptr; }
-    gpu::eventDestroy(r.unpack_event);
-    r.unpack_event = nullptr;
   }
   for (int i = 0; i < kMaxSockets; ++i) {
     for (uint32_t k = 0; k < kMaxTasks; ++k) {

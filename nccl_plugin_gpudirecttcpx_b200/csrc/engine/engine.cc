@@ -90,7 +90,7 @@ struct SendSpec {
 
 struct PendingUnpack {
   Request* req;
-  gpu::Event event;
+  uint32_t mark;  // value of the engine's stream counter once the request's kernel has finished
 };
 
 struct Engine {
@@ -111,7 +111,7 @@ struct Engine {
   uint32_t* ticket = nullptr;       // fan-out completion counter (device)
   uint32_t* status_host = nullptr;  // kernel status block (pinned, device-mapped)
   uint32_t* status_dev = nullptr;
-  std::vector<gpu::Event> event_pool;
+  gpu::StreamCounter kernel_marks;  // advanced on the caller's stream behind every unpack launch
   gpu::Event dep_event = nullptr;
   tcpxbEngineStats stats;
   int req_bytes = 4 << 20, inflight = 8, ctas = 16;
@@ -154,17 +154,6 @@ int ensureScratch(Engine* e, uint64_t bytes) {
   e->scratch = static_cast<uint8_t*>(p);
   e->scratch_bytes = bytes;
   return 0;
-}
-
-gpu::Event takeEvent(Engine* e) {
-  if (!e->event_pool.empty()) {
-    gpu::Event ev = e->event_pool.back();
-    e->event_pool.pop_back();
-    return ev;
-  }
-  gpu::Event ev = nullptr;
-  gpu::eventCreate(&ev);
-  return ev;
 }
 
 // The kernels report into a pinned status block; a non-zero first word means a
@@ -327,9 +316,9 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
         const bool publish = rs.last && (launched_r + 1 == n_recv);
         lap(e->stats.t_test_recv);
         ENG_TRY(launchUnpack(e, rq[r].front(), rs, off, want, publish, stream));
-        gpu::Event ev = takeEvent(e);
-        ENG_NET(gpu::eventRecord(ev, stream));
-        uq[r].push_back({rq[r].front(), ev});
+        uint32_t done_mark = 0;
+        ENG_NET(e->kernel_marks.mark(stream, &done_mark));
+        uq[r].push_back({rq[r].front(), done_mark});
         rq[r].pop_front();
         rq_idx[r].pop_front();
         ++launched_r;
@@ -340,12 +329,9 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
       }
       lap(e->stats.t_test_recv);
       while (!uq[r].empty()) {
-        Result q = gpu::eventQuery(uq[r].front().event);
-        if (q == kInProgress) break;
-        ENG_NET(q);
+        if (!e->kernel_marks.reached(uq[r].front().mark)) break;
         ENG_TRY(checkDeviceStatus(e));
         ENG_NET(netIrecvConsumed(e->rails[r].recv, 1, uq[r].front().req));
-        e->event_pool.push_back(uq[r].front().event);
         uq[r].pop_front();
         moved = true;
       }
@@ -390,11 +376,13 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
   }
   if (armed) e->notifier.armed.store(0, std::memory_order_release);
   // pool pages go back once the kernels that read them have finished
+  bool any_left = false;
+  for (int r = 0; r < R; ++r) any_left = any_left || !uq[r].empty();
+  if (any_left) ENG_NET(gpu::streamSynchronize(stream));
   for (int r = 0; r < R; ++r) {
     while (!uq[r].empty()) {
-      ENG_NET(gpu::eventSynchronize(uq[r].front().event));
+      if (!e->kernel_marks.reached(uq[r].front().mark)) return fail("unpack completion mark missing after a stream synchronize%s", "");
       ENG_NET(netIrecvConsumed(e->rails[r].recv, 1, uq[r].front().req));
-      e->event_pool.push_back(uq[r].front().event);
       uq[r].pop_front();
     }
   }
@@ -475,7 +463,7 @@ void* tcpxb_engine_create(const tcpxbEngineConfig* cfg) {
   void* t = nullptr;
   if (gpu::hostAllocMapped(64, &h, &d) != kSuccess || gpu::deviceAlloc(64, &t) != kSuccess ||
       gpu::memsetAsync(t, 0, 64, nullptr) != kSuccess || gpu::streamSynchronize(nullptr) != kSuccess ||
-      gpu::eventCreate(&e->dep_event) != kSuccess) {
+      gpu::eventCreate(&e->dep_event) != kSuccess || e->kernel_marks.init() != kSuccess) {
     fail("engine device allocations failed: %s", gpu::lastError());
     delete e;
     return nullptr;
@@ -496,7 +484,6 @@ void tcpxb_engine_destroy(void* engine) {
     if (r.listen) netCloseListen(r.listen);
   }
   if (e->notifier.event_fd >= 0) close(e->notifier.event_fd);
-  for (gpu::Event ev : e->event_pool) gpu::eventDestroy(ev);
   gpu::eventDestroy(e->dep_event);
   gpu::deviceFree(e->scratch);
   gpu::deviceFree(e->ticket);
@@ -539,6 +526,9 @@ int tcpxb_engine_connect(void* engine, const void* next_handles) {
     sched_yield();
   }
   for (Rail& rail : e->rails) {
+    // staging no larger than what can be in flight: a small ring stays cache-resident
+    const uint64_t want = (uint64_t)(e->inflight + 1) * (uint64_t)e->req_bytes;
+    netSetTxStagingBytes(rail.send, std::min<uint64_t>(want, (uint64_t)flags().tx_staging_bytes));
     ENG_NET(netPrepareCuda(rail.send, e->cfg.gpu_dev));
     ENG_NET(netPrepareCuda(rail.recv, e->cfg.gpu_dev));
     netSetNotifier(rail.send, &e->notifier);

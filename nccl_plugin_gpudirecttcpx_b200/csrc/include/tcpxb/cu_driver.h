@@ -72,6 +72,12 @@ Result sharedCreate(int dev, size_t bytes, SharedAllocation* out, int* fd_out);
 Result sharedImport(int dev, int fd, size_t bytes, SharedAllocation* out);
 void sharedRelease(SharedAllocation* a);
 
+// ---- stream-ordered host flags -----------------------------------------------------------
+// Makes `stream` write `value` to the 32-bit word at device address `dev_word` (pinned,
+// device-mapped host memory) once everything queued before it has finished, with the
+// driver's stream memory operation.  kInvalidUsage when the driver offers none.
+Result streamWriteValue32(void* stream, void* dev_word, uint32_t value);
+
 // ---- dma-buf export ---------------------------------------------------------------------
 // A dma-buf file descriptor covering the device range [ptr, ptr + bytes): what a
 // devmem-capable NIC driver binds for zero-copy transmit.  The exported range is

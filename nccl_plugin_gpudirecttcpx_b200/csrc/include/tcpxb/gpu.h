@@ -70,6 +70,32 @@ Result copyToHostAsync(void* host_dst, const void* dev_src, size_t bytes, Stream
 Result copyToDeviceAsync(void* dev_dst, const void* host_src, size_t bytes, Stream s);
 Result memsetAsync(void* dev, int value, size_t bytes, Stream s);
 
+// A counter in pinned, device-mapped host memory that streams advance: mark() queues
+// "counter = next value" behind everything already in the stream, reached() is one plain
+// load.  It stands where a CUDA event per point would: no event to create, record or
+// query, which matters to a thread that tracks hundreds of copies and kernels per
+// millisecond.  Marks must be issued in the order in which they will complete (one
+// stream, or streams the caller orders).
+class StreamCounter {
+ public:
+  StreamCounter() = default;
+  ~StreamCounter();
+  StreamCounter(const StreamCounter&) = delete;
+  StreamCounter& operator=(const StreamCounter&) = delete;
+  Result init();
+  bool ready() const { return host_ != nullptr; }
+  // Queues the next value on `s` and returns it in *value.
+  Result mark(Stream s, uint32_t* value);
+  bool reached(uint32_t value) const { return (int32_t)(__atomic_load_n(host_, __ATOMIC_ACQUIRE) - value) >= 0; }
+  uint32_t issued() const { return issued_; }
+
+ private:
+  uint32_t* host_ = nullptr;
+  uint32_t* dev_ = nullptr;
+  uint32_t issued_ = 0;
+  bool use_kernel_ = false;  // the driver has no stream memory operation: a one-thread kernel writes instead
+};
+
 const char* lastError();
 
 }  // namespace gpu

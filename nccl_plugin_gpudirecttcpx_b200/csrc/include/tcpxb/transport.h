@@ -138,14 +138,14 @@ struct Request {
   uint8_t* stage = nullptr;
   uint64_t stage_bytes = 0;
   int seg_bytes = 0, n_segs = 0, segs_done = 0;
-  gpu::Event seg_event[kMaxTxSegments] = {};
+  uint32_t seg_mark[kMaxTxSegments] = {};  // value the comm's staging counter reaches when segment i is in host memory
   // CUDA receive
   UnpackSlot slot;
   std::vector<PageRun> pages;
   bool pages_promised = false;    // the pool promised every page this message needs
   uint32_t pages_reserved = 0;    // what is left of that promise
   bool unpack_launched = false;
-  gpu::Event unpack_event = nullptr;
+  uint32_t unpack_mark = 0;       // value the comm's unpack counter reaches when this request's kernel (or placement) is done
   uint64_t posted_ns = 0, last_stall_report_ns = 0;
   // inline transfer progress
   int inline_off = 0;
@@ -227,6 +227,9 @@ struct Comm {
   uint32_t* unpack_status_host = nullptr;
   uint32_t* unpack_status_dev = nullptr;
   gpu::Event send_dependency = nullptr;
+  // stream-ordered completion counters in mapped host memory: staging copies (send
+  // side) and unpack kernels / page placements (receive side) on `stream`
+  gpu::StreamCounter stage_marks, unpack_marks;
   bool cuda_prepared = false;
   uint32_t api_calls = 0, done_calls = 0;  // for the first-calls INFO lines
   std::atomic<const char*> where{"idle"};  // last checkpoint the API thread passed (watchdog)
@@ -289,6 +292,11 @@ Result netIrecvConsumed(Comm* comm, int n, Request* req);
 // netAccept (used by the collective engine, which unpacks with its own kernels).
 void netSetAcceptRecvMode(ListenComm* lcomm, int recv_mode);
 
+// Size of a send comm's pinned staging ring for CUDA buffers, instead of the
+// TX_STAGING_BYTES flag.  A ring just large enough for the requests in flight is walked
+// over and over and stays in the CPU's caches; a large one is always cold.  Call before
+// the comm's first CUDA send (before netPrepareCuda).
+Result netSetTxStagingBytes(Comm* comm, uint64_t bytes);
 // Completion wake-ups for a driving thread that sleeps (see Notifier); null detaches.
 // Set it while no request is in flight.
 void netSetNotifier(Comm* comm, Notifier* notifier);

@@ -23,6 +23,9 @@ def main():
     world = int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
+    G = int(os.environ.get("TCPXB_TEST_GPUS_PER_NODE", "1"))
+    if G > 1:  # emulated nodes of G GPUs: same host id inside a node, before NCCL initialises
+        os.environ["NCCL_HOSTID"] = f"tcpxb-node-{rank // G}"
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = torch.device("cuda", local)
     sizes = [int(s) for s in os.environ.get("TCPXB_TEST_SIZES", "256,65536,4194304").split(",")]
@@ -40,6 +43,7 @@ def main():
         print(f"rank {rank} repeat pattern: {pattern}", flush=True)
     ok = True
     detail = []
+    samples = []  # a few result values per case, for comparing two transports with each other
     for dtype in (torch.bfloat16, torch.float32):
         for n in sizes:
             gens = [torch.Generator().manual_seed(1000 * r + n % 997) for r in range(world)]
@@ -50,6 +54,7 @@ def main():
             err = (x.float().cpu() - want).abs().max().item()
             tol = 0.05 * world if dtype == torch.bfloat16 else 1e-4 * world
             good = err <= tol
+            samples.append([round(v, 6) for v in x.float().cpu()[:: max(1, n // 8)][:8].tolist()])
             # all_gather: exact
             outs = [torch.empty(n, dtype=dtype, device=dev) for _ in range(world)]
             dist.all_gather(outs, ins[rank].to(dev))
@@ -79,8 +84,8 @@ def main():
     t = torch.tensor([ms], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     busbw = n * 2 / (t.item() * 1e-3) * 2 * (world - 1) / world / 1e9
-    print(json.dumps({"rank": rank, "world": world, "ok": bool(ok), "allreduce_ms": t.item(), "busbw_GBps": busbw,
-                      "detail": detail}), flush=True)
+    print(json.dumps({"rank": rank, "world": world, "G": G, "ok": bool(ok), "allreduce_ms": t.item(), "busbw_GBps": busbw,
+                      "detail": detail, "samples": samples}), flush=True)
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(0 if ok else 1)

@@ -13,13 +13,16 @@ from pathlib import Path
 import pytest
 import torch
 
+from conftest import free_port
+
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 ROOT = Path(__file__).resolve().parent.parent
 NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-def _run(worker, nproc, env_extra, timeout=150, port=29531):
+def _run(worker, nproc, env_extra, timeout=150, port=None):
+    port = port or free_port()
     env = dict(os.environ)
     env.update(env_extra)
     env.setdefault("TCPXB_TEST_DUMP_AFTER", str(timeout - 20))
@@ -54,6 +57,34 @@ def test_nccl_socket_transport_gives_the_same_results():
     r, rows = _run("nccl_plugin_worker.py", 2, env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert len(rows) == 2 and all(row["ok"] for row in rows)
+
+
+@pytest.mark.parametrize("world,G", [(2, 1), (4, 1), (4, 2), (8, 1), (8, 4)])
+def test_nccl_plugin_agrees_with_the_socket_transport(world, G):
+    """The same seeded collectives through stock NCCL twice: over this plugin and over NCCL's own
+    socket transport, `world` ranks in nodes of G GPUs.  Each run is held to the fp32 oracle by the
+    worker; here the two are also held to each other (all_gather bit for bit inside the worker,
+    all_reduce samples within the rounding the differing channel layouts allow)."""
+    if NGPU < world:
+        pytest.skip(f"needs {world} GPUs")
+    from nccl_plugin_gpudirecttcpx_b200.parallel import plugin_env
+    results = {}
+    for arm in ("plugin", "socket"):
+        env = plugin_env(nics=2, nthreads=2, builtin_socket=(arm == "socket"), rx_pool_mb=256)
+        if G > 1:  # nodes by host id: NVLink inside a node, the net transport between nodes
+            env.pop("NCCL_P2P_DISABLE", None)
+            env.pop("NCCL_SHM_DISABLE", None)
+        env["TCPXB_TEST_GPUS_PER_NODE"] = str(G)
+        env["TCPXB_TEST_SIZES"] = "256,65536,1048576"
+        env["TCPXB_TEST_BW_ELEMS"] = str(1 << 20)
+        r, rows = _run("nccl_plugin_worker.py", world, env, timeout=240)
+        assert r.returncode == 0, arm + ": " + r.stdout[-2000:] + r.stderr[-3000:]
+        assert len(rows) == world and all(row["ok"] for row in rows), arm
+        results[arm] = {row["rank"]: row["samples"] for row in rows}
+    for rank in range(world):
+        for a, b in zip(results["plugin"][rank], results["socket"][rank]):
+            for va, vb in zip(a, b):
+                assert abs(va - vb) <= 0.05 * world * max(1.0, abs(vb)) * 2 ** -3, (rank, va, vb)
 
 
 @pytest.mark.parametrize("world,G", [(2, 1), (4, 1), (4, 2), (8, 4)])
