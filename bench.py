@@ -172,8 +172,31 @@ def unpack_microbench(torch, peaks, iters=20, warm=4):
         torch.cuda.synchronize()
         return ts[len(ts) // 2] * 1e-3, a.elapsed_time(b) / n_iter * 1e-3
 
-    t_copy, tb_copy = timed(lambda i: U.unpack_copy(pool, dsts[i % 3], descs[i % variants], status=st))
-    t_red, tb_red = timed(lambda i: U.unpack_reduce(pool, dsts[i % 3], descs[i % variants], status=st))
+    def graphed(fn, n_iter=iters):
+        """The same launches captured once in a CUDA graph and replayed: what the GPU needs per
+        launch when the host (here Python + ctypes, ~10 us per call) is out of the way."""
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for i in range(n_iter):
+                    fn(i)
+            g.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / n_iter * 1e-3
+        except Exception as e:  # capture is an extra, never a reason to lose the other numbers
+            sys.stderr.write(f"graph capture failed: {e}\n")
+            return None
+
+    copy_fn = lambda i: U.unpack_copy(pool, dsts[i % 3], descs[i % variants], status=st)
+    red_fn = lambda i: U.unpack_reduce(pool, dsts[i % 3], descs[i % variants], status=st)
+    t_copy, tb_copy = timed(copy_fn)
+    t_red, tb_red = timed(red_fn)
+    tg_copy, tg_red = graphed(copy_fn), graphed(red_fn)
     # fused reduce + fan-out with the three "peers" emulated by buffers on this GPU (no NVLink in
     # this number: it shows the kernel's cost of writing four copies of every reduced fragment)
     peers = [torch.empty((64 << 20) // 2, dtype=torch.bfloat16, device=dev) for _ in range(3)]
@@ -191,7 +214,9 @@ def unpack_microbench(torch, peaks, iters=20, warm=4):
 
     t_unf, tb_unf = timed(unfused)
     flat = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
-    t_ref, tb_ref = timed(lambda i: dsts[i % 3].view(torch.uint8).copy_(flat))
+    ref_fn = lambda i: dsts[i % 3].view(torch.uint8).copy_(flat)
+    t_ref, tb_ref = timed(ref_fn)
+    tg_ref = graphed(ref_fn)
     hbm = peaks.get("hbm_gbs", 6650.0)
     tag = "of measured" if "hbm_gbs" in peaks else "of fallback"
     out = {
@@ -203,6 +228,11 @@ def unpack_microbench(torch, peaks, iters=20, warm=4):
                          "unpack_reduce_us": tb_red * 1e6, "unpack_reduce_frac_hbm": 3 * total / tb_red / 1e9 / hbm,
                          "torch_copy_64MiB_us": tb_ref * 1e6, "torch_copy_64MiB_frac_hbm": 2 * (64 << 20) / tb_ref / 1e9 / hbm},
         "torch_copy_64MiB_us": t_ref * 1e6,
+        "graph_replay": None if not (tg_copy and tg_red and tg_ref) else {
+            "unpack_copy_us": tg_copy * 1e6, "unpack_copy_frac_hbm": 2 * total / tg_copy / 1e9 / hbm,
+            "unpack_reduce_us": tg_red * 1e6, "unpack_reduce_frac_hbm": 3 * total / tg_red / 1e9 / hbm,
+            "torch_copy_64MiB_us": tg_ref * 1e6, "torch_copy_64MiB_frac_hbm": 2 * (64 << 20) / tg_ref / 1e9 / hbm,
+            "note": "20 launches captured in one CUDA graph, one replay timed"},
         "unpack_reduce_fanout3_us": t_fan * 1e6, "unpack_reduce_fanout3_GBps": 6 * total / t_fan / 1e9,
         "unpack_reduce_fanout3_frac_hbm": 6 * total / t_fan / 1e9 / hbm,
         "unpack_reduce_fanout3_back_to_back_us": tb_fan * 1e6,

@@ -51,7 +51,9 @@ inline void traceReq(Comm* c, const Request* r, int stage) {
 std::mutex g_wd_mu;
 std::vector<Comm*> g_wd_comms;
 bool g_wd_started = false;
+std::atomic<bool> g_wd_on{false};  // checkpoints cost a clock read each: taken only while the watchdog runs
 inline void mark(Comm* c, const char* where) {
+  if (!g_wd_on.load(std::memory_order_relaxed)) return;
   c->where.store(where, std::memory_order_relaxed);
   c->where_ns.store(monotonicNanos(), std::memory_order_relaxed);
 }
@@ -61,6 +63,7 @@ void watchdogRegister(Comm* c) {
   const int secs = std::max(1, atoi(v));
   std::lock_guard<std::mutex> l(g_wd_mu);
   g_wd_comms.push_back(c);
+  g_wd_on.store(true, std::memory_order_relaxed);
   if (g_wd_started) return;
   g_wd_started = true;
   std::thread([secs] {
@@ -269,6 +272,7 @@ void helperMain(Comm* comm, int tid) {
   char name[16];
   snprintf(name, sizeof name, "tcpxb-%s%d", comm->passive ? "rx" : "tx", tid);
   prctl(PR_SET_NAME, name, 0, 0, 0);
+  prctl(PR_SET_TIMERSLACK, 1, 0, 0, 0);  // naps of tens of microseconds must not be rounded up to the default 50 us slack
   applyAffinity(comm, tid);
   HelperThread& me = comm->helpers[tid];
   const Flags& f = flags();
@@ -345,6 +349,16 @@ void helperMain(Comm* comm, int tid) {
       continue;
     }
     if (++idle_rounds < 64) continue;  // short spin: the next chunk usually follows at once
+    // No task.  Nap in short steps for a while before going to sleep for good: a nap
+    // needs nobody to wake it, whereas every real sleep costs the thread that queues
+    // the next task a futex system call, and with small requests that is every task.
+    if (f.helper_nap_us > 0 && idle_rounds < 64 + f.helper_nap_rounds) {
+      const uint64_t t0 = monotonicNanos();
+      struct timespec ts = {0, (long)f.helper_nap_us * 1000};
+      nanosleep(&ts, nullptr);
+      me.idle_ns.fetch_add(monotonicNanos() - t0, std::memory_order_relaxed);
+      continue;
+    }
     const uint64_t idle_t0 = monotonicNanos();
     std::unique_lock<std::mutex> l(me.mu);
     me.sleeping.store(true, std::memory_order_seq_cst);
@@ -674,13 +688,16 @@ Result progressRecvRequest(Comm* comm, Request* r) {
     if (!comm->have_ctrl) {
       // An empty control socket costs a system call to discover; callers poll in
       // tight loops, so after one empty read the next look waits a microsecond.
-      if (comm->ctrl_recv.buffered() < (int)sizeof(CtrlMsg) && comm->ctrl_quiet_until_ns != 0) {
+      if (comm->ctrl_recv.buffered() < (int)sizeof(CtrlMsg) && comm->ctrl_quiet_until_ns != 0 && !comm->ctrl_readable_hint) {
         if (monotonicNanos() < comm->ctrl_quiet_until_ns) return kSuccess;
         comm->ctrl_quiet_until_ns = 0;
       }
       Result pr = comm->ctrl_recv.pop(&comm->ctrl);
       if (pr == kInProgress) {
-        comm->ctrl_quiet_until_ns = monotonicNanos() + 1000;
+        // a caller that tells us when the socket is readable (netHintCtrlReadable) needs
+        // the blind retry only as a safety net
+        comm->ctrl_readable_hint = false;
+        comm->ctrl_quiet_until_ns = monotonicNanos() + (comm->ctrl_hinted ? 200000 : 1000);
         if (f.slow_switch[kSlowRxCtrl]) {
           uint64_t ns = 0;
           if (comm->ctrl_stall.shouldWarn(&ns) && f.slow_report[kSlowRxCtrl])
@@ -1260,6 +1277,12 @@ Result netSetTxStagingBytes(Comm* comm, uint64_t bytes) {
 
 void netSetNotifier(Comm* comm, Notifier* notifier) {
   if (comm != nullptr) comm->notifier = notifier;
+}
+
+void netHintCtrlReadable(Comm* comm) {
+  if (comm == nullptr) return;
+  comm->ctrl_hinted = true;
+  comm->ctrl_readable_hint = true;
 }
 
 int netCtrlPollFd(Comm* comm) {

@@ -7,6 +7,7 @@
 #include <stdlib.h>
 #include <string.h>
 #include <sys/eventfd.h>
+#include <sys/prctl.h>
 #include <time.h>
 #include <unistd.h>
 
@@ -118,25 +119,45 @@ struct Engine {
   bool yield_when_idle = false;
   // idle policy of the driving thread
   Notifier notifier;
-  int idle_spin_us = 20, idle_sleep_us = 200;
+  int idle_spin_us = 20, idle_sleep_us = 30;
+  bool wake_on_events = false;  // sleep in ppoll on the control sockets and an eventfd instead of napping
 };
+
+// One look at every receive comm's control socket: a single poll() with no wait, then a
+// hint to the comms whose socket has data.  Replaces one recv() attempt per comm and
+// progress round.
+void pollCtrlSockets(Engine* e) {
+  struct pollfd pfds[TCPXB_ENGINE_MAX_RAILS];
+  Comm* owner[TCPXB_ENGINE_MAX_RAILS];
+  int n = 0;
+  for (Rail& r : e->rails) {
+    const int fd = netCtrlPollFd(r.recv);
+    if (fd >= 0) { pfds[n] = {fd, POLLIN, 0}; owner[n] = r.recv; ++n; }
+  }
+  if (n == 0 || poll(pfds, (nfds_t)n, 0) <= 0) return;
+  for (int i = 0; i < n; ++i)
+    if (pfds[i].revents & (POLLIN | POLLHUP | POLLERR)) netHintCtrlReadable(owner[i]);
+}
 
 // Blocks the driving thread until a helper thread finishes a task, a control record
 // arrives, or `timeout_us` passes (GPU events have no descriptor: the timeout bounds
 // how late their completion is noticed).
 void sleepUntilWork(Engine* e, bool want_ctrl, int timeout_us) {
   struct pollfd pfds[1 + TCPXB_ENGINE_MAX_RAILS];
+  Comm* owner[1 + TCPXB_ENGINE_MAX_RAILS] = {};
   int n = 0;
   pfds[n++] = {e->notifier.event_fd, POLLIN, 0};
   if (want_ctrl) {
     for (Rail& r : e->rails) {
       const int fd = netCtrlPollFd(r.recv);
-      if (fd >= 0) pfds[n++] = {fd, POLLIN, 0};
+      if (fd >= 0) { pfds[n] = {fd, POLLIN, 0}; owner[n] = r.recv; ++n; }
     }
   }
   struct timespec ts = {0, (long)timeout_us * 1000};
   const int rc = ppoll(pfds, (nfds_t)n, &ts, nullptr);
   e->notifier.armed.store(0, std::memory_order_release);
+  for (int i = 1; i < n && rc > 0; ++i)
+    if (pfds[i].revents & (POLLIN | POLLHUP | POLLERR)) netHintCtrlReadable(owner[i]);
   if (rc > 0 && (pfds[0].revents & POLLIN)) {
     uint64_t v;
     ssize_t got = read(e->notifier.event_fd, &v, sizeof v);
@@ -270,8 +291,13 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
   auto lap = [&tp](double& acc) { const double n = nowSec(); acc += n - tp; tp = n; };
   double idle_since = 0;
   bool armed = false;
+  // Small exchanges are latency-bound: spin a little before sleeping.  Large ones have
+  // requests queued on every rail, and every microsecond of spinning is taken from the
+  // helper threads when cores are scarce: sleep at once.
+  const double spin_us = (ss.bytes + rs.bytes <= (1u << 20)) ? (double)e->idle_spin_us : 0.0;
   while (done_s < n_send || launched_r < n_recv) {
     bool moved = false;
+    if (launched_r < n_recv) pollCtrlSockets(e);  // which control sockets have records: one system call for all rails
     // post receives (they claim pool pages as control records arrive)
     while (post_r < n_recv) {
       const int r = (int)(post_r % R);
@@ -356,11 +382,19 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
     // messages are small), then sleep: on a box where helper threads outnumber the
     // cores, a spinning driver takes a core away from the threads that move the bytes.
     if (idle_since == 0) idle_since = tp;
-    const bool may_sleep = e->idle_sleep_us > 0 && e->notifier.event_fd >= 0;
-    if (!may_sleep || (tp - idle_since) * 1e6 < (double)e->idle_spin_us) {
+    const bool may_sleep = e->idle_sleep_us > 0;
+    if (!may_sleep || (tp - idle_since) * 1e6 < spin_us) {
       if (e->yield_when_idle) sched_yield();
       else for (int i = 0; i < 64; ++i) __builtin_ia32_pause();
       lap(e->stats.t_idle);
+    } else if (!e->wake_on_events) {
+      // Nap: a fixed short sleep that nobody has to end.  With several requests queued on
+      // every rail, looking again after a few tens of microseconds loses nothing, and the
+      // helper threads never pay a system call to wake this thread.
+      struct timespec ts = {0, (long)e->idle_sleep_us * 1000};
+      nanosleep(&ts, nullptr);
+      ++e->stats.sleeps;
+      lap(e->stats.t_sleep);
     } else if (!armed) {
       // arm, then look once more: a completion between the last look and the arming is not lost
       e->notifier.armed.store(1, std::memory_order_seq_cst);
@@ -454,7 +488,9 @@ void* tcpxb_engine_create(const tcpxbEngineConfig* cfg) {
   e->yield_when_idle = getenv("TCPXB_ENGINE_YIELD") != nullptr;
   if (cfg->idle_spin_us > 0) e->idle_spin_us = cfg->idle_spin_us;
   if (cfg->idle_sleep_us != 0) e->idle_sleep_us = cfg->idle_sleep_us;
-  e->notifier.event_fd = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
+  e->wake_on_events = cfg->wake_on_events != 0;
+  if (e->wake_on_events) e->notifier.event_fd = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
+  prctl(PR_SET_TIMERSLACK, 1, 0, 0, 0);  // naps are tens of microseconds: no 50 us default slack on this thread
   int ndev = 0;
   netDevices(&ndev);
   e->rails.resize((size_t)std::min(ndev, TCPXB_ENGINE_MAX_RAILS));
@@ -531,8 +567,10 @@ int tcpxb_engine_connect(void* engine, const void* next_handles) {
     netSetTxStagingBytes(rail.send, std::min<uint64_t>(want, (uint64_t)flags().tx_staging_bytes));
     ENG_NET(netPrepareCuda(rail.send, e->cfg.gpu_dev));
     ENG_NET(netPrepareCuda(rail.recv, e->cfg.gpu_dev));
-    netSetNotifier(rail.send, &e->notifier);
-    netSetNotifier(rail.recv, &e->notifier);
+    if (e->wake_on_events) {
+      netSetNotifier(rail.send, &e->notifier);
+      netSetNotifier(rail.recv, &e->notifier);
+    }
   }
   e->connected = true;
   return 0;
@@ -565,9 +603,6 @@ int tcpxb_engine_all_reduce(void* engine, const void* in_, void* out_, uint64_t 
   uint8_t* out = static_cast<uint8_t*>(out_);
   if (e->G > 1 && (in != e->work[e->local] || out != e->out[e->local] || bytes > e->buffer_bytes))
     return fail("with several GPUs per node, in/out must be the registered work/output buffers%s", "");
-  // two nodes swap shards request by request: a request summed into `out` would overwrite
-  // input that a later request has yet to send
-  if (e->G == 1 && e->nodes == 2 && in == out) return fail("all_reduce between two nodes needs an output separate from its input%s", "");
   ++e->epoch;
   const uint64_t shard = bytes / (uint64_t)e->G;
   const uint64_t shard_off = shard * (uint64_t)e->local;
@@ -579,6 +614,13 @@ int tcpxb_engine_all_reduce(void* engine, const void* in_, void* out_, uint64_t 
     std::vector<void*> srcs;
     for (int l = 0; l < e->G; ++l) srcs.push_back(e->work[l]);
     ENG_K(tcpxb_peer_reduce(e->scratch, srcs.data(), e->G, shard_off, shard, dtype, stream));
+    red = e->scratch;
+  } else if (e->nodes == 2 && in == out) {
+    // In place between two nodes: shards are swapped request by request, and a request
+    // summed into `out` would overwrite input that a later request has yet to send.
+    // Sends and addends therefore come from a copy of the input.
+    ENG_TRY(ensureScratch(e, bytes + (uint64_t)e->req_bytes));
+    ENG_NET(gpu::copyDeviceToDeviceAsync(e->scratch, in, bytes, stream));
     red = e->scratch;
   } else if (e->cfg.plain_mode) {
     ENG_TRY(ensureScratch(e, (uint64_t)e->req_bytes));

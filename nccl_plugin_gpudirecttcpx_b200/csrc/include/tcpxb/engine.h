@@ -46,9 +46,11 @@ typedef struct tcpxbEngineConfig {
   int use_nvls;           // use the multimem fan-out when a multicast mapping is given
   int plain_mode;         // 1 = baseline: unpack_copy to a bounce buffer, separate add, no fused fan-out
   // The driving thread of an exchange spins for idle_spin_us without progress, then sleeps
-  // (ppoll on the control sockets and on an eventfd the helper threads write) for at most
-  // idle_sleep_us at a time.  0 = defaults (20 / 200); idle_sleep_us < 0 = never sleep.
-  int idle_spin_us, idle_sleep_us;
+  // idle_sleep_us at a time.  0 = defaults (20 / 30); idle_sleep_us < 0 = never sleep.
+  // By default the sleep is a plain nap that nobody ends early; with wake_on_events it is a
+  // ppoll on the control sockets and on an eventfd that helper threads write when a task
+  // finishes (lower latency per event, one system call per wake-up on both sides).
+  int idle_spin_us, idle_sleep_us, wake_on_events;
 } tcpxbEngineConfig;
 
 typedef struct tcpxbEngineStats {
@@ -86,7 +88,7 @@ int tcpxb_engine_set_peers(void* engine, void* const* work_ptrs, void* const* ou
 
 // Collectives.  With gpus_per_node > 1, `in` must be this rank's work buffer and
 // `out` its output buffer as registered with tcpxb_engine_set_peers.  With one GPU per
-// node and two nodes, all_reduce needs `out` != `in`.
+// node, `out` may be `in` (in place; between two nodes that costs one device copy).
 int tcpxb_engine_all_reduce(void* engine, const void* in, void* out, uint64_t bytes, int dtype, void* stream);
 // all_gather: `in` holds bytes_per_rank; out receives world x bytes_per_rank in rank order.
 int tcpxb_engine_all_gather(void* engine, const void* in, void* out, uint64_t bytes_per_rank, void* stream);

@@ -216,6 +216,8 @@ struct Comm {
   bool have_ctrl = false;
   CtrlMsg ctrl;
   uint64_t ctrl_quiet_until_ns = 0;  // no control-socket read before this time (after an empty read)
+  bool ctrl_hinted = false;          // the caller polls the control socket itself and calls netHintCtrlReadable
+  bool ctrl_readable_hint = false;   // ... and said so since the last empty read
   // CUDA resources (lazy)
   int gpu_dev = -1;
   int recv_mode = kRecvModeHost;
@@ -304,6 +306,11 @@ void netSetNotifier(Comm* comm, Notifier* notifier);
 // has not read yet" (receive side), or -1 when waiting on it would return at once
 // (a record is already buffered) or never (send side).
 int netCtrlPollFd(Comm* comm);
+// For callers that poll() the descriptors of netCtrlPollFd themselves: "this comm's
+// control socket is readable".  From the first call on, the comm reads its control
+// socket only after such a hint (plus a rare blind retry), instead of trying, and
+// paying a system call, on every progress round.
+void netHintCtrlReadable(Comm* comm);
 // Bytes per chunk for a message of `message_bytes` on a comm with `num_socks` data sockets.
 int chunkBytesFor(int message_bytes, int num_socks);
 constexpr int kMaxAdaptiveChunk = 4 << 20;

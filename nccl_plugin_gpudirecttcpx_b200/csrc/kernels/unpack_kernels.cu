@@ -118,6 +118,20 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uin
       "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar)
       : "memory");
 }
+// The same load with an L2 eviction-priority hint: rx pool pages are read exactly once.
+__device__ __forceinline__ void bulk_g2s_hint(uint32_t dst_smem, const void* src, uint32_t bytes,
+                                              uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::
+          "r"(dst_smem),
+      "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
 __device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src_smem, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
                    __cvta_generic_to_global(dst)),
@@ -367,6 +381,7 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
   const uint32_t n = (gw < p.count) ? (p.count - gw + G - 1) / G : 0;
   const uint64_t wait_ns = p.wait_ns ? p.wait_ns : kDefaultWaitNs;
 
+  const uint64_t pool_policy = policy_evict_first();
   uint32_t cached_blk = 0xffffffffu;
   uint4 cached = make_uint4(0, 0, 0, 0);
   uint32_t ready_seen = 0;
@@ -435,7 +450,7 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
       const uint32_t bar = smem_u32(&bars[slot]);
       if (bulk) {
         mbar_expect_tx(bar, C::kAccSlot ? 2 * bulk : bulk);
-        bulk_g2s(smem_u32(wbuf + slot * C::kStride), p.pool + so, bulk, bar);
+        bulk_g2s_hint(smem_u32(wbuf + slot * C::kStride), p.pool + so, bulk, bar, pool_policy);
         if (C::kAccSlot) bulk_g2s(smem_u32(wbuf + slot * C::kStride + kSlot), p.acc + dof, bulk, bar);
       } else {
         mbar_arrive(bar);

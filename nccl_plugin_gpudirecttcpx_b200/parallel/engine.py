@@ -27,7 +27,7 @@ DTYPE_CODE = {torch.bfloat16: 1, torch.float32: 2}
 class _Config(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in (
         "rank", "world", "gpus_per_node", "gpu_dev", "request_bytes", "max_inflight", "unpack_ctas",
-        "reduce_impl", "use_nvls", "plain_mode", "idle_spin_us", "idle_sleep_us")]
+        "reduce_impl", "use_nvls", "plain_mode", "idle_spin_us", "idle_sleep_us", "wake_on_events")]
 
 
 class EngineStats(ctypes.Structure):
@@ -94,7 +94,7 @@ class HierarchicalEngine:
     def __init__(self, gpus_per_node: int = 1, buffer_bytes: int = 0, request_bytes: int = 4 << 20,
                  max_inflight: int = 8, unpack_ctas: int = 16, reduce_impl: int = 0, use_nvls: bool = False,
                  plain_mode: bool = False, device: Optional[torch.device] = None,
-                 idle_spin_us: int = 0, idle_sleep_us: int = 0):
+                 idle_spin_us: int = 0, idle_sleep_us: int = 0, wake_on_events: bool = False):
         import torch.distributed as dist
         self._api = self._load_api()
         self._dist = dist if dist.is_available() and dist.is_initialized() else None
@@ -104,7 +104,7 @@ class HierarchicalEngine:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.nodes = max(2, self.world // self.G) if self.world > 1 else 2
         cfg = _Config(self.rank, self.world, self.G, self.device.index or 0, request_bytes, max_inflight, unpack_ctas,
-                      reduce_impl, int(use_nvls), int(plain_mode), idle_spin_us, idle_sleep_us)
+                      reduce_impl, int(use_nvls), int(plain_mode), idle_spin_us, idle_sleep_us, int(wake_on_events))
         self._h = self._api.tcpxb_engine_create(ctypes.byref(cfg))
         if not self._h:
             raise RuntimeError("engine create failed: " + self._api.tcpxb_engine_last_error().decode())
@@ -201,13 +201,6 @@ class HierarchicalEngine:
                     out.copy_(res)
                     return out
                 return res
-            if out is not None and out.data_ptr() == x.data_ptr():
-                # in place: later requests are still being sent from `x` while earlier ones are summed,
-                # so the result goes to a scratch tensor first
-                tmp = torch.empty_like(x)
-                self._check(self._api.tcpxb_engine_all_reduce(self._h, x.data_ptr(), tmp.data_ptr(), nbytes, code, self._stream()))
-                out.copy_(tmp)
-                return out
             if out is None:
                 out = torch.empty_like(x)
             self._check(self._api.tcpxb_engine_all_reduce(self._h, x.data_ptr(), out.data_ptr(), nbytes, code, self._stream()))
