@@ -12,7 +12,13 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <condition_variable>
 #include <deque>
+#include <functional>
+#include <map>
+#include <mutex>
+#include <string>
+#include <thread>
 #include <vector>
 
 #ifndef TCPXB_NO_CUDA
@@ -121,6 +127,24 @@ struct Engine {
   Notifier notifier;
   int idle_spin_us = 20, idle_sleep_us = 30;
   bool wake_on_events = false;  // sleep in ppoll on the control sockets and an eventfd instead of napping
+  // asynchronous calls: jobs run in order on a thread and a stream of the engine's own
+  struct Job {
+    uint64_t ticket = 0;
+    std::function<int(void* stream)> run;
+    gpu::Event after = nullptr;  // the engine's stream waits for this before the job (caller's event, may be null)
+    gpu::Event done = nullptr;   // recorded on the engine's stream behind the job's last kernel
+    int rc = 0;
+    bool finished = false;
+    std::string error;
+  };
+  std::thread worker;
+  std::mutex job_mu;
+  std::condition_variable job_cv;
+  std::deque<Job*> job_queue;
+  std::map<uint64_t, Job*> jobs;  // every job not yet released, by ticket
+  uint64_t next_ticket = 0;
+  bool worker_stop = false;
+  gpu::Stream async_stream = nullptr;
 };
 
 // One look at every receive comm's control socket: a single poll() with no wait, then a
@@ -455,6 +479,66 @@ int waitFanout(Engine* e, void* stream) {
   return 0;
 }
 
+// ---- worker thread of the asynchronous calls
+
+void workerMain(Engine* e) {
+  prctl(PR_SET_NAME, "tcpxb-engine", 0, 0, 0);
+  prctl(PR_SET_TIMERSLACK, 1, 0, 0, 0);
+  gpu::setDevice(e->cfg.gpu_dev);
+  for (;;) {
+    Engine::Job* job = nullptr;
+    {
+      std::unique_lock<std::mutex> l(e->job_mu);
+      e->job_cv.wait(l, [e] { return e->worker_stop || !e->job_queue.empty(); });
+      if (e->job_queue.empty()) return;  // stop requested and nothing left
+      job = e->job_queue.front();
+      e->job_queue.pop_front();
+    }
+    int rc = 0;
+    if (job->after != nullptr && gpu::streamWaitEvent(e->async_stream, job->after) != kSuccess) rc = fail("waiting for the caller's event failed%s", "");
+    if (rc == 0) rc = job->run(e->async_stream);
+    if (rc == 0 && gpu::eventRecord(job->done, e->async_stream) != kSuccess) rc = fail("recording the completion event failed%s", "");
+    {
+      std::lock_guard<std::mutex> l(e->job_mu);
+      job->rc = rc;
+      if (rc != 0) job->error = g_err;  // g_err belongs to this thread: hand the text over
+      job->finished = true;
+    }
+    e->job_cv.notify_all();
+  }
+}
+
+uint64_t submit(Engine* e, std::function<int(void*)> fn, void* after_event) {
+  std::lock_guard<std::mutex> l(e->job_mu);
+  if (e->async_stream == nullptr) {
+    if (gpu::setDevice(e->cfg.gpu_dev) != kSuccess || gpu::streamCreate(&e->async_stream) != kSuccess) { fail("engine stream: %s", gpu::lastError()); return 0; }
+    e->worker = std::thread(workerMain, e);
+  }
+  auto* job = new Engine::Job();
+  if (gpu::eventCreate(&job->done) != kSuccess) { delete job; fail("event: %s", gpu::lastError()); return 0; }
+  job->ticket = ++e->next_ticket;
+  job->run = std::move(fn);
+  job->after = after_event;
+  e->jobs[job->ticket] = job;
+  e->job_queue.push_back(job);
+  e->job_cv.notify_all();
+  return job->ticket;
+}
+
+void stopWorker(Engine* e) {
+  {
+    std::lock_guard<std::mutex> l(e->job_mu);
+    e->worker_stop = true;
+  }
+  e->job_cv.notify_all();
+  if (e->worker.joinable()) e->worker.join();
+  for (auto& kv : e->jobs) { gpu::eventDestroy(kv.second->done); delete kv.second; }
+  e->jobs.clear();
+  gpu::streamDestroy(e->async_stream);
+  e->async_stream = nullptr;
+}
+
+
 }  // namespace
 
 extern "C" {
@@ -514,6 +598,7 @@ void* tcpxb_engine_create(const tcpxbEngineConfig* cfg) {
 void tcpxb_engine_destroy(void* engine) {
   Engine* e = static_cast<Engine*>(engine);
   if (e == nullptr) return;
+  stopWorker(e);
   for (Rail& r : e->rails) {
     if (r.send) netClose(r.send);
     if (r.recv) netClose(r.recv);
@@ -767,6 +852,76 @@ int tcpxb_engine_recv_prev(void* engine, void* buf, uint64_t bytes, void* stream
   RecvSpec rs;
   rs.bytes = bytes; rs.dst = static_cast<uint8_t*>(buf);
   return exchange(e, ss, rs, stream);
+}
+
+// ---- asynchronous calls ----------------------------------------------------------------
+uint64_t tcpxb_engine_all_reduce_async(void* engine, const void* in, void* out, uint64_t bytes, int dtype, void* after_event) {
+  Engine* e = static_cast<Engine*>(engine);
+  if (e == nullptr) { fail("null engine%s", ""); return 0; }
+  return submit(e, [=](void* stream) { return tcpxb_engine_all_reduce(e, in, out, bytes, dtype, stream); }, after_event);
+}
+
+uint64_t tcpxb_engine_all_gather_async(void* engine, const void* in, void* out, uint64_t bytes_per_rank, void* after_event) {
+  Engine* e = static_cast<Engine*>(engine);
+  if (e == nullptr) { fail("null engine%s", ""); return 0; }
+  return submit(e, [=](void* stream) { return tcpxb_engine_all_gather(e, in, out, bytes_per_rank, stream); }, after_event);
+}
+
+uint64_t tcpxb_engine_reduce_scatter_async(void* engine, const void* in, void* out, uint64_t bytes_per_rank, int dtype, void* after_event) {
+  Engine* e = static_cast<Engine*>(engine);
+  if (e == nullptr) { fail("null engine%s", ""); return 0; }
+  return submit(e, [=](void* stream) { return tcpxb_engine_reduce_scatter(e, in, out, bytes_per_rank, dtype, stream); }, after_event);
+}
+
+int tcpxb_engine_test(void* engine, uint64_t ticket, int* done) {
+  Engine* e = static_cast<Engine*>(engine);
+  if (e == nullptr || done == nullptr) return fail("null argument%s", "");
+  std::lock_guard<std::mutex> l(e->job_mu);
+  auto it = e->jobs.find(ticket);
+  if (it == e->jobs.end()) return fail("unknown ticket%s", "");
+  *done = it->second->finished ? 1 : 0;
+  if (it->second->finished && it->second->rc != 0) { snprintf(g_err, sizeof g_err, "%s", it->second->error.c_str()); return -1; }
+  return 0;
+}
+
+int tcpxb_engine_wait(void* engine, uint64_t ticket) {
+  Engine* e = static_cast<Engine*>(engine);
+  if (e == nullptr) return fail("null engine%s", "");
+  std::unique_lock<std::mutex> l(e->job_mu);
+  auto it = e->jobs.find(ticket);
+  if (it == e->jobs.end()) return fail("unknown ticket%s", "");
+  Engine::Job* job = it->second;
+  e->job_cv.wait(l, [job] { return job->finished; });
+  if (job->rc != 0) { snprintf(g_err, sizeof g_err, "%s", job->error.c_str()); return -1; }
+  return 0;
+}
+
+int tcpxb_engine_stream_wait(void* engine, uint64_t ticket, void* stream) {
+  Engine* e = static_cast<Engine*>(engine);
+  if (e == nullptr) return fail("null engine%s", "");
+  gpu::Event done = nullptr;
+  {
+    std::lock_guard<std::mutex> l(e->job_mu);
+    auto it = e->jobs.find(ticket);
+    if (it == e->jobs.end()) return fail("unknown ticket%s", "");
+    if (!it->second->finished) return fail("the job has not finished queueing its kernels: call tcpxb_engine_wait first%s", "");
+    done = it->second->done;
+  }
+  ENG_NET(gpu::streamWaitEvent(stream, done));
+  return 0;
+}
+
+int tcpxb_engine_release(void* engine, uint64_t ticket) {
+  Engine* e = static_cast<Engine*>(engine);
+  if (e == nullptr) return fail("null engine%s", "");
+  std::lock_guard<std::mutex> l(e->job_mu);
+  auto it = e->jobs.find(ticket);
+  if (it == e->jobs.end()) return fail("unknown ticket%s", "");
+  if (!it->second->finished) return fail("the job is still running%s", "");
+  gpu::eventDestroy(it->second->done);
+  delete it->second;
+  e->jobs.erase(it);
+  return 0;
 }
 
 int tcpxb_engine_stats(void* engine, tcpxbEngineStats* out) {

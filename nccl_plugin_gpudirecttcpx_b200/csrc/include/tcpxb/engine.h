@@ -21,8 +21,9 @@
 //      reduce-scatter (unpack_reduce) then a ring all-gather (unpack_fanout);
 //   3. the kernels of step 2 store every finished fragment into all local GPUs'
 //      output buffers, so the intra-node all-gather rides on the receive path.
-// Calls block the host until every network transfer is done and every kernel is
-// queued on the caller's stream.
+// Synchronous calls block the host until every network transfer is done and every kernel
+// is queued on the caller's stream; the asynchronous forms below hand the same work to a
+// thread of the engine's own.
 #ifndef TCPXB_ENGINE_H_
 #define TCPXB_ENGINE_H_
 
@@ -97,6 +98,23 @@ int tcpxb_engine_reduce_scatter(void* engine, const void* in, void* out, uint64_
 // Point-to-point over rail 0..n to the next / from the previous node (same local index).
 int tcpxb_engine_send_next(void* engine, const void* buf, uint64_t bytes, void* stream);
 int tcpxb_engine_recv_prev(void* engine, void* buf, uint64_t bytes, void* stream);
+
+// Asynchronous forms.  The call queues the collective on a thread and a stream of the
+// engine's own and returns a ticket (> 0; 0 = failure) at once, so the caller's thread is
+// free and may queue more: jobs run in the order they were queued.  `after_event` (a CUDA
+// event, or NULL) is what the engine's stream waits for before it touches the buffers.
+//   tcpxb_engine_test / _wait   has the job finished its network part and queued its last
+//                               kernel?  (_wait blocks.)  Return -1 when the job failed.
+//   tcpxb_engine_stream_wait    makes `stream` wait for the job's kernels (after _wait).
+//   tcpxb_engine_release        forgets a finished job.
+// Synchronous and asynchronous calls must not be mixed while jobs are queued.
+uint64_t tcpxb_engine_all_reduce_async(void* engine, const void* in, void* out, uint64_t bytes, int dtype, void* after_event);
+uint64_t tcpxb_engine_all_gather_async(void* engine, const void* in, void* out, uint64_t bytes_per_rank, void* after_event);
+uint64_t tcpxb_engine_reduce_scatter_async(void* engine, const void* in, void* out, uint64_t bytes_per_rank, int dtype, void* after_event);
+int tcpxb_engine_test(void* engine, uint64_t ticket, int* done);
+int tcpxb_engine_wait(void* engine, uint64_t ticket);
+int tcpxb_engine_stream_wait(void* engine, uint64_t ticket, void* stream);
+int tcpxb_engine_release(void* engine, uint64_t ticket);
 
 int tcpxb_engine_stats(void* engine, tcpxbEngineStats* out);
 // First device-side status word the unpack kernels reported (0 = clean).

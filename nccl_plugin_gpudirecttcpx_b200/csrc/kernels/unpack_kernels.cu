@@ -460,7 +460,7 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
   };
 
   const uint32_t pro = n < (uint32_t)D ? n : (uint32_t)D;
-  for (uint32_t k = 0; k < pro; ++k) issue(k);
+  for (uint32_t k = 0; k < pro && !dead; ++k) issue(k);  // a wait that ran out is not repeated for the next slot
 
   for (uint32_t k = 0; k < n; ++k) {
     // After a time-out only the loads already issued are waited for (at most D of

@@ -87,9 +87,11 @@ def _dtype_code(t: torch.Tensor) -> int:
 
 
 def _need_cuda(*ts: Optional[torch.Tensor]) -> None:
+    """Every tensor a kernel touches is device memory, or pinned host memory (which the device
+    addresses directly: the transport's default rx page pool is such memory)."""
     for t in ts:
-        if t is not None and not (t.is_cuda and t.is_contiguous()):
-            raise ValueError("tensors must be contiguous CUDA tensors")
+        if t is not None and not ((t.is_cuda or t.is_pinned()) and t.is_contiguous()):
+            raise ValueError("tensors must be contiguous CUDA (or pinned host) tensors")
 
 
 # ----------------------------------------------------------------- descriptors

@@ -59,6 +59,15 @@ def bind_engine_api(lib):
     lib.tcpxb_engine_reduce_scatter.argtypes = [vp, vp, vp, u64, ci, vp]
     lib.tcpxb_engine_send_next.argtypes = [vp, vp, u64, vp]
     lib.tcpxb_engine_recv_prev.argtypes = [vp, vp, u64, vp]
+    for name in ("tcpxb_engine_all_reduce_async", "tcpxb_engine_reduce_scatter_async"):
+        getattr(lib, name).restype = u64
+        getattr(lib, name).argtypes = [vp, vp, vp, u64, ci, vp]
+    lib.tcpxb_engine_all_gather_async.restype = u64
+    lib.tcpxb_engine_all_gather_async.argtypes = [vp, vp, vp, u64, vp]
+    lib.tcpxb_engine_test.argtypes = [vp, u64, ctypes.POINTER(ci)]
+    lib.tcpxb_engine_wait.argtypes = [vp, u64]
+    lib.tcpxb_engine_stream_wait.argtypes = [vp, u64, vp]
+    lib.tcpxb_engine_release.argtypes = [vp, u64]
     lib.tcpxb_engine_stats.argtypes = [vp, ctypes.POINTER(EngineStats)]
     lib.tcpxb_engine_device_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint32 * 4)]
     lib.tcpxb_engine_last_error.restype = ctypes.c_char_p
@@ -87,9 +96,38 @@ def default_transport_env(nics: int = 4, nthreads: int = 4, nsocks_per_thread: i
         os.environ.setdefault(k, v)
 
 
+class AsyncWork:
+    """A collective queued on the engine's own thread and stream (`all_reduce_async`).
+
+    `wait()` blocks the calling host thread until the network part is over and the last
+    kernel is queued, makes the caller's current stream wait for those kernels, and returns
+    the result tensor.  `done()` polls without blocking.  Errors of the job surface here."""
+
+    def __init__(self, engine: "HierarchicalEngine", ticket: int, result: torch.Tensor, keep=()):
+        self._engine, self._ticket, self._result, self._keep = engine, ticket, result, keep
+
+    def done(self) -> bool:
+        if not self._ticket:
+            return True  # already waited for
+        flag = ctypes.c_int(0)
+        self._engine._check(self._engine._api.tcpxb_engine_test(self._engine._h, self._ticket, ctypes.byref(flag)))
+        return bool(flag.value)
+
+    def wait(self) -> torch.Tensor:
+        if self._ticket:
+            eng = self._engine
+            eng._check(eng._api.tcpxb_engine_wait(eng._h, self._ticket))
+            eng._check(eng._api.tcpxb_engine_stream_wait(eng._h, self._ticket, eng._stream()))
+            eng._check(eng._api.tcpxb_engine_release(eng._h, self._ticket))
+            self._ticket = 0
+            self._keep = ()
+        return self._result
+
+
 class HierarchicalEngine:
     """Collectives whose inter-node stage runs through the transport and whose receive
-    side is the fused unpack kernel.  All calls are host-blocking and stream-ordered."""
+    side is the fused unpack kernel.  The plain calls are host-blocking and stream-ordered;
+    `all_reduce_async` queues the same work on a thread and a stream of the engine's own."""
 
     def __init__(self, gpus_per_node: int = 1, buffer_bytes: int = 0, request_bytes: int = 4 << 20,
                  max_inflight: int = 8, unpack_ctas: int = 16, reduce_impl: int = 0, use_nvls: bool = False,
@@ -219,6 +257,42 @@ class HierarchicalEngine:
             out.copy_(res)
             return out
         return res
+
+    def _event_after_current_stream(self):
+        """A CUDA event at the current point of the caller's stream: (object to keep alive, raw handle)."""
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        return ev, ev.cuda_event
+
+    def all_reduce_async(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> AsyncWork:
+        """`all_reduce` without blocking the caller: the engine's own thread drives the network
+        and queues the kernels on the engine's own stream, after everything the caller's current
+        stream holds at the time of the call.  Several calls may be outstanding; they run in
+        order.  With one GPU per node `x` must be contiguous with a size that is a multiple of
+        the native granularity (32 bytes between two nodes), and must stay untouched until
+        `wait()`; with several GPUs per node `x` is copied into the symmetric work buffer at
+        once, so only one call can be outstanding."""
+        nbytes = x.numel() * x.element_size()
+        code = DTYPE_CODE[x.dtype]
+        unit = self._all_reduce_unit()
+        if nbytes % unit != 0 or not x.is_contiguous():
+            raise ValueError(f"all_reduce_async needs a contiguous tensor whose size is a multiple of {unit} bytes")
+        if self.G == 1:
+            res = out if out is not None else torch.empty_like(x)
+            src, dst = x.data_ptr(), res.data_ptr()
+        else:
+            if nbytes > self.buffer_bytes:
+                raise ValueError(f"all_reduce of {nbytes} bytes does not fit the {self.buffer_bytes}-byte symmetric buffers")
+            w = self.work.view(torch.uint8)[:nbytes].view(x.dtype)
+            if x.data_ptr() != w.data_ptr():
+                w.copy_(x.reshape(-1))
+            res = self.out.view(torch.uint8)[:nbytes].view(x.dtype).view(x.shape)
+            src, dst = self.work.data_ptr(), self.out.data_ptr()
+        keep, after = self._event_after_current_stream()
+        ticket = self._api.tcpxb_engine_all_reduce_async(self._h, src, dst, nbytes, code, after)
+        if not ticket:
+            raise RuntimeError("engine call failed: " + self._api.tcpxb_engine_last_error().decode())
+        return AsyncWork(self, ticket, res, keep=(keep, x, res))
 
     def work_view(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         """The symmetric work buffer as a tensor, for producers that write in place."""

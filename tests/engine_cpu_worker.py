@@ -113,6 +113,20 @@ def main():
         good = y is mine and torch.allclose(mine, torch.stack(xs).sum(0), atol=1e-4 * ranks)
         ok = ok and good
         detail.append(("all_reduce_in_place", "f32", 600000, 0, 0.0, good))
+    if G == 1:
+        # asynchronous form: three buckets queued at once on the engine's thread, waited for out of order
+        xs3 = [[torch.randn(98304 * (k + 1), generator=torch.Generator().manual_seed(13 * r + k)).float() for r in range(world)]
+               for k in range(3)]
+        if world == 1:
+            xs3 = [b * 2 for b in xs3]
+        mine3 = [b[rank].clone() for b in xs3]
+        works = [eng.all_reduce_async(t) for t in mine3]
+        good = True
+        for k in (2, 0, 1):
+            y = works[k].wait()
+            good = good and torch.allclose(y, torch.stack(xs3[k]).sum(0), atol=1e-4 * ranks) and works[k].done()
+        ok = ok and good
+        detail.append(("all_reduce_async_x3", "f32", 98304, 0, 0.0, good))
     # all_gather and reduce_scatter blocks that are no multiple of 16 bytes
     per = 1001
     xs = [torch.randn(per * ranks, generator=torch.Generator().manual_seed(11 * r + 5)).float() for r in range(world)]

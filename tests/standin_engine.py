@@ -52,6 +52,9 @@ class StandinEngine(HierarchicalEngine):
     def _stream(self):
         return None
 
+    def _event_after_current_stream(self):
+        return None, None  # the stand-in's streams run everything at once: nothing to wait for
+
     def _setup_symmetric(self, buffer_bytes: int, use_nvls: bool) -> None:
         dist = self._dist
         node = self.rank // self.G
