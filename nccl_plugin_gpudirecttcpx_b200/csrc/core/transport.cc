@@ -280,13 +280,37 @@ void helperMain(Comm* comm, int tid) {
   const bool slow_txc = f.slow_switch[kSlowTxComp];
   int idle_rounds = 0;
   while (!comm->stop.load(std::memory_order_acquire)) {
-    bool moved = false, blocked = false, finished = false;
+    bool moved = false, blocked = false, finished = false, staging = false;
     struct pollfd pfds[kMaxSockets];
     int npfd = 0;
     for (int idx = tid; idx < comm->num_socks; idx += comm->num_threads) {
       SocketCtx* s = &comm->sock[idx];
+      // Completion stage: a task whose bytes have all moved (and, for zero-copy sends,
+      // whose notices have all come back) is handed back to the progress engine.
+      auto retireCompleted = [&] {
+        while (s->tasks.has(kTaskCompleting)) {
+          Task* t = &s->tasks.front(kTaskCompleting);
+          if (t->zerocopy && t->zc_count > 0) {
+            // done once every notification id of this task is below zc_done (wrap-safe)
+            const uint32_t last = t->zc_first + t->zc_count;
+            if ((int32_t)(s->zc_done - last) < 0) break;
+          } else if (t->op == kSockSend) {
+            s->stats.tx_completion_cnt.fetch_add(1, std::memory_order_relaxed);
+          }
+          s->stats.bytes_done.fetch_add((uint64_t)t->size, std::memory_order_relaxed);
+          traceTask(comm, t, kTaskInactive);
+          s->tasks.advance(kTaskCompleting);
+          moved = true;
+          finished = true;
+        }
+      };
       while (s->tasks.has(kTaskActive)) {
         Task* t = &s->tasks.front(kTaskActive);
+        if (t->wait_counter != nullptr) {
+          // a send whose payload the copy engine is still staging: not ready, and nobody to wait on but time
+          if (!t->wait_counter->reached(t->wait_mark)) { staging = true; break; }
+          t->wait_counter = nullptr;
+        }
         int rc = progressTask(comm, s, t);
         if (rc < 0) { notifyDriver(comm); return; }
         if (rc == 0) {
@@ -300,8 +324,9 @@ void helperMain(Comm* comm, int tid) {
         moved = true;
         traceTask(comm, t, kTaskCompleting);
         s->tasks.advance(kTaskActive);
+        retireCompleted();  // at once: the next task may keep this thread busy for a long time
       }
-      // completion stage: zero-copy sends wait for the kernel's notification
+      // zero-copy sends wait for the kernel's notification
       if (s->zc_done != s->zc_next) {
         int c = readZerocopyCompletions(s);
         if (c < 0) { setError(comm, kSystemError); notifyDriver(comm); return; }
@@ -320,25 +345,19 @@ void helperMain(Comm* comm, int tid) {
           }
         }
       }
-      while (s->tasks.has(kTaskCompleting)) {
-        Task* t = &s->tasks.front(kTaskCompleting);
-        if (t->zerocopy && t->zc_count > 0) {
-          // done once every notification id of this task is below zc_done (wrap-safe)
-          const uint32_t last = t->zc_first + t->zc_count;
-          if ((int32_t)(s->zc_done - last) < 0) break;
-        } else if (t->op == kSockSend) {
-          s->stats.tx_completion_cnt.fetch_add(1, std::memory_order_relaxed);
-        }
-        s->stats.bytes_done.fetch_add((uint64_t)t->size, std::memory_order_relaxed);
-        traceTask(comm, t, kTaskInactive);
-        s->tasks.advance(kTaskCompleting);
-        moved = true;
-        finished = true;
-      }
+      retireCompleted();
     }
     if (finished) notifyDriver(comm);
     if (moved) { idle_rounds = 0; continue; }
     if (spin) continue;
+    if (staging && !blocked) {
+      // the copy engine finishes within tens of microseconds: look again soon, without a wake-up from anybody
+      if (++idle_rounds > 16) {
+        struct timespec ts = {0, 5000};
+        nanosleep(&ts, nullptr);
+      }
+      continue;
+    }
     if (blocked) {
       // every owned socket with work would block: sleep in the kernel until one is ready
       if (++idle_rounds > 8 && f.poll_block_us > 0) {
@@ -508,6 +527,13 @@ void fillSendTask(Comm* comm, Request* r, int sock_idx, int chunk) {
   Task& t = s.tasks.nextFree();
   t.r = r;
   t.op = kSockSend;
+  t.wait_counter = nullptr;
+  if (r->mem_type == kPtrCuda && r->size > 0) {
+    // the helper thread itself waits for the staging copy that covers this chunk
+    const int seg = (r->offset + chunk + r->seg_bytes - 1) / r->seg_bytes - 1;
+    t.wait_counter = &comm->stage_marks;
+    t.wait_mark = r->seg_mark[seg];
+  }
   t.host_ptr = (r->mem_type == kPtrCuda ? r->stage : r->data) + r->offset;
   t.size = chunk;
   t.offset = 0;
@@ -661,7 +687,9 @@ Result progressSendRequest(Comm* comm, Request* r) {
   const int chunk_size = chunkBytesFor(r->size, comm->num_socks);
   while (r->offset < r->size && comm->mapper->hasFlow()) {
     const int chunk = std::min(chunk_size, r->size - r->offset);
-    if (r->mem_type == kPtrCuda && !stagedUpTo(r, r->offset + chunk)) break;
+    // A chunk of a CUDA send is announced and queued before its staging copy has
+    // finished: the control record lets the receiver set up, and the helper thread waits
+    // for the copy itself (Task::wait_mark), so no progress round is spent on noticing it.
     if (comm->ctrl_send.full()) {
       Result fr = comm->ctrl_send.flush();
       if (fr == kInProgress) break;

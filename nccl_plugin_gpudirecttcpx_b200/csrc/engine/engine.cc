@@ -325,7 +325,10 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
     // post receives (they claim pool pages as control records arrive)
     while (post_r < n_recv) {
       const int r = (int)(post_r % R);
-      if ((int)(rq[r].size() + uq[r].size()) >= e->inflight) break;
+      // Requests whose kernel is queued no longer need the network: they do not count
+      // against the window, so that receiving goes on while kernels run.  They still
+      // hold pool pages and a scatter-list slot each, hence the second bound.
+      if ((int)rq[r].size() >= e->inflight || (int)(rq[r].size() + uq[r].size()) >= 2 * e->inflight) break;
       const uint64_t off = post_r * rb;
       void* data = rs.dst + off;
       int sz = (int)std::min<uint64_t>(rb, rs.bytes - off), tag = 0;

@@ -65,8 +65,9 @@ typedef enum tcpxbDeviceStatus {
 typedef struct tcpxbUnpackOpts {
   // Streaming: when non-null the kernel treats descriptor i as published once
   // *ready_count > i (a host-mapped or device counter the producer advances with
-  // release semantics) and waits for it, at most wait_ns nanoseconds per descriptor
-  // (a producer that keeps advancing never trips the limit, however long the launch).
+  // release semantics) and waits for it; the wait gives up when the counter has not
+  // moved for wait_ns nanoseconds (a producer that keeps advancing never trips the
+  // limit, however long the launch lasts).
   const uint32_t* ready_count;
   uint64_t wait_ns;        // 0 = default (2 s)
   // Fan-out completion: when flag_value != 0, after every store of the launch has

@@ -117,6 +117,10 @@ struct Task {
   // zero-copy accounting: notification ids [zc_first, zc_first + zc_count)
   uint32_t zc_first = 0, zc_count = 0;
   bool zerocopy = false;
+  // a send from the staging ring may be queued before the copy engine has filled it:
+  // the helper starts once the counter has reached the mark (null = nothing to wait for)
+  const gpu::StreamCounter* wait_counter = nullptr;
+  uint32_t wait_mark = 0;
 };
 
 enum ReqStage { kReqPosted = 1, kReqActive = 2, kReqTransmitting = 3, kReqFinished = 4 };

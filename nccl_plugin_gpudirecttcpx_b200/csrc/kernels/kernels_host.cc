@@ -122,10 +122,13 @@ int run(const Job& j) {
   for (uint32_t i = 0; i < count; ++i) {
     if (ready != nullptr) {
       // streaming: record i exists once the producer's counter has passed it; the limit
-      // is per wait, and after a time-out nothing further is attempted
-      const uint64_t t0 = nowNs();
+      // bounds how long the producer may stay silent, and after a time-out nothing further is attempted
+      uint64_t t0 = nowNs();
+      uint32_t seen = __atomic_load_n(ready, __ATOMIC_ACQUIRE);
       bool timed_out = false;
-      while (__atomic_load_n(ready, __ATOMIC_ACQUIRE) <= i) {
+      while (seen <= i) {
+        const uint32_t now_seen = __atomic_load_n(ready, __ATOMIC_ACQUIRE);
+        if (now_seen != seen) { seen = now_seen; t0 = nowNs(); continue; }
         if (nowNs() - t0 > wait_ns) { timed_out = true; break; }
       }
       if (timed_out) { report(j.status, TCPXB_ST_TIMEOUT, i); errors = true; break; }

@@ -399,8 +399,10 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
       // Streaming: descriptor idx exists once the producer's counter passed it.
       if (lane == 0 && ready_seen <= idx) {
         for (uint32_t spin = 0;; ++spin) {
+          const uint32_t before = ready_seen;
           ready_seen = ld_acquire_sys(p.ready);
-          if (ready_seen > idx) { ready_t0 = 0; break; }  // the limit is per wait, not per launch
+          if (ready_seen != before) ready_t0 = 0;  // the producer moved: the limit bounds its silence, not the launch
+          if (ready_seen > idx) break;
           if ((spin & 0x3f) == 0x3f) {
             uint64_t now = globaltimer_ns();
             if (ready_t0 == 0) ready_t0 = now;
