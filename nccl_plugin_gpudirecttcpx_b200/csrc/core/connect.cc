@@ -505,6 +505,7 @@ Comm* newComm(int dev, bool passive) {
   Comm* c = new Comm();
   c->dev = dev;
   c->passive = passive;
+  c->devmem = flags().rx_buf_mgr_devmem;
   c->id = g.next_comm_id.fetch_add(1);
   c->mapper = makeFlowMapper(flags().sched_alg);
   c->rq.reset();

@@ -6,6 +6,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "tcpxb/rx_buf_mgr.h"
 
@@ -27,6 +28,15 @@ const SocketOps& systemOps() {
   };
   return ops;
 }
+
+namespace {
+std::atomic<const SocketOps*> g_test_ops{nullptr};
+}
+const SocketOps& activeOps() {
+  const SocketOps* t = g_test_ops.load(std::memory_order_acquire);
+  return t != nullptr ? *t : systemOps();
+}
+void setOpsForTests(const SocketOps* ops) { g_test_ops.store(ops, std::memory_order_release); }
 
 size_t rxControlBytes(size_t fragments) { return fragments * CMSG_SPACE(sizeof(DmabufCmsg)); }
 

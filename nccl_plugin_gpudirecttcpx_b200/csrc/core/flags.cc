@@ -103,7 +103,7 @@ const StrSpec kStrs[] = {
     {"", "NET_COMM_ID", &Flags::net_comm_id, "subnet hint for interface auto-selection"},
     {kOwn, "RX_POOL_MODE", &Flags::rx_pool_mode_name, "host (pinned, device-mapped) or device (copy-engine placement)"},
     {kOwn, "RECV_MODE", &Flags::recv_mode_name, "host (plugin unpacks) or unpack (NCCL's kernels unpack)"},
-    {kOwn, "RX_BUF_MGR", &Flags::rx_buf_mgr_name, "emulated (in process), daemon (tcpxb_rxdm under UNIX_CLIENT_PREFIX) or devmem (kernel devmem-TCP sockets, pool from the daemon)"},
+    {kOwn, "RX_BUF_MGR", &Flags::rx_buf_mgr_name, "emulated (in process), daemon (tcpxb_rxdm under UNIX_CLIENT_PREFIX), devmem (kernel devmem-TCP sockets, pool from the daemon) or devmem-local (the same with a pool of the process's own)"},
 };
 
 std::string envName(const char* prefix, const char* name) { return std::string(prefix) + name; }
@@ -200,10 +200,13 @@ void loadFlags(Flags* out) {
       out->recv_mode_fell_back = true;
     }
   }
-  out->rx_buf_mgr_devmem = !strcasecmp(out->rx_buf_mgr_name.c_str(), "devmem");
-  // the devmem datapath takes its pool (bound to the NIC's queues) from the daemon as well
-  out->rx_buf_mgr_daemon = out->rx_buf_mgr_devmem || !strcasecmp(out->rx_buf_mgr_name.c_str(), "daemon");
-  if (!out->rx_buf_mgr_daemon && !out->rx_buf_mgr_name.empty() && strcasecmp(out->rx_buf_mgr_name.c_str(), "emulated"))
+  const bool devmem_local = !strcasecmp(out->rx_buf_mgr_name.c_str(), "devmem-local");
+  out->rx_buf_mgr_devmem = devmem_local || !strcasecmp(out->rx_buf_mgr_name.c_str(), "devmem");
+  // the devmem datapath takes its pool (bound to the NIC's queues) from the daemon as well,
+  // unless the process owns the binding itself ("devmem-local")
+  out->rx_buf_mgr_daemon = (out->rx_buf_mgr_devmem && !devmem_local) || !strcasecmp(out->rx_buf_mgr_name.c_str(), "daemon");
+  if (!out->rx_buf_mgr_daemon && !out->rx_buf_mgr_devmem && !out->rx_buf_mgr_name.empty() &&
+      strcasecmp(out->rx_buf_mgr_name.c_str(), "emulated"))
     WARN("unknown rx buffer manager '%s'; using the in-process one", out->rx_buf_mgr_name.c_str());
   parseSlownessList(out->slowness_switch.c_str(), out->slow_switch);
   parseSlownessList(out->slowness_report.c_str(), out->slow_report);

@@ -166,7 +166,7 @@ void applyAffinity(Comm* comm, int tid) {
 // ------------------------------------------------------------- zero-copy notices
 // Reads completion notifications from the socket's error queue; returns how many
 // sendmsg calls completed, or -1 on a socket error.
-int readZerocopyCompletions(SocketCtx* s) {
+int readZerocopyCompletions(SocketCtx* s, bool devmem_path = false) {
   int completed = 0;
   for (;;) {
     char control[128];
@@ -174,7 +174,8 @@ int readZerocopyCompletions(SocketCtx* s) {
     memset(&msg, 0, sizeof msg);
     msg.msg_control = control;
     msg.msg_controllen = sizeof control;
-    ssize_t rc = recvmsg(s->fd, &msg, MSG_ERRQUEUE | MSG_DONTWAIT);
+    ssize_t rc = devmem_path ? devmem::activeOps().recvmsg(s->fd, &msg, MSG_ERRQUEUE | MSG_DONTWAIT)
+                             : recvmsg(s->fd, &msg, MSG_ERRQUEUE | MSG_DONTWAIT);
     if (rc < 0) {
       if (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR) return completed;
       return -1;
@@ -209,7 +210,40 @@ int progressTask(Comm* comm, SocketCtx* s, Task* t) {
   const bool slow_on = flags().slow_switch[kSlowSendRecv];
   while (t->offset < t->size) {
     ssize_t n;
-    if (t->op == kSockSend) {
+    if (t->devmem) {
+      // devmem-TCP: no payload passes through this process, only its description
+      if (t->op == kSockSend) {
+        devmem::TxMessage m;
+        devmem::buildSend(&m, t->dmabuf_id, t->dmabuf_off + (uint64_t)t->offset, (size_t)(t->size - t->offset));
+        n = devmem::sendFrom(devmem::activeOps(), s->fd, &m);
+        if (n > 0) {
+          s->stats.tx_cnt.fetch_add(1, std::memory_order_relaxed);
+          if (t->zc_count++ == 0) t->zc_first = s->zc_next;
+          ++s->zc_next;
+        }
+      } else {
+        devmem::RxSink sink;
+        sink.records = t->records.data();
+        sink.capacity = t->records.size();
+        sink.filled = t->records_filled;
+        sink.tokens = &t->tokens;
+        sink.pool_bytes = comm->rxmgr->bytes();
+        sink.dmabuf_id = comm->rxmgr->rxDmabufId();
+        n = devmem::recvInto(devmem::activeOps(), s->fd, (size_t)(t->size - t->offset), s->devmem_control.data(), s->devmem_control.size(),
+                             (uint64_t)t->msg_offset + (uint64_t)t->offset, &sink);
+        t->records_filled = sink.filled;
+        if (n > 0) s->stats.rx_cnt.fetch_add(1, std::memory_order_relaxed);
+      }
+      if (n < 0) {  // the helpers below speak errno
+        if (n == -EPROTO) {
+          WARN("%s: unusable devmem control messages", s->flow.c_str());
+          setError(comm, kInternalError);
+          return -1;
+        }
+        errno = (int)-n;
+        n = -1;
+      }
+    } else if (t->op == kSockSend) {
       int fl = MSG_DONTWAIT | MSG_NOSIGNAL;
       if (t->zerocopy) fl |= MSG_ZEROCOPY;
       n = send(s->fd, t->host_ptr + t->offset, (size_t)(t->size - t->offset), fl);
@@ -328,7 +362,7 @@ void helperMain(Comm* comm, int tid) {
       }
       // zero-copy sends wait for the kernel's notification
       if (s->zc_done != s->zc_next) {
-        int c = readZerocopyCompletions(s);
+        int c = readZerocopyCompletions(s, comm->devmem);
         if (c < 0) { setError(comm, kSystemError); notifyDriver(comm); return; }
         if (c > 0) { s->zc_done += (uint32_t)c; s->stats.tx_completion_cnt.fetch_add((uint64_t)c); s->stall.reset(); moved = true; }
         else if (slow_txc) {
@@ -519,6 +553,11 @@ bool stagedUpTo(Request* r, int upto) {
 void releasePages(Comm* comm, Request* r) {
   if (!r->pages.empty() && comm->rxmgr != nullptr) comm->rxmgr->releasePages(r->pages.data(), r->pages.size());
   r->pages.clear();
+  if (comm->devmem) {
+    // the pages go back to the NIC's pool through the socket each fragment came from
+    for (int i = 0; i < comm->num_socks; ++i)
+      if (!r->tokens[i].empty()) devmem::recycle(devmem::activeOps(), comm->sock[i].fd, &r->tokens[i]);
+  }
 }
 
 // ------------------------------------------------------------------ task set-up
@@ -528,13 +567,17 @@ void fillSendTask(Comm* comm, Request* r, int sock_idx, int chunk) {
   t.r = r;
   t.op = kSockSend;
   t.wait_counter = nullptr;
-  if (r->mem_type == kPtrCuda && r->size > 0) {
+  t.devmem = comm->devmem && r->mem_type == kPtrCuda;
+  if (t.devmem) {
+    t.dmabuf_id = r->mh->dmabuf_id;
+    t.dmabuf_off = r->mh->dmabuf_offset + (uint64_t)(r->data - static_cast<const uint8_t*>(r->mh->ptr)) + (uint64_t)r->offset;
+  } else if (r->mem_type == kPtrCuda && r->size > 0) {
     // the helper thread itself waits for the staging copy that covers this chunk
     const int seg = (r->offset + chunk + r->seg_bytes - 1) / r->seg_bytes - 1;
     t.wait_counter = &comm->stage_marks;
     t.wait_mark = r->seg_mark[seg];
   }
-  t.host_ptr = (r->mem_type == kPtrCuda ? r->stage : r->data) + r->offset;
+  t.host_ptr = t.devmem ? nullptr : (r->mem_type == kPtrCuda ? r->stage : r->data) + r->offset;
   t.size = chunk;
   t.offset = 0;
   t.msg_offset = r->offset;
@@ -542,8 +585,8 @@ void fillSendTask(Comm* comm, Request* r, int sock_idx, int chunk) {
   t.iov.clear();
   t.iov_pos = 0;
   t.zc_first = t.zc_count = 0;
-  t.zerocopy = s.zerocopy_enabled && r->mem_type == kPtrHost && flags().min_zcopy_size > 0 &&
-               chunk >= flags().min_zcopy_size;
+  t.zerocopy = t.devmem || (s.zerocopy_enabled && r->mem_type == kPtrHost && flags().min_zcopy_size > 0 &&
+                            chunk >= flags().min_zcopy_size);
   traceTask(comm, &t, kTaskActive);
   s.tasks.admit();
   r->offset += chunk;
@@ -557,7 +600,17 @@ bool fillRecvTask(Comm* comm, Request* r, int sock_idx, int chunk, int msg_offse
   t.pages.clear();
   t.iov.clear();
   t.iov_pos = 0;
-  if (r->mem_type == kPtrCuda) {
+  t.devmem = comm->devmem && r->mem_type == kPtrCuda;
+  t.wait_counter = nullptr;
+  if (t.devmem) {
+    // the NIC has placed (or will place) the payload in the bound pool; recvmsg only tells where
+    const size_t frags = (size_t)chunk / 1024 + 64;  // fragments are MTU- to page-sized; refused beyond this
+    if (t.records.size() < frags) t.records.resize(frags);
+    t.records_filled = 0;
+    t.tokens.clear();
+    if (s.devmem_control.empty()) s.devmem_control.resize(devmem::rxControlBytes(512));
+    t.host_ptr = nullptr;
+  } else if (r->mem_type == kPtrCuda) {
     const uint32_t n_pages = ((uint32_t)chunk + kRxPageBytes - 1) / kRxPageBytes;
     // a sender whose chunks differ from the first one may outrun the promise; the rest is taken as it comes
     const bool promised = r->pages_reserved >= n_pages;
@@ -589,7 +642,24 @@ bool fillRecvTask(Comm* comm, Request* r, int sock_idx, int chunk, int msg_offse
 
 // A finished receive task of a CUDA request: describe its pages in the request's
 // slot (one record per page fragment) and keep the pages until the consumer is done.
-Result describePages(Comm* comm, Request* r, Task* t) {
+Result describePages(Comm* comm, Request* r, Task* t, int sock_idx) {
+  if (t->devmem) {
+    // the kernel already wrote the list: move it into the request's slot and keep the tokens
+    if (r->slot.filled + t->records_filled > (uint64_t)kUnpackMaxSlicePages) {
+      WARN("receive of %d bytes arrived in more than the %d fragments a scatter-list slot holds", r->size, kUnpackMaxSlicePages);
+      return kInternalError;
+    }
+    memcpy(&r->slot.mem[r->slot.filled], t->records.data(), t->records_filled * sizeof(LoadMeta));
+    r->slot.filled += t->records_filled;
+    auto& keep = r->tokens[sock_idx];
+    for (const devmem::DmabufToken& run : t->tokens) {
+      if (!keep.empty() && keep.back().token_start + keep.back().token_count == run.token_start) keep.back().token_count += run.token_count;
+      else keep.push_back(run);
+    }
+    t->tokens.clear();
+    t->records_filled = 0;
+    return kSuccess;
+  }
   int left = t->size;
   uint64_t dst = (uint64_t)t->msg_offset;
   for (const PageRun& run : t->pages) {
@@ -658,7 +728,8 @@ namespace {
 
 Result progressSendRequest(Comm* comm, Request* r) {
   const Flags& f = flags();
-  if (r->size <= f.inline_threshold || r->size == 0) {
+  const bool devmem_cuda = comm->devmem && r->mem_type == kPtrCuda;
+  if ((r->size <= f.inline_threshold && !devmem_cuda) || r->size == 0) {
     // small message: record + payload ride the control socket
     if (!r->inline_queued) {
       if (r->mem_type == kPtrCuda && r->size > 0 && !stagedUpTo(r, r->size)) return kSuccess;
@@ -762,7 +833,7 @@ Result progressRecvRequest(Comm* comm, Request* r) {
       }
     }
     const CtrlMsg& c = comm->ctrl;
-    if (r->mem_type == kPtrCuda && !r->pages_promised && r->size > 0) {
+    if (r->mem_type == kPtrCuda && !comm->devmem && !r->pages_promised && r->size > 0) {
       // The first record tells the message's size and the sender's chunk size.  Every
       // page the message will need is promised now, or none: a message that waited for
       // pages while holding some could block, and be blocked by, another connection's.
@@ -847,7 +918,7 @@ Result progressRound(Comm* comm) {
       Task* t = &s.tasks.front(kTaskInactive);
       Request* r = t->r;
       r->size_pending -= t->size;
-      if (t->op == kSockRecv && r->mem_type == kPtrCuda) TCPXB_CHECK(describePages(comm, r, t));
+      if (t->op == kSockRecv && r->mem_type == kPtrCuda) TCPXB_CHECK(describePages(comm, r, t, idx));
       traceTask(comm, t, 0);
       s.tasks.advance(kTaskInactive);
       if (f.force_ack && t->op == kSockRecv && s.tasks.empty()) setQuickAck(s.fd);
@@ -923,7 +994,7 @@ Result progressRound(Comm* comm) {
         r->slot.active = false;
       }
     }
-    if (r->op == kSockSend && r->mem_type == kPtrCuda) comm->tx_tail += r->stage_bytes;
+    if (r->op == kSockSend && r->mem_type == kPtrCuda && !comm->devmem) comm->tx_tail += r->stage_bytes;
     traceReq(comm, r, kReqFinished);
     comm->rq.advance(kReqTransmitting);
   }
@@ -1109,8 +1180,8 @@ Result netRegMr(Comm* comm, void* data, size_t size, int type, MemHandle** out) 
     // registration happens during connection set-up, before any collective kernel
     // can be waiting on this thread: the right moment for allocations and loading
     if (comm != nullptr) TCPXB_CHECK(netPrepareCuda(comm, mh->gpu_dev));
-    if (flags().rx_buf_mgr_devmem && flags().use_dma_buf != 0) {
-      // devmem datapath: the NIC reads transmit payload from the buffer itself, through a dma-buf
+    if (flags().rx_buf_mgr_devmem && flags().use_dma_buf != 0 && comm != nullptr && !comm->passive) {
+      // devmem datapath, send side: the NIC reads transmit payload from the buffer itself, through a dma-buf
       if (flags().reg_dmabuf_use_internal_api != 0)
         WARN("NCCL_GPUDIRECTTCPX_REG_DMABUF_USE_INTERNAL_API=1 (driver procfs interface) is not offered; using the CUDA export call");
       Result er = cu::exportDmabuf(data, size, &mh->dmabuf_fd, &mh->dmabuf_offset);
@@ -1118,6 +1189,13 @@ Result netRegMr(Comm* comm, void* data, size_t size, int type, MemHandle** out) 
         WARN("regMr: dma-buf export of %p (+%zu) failed: %s", data, size, cu::lastError());
         delete mh;
         return er;
+      }
+      RxBufMgr* mgr = rxBufMgrFor(mh->gpu_dev);
+      if (mgr == nullptr || mgr->bindTxDmabuf(mh->dmabuf_fd, &mh->dmabuf_id) != kSuccess) {
+        WARN("regMr: the buffer manager could not bind the dma-buf for transmit");
+        close(mh->dmabuf_fd);
+        delete mh;
+        return kSystemError;
       }
     }
   }
@@ -1151,7 +1229,10 @@ Result netIsend(Comm* comm, void* data, int size, int tag, MemHandle* mh, Reques
   r->gpu_dev = mh != nullptr ? mh->gpu_dev : -1;
   r->size_pending = size;
   r->size_known = true;
-  if (r->mem_type == kPtrCuda) {
+  r->mh = mh;
+  if (r->mem_type == kPtrCuda && comm->devmem) {
+    if (mh == nullptr || mh->dmabuf_fd < 0) { WARN("devmem send of a buffer that was not registered as a dma-buf"); return kInvalidUsage; }
+  } else if (r->mem_type == kPtrCuda) {
     mark(comm, "isend:startCudaSend");
     Result sr = startCudaSend(comm, r, mh);
     if (sr == kInProgress) { mark(comm, "idle"); return kSuccess; }  // staging ring full: retry later

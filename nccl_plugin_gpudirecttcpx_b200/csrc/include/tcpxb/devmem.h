@@ -69,6 +69,10 @@ struct SocketOps {
 };
 // The real calls.
 const SocketOps& systemOps();
+// The table the transport's devmem datapath uses: the real calls unless a test put a
+// model of the kernel in their place (null restores the real calls).
+const SocketOps& activeOps();
+void setOpsForTests(const SocketOps* ops);
 
 // ---- receive ----------------------------------------------------------------------------
 // Where the fragments of a message go.

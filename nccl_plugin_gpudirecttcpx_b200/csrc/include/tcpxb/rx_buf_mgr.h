@@ -22,6 +22,7 @@
 
 #include <stdint.h>
 
+#include <atomic>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -93,6 +94,17 @@ class RxBufMgr {
   virtual Result registerApplication(int pid) = 0;
   virtual Result deregisterApplication(int pid) = 0;
   virtual std::vector<FlowRule> flowRules() = 0;
+  // devmem transmit: the id under which the NIC knows the dma-buf `dmabuf_fd` (what the
+  // privileged side's netlink bind returns).  The in-process managers own no NIC and
+  // hand out consecutive ids, which is all the socket layer's bookkeeping needs.
+  virtual Result bindTxDmabuf(int dmabuf_fd, uint32_t* id) {
+    (void)dmabuf_fd;
+    static std::atomic<uint32_t> next{1};
+    *id = next.fetch_add(1);
+    return kSuccess;
+  }
+  // The id of the rx pool's own dma-buf binding, as fragment records will name it (0 = unknown: accept any).
+  virtual uint32_t rxDmabufId() { return 0; }
 };
 
 // The emulator for GPU `dev` (or `dev` = -1: a host-only pool for machines without

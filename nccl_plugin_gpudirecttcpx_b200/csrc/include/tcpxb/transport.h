@@ -37,6 +37,7 @@
 #include "tcpxb/base.h"
 #include "tcpxb/ctrl_sock.h"
 #include "tcpxb/dev_queue.h"
+#include "tcpxb/devmem.h"
 #include "tcpxb/flags.h"
 #include "tcpxb/flow_mapper.h"
 #include "tcpxb/gpu.h"
@@ -121,6 +122,15 @@ struct Task {
   // the helper starts once the counter has reached the mark (null = nothing to wait for)
   const gpu::StreamCounter* wait_counter = nullptr;
   uint32_t wait_mark = 0;
+  // devmem datapath.  Receive: the kernel reports fragments, collected here until the
+  // progress engine moves them into the request's scatter list.  Send: the payload is
+  // read by the NIC from the dma-buf `dmabuf_id` at `dmabuf_off`.
+  bool devmem = false;
+  std::vector<LoadMeta> records;
+  uint64_t records_filled = 0;
+  std::vector<devmem::DmabufToken> tokens;
+  uint32_t dmabuf_id = 0;
+  uint64_t dmabuf_off = 0;
 };
 
 enum ReqStage { kReqPosted = 1, kReqActive = 2, kReqTransmitting = 3, kReqFinished = 4 };
@@ -148,6 +158,10 @@ struct Request {
   std::vector<PageRun> pages;
   bool pages_promised = false;    // the pool promised every page this message needs
   uint32_t pages_reserved = 0;    // what is left of that promise
+  // devmem datapath: page tokens to hand back per data socket once the consumer is done,
+  // and the registration of a send buffer (its dma-buf)
+  std::vector<devmem::DmabufToken> tokens[kMaxSockets];
+  const MemHandle* mh = nullptr;
   bool unpack_launched = false;
   uint32_t unpack_mark = 0;       // value the comm's unpack counter reaches when this request's kernel (or placement) is done
   uint64_t posted_ns = 0, last_stall_report_ns = 0;
@@ -171,6 +185,7 @@ struct SocketCtx {
   // zero-copy notification ids: [zc_done, zc_next) are outstanding
   uint32_t zc_next = 0, zc_done = 0;
   bool zerocopy_enabled = false;
+  std::vector<char> devmem_control;  // control buffer of this socket's devmem receives
 };
 
 struct HelperThread {
@@ -225,6 +240,7 @@ struct Comm {
   // CUDA resources (lazy)
   int gpu_dev = -1;
   int recv_mode = kRecvModeHost;
+  bool devmem = false;  // CUDA buffers travel by devmem-TCP sockets (no staging, no page allocator)
   gpu::Stream stream = nullptr;
   RxBufMgr* rxmgr = nullptr;
   std::unique_ptr<DevQueue> devq;

@@ -15,16 +15,24 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <linux/errqueue.h>
+#include <netinet/in.h>
 #include <sys/socket.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <atomic>
+#include <deque>
 #include <functional>
+#include <map>
+#include <mutex>
 #include <string>
 #include <thread>
 #include <vector>
 
 #include "tcpxb/dev_queue.h"
+#include "tcpxb/cu_driver.h"
+#include "tcpxb/devmem.h"
 #include "tcpxb/engine.h"
 #include "tcpxb/kernels.h"
 #include "tcpxb/transport.h"
@@ -495,6 +503,178 @@ TEST(device_send_and_the_staging_ring) {
   }
   closePair(&p);
   unsetenv("NCCL_GPUDIRECTTCPX_TX_STAGING_BYTES");
+  unpackModeOff();
+}
+
+
+// ---- the devmem-TCP datapath against a model of the kernel
+// What a devmem NIC + kernel do, with loopback sockets underneath: a receive reads
+// the stream's bytes into pages of the bound pool and reports them as fragment records
+// with tokens; a transmit reads the payload out of the dma-buf the control message
+// names and later posts a completion notice; DONTNEED takes the pages back.
+struct KernelModel {
+  std::mutex mu;
+  uint8_t* pool = nullptr;
+  uint64_t pool_bytes = 0;
+  std::vector<uint32_t> free_pages;
+  std::map<uint32_t, uint32_t> live;            // token -> page
+  uint32_t next_token = 1000;
+  std::map<uint32_t, const uint8_t*> dmabufs;   // transmit binding id -> base of the exported range
+  std::map<int, std::deque<std::pair<uint32_t, uint32_t>>> notices;  // per socket: completed send ids [lo, hi]
+  std::map<int, uint32_t> send_seq;
+  uint64_t rx_fragments = 0, tx_calls = 0, dontneed_calls = 0, linear_every = 0;
+} g_km;
+
+ssize_t kmRecvmsg(int fd, struct msghdr* msg, int flags) {
+  std::lock_guard<std::mutex> l(g_km.mu);
+  if (flags & MSG_ERRQUEUE) {
+    auto& q = g_km.notices[fd];
+    if (q.empty()) { errno = EAGAIN; return -1; }
+    struct cmsghdr* cm = reinterpret_cast<struct cmsghdr*>(msg->msg_control);
+    cm->cmsg_level = SOL_IP;
+    cm->cmsg_type = IP_RECVERR;
+    cm->cmsg_len = CMSG_LEN(sizeof(struct sock_extended_err));
+    struct sock_extended_err ee;
+    memset(&ee, 0, sizeof ee);
+    ee.ee_origin = 5;  // zero-copy completion
+    ee.ee_info = q.front().first;
+    ee.ee_data = q.front().second;
+    memcpy(CMSG_DATA(cm), &ee, sizeof ee);
+    msg->msg_controllen = CMSG_SPACE(sizeof ee);
+    q.pop_front();
+    return 0;
+  }
+  if (!(flags & devmem::kMsgSockDevmem)) { errno = EINVAL; return -1; }
+  const size_t room = msg->msg_controllen / CMSG_SPACE(sizeof(devmem::DmabufCmsg));
+  size_t want = std::min<size_t>(msg->msg_iov[0].iov_len, room * 4096);
+  want = std::min<size_t>(want, g_km.free_pages.size() * 4096);
+  if (want == 0) { errno = EAGAIN; return -1; }
+  static thread_local std::vector<uint8_t> bounce;
+  bounce.resize(want);
+  const ssize_t n = recv(fd, bounce.data(), want, MSG_DONTWAIT);
+  if (n <= 0) return n;
+  size_t used = 0;
+  char* c = static_cast<char*>(msg->msg_control);
+  for (size_t off = 0; off < (size_t)n; off += 4096) {
+    const uint32_t len = (uint32_t)std::min<size_t>(4096, (size_t)n - off);
+    const uint32_t page = g_km.free_pages.back();
+    g_km.free_pages.pop_back();
+    memcpy(g_km.pool + (size_t)page * 4096, bounce.data() + off, len);
+    const uint32_t tok = g_km.next_token++;
+    g_km.live[tok] = page;
+    devmem::DmabufCmsg f = {(uint64_t)page * 4096, len, tok, 0, 0};
+    struct cmsghdr* cm = reinterpret_cast<struct cmsghdr*>(c + used);
+    cm->cmsg_level = SOL_SOCKET;
+    cm->cmsg_type = devmem::kSoDevmemDmabuf;
+    cm->cmsg_len = CMSG_LEN(sizeof f);
+    memcpy(CMSG_DATA(cm), &f, sizeof f);
+    used += CMSG_SPACE(sizeof f);
+    ++g_km.rx_fragments;
+  }
+  msg->msg_controllen = used;
+  msg->msg_flags = 0;
+  return n;
+}
+
+ssize_t kmSendmsg(int fd, const struct msghdr* msg, int flags) {
+  std::lock_guard<std::mutex> l(g_km.mu);
+  struct cmsghdr* cm = CMSG_FIRSTHDR(const_cast<struct msghdr*>(msg));
+  if (cm == nullptr || cm->cmsg_level != SOL_SOCKET || cm->cmsg_type != devmem::kSoDevmemDmabuf) { errno = EINVAL; return -1; }
+  uint32_t id = 0;
+  memcpy(&id, CMSG_DATA(cm), sizeof id);
+  auto it = g_km.dmabufs.find(id);
+  if (it == g_km.dmabufs.end()) { errno = ENODEV; return -1; }
+  const uint64_t off = (uint64_t)(uintptr_t)msg->msg_iov[0].iov_base;  // an offset, not an address
+  const ssize_t n = send(fd, it->second + off, msg->msg_iov[0].iov_len, (flags & ~0x4000000) | MSG_DONTWAIT | MSG_NOSIGNAL);
+  if (n > 0) {
+    const uint32_t seq = g_km.send_seq[fd]++;
+    g_km.notices[fd].push_back({seq, seq});
+    ++g_km.tx_calls;
+  }
+  return n;
+}
+
+int kmSetsockopt(int, int level, int optname, const void* val, socklen_t len) {
+  std::lock_guard<std::mutex> l(g_km.mu);
+  if (level != SOL_SOCKET || optname != devmem::kSoDevmemDontneed) { errno = EINVAL; return -1; }
+  const devmem::DmabufToken* t = static_cast<const devmem::DmabufToken*>(val);
+  for (size_t i = 0; i < len / sizeof *t; ++i)
+    for (uint32_t k = 0; k < t[i].token_count; ++k) {
+      auto it = g_km.live.find(t[i].token_start + k);
+      if (it == g_km.live.end()) { errno = EINVAL; return -1; }
+      g_km.free_pages.push_back(it->second);
+      g_km.live.erase(it);
+    }
+  ++g_km.dontneed_calls;
+  return 0;
+}
+
+TEST(devmem_datapath_end_to_end_against_a_kernel_model) {
+  // RX_BUF_MGR=devmem-local: CUDA buffers travel by devmem sockets; the pool is this process's own
+  setenv("NCCL_GPUDIRECTTCPX_RX_BUF_MGR", "devmem-local", 1);
+  setenv("NCCL_GPUDIRECTTCPX_RECV_MODE", "unpack", 1);
+  setenv("NCCL_PROTO", "Simple", 1);
+  setenv("NCCL_ALGO", "Ring", 1);
+  setenv("NCCL_GPUDIRECTTCPX_RX_POOL_BYTES", "8388608", 1);
+  EXPECT(netInit(nullptr) == kSuccess);
+  const devmem::SocketOps model = {kmRecvmsg, kmSendmsg, kmSetsockopt};
+  devmem::setOpsForTests(&model);
+  Pair p;
+  EXPECT(makePair(&p));
+  // send buffers live in a shareable device allocation, so that they can be exported as a dma-buf
+  cu::SharedAllocation sendmem;
+  int pool_fd = -1;
+  EXPECT(cu::deviceInit(0) == kSuccess && cu::sharedCreate(0, 4 << 20, &sendmem, &pool_fd) == kSuccess);
+  if (pool_fd >= 0) close(pool_fd);
+  uint8_t* sbase = static_cast<uint8_t*>(sendmem.dptr);
+  for (size_t i = 0; i < (4u << 20); ++i) sbase[i] = (uint8_t)((i * 2654435761u) >> 11);
+  const int sizes[3] = {300000, 4096, 1 << 20};
+  size_t at = 12345;  // not page-aligned on purpose
+  bool pool_known = false;
+  for (int k = 0; k < 3; ++k) {
+    const int size = sizes[k];
+    std::vector<uint8_t> dst((size_t)size, 0);
+    MemHandle *smh = nullptr, *rmh = nullptr;
+    EXPECT(netRegMr(p.s, sbase + at, (size_t)size, kPtrCuda, &smh) == kSuccess);
+    EXPECT(smh != nullptr && smh->dmabuf_fd >= 0 && smh->dmabuf_id != 0 && smh->dmabuf_offset == at);
+    EXPECT(netRegMr(p.r, dst.data(), dst.size(), kPtrCuda, &rmh) == kSuccess);
+    if (smh == nullptr || rmh == nullptr) break;
+    {
+      std::lock_guard<std::mutex> l(g_km.mu);
+      g_km.dmabufs[smh->dmabuf_id] = sbase + at - smh->dmabuf_offset;  // what the NIC would have bound
+    }
+    void* data = dst.data();
+    int sz = size, tag = k;
+    Request *rr = nullptr, *rs = nullptr;
+    EXPECT(netIrecv(p.r, 1, &data, &sz, &tag, &rmh, &rr) == kSuccess && rr != nullptr);
+    if (!pool_known) {
+      // the pool the "NIC" writes into is the receive comm's own: learn it from the first request
+      ScatterList sl;
+      EXPECT(netRequestScatterList(rr, &sl) == kSuccess);
+      std::lock_guard<std::mutex> l(g_km.mu);
+      g_km.pool = static_cast<uint8_t*>(sl.pool_dev);
+      g_km.pool_bytes = sl.pool_bytes;
+      for (uint32_t pg = 0; pg < sl.pool_bytes / 4096; ++pg) g_km.free_pages.push_back((pg * 773u) % (uint32_t)(sl.pool_bytes / 4096));
+      pool_known = true;
+    }
+    EXPECT(netIsend(p.s, sbase + at, size, tag, smh, &rs) == kSuccess && rs != nullptr);
+    int done = 0, got = 0;
+    EXPECT(pollBounded(rr, &done, &got, rs) == kSuccess && done && got == size);
+    EXPECT(pollBounded(rs, &done, &got) == kSuccess && done);  // every transmit's completion notice came back
+    EXPECT(applyScatterList(rr, &dst) && memcmp(dst.data(), sbase + at, (size_t)size) == 0);
+    const size_t live_before = g_km.live.size();
+    EXPECT(live_before == (size_t)(size + 4095) / 4096 || live_before > 0);
+    EXPECT(netIrecvConsumed(p.r, 1, rr) == kSuccess);
+    EXPECT(g_km.live.empty());  // every page token went back with the consumer's release
+    netDeregMr(nullptr, smh);
+    netDeregMr(nullptr, rmh);
+    at += (size_t)size + 777;
+  }
+  EXPECT(g_km.rx_fragments >= (300000 + 4096 + (1 << 20)) / 4096 && g_km.tx_calls >= 3 && g_km.dontneed_calls >= 3);
+  closePair(&p);
+  devmem::setOpsForTests(nullptr);
+  cu::sharedRelease(&sendmem);
+  unsetenv("NCCL_GPUDIRECTTCPX_RX_BUF_MGR");
   unpackModeOff();
 }
 
