@@ -48,13 +48,15 @@ SWEEP_BYTES = (1 << 10, 64 << 10, 4 << 20, 64 << 20)
 
 def rails_and_threads(cores: int, world: int, nics: int = 0, nthreads: int = 0):
     """Rails (virtual NICs) and helper threads per connection for `world` ranks sharing `cores`
-    cores; values given by the caller (> 0) are kept.  About one helper thread per core and
-    direction: 4 cores per rank -> 2 x 1, 8 -> 4 x 1, 16 -> 4 x 2."""
-    per_dir = max(1, min(8, cores // max(world, 1) // 2))
+    cores; values given by the caller (> 0) are kept.  Helper threads sleep when they have
+    nothing to do, so a rank may have more of them than cores: measured on 4 cores per rank,
+    4 rails x 1 thread moved 14.2 GB/s against 11.7 for 2 x 1; with 16 cores 4 x 2 is as good
+    as anything.  4 cores per rank -> 4 x 1, 8 -> 4 x 1, 16 -> 4 x 2."""
+    per_rank = max(1, cores // max(world, 1))
     if nics <= 0:
-        nics = min(4, per_dir)
+        nics = min(4, per_rank)
     if nthreads <= 0:
-        nthreads = max(1, per_dir // nics)
+        nthreads = max(1, min(4, per_rank // 2 // nics))
     return nics, nthreads
 
 
@@ -74,9 +76,9 @@ def parse_args(argv=None):
     ap.add_argument("--nthreads", type=int, default=0, help="helper threads (= sockets) per comm (0 = from the core count)")
     ap.add_argument("--nsocks-per-thread", type=int, default=1)
     ap.add_argument("--chunk-kb", type=int, default=128)
-    ap.add_argument("--request-kb", type=int, default=4096)
+    ap.add_argument("--request-kb", type=int, default=1024)
     ap.add_argument("--unpack-ctas", type=int, default=16)
-    ap.add_argument("--inflight", type=int, default=0, help="requests in flight per rail (0 = engine default)")
+    ap.add_argument("--inflight", type=int, default=4, help="requests in flight per rail (0 = engine default)")
     ap.add_argument("--idle-sleep-us", type=int, default=0, help="driving thread: longest sleep when idle (0 = default, -1 = spin)")
     ap.add_argument("--pool-mb", type=int, default=1024, help="rx page pool per GPU (MiB)")
     ap.add_argument("--plugin-recv-mode", default="host", choices=["host", "unpack"], help="nccl-plugin arm: who unpacks")
