@@ -48,10 +48,10 @@ thread_local int t_ctx_depth = 0;
 
 bool available() { return fake(); }
 
-Result deviceInit(int dev) {
+Result deviceInit(int dev, bool owns_its_memory) {
   if (!fake() || dev != 0) return failed("deviceInit", "no such device");
   std::lock_guard<std::mutex> l(g_mu);
-  g_own_ctx[0] = flags().cuda_use_primary_ctx == 0;
+  g_own_ctx[0] = flags().cuda_use_primary_ctx == 0 && owns_its_memory;
   return kSuccess;
 }
 bool usesOwnContext(int dev) { return dev == 0 && g_own_ctx[0]; }
@@ -230,7 +230,7 @@ Result mapReadWrite(int dev, CUmemGenericAllocationHandle h, size_t bytes, size_
 
 bool available() { return api().ok; }
 
-Result deviceInit(int dev) {
+Result deviceInit(int dev, bool owns_its_memory) {
   if (!api().ok) return failed("deviceInit", "the CUDA driver library could not be loaded");
   if (dev < 0 || dev >= kMaxDev) return failed("deviceInit", "device ordinal out of range");
   std::lock_guard<std::mutex> l(g_mu);
@@ -239,7 +239,9 @@ Result deviceInit(int dev) {
   const Api& a = api();
   CUdevice cd;
   TCPXB_CHECK(CUD(a.DeviceGet(&cd, dev)));
-  if (flags().cuda_use_primary_ctx != 0) {
+  if (flags().cuda_use_primary_ctx != 0 || !owns_its_memory) {
+    if (flags().cuda_use_primary_ctx == 0)
+      INFO(kSubInit, "GPU %d: NCCL_GPUDIRECTTCPX_CUDA_USE_PRIMARY_CTX=0 ignored here: the application's buffers live in the primary context", dev);
     TCPXB_CHECK(CUD(a.PrimaryCtxRetain(&d.ctx, cd)));
     d.primary_retained = true;
   } else {

@@ -121,7 +121,7 @@ struct Engine {
   gpu::StreamCounter kernel_marks;  // advanced on the caller's stream behind every unpack launch
   gpu::Event dep_event = nullptr;
   tcpxbEngineStats stats;
-  int req_bytes = 4 << 20, inflight = 8, ctas = 16;
+  int req_bytes = 1 << 20, inflight = 4, ctas = 16;
   bool yield_when_idle = false;
   // idle policy of the driving thread
   Notifier notifier;

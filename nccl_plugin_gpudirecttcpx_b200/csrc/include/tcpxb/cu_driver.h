@@ -34,7 +34,10 @@ const char* lastError();
 // Chooses, once per device, the context this library's own threads use: the device's
 // primary context (retained; NCCL_GPUDIRECTTCPX_CUDA_USE_PRIMARY_CTX=1, the default,
 // which is also what the runtime API uses) or a context of the library's own (=0).
-Result deviceInit(int dev);
+// An own context cannot reach memory the application allocated in the primary one, so
+// it is created only for a caller that says it owns all the device memory it touches
+// (`owns_its_memory`: the buffer manager daemon); everybody else gets the primary context.
+Result deviceInit(int dev, bool owns_its_memory = false);
 // Whether deviceInit created an own context for `dev` (false: primary, or not initialised).
 bool usesOwnContext(int dev);
 // Makes the chosen context current on the calling thread for the lifetime of the

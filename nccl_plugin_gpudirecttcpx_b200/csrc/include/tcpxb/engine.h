@@ -40,8 +40,8 @@ extern "C" {
 typedef struct tcpxbEngineConfig {
   int rank, world, gpus_per_node;
   int gpu_dev;            // CUDA device of this rank
-  int request_bytes;      // bytes per network request (<= 4 MiB, multiple of 4096); 0 = 4 MiB
-  int max_inflight;       // requests in flight per rail (<= 12); 0 = 8
+  int request_bytes;      // bytes per network request (<= 4 MiB, multiple of 4096); 0 = 1 MiB
+  int max_inflight;       // requests in flight per rail (<= 12); 0 = 4 (little in flight stays in the CPU's caches)
   int unpack_ctas;        // CTAs per unpack launch; 0 = 16
   int reduce_impl;        // TCPXB_REDUCE_SM or TCPXB_REDUCE_L2
   int use_nvls;           // use the multimem fan-out when a multicast mapping is given

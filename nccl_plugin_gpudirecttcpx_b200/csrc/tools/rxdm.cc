@@ -94,7 +94,7 @@ Pool* poolFor(State* st, const std::string& pci) {
     for (int d = 0; d < gpu::deviceCount(); ++d)
       if (gpu::pciBusId(d) == pci) dev = d;
     if (dev < 0) { fprintf(stderr, "[rxdm] no GPU with PCI address %s\n", pci.c_str()); return nullptr; }
-    if (cu::deviceInit(dev) != kSuccess || cu::sharedCreate(dev, st->pool_bytes, &p.dev, &p.fd) != kSuccess) {
+    if (cu::deviceInit(dev, /*owns_its_memory=*/true) != kSuccess || cu::sharedCreate(dev, st->pool_bytes, &p.dev, &p.fd) != kSuccess) {
       fprintf(stderr, "[rxdm] device pool on GPU %s failed: %s\n", pci.c_str(), cu::lastError());
       return nullptr;
     }

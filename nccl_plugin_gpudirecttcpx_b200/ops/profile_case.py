@@ -18,7 +18,7 @@ import argparse
 import json
 import sys
 
-KERNELS = ("copy", "reduce", "reduce_l2", "fanout", "reduce_fanout", "peer_reduce", "checksum", "copy_host_pool")
+KERNELS = ("copy", "reduce", "reduce_l2", "fanout", "reduce_fanout", "peer_reduce", "checksum", "copy_host_pool", "reduce_host_pool")
 
 
 def main(argv=None) -> int:
@@ -38,7 +38,7 @@ def main(argv=None) -> int:
     pool_bytes = 256 << 20
     g = torch.Generator(device=dev).manual_seed(1)
     pool = torch.randn(pool_bytes // 2, device=dev, generator=g).to(torch.bfloat16)
-    if args.kernel == "copy_host_pool":
+    if args.kernel in ("copy_host_pool", "reduce_host_pool"):
         # the transport's default rx pool placement: pinned host memory the kernel reads over PCIe
         host = torch.empty(pool_bytes // 2, dtype=torch.bfloat16).pin_memory()
         host.copy_(pool)
@@ -57,7 +57,7 @@ def main(argv=None) -> int:
         k = args.kernel
         if k in ("copy", "copy_host_pool"):
             U.unpack_copy(pool, dst, descs, status=st, **kw)
-        elif k == "reduce":
+        elif k in ("reduce", "reduce_host_pool"):
             U.unpack_reduce(pool, dst, descs, status=st, **kw)
         elif k == "reduce_l2":
             U.unpack_reduce(pool, dst, descs, status=st, impl=U.REDUCE_L2, **kw)

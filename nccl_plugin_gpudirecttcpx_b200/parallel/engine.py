@@ -129,8 +129,8 @@ class HierarchicalEngine:
     side is the fused unpack kernel.  The plain calls are host-blocking and stream-ordered;
     `all_reduce_async` queues the same work on a thread and a stream of the engine's own."""
 
-    def __init__(self, gpus_per_node: int = 1, buffer_bytes: int = 0, request_bytes: int = 4 << 20,
-                 max_inflight: int = 8, unpack_ctas: int = 16, reduce_impl: int = 0, use_nvls: bool = False,
+    def __init__(self, gpus_per_node: int = 1, buffer_bytes: int = 0, request_bytes: int = 1 << 20,
+                 max_inflight: int = 4, unpack_ctas: int = 16, reduce_impl: int = 0, use_nvls: bool = False,
                  plain_mode: bool = False, device: Optional[torch.device] = None,
                  idle_spin_us: int = 0, idle_sleep_us: int = 0, wake_on_events: bool = False):
         import torch.distributed as dist

@@ -35,7 +35,9 @@ def parse_args(argv=None):
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--nics", type=int, default=4)
-    ap.add_argument("--nthreads", type=int, default=4)
+    ap.add_argument("--nthreads", type=int, default=0, help="helper threads per connection (0 = from the cores per rank)")
+    ap.add_argument("--request-kb", type=int, default=1024, help="engine paths: bytes per network request")
+    ap.add_argument("--inflight", type=int, default=4, help="engine paths: requests in flight per rail")
     ap.add_argument("--nsocks-per-thread", type=int, default=1)
     ap.add_argument("--chunk-kb", type=int, default=512)
     return ap.parse_args(argv)
@@ -48,6 +50,11 @@ def main(argv=None) -> int:
     local = int(os.environ.get("LOCAL_RANK", "0"))
     G = args.gpus_per_node
     nccl_path = args.path.startswith("nccl")
+    if args.nthreads <= 0:
+        cores_per_rank = max(1, len(os.sched_getaffinity(0)) // max(1, int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))))
+        # NCCL paths: 2 threads below 6 cores per rank, else 4 (what NCCL's socket transport liked best);
+        # engine paths: helper threads beyond the rails only when cores are plentiful
+        args.nthreads = (2 if cores_per_rank < 6 else 4) if nccl_path else max(1, min(4, cores_per_rank // 2 // max(1, args.nics)))
     if nccl_path:
         from .plugin_env import plugin_env
         env = plugin_env(nics=args.nics, nthreads=args.nthreads, nsocks_per_thread=args.nsocks_per_thread,
@@ -77,6 +84,7 @@ def main(argv=None) -> int:
         default_transport_env(nics=args.nics, nthreads=args.nthreads, nsocks_per_thread=args.nsocks_per_thread,
                               chunk_bytes=args.chunk_kb << 10)
         eng = HierarchicalEngine(gpus_per_node=G, buffer_bytes=max(sizes) if G > 1 else 0,
+                                 request_bytes=args.request_kb << 10, max_inflight=args.inflight,
                                  plain_mode=(args.path == "engine-plain"), device=dev)
     nodes = max(2, world // G) if world > 1 else 2
     ranks = world if world > 1 else 2  # the single rank stands for a pair of twin nodes
