@@ -82,6 +82,9 @@ def parse_args(argv=None):
     ap.add_argument("--idle-sleep-us", type=int, default=0, help="driving thread: longest sleep when idle (0 = default, -1 = spin)")
     ap.add_argument("--pool-mb", type=int, default=1024, help="rx page pool per GPU (MiB)")
     ap.add_argument("--plugin-recv-mode", default="host", choices=["host", "unpack"], help="nccl-plugin arm: who unpacks")
+    ap.add_argument("--pin", default="none", choices=["none", "block", "pair"],
+                    help="CPU affinity of each rank's process: none; block = rank r gets the r-th slice of the cores; "
+                         "pair = the two ranks of a rail (same local index in the two nodes) get neighbouring slices")
     ap.add_argument("--no-microbench", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-compare", action="store_true", help="skip the raw-socket ceiling and the NCCL socket child run")
@@ -322,7 +325,7 @@ def run_child_arm(impl: str, args, world: int):
         cmd += ["-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
                 "--master-port", str(free_port())]
     cmd += [str(ROOT / "bench.py"), "--impl", impl, "--gpus", str(world), "--steps", str(args.steps), "--warmup", str(args.warmup),
-            "--size-mb", str(args.size_mb), "--no-microbench", "--no-compare"]
+            "--size-mb", str(args.size_mb), "--no-microbench", "--no-compare", "--pin", args.pin]
     if args.no_sweep:
         cmd.append("--no-sweep")
     drop = ("NCCL_", "TORCHELASTIC", "MASTER_", "RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_", "ROLE_", "TORCH_NCCL")
@@ -364,8 +367,19 @@ def main():
     if args.gpus > 1 and world == 1:
         raise SystemExit("launch with torch.distributed.run for --gpus > 1")
     nccl_arm = args.impl.startswith("nccl")
-    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 16)
     G = max(1, world // 2)
+    if args.pin != "none" and world > 1 and hasattr(os, "sched_setaffinity"):
+        # before any thread exists: helper threads, CUDA's and NCCL's inherit the mask
+        avail = sorted(os.sched_getaffinity(0))
+        per = max(1, len(avail) // world)
+        slot = rank if args.pin == "block" else (rank % G) * 2 + rank // G
+        mine = avail[slot * per:(slot + 1) * per]
+        if mine:
+            os.sched_setaffinity(0, mine)
+    total_cores = os.cpu_count() or 16
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else total_cores
+    if args.pin != "none" and world > 1:
+        cores = cores * world  # the helpers below size threads from the box's cores shared by all ranks
 
     if nccl_arm:
         if world < 2:
@@ -418,11 +432,11 @@ def main():
         eng = HierarchicalEngine(gpus_per_node=G, buffer_bytes=nbytes if G > 1 else 0, request_bytes=args.request_kb << 10,
                                  unpack_ctas=args.unpack_ctas, plain_mode=(args.impl == "plain"), device=dev,
                                  max_inflight=args.inflight, idle_sleep_us=args.idle_sleep_us)
-        transport = {"cpu_cores": cores, "nics": args.nics, "threads": args.nthreads, "socks_per_thread": args.nsocks_per_thread,
+        transport = {"cpu_cores": cores, "pin": args.pin, "nics": args.nics, "threads": args.nthreads, "socks_per_thread": args.nsocks_per_thread,
                      "chunk_kb": args.chunk_kb, "request_kb": args.request_kb, "unpack_ctas": args.unpack_ctas,
                      "streams_per_direction_on_the_box": max(world, 1) * args.nics * args.nthreads * args.nsocks_per_thread}
     else:
-        transport = {"cpu_cores": cores, "env": {k: v for k, v in os.environ.items() if k.startswith("NCCL_") and "PLUGIN" not in k}}
+        transport = {"cpu_cores": cores, "pin": args.pin, "env": {k: v for k, v in os.environ.items() if k.startswith("NCCL_") and "PLUGIN" not in k}}
     is_engine = eng is not None
 
     # seeded synthetic input, N(0,1) bf16; every rank a different stream

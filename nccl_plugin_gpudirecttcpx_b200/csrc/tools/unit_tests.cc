@@ -31,6 +31,7 @@
 #include "tcpxb/devmem.h"
 #include "tcpxb/flags.h"
 #include "tcpxb/flow_mapper.h"
+#include "tcpxb/gpu.h"
 #include "tcpxb/rx_buf_mgr.h"
 #include "tcpxb/rxdm.h"
 #include "tcpxb/socket_utils.h"
@@ -964,6 +965,38 @@ TEST(shared_device_allocation_and_dmabuf_export_on_standin_device) {
   cu::sharedRelease(&client);
   cu::sharedRelease(&owner);
   EXPECT(owner.dptr == nullptr && client.dptr == nullptr);
+}
+
+TEST(chunk_size_follows_the_sockets) {
+  // one chunk per socket and message, page-rounded, never below the striping quantum and
+  // never above 4 MiB; ADAPTIVE_CHUNK=0 keeps the fixed quantum
+  unsetenv("NCCL_GPUDIRECTTCPX_ADAPTIVE_CHUNK");
+  setenv("NCCL_DYNAMIC_CHUNK_SIZE", "131072", 1);
+  reloadFlags();
+  EXPECT(chunkBytesFor(4 << 20, 1) == 4 << 20);
+  EXPECT(chunkBytesFor(4 << 20, 4) == 1 << 20);
+  EXPECT(chunkBytesFor(1 << 20, 8) == 131072);          // size / sockets is the quantum itself
+  EXPECT(chunkBytesFor(300000, 2) == 151552);           // 150000 rounded up to whole pages
+  EXPECT(chunkBytesFor(100000, 4) == 131072);           // small messages: one chunk of at most the quantum
+  EXPECT(chunkBytesFor(64 << 20, 2) == kMaxAdaptiveChunk);
+  EXPECT(chunkBytesFor(0, 4) == 131072);
+  setenv("NCCL_GPUDIRECTTCPX_ADAPTIVE_CHUNK", "0", 1);
+  reloadFlags();
+  EXPECT(chunkBytesFor(4 << 20, 1) == 131072);
+  unsetenv("NCCL_GPUDIRECTTCPX_ADAPTIVE_CHUNK");
+  unsetenv("NCCL_DYNAMIC_CHUNK_SIZE");
+  reloadFlags();
+}
+
+TEST(stream_counter_on_standin_device) {
+  if (!gpu::available()) { printf("  skipped: no device (set TCPXB_FAKE_GPU=1)\n"); return; }
+  gpu::StreamCounter c;
+  EXPECT(c.init() == kSuccess && c.ready() && c.issued() == 0);
+  EXPECT(c.reached(0) && !c.reached(1));
+  uint32_t a = 0, b = 0;
+  EXPECT(c.mark(nullptr, &a) == kSuccess && a == 1);
+  EXPECT(c.mark(nullptr, &b) == kSuccess && b == 2 && c.issued() == 2);
+  EXPECT(c.reached(1) && c.reached(2) && !c.reached(3));  // the stand-in's streams run everything at once
 }
 
 TEST(result_strings_and_handle_layout) {

@@ -144,6 +144,16 @@ def _props(stdout):
     return rows
 
 
+@pytest.mark.parametrize("which", ["shared_device_allocation", "stream_counter"])
+def test_unit_tests_that_need_the_standin_device(host_lib, which):
+    """Driver-API services (shareable allocation by file descriptor, dma-buf export, context guard) and
+    the stream-ordered host counter, on the host-only library's stand-in device."""
+    r = subprocess.run([str(LIB / "tcpxb_unit_tests"), which], capture_output=True, text=True, timeout=120,
+                       env=dict(os.environ, TCPXB_FAKE_GPU="1"))
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert f"ok {which}" in r.stdout and "skipped" not in r.stdout and "1 test(s), 0 failure(s)" in r.stdout
+
+
 def test_device_properties_as_nccl_sees_them(host_lib):
     """Values of getProperties through both table versions (reference: src/net_tcpx.cc:705-744):
     host pointers only by default, 65536 comms, one receive per irecv, 10000 Mb/s when sysfs has no speed;
@@ -311,7 +321,7 @@ def test_fault_paths_surface_as_errors(host_lib):
     pages: error codes, "try again" or back-pressure, never a hang."""
     r = subprocess.run([str(LIB / "tcpxb_fault_tests")], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert "18 test(s), 0 failure(s)" in r.stdout
+    assert "19 test(s), 0 failure(s)" in r.stdout
 
 
 @pytest.mark.parametrize("san", ["address", "thread", "undefined"])
