@@ -506,6 +506,8 @@ Comm* newComm(int dev, bool passive) {
   c->dev = dev;
   c->passive = passive;
   c->devmem = flags().rx_buf_mgr_devmem;
+  c->helper_nap_us.store((int)flags().helper_nap_us);
+  c->helper_nap_rounds.store((int)flags().helper_nap_rounds);
   c->id = g.next_comm_id.fetch_add(1);
   c->mapper = makeFlowMapper(flags().sched_alg);
   c->rq.reset();

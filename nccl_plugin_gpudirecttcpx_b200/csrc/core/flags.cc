@@ -80,7 +80,7 @@ const IntSpec kInts[] = {
     {kOwn, "NIC_SPEED_MBPS", &Flags::nic_speed_mbps, 0, 100000000, "speed reported to NCCL (0 = sysfs, else 10000)"},
     {kOwn, "CUDA_BUFFERS", &Flags::cuda_buffers, 0, 2, "host receive mode also takes CUDA pointers (plugin-side copies and kernels)"},
     {kOwn, "ADAPTIVE_CHUNK", &Flags::adaptive_chunk, 0, 2, "cut a message into about one chunk per socket (0 = always NCCL_DYNAMIC_CHUNK_SIZE)"},
-    {kOwn, "HELPER_NAP_US", &Flags::helper_nap_us, 0, 100000, "idle helper threads nap this long at a time before sleeping until woken (0 = sleep at once)"},
+    {kOwn, "HELPER_NAP_US", &Flags::helper_nap_us, 0, 100000, "idle helper threads nap this long at a time before sleeping until woken (0 = sleep at once; the collective engine uses 20 for its own comms)"},
     {kOwn, "HELPER_NAP_ROUNDS", &Flags::helper_nap_rounds, 0, 1000000, "naps an idle helper thread takes before it sleeps until woken"},
     {kOwn, "POLL_BLOCK_US", &Flags::poll_block_us, 0, 1000000, "helper threads block in poll() this long when idle on EAGAIN"},
 };

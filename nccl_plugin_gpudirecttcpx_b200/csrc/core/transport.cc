@@ -405,9 +405,10 @@ void helperMain(Comm* comm, int tid) {
     // No task.  Nap in short steps for a while before going to sleep for good: a nap
     // needs nobody to wake it, whereas every real sleep costs the thread that queues
     // the next task a futex system call, and with small requests that is every task.
-    if (f.helper_nap_us > 0 && idle_rounds < 64 + f.helper_nap_rounds) {
+    const int nap_us = comm->helper_nap_us.load(std::memory_order_relaxed);
+    if (nap_us > 0 && idle_rounds < 64 + comm->helper_nap_rounds.load(std::memory_order_relaxed)) {
       const uint64_t t0 = monotonicNanos();
-      struct timespec ts = {0, (long)f.helper_nap_us * 1000};
+      struct timespec ts = {0, (long)nap_us * 1000};
       nanosleep(&ts, nullptr);
       me.idle_ns.fetch_add(monotonicNanos() - t0, std::memory_order_relaxed);
       continue;
@@ -1376,6 +1377,12 @@ Result netIrecvConsumed(Comm* comm, int n, Request* r) {
 }
 
 void netSetSendDependency(Comm* comm, gpu::Event event) { comm->send_dependency = event; }
+
+void netSetHelperNap(Comm* comm, int nap_us, int rounds) {
+  if (comm == nullptr) return;
+  comm->helper_nap_us.store(nap_us < 0 ? 0 : nap_us, std::memory_order_relaxed);
+  comm->helper_nap_rounds.store(rounds < 0 ? 0 : rounds, std::memory_order_relaxed);
+}
 
 Result netSetTxStagingBytes(Comm* comm, uint64_t bytes) {
   if (comm == nullptr || comm->passive || bytes < 4096) return kInvalidArgument;

@@ -655,6 +655,11 @@ int tcpxb_engine_connect(void* engine, const void* next_handles) {
     netSetTxStagingBytes(rail.send, std::min<uint64_t>(want, (uint64_t)flags().tx_staging_bytes));
     ENG_NET(netPrepareCuda(rail.send, e->cfg.gpu_dev));
     ENG_NET(netPrepareCuda(rail.recv, e->cfg.gpu_dev));
+    // a handful of busy comms per process: napping helpers beat a futex call per task
+    if (flags().helper_nap_us == 0) {
+      netSetHelperNap(rail.send, 20, 50);
+      netSetHelperNap(rail.recv, 20, 50);
+    }
     if (e->wake_on_events) {
       netSetNotifier(rail.send, &e->notifier);
       netSetNotifier(rail.recv, &e->notifier);

@@ -90,7 +90,7 @@ struct Flags {
   int64_t nic_speed_mbps = 0;          // NIC_SPEED_MBPS override for getProperties (0 = sysfs, else 10000)
   int64_t cuda_buffers = 0;            // CUDA_BUFFERS: accept CUDA pointers in host receive mode (see transport.h)
   int64_t adaptive_chunk = 1;          // ADAPTIVE_CHUNK: about one chunk per socket and message (see chunkBytesFor)
-  int64_t helper_nap_us = 20;          // HELPER_NAP_US: idle helper threads nap this long at a time ...
+  int64_t helper_nap_us = 0;           // HELPER_NAP_US: idle helper threads nap this long at a time (0 = off; the engine turns it on for its comms) ...
   int64_t helper_nap_rounds = 50;      // HELPER_NAP_ROUNDS: ... this many times before they sleep until woken
   int64_t poll_block_us = 200;         // helper threads block in poll() this long when every socket would block
   std::string rx_pool_mode_name;       // RX_POOL_MODE: host | device

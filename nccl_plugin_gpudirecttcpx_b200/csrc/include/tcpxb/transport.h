@@ -229,6 +229,8 @@ struct Comm {
   std::atomic<bool> stop{false};
   bool threads_started = false;
   int rotate = 0;  // socket the reaping pass starts from
+  // idle helper threads nap this long, this many times, before they sleep until woken (0 = sleep at once)
+  std::atomic<int> helper_nap_us{0}, helper_nap_rounds{0};
   uint32_t kick_mask = 0;        // helpers that got new tasks in the current progress round
   Notifier* notifier = nullptr;  // owned by the caller of netSetNotifier
   // pending control record on the receive side
@@ -314,6 +316,12 @@ Result netIrecvConsumed(Comm* comm, int n, Request* req);
 // netAccept (used by the collective engine, which unpacks with its own kernels).
 void netSetAcceptRecvMode(ListenComm* lcomm, int recv_mode);
 
+// How the comm's idle helper threads wait for their next task, instead of what the
+// HELPER_NAP_* flags say: nap `nap_us` at a time for `rounds` rounds, then sleep on their
+// condition variable.  Naps spare the queueing thread a futex call per task, at the price of
+// periodic wake-ups; right for a process with a handful of busy comms (the collective engine),
+// wrong for one with dozens (NCCL with many channels), hence off by default.
+void netSetHelperNap(Comm* comm, int nap_us, int rounds);
 // Size of a send comm's pinned staging ring for CUDA buffers, instead of the
 // TX_STAGING_BYTES flag.  A ring just large enough for the requests in flight is walked
 // over and over and stays in the CPU's caches; a large one is always cold.  Call before
