@@ -104,6 +104,7 @@ const StrSpec kStrs[] = {
     {kOwn, "RX_POOL_MODE", &Flags::rx_pool_mode_name, "host (pinned, device-mapped) or device (copy-engine placement)"},
     {kOwn, "RECV_MODE", &Flags::recv_mode_name, "host (plugin unpacks) or unpack (NCCL's kernels unpack)"},
     {kOwn, "RX_BUF_MGR", &Flags::rx_buf_mgr_name, "emulated (in process), daemon (tcpxb_rxdm under UNIX_CLIENT_PREFIX), devmem (kernel devmem-TCP sockets, pool from the daemon) or devmem-local (the same with a pool of the process's own)"},
+    {kOwn, "RXDM_WIRE", &Flags::rxdm_wire_name, "native (fixed structs, tcpxb_rxdm) or proto (the protobuf messages and per-GPU socket names of Google's daemon)"},
 };
 
 std::string envName(const char* prefix, const char* name) { return std::string(prefix) + name; }
@@ -208,6 +209,9 @@ void loadFlags(Flags* out) {
   if (!out->rx_buf_mgr_daemon && !out->rx_buf_mgr_devmem && !out->rx_buf_mgr_name.empty() &&
       strcasecmp(out->rx_buf_mgr_name.c_str(), "emulated"))
     WARN("unknown rx buffer manager '%s'; using the in-process one", out->rx_buf_mgr_name.c_str());
+  out->rxdm_wire_proto = !strcasecmp(out->rxdm_wire_name.c_str(), "proto") || !strcasecmp(out->rxdm_wire_name.c_str(), "protobuf");
+  if (!out->rxdm_wire_proto && !out->rxdm_wire_name.empty() && strcasecmp(out->rxdm_wire_name.c_str(), "native"))
+    WARN("unknown rx buffer manager wire format '%s'; using the native one", out->rxdm_wire_name.c_str());
   parseSlownessList(out->slowness_switch.c_str(), out->slow_switch);
   parseSlownessList(out->slowness_report.c_str(), out->slow_report);
   if (out->inline_threshold > out->dynamic_chunk_size) out->inline_threshold = out->dynamic_chunk_size;

@@ -6,11 +6,13 @@
 #include <unistd.h>
 
 #include <sys/mman.h>
+#include <sys/stat.h>
 
 #include "tcpxb/cu_driver.h"
 #include "tcpxb/flags.h"
 #include "tcpxb/gpu.h"
 #include "tcpxb/rxdm.h"
+#include "tcpxb/rxdm_proto.h"
 
 namespace tcpxb {
 
@@ -201,16 +203,39 @@ class DaemonRxBufMgr final : public RxBufMgr {
   Result init() {
     pci_ = dev_ >= 0 ? gpu::pciBusId(dev_) : std::string("host");
     if (pci_.empty()) pci_ = "gpu" + std::to_string(dev_);
-    RxdmMessage q, rep;
-    memset(&q, 0, sizeof q);
-    q.magic = kRxdmMagic;
-    q.type = kRxdmGetGpuMetadata;
-    snprintf(q.gpu.gpu_pci, sizeof q.gpu.gpu_pci, "%s", pci_.c_str());
-    TCPXB_CHECK(rxdmCall(prefix_, "get_gpu_metadata", q, &rep, nullptr));
-    bytes_ = rep.reply.a / kRxPageBytes * kRxPageBytes;
-    device_pool_ = rep.reply.c == (uint64_t)kRxdmPoolDevice;
-    q.type = kRxdmGetGpuFd;
-    TCPXB_CHECK(rxdmCall(prefix_, "get_gpu_fd", q, &rep, &pool_fd_));
+    proto_wire_ = flags().rxdm_wire_proto;
+    if (proto_wire_) {
+      // the reference's exchange: one socket pair per GPU, the request carries the PCI
+      // address as raw bytes, the descriptor comes first and {fd, size, align} second
+      // (reference: src/gpu/rx_pool.cu:62-124)
+      rxproto::Message q, rep;
+      q.kind = rxproto::kRawBytes;
+      q.raw_bytes = pci_;
+      TCPXB_CHECK(rxproto::call(prefix_, "get_gpu_fd_" + pci_, q, nullptr, &pool_fd_));
+      TCPXB_CHECK(rxproto::call(prefix_, "get_gpu_metadata_" + pci_, q, &rep, nullptr));
+      rxproto::GpuMemMetadata md;
+      if (rep.kind != rxproto::kRawBytes || !rxproto::decodeMetadata(rep.raw_bytes, &md)) {
+        WARN("rx buffer manager sent no pool metadata for %s", pci_.c_str());
+        return kRemoteError;
+      }
+      bytes_ = md.size / kRxPageBytes * kRxPageBytes;
+      // That daemon only hands out device memory and says nothing about the kind.  This
+      // repository's daemon can also serve a memfd of host memory, which is a regular
+      // file of the pool's size; a shareable handle of device memory is not.
+      struct stat sb;
+      device_pool_ = !(pool_fd_ >= 0 && fstat(pool_fd_, &sb) == 0 && S_ISREG(sb.st_mode) && (uint64_t)sb.st_size >= md.size);
+    } else {
+      RxdmMessage q, rep;
+      memset(&q, 0, sizeof q);
+      q.magic = kRxdmMagic;
+      q.type = kRxdmGetGpuMetadata;
+      snprintf(q.gpu.gpu_pci, sizeof q.gpu.gpu_pci, "%s", pci_.c_str());
+      TCPXB_CHECK(rxdmCall(prefix_, "get_gpu_metadata", q, &rep, nullptr));
+      bytes_ = rep.reply.a / kRxPageBytes * kRxPageBytes;
+      device_pool_ = rep.reply.c == (uint64_t)kRxdmPoolDevice;
+      q.type = kRxdmGetGpuFd;
+      TCPXB_CHECK(rxdmCall(prefix_, "get_gpu_fd", q, &rep, &pool_fd_));
+    }
     if (pool_fd_ < 0 || bytes_ == 0) { WARN("rx buffer manager sent no pool for %s", pci_.c_str()); return kRemoteError; }
     if (bytes_ > (4ull << 30)) { WARN("rx pool of %lu bytes is larger than 4 GiB (record offsets are 32-bit)", (unsigned long)bytes_); return kInvalidUsage; }
     if (device_pool_) {
@@ -273,8 +298,12 @@ class DaemonRxBufMgr final : public RxBufMgr {
     if (getsockname(fd, &r.local.sa, &ll) != 0 || getpeername(fd, &r.peer.sa, &pl) != 0) return kSystemError;
     r.gpu_pci = gpu_pci.empty() ? pci_ : gpu_pci;
     r.fd = fd;
-    RxdmMessage rep;
-    TCPXB_CHECK(rxdmCall(prefix_, "rx_rule_manager", rxdmMakeRule(kRxdmFlowRule, r.local, r.peer, r.gpu_pci), &rep, nullptr));
+    if (proto_wire_) {
+      TCPXB_CHECK(protoRuleCall("rx_rule_manager", r));
+    } else {
+      RxdmMessage rep;
+      TCPXB_CHECK(rxdmCall(prefix_, "rx_rule_manager", rxdmMakeRule(kRxdmFlowRule, r.local, r.peer, r.gpu_pci), &rep, nullptr));
+    }
     std::lock_guard<std::mutex> l(mu_);
     rules_.push_back(r);
     return kSuccess;
@@ -288,11 +317,24 @@ class DaemonRxBufMgr final : public RxBufMgr {
         if (rules_[i].fd == fd) { found = rules_[i]; rules_.erase(rules_.begin() + (long)i); have = true; break; }
     }
     if (!have) return kSuccess;
+    if (proto_wire_) return protoRuleCall("rx_rule_uninstall", found);
     RxdmMessage rep;
     return rxdmCall(prefix_, "rx_rule_uninstall", rxdmMakeRule(kRxdmFlowRuleUninstall, found.local, found.peer, found.gpu_pci),
                     &rep, nullptr);
   }
   Result registerApplication(int pid) override {
+    if (proto_wire_) {
+      // the registration is the open connection here too; the daemon learns the pid from the socket's credentials
+      rxproto::Message m, rep;
+      m.kind = rxproto::kAppRegister;
+      m.register_client = true;
+      int fd = -1;
+      TCPXB_CHECK(proto_keepalive_.connectTo(prefix_ + "/rxdm_application_registry"));
+      TCPXB_CHECK(proto_keepalive_.sendMessage(m));
+      Result r = proto_keepalive_.recv(&rep, &fd);
+      if (fd >= 0) close(fd);
+      return r == kSuccess ? kSuccess : kRemoteError;
+    }
     RxdmMessage m, rep;
     memset(&m, 0, sizeof m);
     m.magic = kRxdmMagic;
@@ -306,6 +348,14 @@ class DaemonRxBufMgr final : public RxBufMgr {
     return (r == kSuccess && rep.reply.status == 0) ? kSuccess : kRemoteError;
   }
   Result deregisterApplication(int /*pid*/) override {
+    if (proto_wire_ && proto_keepalive_.fd() >= 0) {
+      rxproto::Message m, rep;
+      m.kind = rxproto::kAppRegister;
+      m.register_client = false;
+      (void)rxproto::call(prefix_, "rxdm_application_registry", m, &rep, nullptr);
+      proto_keepalive_.closeNow();
+      return kSuccess;
+    }
     keepalive_.closeNow();
     return kSuccess;
   }
@@ -315,8 +365,20 @@ class DaemonRxBufMgr final : public RxBufMgr {
   }
 
  private:
+  Result protoRuleCall(const char* service, const FlowRule& r) {
+    rxproto::Message rep;
+    TCPXB_CHECK(rxproto::call(prefix_, service, rxproto::makeRule(r.local, r.peer, r.gpu_pci), &rep, nullptr));
+    if (rep.kind != rxproto::kRawBytes || rep.raw_bytes != "Ok.") {
+      WARN("rx buffer manager refused %s: %s", service, rep.kind == rxproto::kRawBytes ? rep.raw_bytes.c_str() : "(no text)");
+      return kRemoteError;
+    }
+    return kSuccess;
+  }
+
   int dev_;
   std::string prefix_, pci_;
+  bool proto_wire_ = false;
+  rxproto::Connection proto_keepalive_;
   std::mutex mu_;
   std::unique_ptr<PageAllocator> alloc_;
   uint8_t* host_base_ = nullptr;

@@ -96,12 +96,14 @@ struct Flags {
   std::string rx_pool_mode_name;       // RX_POOL_MODE: host | device
   std::string recv_mode_name;          // RECV_MODE: host | unpack
   std::string rx_buf_mgr_name;         // RX_BUF_MGR: emulated (in process) | daemon (tcpxb_rxdm over UNIX sockets) | devmem (kernel devmem-TCP)
+  std::string rxdm_wire_name;          // RXDM_WIRE: native | proto
   // --- derived
   int sched_alg = kSchedRR;
   int rx_pool_mode = kRxPoolHostMapped;
   int recv_mode = kRecvModeHost;
   bool recv_mode_fell_back = false;  // unpack was asked for without NCCL_PROTO=Simple + NCCL_ALGO=Ring
   bool rx_buf_mgr_daemon = false;
+  bool rxdm_wire_proto = false;       // talk to the daemon in the reference's protobuf wire format
   bool rx_buf_mgr_devmem = false;    // devmem-TCP datapath: pool from the daemon, fragments from the kernel
   bool slow_switch[kSlowKinds] = {false, false, false};
   bool slow_report[kSlowKinds] = {false, false, false};

@@ -2,6 +2,7 @@
 // application tables, and serves them to plugin processes over AF_UNIX sockets.
 //
 //   tcpxb_rxdm --prefix /tmp/tcpxb --pool-mb 1024 [--max-rules 65536] [--device-pool]
+//              [--wire proto [--gpu-pci ADDR,ADDR,...]]
 //
 // It stands in for the external daemon the reference depends on (reference:
 // README.md:14-16 names it; its clients are src/rx_buf_mgr_client/*).  One pool per
@@ -14,6 +15,13 @@
 // the one that can do that on real hardware.  A client that registers keeps its connection open; when
 // the connection closes the client is deregistered and its flow rules are dropped,
 // which is how a crashed job is cleaned up.
+//
+// --wire proto serves the reference's own wire format instead of this repository's
+// fixed structs: protobuf `UnixSocketProto` bodies, one `get_gpu_fd_<pci>` /
+// `get_gpu_metadata_<pci>` socket pair per GPU, "Ok." replies as raw bytes (reference:
+// src/rx_buf_mgr_client/proto/unix_socket_proto.proto:17-70, rx_rule_client.cc:38-75,
+// src/gpu/rx_pool.cu:62-124).  A plugin started with NCCL_GPUDIRECTTCPX_RXDM_WIRE=proto
+// talks to it, and by the same messages to the daemon the reference was written for.
 #include <poll.h>
 #include <signal.h>
 #include <stdio.h>
@@ -32,6 +40,7 @@
 #include "tcpxb/cu_driver.h"
 #include "tcpxb/gpu.h"
 #include "tcpxb/rxdm.h"
+#include "tcpxb/rxdm_proto.h"
 
 using namespace tcpxb;
 
@@ -53,6 +62,8 @@ struct State {
   uint64_t pool_bytes = 1ull << 30;
   size_t max_rules = 65536;
   bool device_pool = false;
+  bool proto_wire = false;
+  std::vector<std::string> gpu_pcis;  // proto wire: the GPUs that get a socket pair of their own
   std::vector<Rule> rules;
   std::map<int, int> apps;  // connection fd -> pid
   std::map<std::string, Pool> pools;
@@ -172,6 +183,88 @@ bool serve(State* st, UnixSocketConnection* c, const std::string& service) {
   }
 }
 
+RxdmFlowRule ruleFromProto(const rxproto::Message& m) {
+  RxdmFlowRule r;
+  memset(&r, 0, sizeof r);
+  snprintf(r.src_ip, sizeof r.src_ip, "%s", m.src.ip.c_str());
+  r.src_port = (uint16_t)m.src.port;
+  snprintf(r.dst_ip, sizeof r.dst_ip, "%s", m.dst.ip.c_str());
+  r.dst_port = (uint16_t)m.dst.port;
+  r.flow_type = m.flow_type;
+  r.queue_id = m.has_queue_id ? m.queue_id : -1;
+  snprintf(r.gpu_pci, sizeof r.gpu_pci, "%s", m.gpu_pci_addr.c_str());
+  return r;
+}
+
+rxproto::Message rawReply(const std::string& text) {
+  rxproto::Message m;
+  m.kind = rxproto::kRawBytes;
+  m.raw_bytes = text;
+  return m;
+}
+
+// The same services in the reference's wire format.  `service` is the socket's file name;
+// the per-GPU sockets carry the PCI address after their last underscore-separated stem.
+bool serveProto(State* st, rxproto::Connection* c, const std::string& service) {
+  rxproto::Message m;
+  int passed = -1;
+  if (c->recv(&m, &passed, 2000) != kSuccess) return false;
+  if (passed >= 0) { close(passed); return false; }
+  if (service == "rx_rule_manager" || service == "rx_rule_uninstall") {
+    if (m.kind != rxproto::kFlowSteerRule || !m.has_ntuple || !m.src.present || !m.dst.present) {
+      c->sendMessage(rawReply("Invalid argument: the request carries no flow-steering rule"));
+      return false;
+    }
+    const RxdmFlowRule r = ruleFromProto(m);
+    if (service == "rx_rule_manager") {
+      if (st->rules.size() >= st->max_rules) { c->sendMessage(rawReply("Resource exhausted: rule table full")); return false; }
+      st->rules.push_back(Rule{r, -1});
+      c->sendMessage(rawReply("Ok."));
+      return false;
+    }
+    for (size_t i = 0; i < st->rules.size(); ++i)
+      if (sameRule(st->rules[i].r, r)) { st->rules.erase(st->rules.begin() + (long)i); c->sendMessage(rawReply("Ok.")); return false; }
+    c->sendMessage(rawReply("Not found: no such rule"));
+    return false;
+  }
+  const std::string fd_stem = "get_gpu_fd_", md_stem = "get_gpu_metadata_";
+  if (service.compare(0, fd_stem.size(), fd_stem) == 0 || service.compare(0, md_stem.size(), md_stem) == 0) {
+    const bool want_fd = service.compare(0, fd_stem.size(), fd_stem) == 0;
+    const std::string pci = service.substr(want_fd ? fd_stem.size() : md_stem.size());
+    if (m.kind != rxproto::kRawBytes || m.raw_bytes != pci) {
+      c->sendMessage(rawReply("Invalid argument: the request names another GPU than the socket"));
+      return false;
+    }
+    Pool* p = poolFor(st, pci);
+    if (p == nullptr) { c->sendMessage(rawReply("Internal: pool creation failed")); return false; }
+    if (want_fd) { c->sendFd(p->fd); return false; }
+    rxproto::GpuMemMetadata md;
+    md.fd = p->fd;  // the daemon's own number, as the reference's daemon sends it; meaningless to the client
+    md.size = p->size;
+    md.align = p->align;
+    c->sendMessage(rawReply(rxproto::encodeMetadata(md)));
+    return false;
+  }
+  if (service == "rxdm_application_registry") {
+    if (m.kind != rxproto::kAppRegister) { c->sendMessage(rawReply("Invalid argument: not a registration")); return false; }
+    struct ucred cred;
+    socklen_t len = sizeof cred;
+    const int pid = getsockopt(c->fd(), SOL_SOCKET, SO_PEERCRED, &cred, &len) == 0 ? (int)cred.pid : -1;
+    if (m.register_client) {
+      st->apps[c->fd()] = pid;
+      c->sendMessage(rawReply("Ok."));
+      return true;  // keep-alive connection
+    }
+    for (auto it = st->apps.begin(); it != st->apps.end();)
+      it = (it->second == pid) ? st->apps.erase(it) : std::next(it);
+    fprintf(stderr, "[rxdm] application %d deregistered\n", pid);
+    c->sendMessage(rawReply("Ok."));
+    return false;
+  }
+  c->sendMessage(rawReply("Unimplemented: unknown service"));
+  return false;
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -181,10 +274,12 @@ int main(int argc, char** argv) {
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
     if (a == "--help" || a == "-h") {
-      printf("usage: tcpxb_rxdm [--prefix DIR] [--pool-mb N] [--max-rules N] [--device-pool]\n"
+      printf("usage: tcpxb_rxdm [--prefix DIR] [--pool-mb N] [--max-rules N] [--device-pool] [--wire native|proto] [--gpu-pci A,B,...]\n"
              "       tcpxb_rxdm --status [--prefix DIR]\n"
              "Serves the rx buffer manager's UNIX sockets under DIR (default /tmp) until SIGINT or SIGTERM;\n"
-             "with --status asks a running daemon under DIR for its counters and prints one JSON line.\n");
+             "with --status asks a running daemon under DIR for its counters and prints one JSON line.\n"
+             "--wire proto speaks the protobuf messages of Google's daemon, with one get_gpu_fd_<pci> / get_gpu_metadata_<pci>\n"
+             "socket pair per GPU (--gpu-pci lists them; default: every GPU of the machine, or \"host\" without one).\n");
       return 0;
     }
     if (a == "--status") { status_only = true; continue; }
@@ -194,6 +289,18 @@ int main(int argc, char** argv) {
     if (a == "--prefix") st.prefix = v;
     else if (a == "--pool-mb") st.pool_bytes = strtoull(v, nullptr, 0) << 20;
     else if (a == "--max-rules") st.max_rules = strtoull(v, nullptr, 0);
+    else if (a == "--wire") {
+      if (!strcmp(v, "proto")) st.proto_wire = true;
+      else if (strcmp(v, "native")) { fprintf(stderr, "--wire takes native or proto\n"); return 2; }
+    } else if (a == "--gpu-pci") {
+      std::string list = v;
+      for (size_t pos = 0; pos <= list.size();) {
+        size_t comma = list.find(',', pos);
+        if (comma == std::string::npos) comma = list.size();
+        if (comma > pos) st.gpu_pcis.push_back(list.substr(pos, comma - pos));
+        pos = comma + 1;
+      }
+    }
     else { fprintf(stderr, "unknown argument %s (see --help)\n", a.c_str()); return 2; }
   }
   if (status_only) {
@@ -214,44 +321,63 @@ int main(int argc, char** argv) {
   signal(SIGTERM, onSignal);
   signal(SIGPIPE, SIG_IGN);
   // fixed services; the per-GPU ones share a wildcard socket each: the client names the GPU in the request
-  const std::vector<std::string> services = {"rx_rule_manager", "rx_rule_uninstall", "get_gpu_fd", "get_gpu_metadata",
-                                             "rxdm_application_registry", "rxdm_status"};
+  std::vector<std::string> services = {"rx_rule_manager", "rx_rule_uninstall", "get_gpu_fd", "get_gpu_metadata",
+                                       "rxdm_application_registry", "rxdm_status"};
+  if (st.proto_wire) {
+    if (st.gpu_pcis.empty()) {
+      for (int d = 0; d < gpu::deviceCount(); ++d) {
+        const std::string pci = gpu::pciBusId(d);
+        st.gpu_pcis.push_back(pci.empty() ? "gpu" + std::to_string(d) : pci);
+      }
+      if (st.gpu_pcis.empty()) st.gpu_pcis.push_back("host");
+    }
+    services = {"rx_rule_manager", "rx_rule_uninstall", "rxdm_application_registry", "rxdm_status"};
+    for (const auto& pci : st.gpu_pcis) {
+      services.push_back("get_gpu_fd_" + pci);
+      services.push_back("get_gpu_metadata_" + pci);
+    }
+  }
   std::vector<int> lfds;
   for (const auto& s : services) {
     int fd = listenOn(st.prefix + "/" + s);
     if (fd < 0) { fprintf(stderr, "[rxdm] cannot listen on %s/%s\n", st.prefix.c_str(), s.c_str()); return 1; }
     lfds.push_back(fd);
   }
-  fprintf(stderr, "[rxdm] serving under %s\n", st.prefix.c_str());
+  fprintf(stderr, "[rxdm] serving under %s (%s wire format)\n", st.prefix.c_str(), st.proto_wire ? "protobuf" : "native");
   printf("ready\n");
   fflush(stdout);
-  std::vector<UnixSocketConnection*> keep;
+  std::vector<int> keep;  // registered applications' connections
   while (!g_stop) {
     std::vector<struct pollfd> pfds;
     for (int fd : lfds) pfds.push_back({fd, POLLIN, 0});
-    for (auto* k : keep) pfds.push_back({k->fd(), POLLIN, 0});
+    for (int k : keep) pfds.push_back({k, POLLIN, 0});
     int pr = poll(pfds.data(), (nfds_t)pfds.size(), 500);
     if (pr <= 0) continue;
     for (size_t i = 0; i < lfds.size(); ++i) {
       if (!(pfds[i].revents & POLLIN)) continue;
       int cfd = accept(lfds[i], nullptr, nullptr);
       if (cfd < 0) continue;
-      auto* c = new UnixSocketConnection(cfd);
-      if (serve(&st, c, services[i])) keep.push_back(c);
-      else delete c;
+      // the status service keeps this repository's framing in both modes (the reference has no such service)
+      if (st.proto_wire && services[i] != "rxdm_status") {
+        rxproto::Connection c(cfd);
+        if (serveProto(&st, &c, services[i])) keep.push_back(c.release());
+      } else {
+        UnixSocketConnection c(cfd);
+        if (serve(&st, &c, services[i])) keep.push_back(c.release());
+      }
     }
     for (size_t k = 0; k < keep.size();) {
       const struct pollfd& p = pfds[lfds.size() + k];
       if (p.revents & (POLLIN | POLLHUP | POLLERR)) {
         char b;
-        ssize_t n = recv(keep[k]->fd(), &b, 1, MSG_DONTWAIT);
+        ssize_t n = recv(keep[k], &b, 1, MSG_DONTWAIT);
         if (n == 0 || (n < 0 && errno != EAGAIN)) {
-          auto it = st.apps.find(keep[k]->fd());
+          auto it = st.apps.find(keep[k]);
           if (it != st.apps.end()) {
             fprintf(stderr, "[rxdm] application %d went away\n", it->second);
             st.apps.erase(it);
           }
-          delete keep[k];
+          close(keep[k]);
           keep.erase(keep.begin() + (long)k);
           pfds.erase(pfds.begin() + (long)(lfds.size() + k));
           continue;
@@ -260,7 +386,7 @@ int main(int argc, char** argv) {
       ++k;
     }
   }
-  for (auto* k : keep) delete k;
+  for (int k : keep) close(k);
   for (size_t i = 0; i < lfds.size(); ++i) { close(lfds[i]); unlink((st.prefix + "/" + services[i]).c_str()); }
   for (auto& p : st.pools) {
     close(p.second.fd);

@@ -34,6 +34,7 @@
 #include "tcpxb/gpu.h"
 #include "tcpxb/rx_buf_mgr.h"
 #include "tcpxb/rxdm.h"
+#include "tcpxb/rxdm_proto.h"
 #include "tcpxb/socket_utils.h"
 #include "tcpxb/stage_ring.h"
 #include "tcpxb/telemetry.h"
@@ -454,6 +455,9 @@ TEST(rxdm_daemon_roundtrip) {
   if (prefix == nullptr) { printf("  (no daemon: skipped)\n"); return; }
   setenv("NCCL_GPUDIRECTTCPX_RX_BUF_MGR", "daemon", 1);
   setenv("NCCL_GPUDIRECTTCPX_UNIX_CLIENT_PREFIX", prefix, 1);
+  // the daemon under test may speak the reference's protobuf wire format instead of the native one
+  const bool proto = getenv("TCPXB_TEST_RXDM_WIRE") != nullptr && !strcmp(getenv("TCPXB_TEST_RXDM_WIRE"), "proto");
+  if (proto) setenv("NCCL_GPUDIRECTTCPX_RXDM_WIRE", "proto", 1);
   reloadFlags();
   auto status = [&](uint64_t* rules, uint64_t* apps, uint64_t* pools) {
     RxdmMessage q, rep;
@@ -474,13 +478,26 @@ TEST(rxdm_daemon_roundtrip) {
   EXPECT(m->allocPages(4, &runs));
   memset(m->hostBase() + (uint64_t)runs[0].first * kRxPageBytes, 0x5a, kRxPageBytes);
   // a second mapping of the same pool sees the bytes: the pool really is shared
-  RxdmMessage q, rep;
-  memset(&q, 0, sizeof q);
-  q.magic = kRxdmMagic;
-  q.type = kRxdmGetGpuFd;
-  snprintf(q.gpu.gpu_pci, sizeof q.gpu.gpu_pci, "host");
   int fd = -1;
-  EXPECT(rxdmCall(prefix, "get_gpu_fd", q, &rep, &fd) == kSuccess && fd >= 0 && rep.reply.a == (8u << 20));
+  if (proto) {
+    rxproto::Message pq;
+    pq.kind = rxproto::kRawBytes;
+    pq.raw_bytes = "host";
+    EXPECT(rxproto::call(prefix, "get_gpu_fd_host", pq, nullptr, &fd) == kSuccess && fd >= 0);
+    // a request that names another GPU than the socket gets words back, not a descriptor
+    rxproto::Message bad = pq, words;
+    bad.raw_bytes = "0000:ff:00.0";
+    int none = -1;
+    EXPECT(rxproto::call(prefix, "get_gpu_fd_host", bad, &words, &none) == kSuccess && none < 0 && words.kind == rxproto::kRawBytes &&
+           words.raw_bytes.find("Invalid argument") == 0);
+  } else {
+    RxdmMessage q, rep;
+    memset(&q, 0, sizeof q);
+    q.magic = kRxdmMagic;
+    q.type = kRxdmGetGpuFd;
+    snprintf(q.gpu.gpu_pci, sizeof q.gpu.gpu_pci, "host");
+    EXPECT(rxdmCall(prefix, "get_gpu_fd", q, &rep, &fd) == kSuccess && fd >= 0 && rep.reply.a == (8u << 20));
+  }
   if (fd >= 0) {
     uint8_t probe = 0;
     EXPECT(pread(fd, &probe, 1, (off_t)runs[0].first * kRxPageBytes + 100) == 1 && probe == 0x5a);
@@ -511,7 +528,91 @@ TEST(rxdm_daemon_roundtrip) {
   close(cfd); close(sfd); close(lfd);
   unsetenv("NCCL_GPUDIRECTTCPX_RX_BUF_MGR");
   unsetenv("NCCL_GPUDIRECTTCPX_UNIX_CLIENT_PREFIX");
+  unsetenv("NCCL_GPUDIRECTTCPX_RXDM_WIRE");
   reloadFlags();
+}
+
+// The protobuf bytes of the daemon protocol, against encodings worked out from the schema
+// by hand (and cross-checked against the protobuf library by the Python tests).
+TEST(rxdm_proto_wire_bytes) {
+  using namespace rxproto;
+  auto hex = [](const std::string& b) {
+    std::string h;
+    char t[4];
+    for (unsigned char c : b) { snprintf(t, sizeof t, "%02x", c); h += t; }
+    return h;
+  };
+  Message ok;
+  ok.kind = kRawBytes;
+  ok.raw_bytes = "Ok.";
+  EXPECT(hex(encode(ok)) == "0a034f6b2e");
+  Message rule;
+  rule.kind = kFlowSteerRule;
+  rule.has_ntuple = true;
+  rule.flow_type = kFlowTcpV4;
+  rule.src.present = rule.dst.present = true;
+  rule.src.ip = "10.0.0.1"; rule.src.port = 5000;
+  rule.dst.ip = "10.0.0.2"; rule.dst.port = 6000;
+  rule.has_queue_id = true; rule.queue_id = 3;
+  rule.gpu_pci_addr = "0000:1b:00.0";
+  const std::string rule_hex =
+      "1232" "0a20" "0801" "120d" "0a08" "31302e302e302e31" "108827" "1a0d" "0a08" "31302e302e302e32" "10f02e"
+      "1003" "1a0c" "303030303a31623a30302e30";
+  EXPECT(hex(encode(rule)) == rule_hex);
+  Message back;
+  const std::string wire = encode(rule);
+  EXPECT(decode(wire.data(), wire.size(), &back) && back.kind == kFlowSteerRule && back.has_ntuple && back.flow_type == 1 &&
+         back.src.ip == "10.0.0.1" && back.src.port == 5000 && back.dst.ip == "10.0.0.2" && back.dst.port == 6000 && back.has_queue_id &&
+         back.queue_id == 3 && back.gpu_pci_addr == "0000:1b:00.0");
+  Message reg;
+  reg.kind = kAppRegister;
+  reg.register_client = true;
+  EXPECT(hex(encode(reg)) == "32020801");
+  Message query;
+  query.kind = kQueueIdQuery;
+  query.gpu_pci_addr = "0000:1b:00.0";
+  EXPECT(hex(encode(query)) == "1a0e0a0c303030303a31623a30302e30");
+  Message resp;
+  resp.kind = kQueueIdResponse;
+  resp.queue_ids = {8, 9, 300};
+  EXPECT(hex(encode(resp)) == "22070808" "0809" "08ac02");
+  // both encodings of a repeated int32 decode: one tag per element, and packed
+  const unsigned char packed[] = {0x22, 0x06, 0x0a, 0x04, 0x08, 0x09, 0xac, 0x02};
+  EXPECT(decode(packed, sizeof packed, &back) && back.kind == kQueueIdResponse && back.queue_ids.size() == 3 && back.queue_ids[2] == 300);
+  EXPECT(decode(encode(resp).data(), encode(resp).size(), &back) && back.queue_ids.size() == 3 && back.queue_ids[0] == 8);
+  // a negative int32 takes ten bytes on the wire and comes back negative
+  Message neg;
+  neg.kind = kFlowSteerRule;
+  neg.has_queue_id = true;
+  neg.queue_id = -1;
+  EXPECT(hex(encode(neg)) == "120b10ffffffffffffffffff01");
+  EXPECT(decode(encode(neg).data(), encode(neg).size(), &back) && back.queue_id == -1);
+  // unknown fields are skipped, whatever their wire type; truncated input is refused
+  const unsigned char with_unknown[] = {0x38, 0x05, 0x0a, 0x03, 'O', 'k', '.', 0x45, 1, 2, 3, 4, 0x49, 1, 2, 3, 4, 5, 6, 7, 8};
+  EXPECT(decode(with_unknown, sizeof with_unknown, &back) && back.kind == kRawBytes && back.raw_bytes == "Ok.");
+  EXPECT(!decode(with_unknown, 4, &back));
+  const unsigned char endless_varint[] = {0x0a, 0xff, 0xff, 0xff, 0xff, 0xff, 0xff, 0xff, 0xff, 0xff, 0xff, 0xff};
+  EXPECT(!decode(endless_varint, sizeof endless_varint, &back));
+  EXPECT(decode(nullptr, 0, &back) && back.kind == kNone);
+  // pool metadata: the daemon's struct {int fd; size_t size; size_t align} as raw bytes
+  GpuMemMetadata md, md2;
+  md.fd = 17; md.size = 1ull << 30; md.align = 2 << 20;
+  const std::string raw = encodeMetadata(md);
+  EXPECT(raw.size() == 24 && decodeMetadata(raw, &md2) && md2.fd == 17 && md2.size == (1ull << 30) && md2.align == (2u << 20));
+  EXPECT(!decodeMetadata(raw.substr(0, 20), &md2));
+  // framing over a socket pair: message, descriptor, message
+  int sv[2];
+  EXPECT(socketpair(AF_UNIX, SOCK_STREAM, 0, sv) == 0);
+  {
+    Connection a(sv[0]), b(sv[1]);
+    EXPECT(a.sendMessage(rule) == kSuccess && a.sendFd(sv[0]) == kSuccess && a.sendMessage(ok) == kSuccess);
+    int fd = -1;
+    EXPECT(b.recv(&back, &fd) == kSuccess && fd < 0 && back.kind == kFlowSteerRule && back.dst.port == 6000);
+    EXPECT(b.recv(&back, &fd) == kSuccess && fd >= 0);
+    if (fd >= 0) close(fd);
+    EXPECT(b.recv(&back, &fd) == kSuccess && fd < 0 && back.kind == kRawBytes && back.raw_bytes == "Ok.");
+    EXPECT(b.recv(&back, &fd, 50) == kInProgress);
+  }
 }
 
 TEST(dev_queue_fifo) {

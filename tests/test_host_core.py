@@ -400,8 +400,9 @@ def test_daemon_pool_carries_device_receives_on_standin_device(host_lib, tmp_pat
     assert f"pool for GPU 0000:00:00.0: 32 MiB of {pool} memory" in log, log[-2000:]  # the pool came from the daemon
 
 
+@pytest.mark.parametrize("wire", ["native", "proto"])
 @pytest.mark.parametrize("san", ["", "address"])
-def test_rx_buffer_manager_daemon_survives_garbage(tmp_path, san):
+def test_rx_buffer_manager_daemon_survives_garbage(tmp_path, san, wire):
     """Random bytes, truncated frames and oversize lengths on every service socket: the daemon drops the
     connection and keeps serving."""
     import random
@@ -412,16 +413,22 @@ def test_rx_buffer_manager_daemon_survives_garbage(tmp_path, san):
         _build.build_host(sanitize=san)
     else:
         _build.build_host()
-    daemon = subprocess.Popen([str(LIB / ("tcpxb_rxdm" + ("_" + san if san else ""))), "--prefix", str(prefix), "--pool-mb", "4"],
+    daemon = subprocess.Popen([str(LIB / ("tcpxb_rxdm" + ("_" + san if san else ""))), "--prefix", str(prefix), "--pool-mb", "4",
+                               "--wire", wire],
                               stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
                               env=dict(os.environ, ASAN_OPTIONS="detect_leaks=0"))
     try:
         assert daemon.stdout.readline().strip() == "ready"
         rng = random.Random(7)
-        services = ["rx_rule_manager", "rx_rule_uninstall", "get_gpu_fd", "get_gpu_metadata", "rxdm_application_registry", "rxdm_status"]
+        per_gpu = ["get_gpu_fd", "get_gpu_metadata"] if wire == "native" else ["get_gpu_fd_host", "get_gpu_metadata_host"]
+        services = ["rx_rule_manager", "rx_rule_uninstall", "rxdm_application_registry", "rxdm_status"] + per_gpu
         for name in services:
             for payload in (b"", b"\x00", struct.pack("!H", 65535) + b"x" * 100, struct.pack("!H", 8) + b"12345678",
-                            bytes(rng.randrange(256) for _ in range(600)), struct.pack("!H", 300)):
+                            bytes(rng.randrange(256) for _ in range(600)), struct.pack("!H", 300),
+                            # well-framed protobuf with nested lengths that overrun, an endless varint, a huge field number
+                            struct.pack("!H", 6) + bytes([0x12, 0x7f, 0x0a, 0x7f, 0x08, 0x01]),
+                            struct.pack("!H", 12) + bytes([0x0a] + [0xff] * 11),
+                            struct.pack("!H", 7) + bytes([0xf8, 0xff, 0xff, 0xff, 0x0f, 0x01, 0x00])):
                 s = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
                 s.settimeout(2)
                 s.connect(str(prefix / name))
