@@ -694,8 +694,21 @@ int tcpxb_engine_all_reduce(void* engine, const void* in_, void* out_, uint64_t 
   if (bytes == 0 || bytes % unit != 0) return fail("all_reduce size must be a multiple of %s%ld bytes", "", (long)unit);
   const uint8_t* in = static_cast<const uint8_t*>(in_);
   uint8_t* out = static_cast<uint8_t*>(out_);
-  if (e->G > 1 && (in != e->work[e->local] || out != e->out[e->local] || bytes > e->buffer_bytes))
-    return fail("with several GPUs per node, in/out must be the registered work/output buffers%s", "");
+  if (e->G > 1 && bytes > e->buffer_bytes) return fail("all_reduce of %s%ld bytes does not fit the symmetric buffers", "", (long)bytes);
+  // Several GPUs per node: peers read the input and write the output through the
+  // symmetric buffers.  Tensors that live elsewhere are staged in and out by device
+  // copies on the caller's stream.  The previous call ended with every local peer's
+  // fan-out signal, which those peers sent after their last read of this GPU's work
+  // buffer, so the buffer is free to overwrite here.
+  uint8_t* user_out = nullptr;
+  if (e->G > 1 && in != e->work[e->local]) {
+    ENG_NET(gpu::copyDeviceToDeviceAsync(e->work[e->local], in, bytes, stream));
+    in = e->work[e->local];
+  }
+  if (e->G > 1 && out != e->out[e->local]) {
+    user_out = out;
+    out = e->out[e->local];
+  }
   ++e->epoch;
   const uint64_t shard = bytes / (uint64_t)e->G;
   const uint64_t shard_off = shard * (uint64_t)e->local;
@@ -762,6 +775,7 @@ int tcpxb_engine_all_reduce(void* engine, const void* in_, void* out_, uint64_t 
     }
   }
   ENG_TRY(waitFanout(e, stream));
+  if (user_out != nullptr) ENG_NET(gpu::copyDeviceToDeviceAsync(user_out, out, bytes, stream));
   return 0;
 }
 

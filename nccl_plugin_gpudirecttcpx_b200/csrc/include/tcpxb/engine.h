@@ -87,9 +87,12 @@ int tcpxb_engine_connect(void* engine, const void* next_handles);
 int tcpxb_engine_set_peers(void* engine, void* const* work_ptrs, void* const* out_ptrs,
                            uint32_t* const* flag_ptrs, void* mc_out, uint64_t buffer_bytes);
 
-// Collectives.  With gpus_per_node > 1, `in` must be this rank's work buffer and
-// `out` its output buffer as registered with tcpxb_engine_set_peers.  With one GPU per
-// node, `out` may be `in` (in place; between two nodes that costs one device copy).
+// Collectives.  With gpus_per_node > 1 the peers read and write the buffers registered
+// with tcpxb_engine_set_peers: all_gather and reduce_scatter take exactly those (`in` =
+// this rank's work buffer where it is read by peers, `out` = its output buffer);
+// all_reduce also takes any other device pointers, `out` == `in` included, and stages them
+// through the registered buffers with one device copy each way.  With one GPU per node,
+// `out` may be `in` (in place; between two nodes that costs one device copy).
 int tcpxb_engine_all_reduce(void* engine, const void* in, void* out, uint64_t bytes, int dtype, void* stream);
 // all_gather: `in` holds bytes_per_rank; out receives world x bytes_per_rank in rank order.
 int tcpxb_engine_all_gather(void* engine, const void* in, void* out, uint64_t bytes_per_rank, void* stream);

@@ -9,9 +9,9 @@ transport: this plugin (`plugin`: host buffers; `unpack`: NCCL's kernels unpack 
 the rx page pool) or NCCL's own socket transport (`socket`, the baseline, with the
 same thread / socket / chunk settings).  `engine` keeps NCCL for set-up only and
 reduces every gradient bucket through the hierarchical engine (fused unpack + reduce +
-NVLink fan-out kernels) from a DDP communication hook; the hook hands buckets to a
-worker thread with its own stream, so backward keeps running while a bucket is on the
-wire.  Model, optimizer and bucketing are stock
+NVLink fan-out kernels) from a DDP communication hook; the hook queues buckets on the
+engine's own thread and stream (`all_reduce_async`), so backward keeps running while
+buckets are on the wire.  Model, optimizer and bucketing are stock
 PyTorch: Llama-style decoder, AdamW, DistributedDataParallel with 25 MB buckets
 overlapped with backward.  Synthetic uniform token ids, random-init weights.
 Rank 0 prints one JSON line with the device-timed step time (max over ranks).
@@ -61,10 +61,13 @@ def setup_env(args, rank: int) -> None:
 class EngineBucketReducer:
     """Averages DDP's gradient buckets through the hierarchical engine.
 
-    The engine's calls block their caller until the network part is done, so they run on
-    a worker thread with its own stream: the hook only records where the bucket became
-    ready and returns a future, backward goes on, and the future completes (carrying the
-    worker stream's event on CUDA) when the averaged bucket is in place."""
+    The hook queues each bucket, in place, on the engine's own thread and stream
+    (`all_reduce_async`, ordered behind the point backward has reached on the current
+    stream) and returns a future at once, so backward keeps running while buckets are on
+    the wire and several buckets can be queued.  A small waiter thread only turns finished
+    jobs into completed futures, in order: it joins the job, scales the bucket on a side
+    stream that waits for the engine's kernels, and completes the future (which carries
+    that stream's event on CUDA)."""
 
     def __init__(self, engine, ranks: int, device):
         import queue
@@ -74,28 +77,38 @@ class EngineBucketReducer:
         self.cuda = device.type == "cuda"
         self.stream = torch.cuda.Stream(device=device) if self.cuda else None
         self.buckets = 0
+        self._unit = engine._all_reduce_unit()
         self._q = queue.Queue()
-        self._thread = threading.Thread(target=self._work, name="tcpxb-ddp", daemon=True)
+        self._thread = threading.Thread(target=self._complete, name="tcpxb-ddp", daemon=True)
         self._thread.start()
 
     def hook(self, _state, bucket):
         import torch
         buf = bucket.buffer()
         fut = torch.futures.Future(devices=[self.device]) if self.cuda else torch.futures.Future()
-        ready = None
-        if self.cuda:
-            ready = torch.cuda.Event()
-            ready.record(torch.cuda.current_stream(self.device))
-        self._q.put((buf, ready, fut))
+        try:
+            nbytes = buf.numel() * buf.element_size()
+            staged = None
+            if nbytes % self._unit != 0 or not buf.is_contiguous():
+                # off the native granularity: travel zero-padded in a tensor of the job's own
+                padded = (nbytes + self._unit - 1) // self._unit * self._unit
+                staged = torch.zeros(padded // buf.element_size(), dtype=buf.dtype, device=buf.device)
+                staged[:buf.numel()].copy_(buf.reshape(-1))
+            t = staged if staged is not None else buf
+            work = self.engine.all_reduce_async(t, out=t)
+            self._q.put((work, buf, staged, fut))
+        except Exception as e:
+            fut.set_exception(e)
         return fut
 
-    def _reduce(self, buf):
-        res = self.engine.all_reduce(buf)   # a fresh tensor, or a view of the symmetric output
-        buf.copy_(res.view_as(buf))
+    def _finish(self, work, buf, staged):
+        res = work.wait()  # the current stream now waits for the engine's kernels
+        if staged is not None:
+            buf.copy_(res[:buf.numel()].view_as(buf))
         buf.div_(self.ranks)
         self.buckets += 1
 
-    def _work(self):
+    def _complete(self):
         import torch
         if self.cuda:
             torch.cuda.set_device(self.device)
@@ -103,15 +116,14 @@ class EngineBucketReducer:
             item = self._q.get()
             if item is None:
                 return
-            buf, ready, fut = item
+            work, buf, staged, fut = item
             try:
                 if self.cuda:
                     with torch.cuda.stream(self.stream):
-                        self.stream.wait_event(ready)
-                        self._reduce(buf)
+                        self._finish(work, buf, staged)
                         fut.set_result(buf)   # records this stream's event for whoever waits
                 else:
-                    self._reduce(buf)
+                    self._finish(work, buf, staged)
                     fut.set_result(buf)
             except Exception as e:  # the training thread gets the error from the future
                 fut.set_exception(e)

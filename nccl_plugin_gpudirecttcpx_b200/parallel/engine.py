@@ -245,6 +245,11 @@ class HierarchicalEngine:
             return out
         if padded > self.buffer_bytes:
             raise ValueError(f"all_reduce of {nbytes} bytes does not fit the {self.buffer_bytes}-byte symmetric buffers")
+        if padded == nbytes and x.is_contiguous() and (out is None or out.is_contiguous()):
+            # the native call stages tensors that live outside the symmetric buffers itself
+            dst = out.data_ptr() if out is not None else self.out.data_ptr()
+            self._check(self._api.tcpxb_engine_all_reduce(self._h, x.data_ptr(), dst, nbytes, code, self._stream()))
+            return out if out is not None else self.out.view(torch.uint8)[:nbytes].view(x.dtype).view(x.shape)
         wb = self.work.view(torch.uint8)
         w = wb[:nbytes].view(x.dtype)
         if x.data_ptr() != w.data_ptr():
@@ -268,26 +273,24 @@ class HierarchicalEngine:
         """`all_reduce` without blocking the caller: the engine's own thread drives the network
         and queues the kernels on the engine's own stream, after everything the caller's current
         stream holds at the time of the call.  Several calls may be outstanding; they run in
-        order.  With one GPU per node `x` must be contiguous with a size that is a multiple of
-        the native granularity (32 bytes between two nodes), and must stay untouched until
-        `wait()`; with several GPUs per node `x` is copied into the symmetric work buffer at
-        once, so only one call can be outstanding."""
+        order.  `x` must be contiguous with a size that is a multiple of the native granularity
+        (32 bytes between two single-GPU nodes) and must stay untouched until `wait()`; `out`
+        may be `x`.  With several GPUs per node the job stages `x` and `out` through the
+        symmetric buffers itself; without `out` the result is a view of the symmetric output,
+        which the next call overwrites."""
         nbytes = x.numel() * x.element_size()
         code = DTYPE_CODE[x.dtype]
         unit = self._all_reduce_unit()
-        if nbytes % unit != 0 or not x.is_contiguous():
-            raise ValueError(f"all_reduce_async needs a contiguous tensor whose size is a multiple of {unit} bytes")
+        if nbytes % unit != 0 or not x.is_contiguous() or (out is not None and not out.is_contiguous()):
+            raise ValueError(f"all_reduce_async needs contiguous tensors whose size is a multiple of {unit} bytes")
         if self.G == 1:
             res = out if out is not None else torch.empty_like(x)
             src, dst = x.data_ptr(), res.data_ptr()
         else:
             if nbytes > self.buffer_bytes:
                 raise ValueError(f"all_reduce of {nbytes} bytes does not fit the {self.buffer_bytes}-byte symmetric buffers")
-            w = self.work.view(torch.uint8)[:nbytes].view(x.dtype)
-            if x.data_ptr() != w.data_ptr():
-                w.copy_(x.reshape(-1))
-            res = self.out.view(torch.uint8)[:nbytes].view(x.dtype).view(x.shape)
-            src, dst = self.work.data_ptr(), self.out.data_ptr()
+            res = out if out is not None else self.out.view(torch.uint8)[:nbytes].view(x.dtype).view(x.shape)
+            src, dst = x.data_ptr(), res.data_ptr()
         keep, after = self._event_after_current_stream()
         ticket = self._api.tcpxb_engine_all_reduce_async(self._h, src, dst, nbytes, code, after)
         if not ticket:

@@ -103,8 +103,8 @@ def main():
         good = tuple(y.shape) == (n,) and torch.allclose(y, torch.stack(xs).sum(0), atol=1e-4 * ranks)
         ok = ok and good
         detail.append(("all_reduce_odd", "f32", n, 0, 0.0, good))
-    if G == 1:
-        # in place (out is the input tensor)
+    if True:
+        # in place (out is the input tensor); with several GPUs per node the native call stages it through the symmetric buffers
         xs = [torch.randn(600000, generator=torch.Generator().manual_seed(3 * r + 1)).float() for r in range(world)]
         if world == 1:
             xs = xs * 2
@@ -113,14 +113,14 @@ def main():
         good = y is mine and torch.allclose(mine, torch.stack(xs).sum(0), atol=1e-4 * ranks)
         ok = ok and good
         detail.append(("all_reduce_in_place", "f32", 600000, 0, 0.0, good))
-    if G == 1:
+    if True:
         # asynchronous form: three buckets queued at once on the engine's thread, waited for out of order
         xs3 = [[torch.randn(98304 * (k + 1), generator=torch.Generator().manual_seed(13 * r + k)).float() for r in range(world)]
                for k in range(3)]
         if world == 1:
             xs3 = [b * 2 for b in xs3]
         mine3 = [b[rank].clone() for b in xs3]
-        works = [eng.all_reduce_async(t) for t in mine3]
+        works = [eng.all_reduce_async(t, out=torch.empty_like(t)) for t in mine3]  # own outputs: several jobs are outstanding
         good = True
         for k in (2, 0, 1):
             y = works[k].wait()

@@ -60,6 +60,20 @@ def main():
                 good = err <= tol
                 ok = ok and good
                 detail.append(("reduce_scatter", str(dtype), n, 0, err, good))
+    # asynchronous form on tensors of the caller's own, the last one in place: three buckets queued at once
+    # on the engine's thread and stream, waited for out of order
+    n3 = 98304
+    xs3 = [[torch.randn(n3 * (k + 1), generator=torch.Generator().manual_seed(13 * r + k)).float() for r in range(world)] for k in range(3)]
+    mine3 = [b[rank].to(dev) for b in xs3]
+    outs3 = [torch.empty_like(mine3[0]), torch.empty_like(mine3[1]), mine3[2]]
+    works = [eng.all_reduce_async(t, out=o) for t, o in zip(mine3, outs3)]
+    good = True
+    for k in (2, 0, 1):
+        y = works[k].wait()
+        torch.cuda.synchronize()
+        good = good and y is outs3[k] and torch.allclose(y.cpu(), torch.stack(xs3[k]).sum(0), atol=1e-4 * world) and works[k].done()
+    ok = ok and good
+    detail.append(("all_reduce_async_x3", "f32", n3, 0, 0.0, good))
     status = eng.device_status()
     ok = ok and status[0] == 0
     bad = [d for d in detail if not d[-1]]
