@@ -49,7 +49,8 @@ namespace {
 volatile sig_atomic_t g_stop = 0;
 void onSignal(int) { g_stop = 1; }
 
-struct Rule { RxdmFlowRule r; int owner_fd; };
+struct Rule { RxdmFlowRule r; int owner_pid; };  // owner: the requesting process, from the socket's credentials
+struct App { int pid; int cred_pid; };          // the pid the client stated, and the one the kernel vouches for
 struct Pool {
   int fd = -1;
   uint64_t size = 0, align = 4096;
@@ -65,7 +66,7 @@ struct State {
   bool proto_wire = false;
   std::vector<std::string> gpu_pcis;  // proto wire: the GPUs that get a socket pair of their own
   std::vector<Rule> rules;
-  std::map<int, int> apps;  // connection fd -> pid
+  std::map<int, App> apps;  // keep-alive connection fd -> application
   std::map<std::string, Pool> pools;
 };
 
@@ -83,6 +84,16 @@ int listenOn(const std::string& path) {
   }
   return fd;
 }
+
+int peerPid(int fd) {
+  struct ucred cred;
+  socklen_t len = sizeof cred;
+  return getsockopt(fd, SOL_SOCKET, SO_PEERCRED, &cred, &len) == 0 ? (int)cred.pid : -1;
+}
+
+// An application's keep-alive connection closed (or it deregistered): forget it and
+// withdraw the flow rules its process installed and did not remove, as after a crash.
+void dropApplication(State* st, std::map<int, App>::iterator it, const char* how);
 
 RxdmMessage reply(int status, const char* text, uint64_t a = 0, uint64_t b = 0, uint64_t c = 0) {
   RxdmMessage m;
@@ -125,6 +136,23 @@ Pool* poolFor(State* st, const std::string& pci) {
   return &st->pools[pci];
 }
 
+void dropApplication(State* st, std::map<int, App>::iterator it, const char* how) {
+  const App app = it->second;
+  st->apps.erase(it);
+  size_t dropped = 0;
+  bool other_registration = false;
+  for (const auto& kv : st->apps) other_registration = other_registration || kv.second.cred_pid == app.cred_pid;
+  if (!other_registration && app.cred_pid > 0) {
+    for (size_t i = 0; i < st->rules.size();) {
+      if (st->rules[i].owner_pid == app.cred_pid) { st->rules.erase(st->rules.begin() + (long)i); ++dropped; }
+      else ++i;
+    }
+  }
+  fprintf(stderr, "[rxdm] application %d %s", app.pid, how);
+  if (dropped) fprintf(stderr, "; %zu flow rule(s) of process %d withdrawn", dropped, app.cred_pid);
+  fprintf(stderr, "\n");
+}
+
 bool sameRule(const RxdmFlowRule& a, const RxdmFlowRule& b) {
   return strcmp(a.src_ip, b.src_ip) == 0 && a.src_port == b.src_port && strcmp(a.dst_ip, b.dst_ip) == 0 &&
          a.dst_port == b.dst_port;
@@ -143,7 +171,7 @@ bool serve(State* st, UnixSocketConnection* c, const std::string& service) {
       m.rule.src_ip[sizeof m.rule.src_ip - 1] = 0;
       m.rule.dst_ip[sizeof m.rule.dst_ip - 1] = 0;
       m.rule.gpu_pci[sizeof m.rule.gpu_pci - 1] = 0;
-      st->rules.push_back(Rule{m.rule, -1});
+      st->rules.push_back(Rule{m.rule, peerPid(c->fd())});
       c->send(reply(0, "Ok."));
       return false;
     }
@@ -164,12 +192,15 @@ bool serve(State* st, UnixSocketConnection* c, const std::string& service) {
     }
     case kRxdmAppRegister: {
       if (m.app.register_client) {
-        st->apps[c->fd()] = m.app.pid;
+        st->apps[c->fd()] = App{m.app.pid, peerPid(c->fd())};
         c->send(reply(0, "Ok."));
         return true;  // keep-alive connection
       }
-      for (auto it = st->apps.begin(); it != st->apps.end();)
-        it = (it->second == m.app.pid) ? st->apps.erase(it) : std::next(it);
+      for (auto it = st->apps.begin(); it != st->apps.end();) {
+        auto next = std::next(it);
+        if (it->second.pid == m.app.pid) dropApplication(st, it, "deregistered");
+        it = next;
+      }
       c->send(reply(0, "Ok."));
       return false;
     }
@@ -218,7 +249,7 @@ bool serveProto(State* st, rxproto::Connection* c, const std::string& service) {
     const RxdmFlowRule r = ruleFromProto(m);
     if (service == "rx_rule_manager") {
       if (st->rules.size() >= st->max_rules) { c->sendMessage(rawReply("Resource exhausted: rule table full")); return false; }
-      st->rules.push_back(Rule{r, -1});
+      st->rules.push_back(Rule{r, peerPid(c->fd())});
       c->sendMessage(rawReply("Ok."));
       return false;
     }
@@ -247,17 +278,17 @@ bool serveProto(State* st, rxproto::Connection* c, const std::string& service) {
   }
   if (service == "rxdm_application_registry") {
     if (m.kind != rxproto::kAppRegister) { c->sendMessage(rawReply("Invalid argument: not a registration")); return false; }
-    struct ucred cred;
-    socklen_t len = sizeof cred;
-    const int pid = getsockopt(c->fd(), SOL_SOCKET, SO_PEERCRED, &cred, &len) == 0 ? (int)cred.pid : -1;
+    const int pid = peerPid(c->fd());
     if (m.register_client) {
-      st->apps[c->fd()] = pid;
+      st->apps[c->fd()] = App{pid, pid};
       c->sendMessage(rawReply("Ok."));
       return true;  // keep-alive connection
     }
-    for (auto it = st->apps.begin(); it != st->apps.end();)
-      it = (it->second == pid) ? st->apps.erase(it) : std::next(it);
-    fprintf(stderr, "[rxdm] application %d deregistered\n", pid);
+    for (auto it = st->apps.begin(); it != st->apps.end();) {
+      auto next = std::next(it);
+      if (it->second.cred_pid == pid) dropApplication(st, it, "deregistered");
+      it = next;
+    }
     c->sendMessage(rawReply("Ok."));
     return false;
   }
@@ -373,10 +404,7 @@ int main(int argc, char** argv) {
         ssize_t n = recv(keep[k], &b, 1, MSG_DONTWAIT);
         if (n == 0 || (n < 0 && errno != EAGAIN)) {
           auto it = st.apps.find(keep[k]);
-          if (it != st.apps.end()) {
-            fprintf(stderr, "[rxdm] application %d went away\n", it->second);
-            st.apps.erase(it);
-          }
+          if (it != st.apps.end()) dropApplication(&st, it, "went away");
           close(keep[k]);
           keep.erase(keep.begin() + (long)k);
           pfds.erase(pfds.begin() + (long)(lfds.size() + k));

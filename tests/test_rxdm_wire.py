@@ -203,15 +203,18 @@ def test_protobuf_library_client_against_the_daemon(host_lib, pb, tmp_path):
         ok = P()
         ok.ParseFromString(read_frame(keep))
         assert ok.raw_bytes == b"Ok."
-        assert daemon_status(prefix)["applications"] == 1
+        st = daemon_status(prefix)
+        assert st["applications"] == 1 and st["flow_rules"] == 1
+        # the process "crashes": its keep-alive connection closes with a rule still installed, and the daemon cleans up
         keep.close()
         for _ in range(100):
             if daemon_status(prefix)["applications"] == 0:
                 break
-        assert daemon_status(prefix)["applications"] == 0
+        st = daemon_status(prefix)
+        assert st["applications"] == 0 and st["flow_rules"] == 0
     finally:
         log = stop_daemon(d)
-    assert f"application {os.getpid()} went away" in log, log[-2000:]
+    assert f"application {os.getpid()} went away; 1 flow rule(s) of process {os.getpid()} withdrawn" in log, log[-2000:]
 
 
 def test_plugin_client_against_the_daemon_in_the_protobuf_format(host_lib, tmp_path):
