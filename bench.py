@@ -25,7 +25,9 @@ API with the step's input copied from pinned host memory and an 8-byte checksum 
 the result read back, every step, inside the timed region.  The `ours` arm also
 reports: a short size sweep (`sweep`), the box's raw socket ceiling for the same
 number of streams and the step's fraction of it (`rawsock_ceiling_GBps`,
-`frac_of_rawsock`), and the same step over NCCL's socket transport run as a child job
+`frac_of_rawsock`: cache-resident 512 KiB blocks; `rawsock_uncached_GBps`,
+`frac_of_rawsock_uncached`: 64 MiB per thread, the case of buffers that GPU DMA fills
+and drains), and the same step over NCCL's socket transport run as a child job
 after the engine has shut down (`nccl_socket`, `vs_nccl_socket`).
 """
 from __future__ import annotations
@@ -303,13 +305,17 @@ def free_port() -> int:
         return s.getsockname()[1]
 
 
-def run_rawsock(streams: int):
+def run_rawsock(streams: int, span_mb: int = 0):
+    """Plain send/recv loops over loopback TCP, `streams` connections.  `span_mb` = 0: every thread reuses one
+    512 KiB block (cache-resident, the kindest case); otherwise each thread walks a buffer of that many MiB,
+    like a transport whose staging and landing memory is written and read by GPU DMA and never cache-warm."""
     from nccl_plugin_gpudirecttcpx_b200.utils import native
     exe = native.LIB_DIR / "tcpxb_rawsock"
     if not exe.exists():
         return None
     try:
-        r = subprocess.run([str(exe), "--streams", str(streams), "--mb-per-stream", "1024"], capture_output=True, text=True, timeout=120)
+        cmd = [str(exe), "--streams", str(streams), "--mb-per-stream", "1024"] + (["--span-mb", str(span_mb)] if span_mb else [])
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=120)
         for line in r.stdout.splitlines():
             if line.startswith("{"):
                 return json.loads(line)
@@ -629,6 +635,10 @@ def main():
             line["rawsock_streams"] = streams
             line["net_stage_GBps"] = net_GBps
             line["frac_of_rawsock"] = net_GBps / raw["GBps"] if raw["GBps"] else None
+            cold = run_rawsock(streams, span_mb=64)
+            if cold and cold.get("GBps"):
+                line["rawsock_uncached_GBps"] = cold["GBps"]
+                line["frac_of_rawsock_uncached"] = net_GBps / cold["GBps"]
         if world > 1:
             child = run_child_arm("nccl-socket", args, world)
             if child and "value" in child:

@@ -39,6 +39,8 @@ def parse_args(argv=None):
     ap.add_argument("--backend", default="nccl", choices=["nccl", "gloo"])
     ap.add_argument("--nics", type=int, default=4)
     ap.add_argument("--nthreads", type=int, default=4)
+    ap.add_argument("--engine-buffer-kb", type=int, default=0,
+                    help="--transport engine, several GPUs per node: size of the symmetric buffers (0 = bucket cap + largest parameter); larger buckets travel in pieces")
     return ap.parse_args(argv)
 
 
@@ -87,24 +89,35 @@ class EngineBucketReducer:
         buf = bucket.buffer()
         fut = torch.futures.Future(devices=[self.device]) if self.cuda else torch.futures.Future()
         try:
-            nbytes = buf.numel() * buf.element_size()
-            staged = None
-            if nbytes % self._unit != 0 or not buf.is_contiguous():
-                # off the native granularity: travel zero-padded in a tensor of the job's own
-                padded = (nbytes + self._unit - 1) // self._unit * self._unit
-                staged = torch.zeros(padded // buf.element_size(), dtype=buf.dtype, device=buf.device)
-                staged[:buf.numel()].copy_(buf.reshape(-1))
-            t = staged if staged is not None else buf
-            work = self.engine.all_reduce_async(t, out=t)
-            self._q.put((work, buf, staged, fut))
+            flat = buf.reshape(-1) if buf.is_contiguous() else None
+            if flat is None:
+                raise ValueError("DDP handed over a bucket that is not contiguous")
+            # A bucket may be larger than the engine's symmetric buffers (DDP's first step reduces
+            # all gradients as one bucket before it has rebuilt its buckets): it travels in pieces.
+            cap = getattr(self.engine, "buffer_bytes", 0) if self.engine.G > 1 else 0
+            piece_elems = flat.numel() if cap <= 0 else max(self._unit, cap // self._unit * self._unit) // flat.element_size()
+            jobs = []
+            for lo in range(0, flat.numel(), piece_elems):
+                piece = flat[lo:lo + piece_elems]
+                nbytes = piece.numel() * piece.element_size()
+                staged = None
+                if nbytes % self._unit != 0:
+                    # off the native granularity: travel zero-padded in a tensor of the job's own
+                    padded = (nbytes + self._unit - 1) // self._unit * self._unit
+                    staged = torch.zeros(padded // piece.element_size(), dtype=piece.dtype, device=piece.device)
+                    staged[:piece.numel()].copy_(piece)
+                t = staged if staged is not None else piece
+                jobs.append((self.engine.all_reduce_async(t, out=t), piece, staged))
+            self._q.put((jobs, buf, fut))
         except Exception as e:
             fut.set_exception(e)
         return fut
 
-    def _finish(self, work, buf, staged):
-        res = work.wait()  # the current stream now waits for the engine's kernels
-        if staged is not None:
-            buf.copy_(res[:buf.numel()].view_as(buf))
+    def _finish(self, jobs, buf):
+        for work, piece, staged in jobs:
+            res = work.wait()  # the current stream now waits for the engine's kernels
+            if staged is not None:
+                piece.copy_(res[:piece.numel()])
         buf.div_(self.ranks)
         self.buckets += 1
 
@@ -116,14 +129,14 @@ class EngineBucketReducer:
             item = self._q.get()
             if item is None:
                 return
-            work, buf, staged, fut = item
+            jobs, buf, fut = item
             try:
                 if self.cuda:
                     with torch.cuda.stream(self.stream):
-                        self._finish(work, buf, staged)
+                        self._finish(jobs, buf)
                         fut.set_result(buf)   # records this stream's event for whoever waits
                 else:
-                    self._finish(work, buf, staged)
+                    self._finish(jobs, buf)
                     fut.set_result(buf)
             except Exception as e:  # the training thread gets the error from the future
                 fut.set_exception(e)
@@ -144,6 +157,8 @@ def make_engine_reducer(args, dev, world: int, model):
     G = args.gpus_per_node if world > 1 else 1
     largest = max(p.numel() * p.element_size() for p in model.parameters())
     buffer_bytes = ((args.bucket_mb << 20) + largest + (1 << 20) - 1) >> 20 << 20
+    if args.engine_buffer_kb > 0:
+        buffer_bytes = args.engine_buffer_kb << 10
     eng = engine_cls(gpus_per_node=G, buffer_bytes=buffer_bytes if G > 1 else 0, device=dev)
     return EngineBucketReducer(eng, world if world > 1 else 2, dev)
 

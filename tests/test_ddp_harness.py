@@ -32,14 +32,16 @@ def test_ddp_harness_two_cpu_ranks():
     assert rows[0]["loss_last"] < rows[0]["loss_first"] + 1.0
 
 
-@pytest.mark.parametrize("nproc,gpn", [(2, 1), (4, 2)])
-def test_ddp_buckets_through_the_engine_on_cpu_ranks(nproc, gpn):
-    """Gradient buckets averaged by the hierarchical engine (communication hook + worker thread) on the
-    stand-in device give the same training trajectory as gloo's own all_reduce."""
+@pytest.mark.parametrize("nproc,gpn,buffer_kb", [(2, 1, 0), (4, 2, 0), (4, 2, 96)])
+def test_ddp_buckets_through_the_engine_on_cpu_ranks(nproc, gpn, buffer_kb):
+    """Gradient buckets averaged by the hierarchical engine (communication hook on the engine's asynchronous
+    calls) on the stand-in device give the same training trajectory as gloo's own all_reduce; with 96 KiB
+    symmetric buffers every bucket is larger than the buffers and travels in pieces."""
     common = ["--backend", "gloo", "--tiny", "--steps", "3", "--warmup", "2", "--micro-batch", "2", "--bucket-mb", "1"]
     env = {"PYTHONPATH": str(ROOT) + os.pathsep + str(ROOT / "tests"), "TCPXB_FAKE_GPU": "1", "OMP_NUM_THREADS": "1"}
     r, rows = _launch(nproc, common + ["--transport", "engine", "--engine-class", "standin_engine:StandinEngine",
-                                       "--gpus-per-node", str(gpn), "--nics", "2", "--nthreads", "2"], env=env)
+                                       "--gpus-per-node", str(gpn), "--nics", "2", "--nthreads", "2",
+                                       "--engine-buffer-kb", str(buffer_kb)], env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert len(rows) == 1 and rows[0]["replicas_in_sync"] and rows[0]["engine_buckets"] >= 5
     ref_r, ref = _launch(nproc, common, env={"OMP_NUM_THREADS": "1"})
