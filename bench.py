@@ -204,6 +204,13 @@ def unpack_microbench(torch, peaks, iters=20, warm=4):
     t_copy, tb_copy = timed(copy_fn)
     t_red, tb_red = timed(red_fn)
     tg_copy, tg_red = graphed(copy_fn), graphed(red_fn)
+    # the same launches allowed to start early (programmatic dependent launch): the next launch is scheduled
+    # while the previous one runs and waits for its completion on the device, so the gap between kernels goes
+    copy_pdl = lambda i: U.unpack_copy(pool, dsts[i % 3], descs[i % variants], status=st, early_launch=True)
+    red_pdl = lambda i: U.unpack_reduce(pool, dsts[i % 3], descs[i % variants], status=st, early_launch=True)
+    tp_copy, tpb_copy = timed(copy_pdl)
+    tp_red, tpb_red = timed(red_pdl)
+    tpg_copy, tpg_red = graphed(copy_pdl), graphed(red_pdl)
     # fused reduce + fan-out with the three "peers" emulated by buffers on this GPU (no NVLink in
     # this number: it shows the kernel's cost of writing four copies of every reduced fragment)
     peers = [torch.empty((64 << 20) // 2, dtype=torch.bfloat16, device=dev) for _ in range(3)]
@@ -240,6 +247,16 @@ def unpack_microbench(torch, peaks, iters=20, warm=4):
             "unpack_reduce_us": tg_red * 1e6, "unpack_reduce_frac_hbm": 3 * total / tg_red / 1e9 / hbm,
             "torch_copy_64MiB_us": tg_ref * 1e6, "torch_copy_64MiB_frac_hbm": 2 * (64 << 20) / tg_ref / 1e9 / hbm,
             "note": "20 launches captured in one CUDA graph, one replay timed"},
+        "early_launch": {
+            "unpack_copy_us": tp_copy * 1e6, "unpack_copy_frac_hbm": 2 * total / tp_copy / 1e9 / hbm,
+            "unpack_reduce_us": tp_red * 1e6, "unpack_reduce_frac_hbm": 3 * total / tp_red / 1e9 / hbm,
+            "back_to_back_unpack_copy_us": tpb_copy * 1e6, "back_to_back_unpack_copy_frac_hbm": 2 * total / tpb_copy / 1e9 / hbm,
+            "back_to_back_unpack_reduce_us": tpb_red * 1e6, "back_to_back_unpack_reduce_frac_hbm": 3 * total / tpb_red / 1e9 / hbm,
+            "graph_replay_unpack_copy_us": None if not tpg_copy else tpg_copy * 1e6,
+            "graph_replay_unpack_copy_frac_hbm": None if not tpg_copy else 2 * total / tpg_copy / 1e9 / hbm,
+            "graph_replay_unpack_reduce_us": None if not tpg_red else tpg_red * 1e6,
+            "graph_replay_unpack_reduce_frac_hbm": None if not tpg_red else 3 * total / tpg_red / 1e9 / hbm,
+            "note": "opts.early_launch = 1 (programmatic dependent launch) on every launch"},
         "unpack_reduce_fanout3_us": t_fan * 1e6, "unpack_reduce_fanout3_GBps": 6 * total / t_fan / 1e9,
         "unpack_reduce_fanout3_frac_hbm": 6 * total / t_fan / 1e9 / hbm,
         "unpack_reduce_fanout3_back_to_back_us": tb_fan * 1e6,

@@ -80,6 +80,12 @@ typedef struct tcpxbUnpackOpts {
   uint32_t flag_value;
   uint32_t* ticket;
   int max_ctas;            // 0 = one CTA per SM
+  // Programmatic dependent launch: when non-zero the launch may be scheduled while the
+  // previous kernel of the stream is still running; its CTAs become resident as SMs free
+  // up, set up their barriers, and wait for that kernel to complete (and its writes to
+  // be visible) before they touch any memory.  Results are the same; back-to-back
+  // launches lose the gap between kernels.
+  int early_launch;
 } tcpxbUnpackOpts;
 
 // K1: dst[dst_off .. +len) = pool[src_off .. +len) for every descriptor.

@@ -363,6 +363,13 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kDataBytes) + warp * D;
   SlotInfo* infos = reinterpret_cast<SlotInfo*>(smem + C::kDataBytes + kWarps * D * 8) + warp * D;
 
+  // Programmatic dependent launch, both roles.  As the earlier kernel: let a dependent
+  // launch be scheduled from now on (its CTAs still need this one's shared memory to
+  // be released before they fit).  As the later kernel: everything up to the wait
+  // below touches only this CTA's shared memory; the wait returns when the previous
+  // kernel of the stream has completed and its writes are visible (at once when the
+  // launch did not ask for an early start).
+  asm volatile("griddepcontrol.launch_dependents;");
   __shared__ uint32_t cta_err;  // any warp of this CTA recorded an error
   if (threadIdx.x == 0) cta_err = 0;
   if (lane == 0) {
@@ -370,6 +377,7 @@ unpack_kernel(const __grid_constant__ UnpackParams p) {
     fence_mbar_init();
   }
   __syncthreads();
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   auto record = [&](uint32_t code, uint32_t index) {  // one lane calls this
     report(p.status, code, index);
     atomicOr(&cta_err, 1u);
@@ -766,7 +774,7 @@ int deviceInfo(int* dev_out) {
 }
 
 template <int RED, bool L2RED, int FAN>
-int launch(const UnpackParams& p, int max_ctas, cudaStream_t stream) {
+int launch(const UnpackParams& p, int max_ctas, bool early, cudaStream_t stream) {
   using C = Cfg<RED, L2RED, FAN>;
   int dev = 0;
   int rc = deviceInfo(&dev);
@@ -778,8 +786,17 @@ int launch(const UnpackParams& p, int max_ctas, cudaStream_t stream) {
   int cap = g_dev[dev].sms;
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (ctas > cap) ctas = cap;
-  unpack_kernel<RED, L2RED, FAN><<<ctas, kThreads, C::kSmemBytes, stream>>>(p);
-  CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)ctas);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = early ? 1 : 0;
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, unpack_kernel<RED, L2RED, FAN>, p));
   return TCPXB_K_OK;
 }
 
@@ -810,16 +827,16 @@ int prepareFan(int dev) {
 }
 
 template <int FAN>
-int dispatch(const UnpackParams& p, int dtype, int impl, int max_ctas, cudaStream_t s) {
+int dispatch(const UnpackParams& p, int dtype, int impl, int max_ctas, bool early, cudaStream_t s) {
   const bool l2 = (impl == TCPXB_REDUCE_L2);
   switch (dtype) {
-    case TCPXB_U8: return launch<TCPXB_U8, false, FAN>(p, max_ctas, s);
+    case TCPXB_U8: return launch<TCPXB_U8, false, FAN>(p, max_ctas, early, s);
     case TCPXB_BF16:
-      return l2 ? launch<TCPXB_BF16, true, FAN>(p, max_ctas, s)
-                : launch<TCPXB_BF16, false, FAN>(p, max_ctas, s);
+      return l2 ? launch<TCPXB_BF16, true, FAN>(p, max_ctas, early, s)
+                : launch<TCPXB_BF16, false, FAN>(p, max_ctas, early, s);
     case TCPXB_F32:
-      return l2 ? launch<TCPXB_F32, true, FAN>(p, max_ctas, s)
-                : launch<TCPXB_F32, false, FAN>(p, max_ctas, s);
+      return l2 ? launch<TCPXB_F32, true, FAN>(p, max_ctas, early, s)
+                : launch<TCPXB_F32, false, FAN>(p, max_ctas, early, s);
     default: return fail(TCPXB_K_INVALID, "unknown dtype");
   }
 }
@@ -930,7 +947,7 @@ int tcpxb_unpack_copy(const void* pool, uint64_t pool_bytes, void* dst, uint64_t
   int rc = fill(p, pool, pool_bytes, nullptr, dst, nullptr, dst_bytes, nullptr, 0, descs, count,
                 status, opts);
   if (rc) return rc;
-  return dispatch<FAN_NONE>(p, TCPXB_U8, 0, opts ? opts->max_ctas : 0,
+  return dispatch<FAN_NONE>(p, TCPXB_U8, 0, opts ? opts->max_ctas : 0, opts != nullptr && opts->early_launch != 0,
                             static_cast<cudaStream_t>(stream));
 }
 
@@ -945,7 +962,7 @@ int tcpxb_unpack_reduce(const void* pool, uint64_t pool_bytes, const void* acc, 
   int rc = fill(p, pool, pool_bytes, acc, dst, nullptr, dst_bytes, nullptr, 0, descs, count, status,
                 opts);
   if (rc) return rc;
-  return dispatch<FAN_NONE>(p, dtype, impl, opts ? opts->max_ctas : 0,
+  return dispatch<FAN_NONE>(p, dtype, impl, opts ? opts->max_ctas : 0, opts != nullptr && opts->early_launch != 0,
                             static_cast<cudaStream_t>(stream));
 }
 
@@ -956,7 +973,7 @@ int tcpxb_unpack_fanout(const void* pool, uint64_t pool_bytes, void* dst, uint64
   int rc = fill(p, pool, pool_bytes, nullptr, dst, nullptr, dst_bytes, peers, npeers, descs, count,
                 status, opts);
   if (rc) return rc;
-  return dispatch<FAN_PEER>(p, TCPXB_U8, 0, opts ? opts->max_ctas : 0,
+  return dispatch<FAN_PEER>(p, TCPXB_U8, 0, opts ? opts->max_ctas : 0, opts != nullptr && opts->early_launch != 0,
                             static_cast<cudaStream_t>(stream));
 }
 
@@ -972,7 +989,7 @@ int tcpxb_unpack_reduce_fanout(const void* pool, uint64_t pool_bytes, const void
   int rc = fill(p, pool, pool_bytes, acc, dst, nullptr, dst_bytes, peers, npeers, descs, count,
                 status, opts);
   if (rc) return rc;
-  return dispatch<FAN_PEER>(p, dtype, impl, opts ? opts->max_ctas : 0,
+  return dispatch<FAN_PEER>(p, dtype, impl, opts ? opts->max_ctas : 0, opts != nullptr && opts->early_launch != 0,
                             static_cast<cudaStream_t>(stream));
 }
 
@@ -985,7 +1002,7 @@ int tcpxb_unpack_fanout_nvls(const void* pool, uint64_t pool_bytes, void* dst, v
   int rc = fill(p, pool, pool_bytes, nullptr, dst, mc_dst, dst_bytes, peers, npeers, descs, count,
                 status, opts);
   if (rc) return rc;
-  return dispatch<FAN_NVLS>(p, TCPXB_U8, 0, opts ? opts->max_ctas : 0,
+  return dispatch<FAN_NVLS>(p, TCPXB_U8, 0, opts ? opts->max_ctas : 0, opts != nullptr && opts->early_launch != 0,
                             static_cast<cudaStream_t>(stream));
 }
 
@@ -1003,7 +1020,7 @@ int tcpxb_unpack_reduce_fanout_nvls(const void* pool, uint64_t pool_bytes, const
   if (rc) return rc;
   // acc == NULL selects the reduce-into-all form (multimem.red into every accumulator).
   return dispatch<FAN_NVLS>(p, dtype, acc == nullptr ? TCPXB_REDUCE_L2 : TCPXB_REDUCE_SM,
-                            opts ? opts->max_ctas : 0, static_cast<cudaStream_t>(stream));
+                            opts ? opts->max_ctas : 0, opts != nullptr && opts->early_launch != 0, static_cast<cudaStream_t>(stream));
 }
 
 int tcpxb_wait_flags(const uint32_t* flags, int n, uint32_t value, uint64_t wait_ns,

@@ -35,6 +35,7 @@ class _Opts(ctypes.Structure):
         ("flag_value", ctypes.c_uint32),
         ("ticket", ctypes.c_void_p),
         ("max_ctas", ctypes.c_int),
+        ("early_launch", ctypes.c_int),
     ]
 
 
@@ -139,8 +140,8 @@ def _desc_args(descs: torch.Tensor):
 
 
 def _opts(ready_count=None, wait_ns=0, peer_flags: Sequence[int] = (), flag_value=0, ticket=None,
-          max_ctas=0):
-    if ready_count is None and not peer_flags and not flag_value and not max_ctas and not wait_ns:
+          max_ctas=0, early_launch=False):
+    if ready_count is None and not peer_flags and not flag_value and not max_ctas and not wait_ns and not early_launch:
         return None, None
     o = _Opts()
     o.ready_count = ready_count if isinstance(ready_count, (int, type(None))) else ready_count.data_ptr()
@@ -150,6 +151,7 @@ def _opts(ready_count=None, wait_ns=0, peer_flags: Sequence[int] = (), flag_valu
     o.flag_value = int(flag_value)
     o.ticket = None if ticket is None else ticket.data_ptr()
     o.max_ctas = int(max_ctas)
+    o.early_launch = int(bool(early_launch))  # programmatic dependent launch: may start while the stream's previous kernel still runs
     return o, ctypes.byref(o)
 
 

@@ -109,6 +109,36 @@ def test_reduce_matches_fp32_oracle(dtype, impl):
         assert bool(((g - w).abs() <= ulp).all())
 
 
+def test_early_launch_keeps_the_order_of_dependent_launches():
+    """Launches that may start early (programmatic dependent launch) still see what the stream's
+    previous kernel wrote: a torch kernel fills the accumulator, then four in-place sums of the same
+    fragments follow back to back, each reading what the one before stored."""
+    dtype = torch.float32
+    pool_bytes = 8 << 20
+    total = 4096 * 1500
+    pool = _pool(pool_bytes, 21, dtype)
+    descs = U.permuted_fragments(total, pool_bytes, seed=23)
+    n_el = total // dtype.itemsize
+    acc = torch.empty(n_el, dtype=dtype, device=DEV)
+    pool_dev, d_dev = pool.to(DEV), U.descriptors_to_device(descs)
+    st = U.status_buffer()
+    torch.cuda.synchronize()
+    acc.fill_(1.0)  # a kernel of another library directly before the first early launch
+    for _ in range(4):
+        U.unpack_reduce(pool_dev, acc, d_dev, status=st, early_launch=True)
+    copy = torch.empty_like(acc)
+    straight = np.zeros(total // 4096, dtype=U.DESC_DTYPE)  # fragment i of the sums to fragment i of the copy
+    straight["src_off"] = straight["dst_off"] = np.arange(total // 4096, dtype=np.uint64) * 4096
+    straight["len"] = 4096
+    U.unpack_copy(acc.view(torch.uint8), copy.view(torch.uint8), U.descriptors_to_device(straight), status=st, early_launch=True)
+    torch.cuda.synchronize()
+    assert st.tolist()[0] == U.ST_OK
+    want = torch.ones(n_el, dtype=dtype)
+    for _ in range(4):
+        want = U.reference_unpack(pool, want, descs, acc=want)
+    assert torch.equal(acc.cpu(), want) and torch.equal(copy.cpu(), want)
+
+
 def test_reduce_out_of_place_and_unaligned_elements():
     pool_bytes = 1 << 20
     pool = _pool(pool_bytes, 8, torch.bfloat16)
