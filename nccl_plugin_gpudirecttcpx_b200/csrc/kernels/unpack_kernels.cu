@@ -655,8 +655,9 @@ __global__ void __launch_bounds__(256) peer_reduce_kernel(const __grid_constant_
   }
 }
 
-// Checksum: per-block partial sums into scratch, the last block to finish adds
-// them in index order, so the result does not depend on scheduling.
+// Checksum: per-block partial sums into scratch; the last block to arrive adds them.
+// The sum is over 64-bit integers (wrapping), so its value depends neither on the order
+// of the additions nor on scheduling.
 constexpr int kCsumBlocks = 592;  // 4 per SM on a 148-SM part
 constexpr int kCsumThreads = 256;
 struct CsumScratch {
@@ -703,20 +704,33 @@ checksum_kernel(const uint8_t* buf, uint64_t bytes, uint64_t* out, CsumScratch* 
     sum += last;
   }
   __shared__ uint64_t red[kCsumThreads / 32];
-  for (int o = 16; o > 0; o >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
-  __syncthreads();
-  if (threadIdx.x == 0) {
+  __shared__ uint32_t is_last;
+  auto block_sum = [&](uint64_t v) -> uint64_t {  // valid in thread 0
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    __syncthreads();  // red[] may still be read from the previous use
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
     uint64_t s = 0;
-    for (int i = 0; i < kCsumThreads / 32; ++i) s += red[i];
-    scratch->partial[blockIdx.x] = s;
+    if (threadIdx.x == 0)
+      for (int i = 0; i < kCsumThreads / 32; ++i) s += red[i];
+    return s;
+  };
+  const uint64_t mine = block_sum(sum);
+  if (threadIdx.x == 0) {
+    scratch->partial[blockIdx.x] = mine;
     __threadfence();
-    const uint32_t t = atomicAdd(&scratch->ticket, 1u);
-    if (t == gridDim.x - 1) {
-      __threadfence();
-      uint64_t total = 0;
-      for (uint32_t b = 0; b < gridDim.x; ++b)
-        total += *reinterpret_cast<volatile uint64_t*>(&scratch->partial[b]);
+    is_last = atomicAdd(&scratch->ticket, 1u) == gridDim.x - 1 ? 1u : 0u;
+  }
+  __syncthreads();
+  if (is_last) {
+    // The last block to arrive adds the partial sums, all threads at once: one thread
+    // walking 592 dependent-latency loads cost 20 us, twice the time of the 64 MiB pass.
+    __threadfence();
+    uint64_t part = 0;
+    for (uint32_t b = threadIdx.x; b < gridDim.x; b += blockDim.x)
+      part += *reinterpret_cast<volatile uint64_t*>(&scratch->partial[b]);
+    const uint64_t total = block_sum(part);
+    if (threadIdx.x == 0) {
       *out = total;
       scratch->ticket = 0;
     }
