@@ -84,6 +84,7 @@ def parse_args(argv=None):
     ap.add_argument("--idle-sleep-us", type=int, default=0, help="driving thread: longest sleep when idle (0 = default, -1 = spin)")
     ap.add_argument("--pool-mb", type=int, default=1024, help="rx page pool per GPU (MiB)")
     ap.add_argument("--plugin-recv-mode", default="host", choices=["host", "unpack"], help="nccl-plugin arm: who unpacks")
+    ap.add_argument("--nic-speed-mbps", type=int, default=200000, help="nccl-plugin arm: link speed the plugin reports per virtual NIC (NCCL sizes its channels from it)")
     ap.add_argument("--pin", default="none", choices=["none", "block", "pair"],
                     help="CPU affinity of each rank's process: none; block = rank r gets the r-th slice of the cores; "
                          "pair = the two ranks of a rail (same local index in the two nodes) get neighbouring slices")
@@ -414,7 +415,8 @@ def main():
         auto = socket_settings_for(cores, world)
         env = plugin_env(nics=args.nics if args.nics > 0 else 4, nthreads=args.nthreads if args.nthreads > 0 else auto["nthreads"],
                          nsocks_per_thread=args.nsocks_per_thread, chunk_bytes=args.chunk_kb << 10,
-                         builtin_socket=(args.impl == "nccl-socket"), recv_mode=args.plugin_recv_mode, rx_pool_mb=args.pool_mb)
+                         builtin_socket=(args.impl == "nccl-socket"), recv_mode=args.plugin_recv_mode, rx_pool_mb=args.pool_mb,
+                         speed_mbps=args.nic_speed_mbps)
         if G > 1:  # nodes are told apart by host id, so NVLink stays on inside a node
             env.pop("NCCL_P2P_DISABLE", None)
             env.pop("NCCL_SHM_DISABLE", None)
