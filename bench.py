@@ -572,7 +572,8 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_e2e = t[0].item(), t[1].item()
 
-    # a short sweep over message sizes (2 timed steps each), for the small-message half of the metric
+    # a short sweep over message sizes, for the small-message half of the metric: 2 timed steps each from 4 MiB
+    # up, 20 below (a pair of steps of 0.1 ms each says little), 3 warm-up steps before either
     sweep = []
     if not args.no_sweep:
         for sb in SWEEP_BYTES:
@@ -586,8 +587,9 @@ def main():
             else:
                 small_out = torch.empty_like(src)
                 fn = lambda: eng.all_reduce(src, small_out)
-            fn()
-            t_ms = timed_steps(torch, fn, 2, barrier)
+            for _ in range(3):
+                fn()
+            t_ms = timed_steps(torch, fn, 2 if sb >= (4 << 20) else 20, barrier)
             tt = torch.tensor([t_ms], device=dev, dtype=torch.float64)
             if world > 1:
                 dist.all_reduce(tt, op=dist.ReduceOp.MAX)
