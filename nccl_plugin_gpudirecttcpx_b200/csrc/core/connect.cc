@@ -120,6 +120,11 @@ void attachSocket(Comm* comm, int index, int fd) {
   SocketCtx& s = comm->sock[index];
   logSocketLocality(comm, index, fd, false);
   s.fd = fd;
+  // Bounded socket buffers keep the bytes a stream holds inside the kernel, and with them
+  // the pages its skbs cycle through, small enough to stay in the caches.
+  const int sndbuf = (int)flags().socket_sndbuf, rcvbuf = (int)flags().socket_rcvbuf;
+  if (sndbuf > 0 && setsockopt(fd, SOL_SOCKET, SO_SNDBUF, &sndbuf, sizeof sndbuf) != 0) WARN("SO_SNDBUF %d failed: %s", sndbuf, strerror(errno));
+  if (rcvbuf > 0 && setsockopt(fd, SOL_SOCKET, SO_RCVBUF, &rcvbuf, sizeof rcvbuf) != 0) WARN("SO_RCVBUF %d failed: %s", rcvbuf, strerror(errno));
   s.flow = flowString(fd, comm->passive);
   s.stats.flow_id = flowIdOf(s.flow);
   s.stall.configure((uint64_t)flags().timeout_threshold_ns, (uint64_t)flags().timeout_frequency_ns);

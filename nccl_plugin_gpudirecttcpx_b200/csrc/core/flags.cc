@@ -72,6 +72,8 @@ const IntSpec kInts[] = {
     {kOwn, "WORKER_SPRAY_STRIDE", &Flags::worker_spray_stride, 0, 4096, "helper placement: stride between comms"},
     {kOwn, "VIRTUAL_NICS", &Flags::virtual_nics, 0, 17, "present N devices on one interface (127.0.0.k on lo)"},
     {kOwn, "RX_POOL_BYTES", &Flags::rx_pool_bytes, 1 << 20, (4ll << 30) + 1, "rx page pool per GPU"},
+    {kOwn, "SOCKET_SNDBUF", &Flags::socket_sndbuf, 0, kMax, "SO_SNDBUF of every data socket in bytes (0 = the kernel's auto-tuning)"},
+    {kOwn, "SOCKET_RCVBUF", &Flags::socket_rcvbuf, 0, kMax, "SO_RCVBUF of every data socket in bytes (0 = the kernel's auto-tuning)"},
     {kOwn, "RX_POOL_SCATTER", &Flags::rx_pool_scatter, 0, 2, "hand out rx pages in a scattered order"},
     {kOwn, "RX_POOL_RUN_PAGES", &Flags::rx_pool_run_pages, 1, 1025, "consecutive pages per scattered group of the rx pool"},
     {kOwn, "TX_STAGING_BYTES", &Flags::tx_staging_bytes, 1 << 16, kMax, "pinned staging per send comm for CUDA buffers"},

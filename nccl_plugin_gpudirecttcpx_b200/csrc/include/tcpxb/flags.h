@@ -82,6 +82,8 @@ struct Flags {
   // --- additions of this implementation (NCCL_GPUDIRECTTCPX_*)
   int64_t virtual_nics = 0;            // VIRTUAL_NICS: present N devices on one interface (127.0.0.k on lo)
   int64_t rx_pool_bytes = 1ll << 30;   // RX_POOL_BYTES per GPU (<= 4 GiB: src_off is 32-bit)
+  int64_t socket_sndbuf = 0;           // SOCKET_SNDBUF: bytes, 0 = auto-tuning
+  int64_t socket_rcvbuf = 0;           // SOCKET_RCVBUF
   int64_t rx_pool_scatter = 1;         // RX_POOL_SCATTER: hand out pages in a scattered order
   int64_t rx_pool_run_pages = 8;       // RX_POOL_RUN_PAGES: consecutive pages per scattered group
   int64_t tx_staging_bytes = 32ll << 20;  // TX_STAGING_BYTES per send comm with CUDA buffers

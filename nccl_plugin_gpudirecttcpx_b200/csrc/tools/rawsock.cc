@@ -3,13 +3,15 @@
 // blocks and nothing else.  The transport cannot beat this number; benchmarks
 // report their socket stage as a fraction of it.
 //   tcpxb_rawsock [--streams 8] [--mb-per-stream 2048] [--block-kb 512] [--nics 4]
-//                 [--span-mb 0] [--nonblocking 0] [--scatter-kb 0]
+//                 [--span-mb 0] [--sndbuf-kb 0] [--nonblocking 0] [--scatter-kb 0]
 // Prints one JSON line.  Stream i uses address 127.0.0.(1 + i % nics).
 // The defaults give the friendliest case (one block per thread, reused, so it stays
 // in the core's cache; blocking calls).  The other options take that apart:
 //   --span-mb M      every thread walks through a buffer of M MiB block by block, so that
 //                    with a large M the copies miss the caches, as a transport's do when
 //                    its staging and landing buffers are as large as the data in flight;
+//   --sndbuf-kb K    SO_SNDBUF of K KiB on every sending socket instead of the kernel's auto-tuning
+//                    (which lets megabytes per stream sit in the kernel, out of the caches);
 //   --nonblocking 1  MSG_DONTWAIT calls with poll() when the socket would block;
 //   --scatter-kb K   the receiver lands every block with one recvmsg over pieces of K KiB
 //                    at shuffled places of its span (page-pool landing).
@@ -46,6 +48,7 @@ struct Options {
   int block_kb = 512;
   int nics = 4;
   long span_mb = 0;
+  long sndbuf_kb = 0;
   int nonblocking = 0;
   int scatter_kb = 0;
 };
@@ -128,9 +131,9 @@ int receiver(const Options& o, int port_pipe, int go_pipe) {
     });
   for (auto& t : th) t.join();
   const double dt = nowSec() - t0;
-  printf("{\"tool\": \"rawsock\", \"streams\": %d, \"block_kb\": %d, \"mb_per_stream\": %ld, \"span_mb\": %ld, \"nonblocking\": %d, "
+  printf("{\"tool\": \"rawsock\", \"streams\": %d, \"block_kb\": %d, \"mb_per_stream\": %ld, \"span_mb\": %ld, \"sndbuf_kb\": %ld, \"nonblocking\": %d, "
          "\"scatter_kb\": %d, \"seconds\": %.4f, \"GBps\": %.3f}\n",
-         o.streams, o.block_kb, o.mb, o.span_mb, o.nonblocking, o.scatter_kb, dt, (double)total * o.streams / dt / 1e9);
+         o.streams, o.block_kb, o.mb, o.span_mb, o.sndbuf_kb, o.nonblocking, o.scatter_kb, dt, (double)total * o.streams / dt / 1e9);
   return 0;
 }
 
@@ -151,6 +154,10 @@ int sender(const Options& o, int port_pipe, int go_pipe) {
     a.sin_port = htons((uint16_t)ports[i]);
     int one = 1;
     setsockopt(fd[i], IPPROTO_TCP, TCP_NODELAY, &one, sizeof one);
+    if (o.sndbuf_kb > 0) {
+      const int bytes = (int)(o.sndbuf_kb << 10);
+      setsockopt(fd[i], SOL_SOCKET, SO_SNDBUF, &bytes, sizeof bytes);
+    }
     if (connect(fd[i], (sockaddr*)&a, sizeof a) != 0) return 1;
   }
   char go;
@@ -186,7 +193,7 @@ int main(int argc, char** argv) {
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
     if (a == "--help" || a == "-h") {
-      printf("usage: tcpxb_rawsock [--streams 8] [--mb-per-stream 2048] [--block-kb 512] [--nics 4] [--span-mb 0] "
+      printf("usage: tcpxb_rawsock [--streams 8] [--mb-per-stream 2048] [--block-kb 512] [--nics 4] [--span-mb 0] [--sndbuf-kb 0] "
              "[--nonblocking 0] [--scatter-kb 0]\n");
       return 0;
     }
@@ -197,6 +204,7 @@ int main(int argc, char** argv) {
     else if (a == "--block-kb") o.block_kb = atoi(v);
     else if (a == "--nics") o.nics = atoi(v);
     else if (a == "--span-mb") o.span_mb = atol(v);
+    else if (a == "--sndbuf-kb") o.sndbuf_kb = atol(v);
     else if (a == "--nonblocking") o.nonblocking = atoi(v);
     else if (a == "--scatter-kb") o.scatter_kb = atoi(v);
     else { fprintf(stderr, "unknown argument %s (see --help)\n", a.c_str()); return 2; }

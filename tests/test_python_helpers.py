@@ -57,6 +57,23 @@ def test_socket_settings_follow_the_cores_per_rank(monkeypatch):
     assert env["NCCL_SOCKET_NTHREADS"] == "2" and env["NCCL_DYNAMIC_CHUNK_SIZE"] == str(128 * 1024)
     env = pe.plugin_env(nthreads=3, chunk_bytes=0, builtin_socket=True)
     assert env["NCCL_SOCKET_NTHREADS"] == "3" and env["NCCL_DYNAMIC_CHUNK_SIZE"] == str(128 * 1024)
+    # four cores per rank: four NCCL channels, for the plugin and for the baseline alike; the caller's own setting wins
+    monkeypatch.delenv("NCCL_MAX_NCHANNELS", raising=False)
+    assert env["NCCL_MAX_NCHANNELS"] == "4" and env["NCCL_MIN_NCHANNELS"] == "4"
+    monkeypatch.setattr(native_mod(), "load", lambda name, build=True: None)
+    plug = pe.plugin_env(nthreads=2)
+    assert plug["NCCL_MAX_NCHANNELS"] == "4" and plug["NCCL_GPUDIRECTTCPX_SOCKET_SNDBUF"] == str(256 * 1024)
+    assert pe.plugin_env(nthreads=2, sndbuf=0, max_channels=0).get("NCCL_MAX_NCHANNELS") is None
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "2")  # sixteen cores per rank: NCCL's own choice
+    assert "NCCL_MAX_NCHANNELS" not in pe.plugin_env(nthreads=2)
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "8")
+    monkeypatch.setenv("NCCL_MAX_NCHANNELS", "12")
+    assert "NCCL_MAX_NCHANNELS" not in pe.plugin_env(nthreads=2)
+
+
+def native_mod():
+    from nccl_plugin_gpudirecttcpx_b200.utils import native
+    return native
 
 
 def test_clock_sampler_without_nvidia_smi(monkeypatch):
