@@ -323,7 +323,7 @@ def free_port() -> int:
         return s.getsockname()[1]
 
 
-def run_rawsock(streams: int, span_mb: int = 0):
+def run_rawsock(streams: int, span_mb: int = 0, sndbuf_kb: int = 0):
     """Plain send/recv loops over loopback TCP, `streams` connections.  `span_mb` = 0: every thread reuses one
     512 KiB block (cache-resident, the kindest case); otherwise each thread walks a buffer of that many MiB,
     like a transport whose staging and landing memory is written and read by GPU DMA and never cache-warm."""
@@ -332,7 +332,8 @@ def run_rawsock(streams: int, span_mb: int = 0):
     if not exe.exists():
         return None
     try:
-        cmd = [str(exe), "--streams", str(streams), "--mb-per-stream", "1024"] + (["--span-mb", str(span_mb)] if span_mb else [])
+        cmd = [str(exe), "--streams", str(streams), "--mb-per-stream", "1024"] + (["--span-mb", str(span_mb)] if span_mb else []) + \
+            (["--sndbuf-kb", str(sndbuf_kb)] if sndbuf_kb else [])
         r = subprocess.run(cmd, capture_output=True, text=True, timeout=120)
         for line in r.stdout.splitlines():
             if line.startswith("{"):
@@ -459,6 +460,7 @@ def main():
                                  max_inflight=args.inflight, idle_sleep_us=args.idle_sleep_us)
         transport = {"cpu_cores": cores, "pin": args.pin, "nics": args.nics, "threads": args.nthreads, "socks_per_thread": args.nsocks_per_thread,
                      "chunk_kb": args.chunk_kb, "request_kb": args.request_kb, "unpack_ctas": args.unpack_ctas,
+                     "sndbuf_kb": int(os.environ.get("NCCL_GPUDIRECTTCPX_SOCKET_SNDBUF", "0")) >> 10,
                      "streams_per_direction_on_the_box": max(world, 1) * args.nics * args.nthreads * args.nsocks_per_thread}
     else:
         transport = {"cpu_cores": cores, "pin": args.pin, "env": {k: v for k, v in os.environ.items() if k.startswith("NCCL_") and "PLUGIN" not in k}}
@@ -656,8 +658,11 @@ def main():
             line["rawsock_streams"] = streams
             line["net_stage_GBps"] = net_GBps
             line["frac_of_rawsock"] = net_GBps / raw["GBps"] if raw["GBps"] else None
-            cold = run_rawsock(streams, span_mb=64)
+            # the same loops with buffers that do not fit the caches and the send buffer the transport uses
+            sndbuf_kb = int(os.environ.get("NCCL_GPUDIRECTTCPX_SOCKET_SNDBUF", "0")) >> 10
+            cold = run_rawsock(streams, span_mb=64, sndbuf_kb=sndbuf_kb)
             if cold and cold.get("GBps"):
+                line["rawsock_uncached_sndbuf_kb"] = sndbuf_kb
                 line["rawsock_uncached_GBps"] = cold["GBps"]
                 line["frac_of_rawsock_uncached"] = net_GBps / cold["GBps"]
         if world > 1:
