@@ -81,19 +81,15 @@ def _e():
     return _lib
 
 
-LOOPBACK_SNDBUF = 256 * 1024
+from .plugin_env import LOOPBACK_SNDBUF, loopback_sndbuf  # noqa: E402,F401
 
 
 def default_transport_env(nics: int = 4, nthreads: int = 4, nsocks_per_thread: int = 1,
-                          chunk_bytes: int = 512 * 1024, pool_mb: int = 1024, sndbuf: int = LOOPBACK_SNDBUF) -> None:
-    """Environment defaults for the transport under the engine (only where unset).
-
-    `sndbuf`: SO_SNDBUF of the data sockets.  Over loopback (no bandwidth-delay product to cover) a
-    bounded send buffer keeps the bytes a stream parks inside the kernel small: with the kernel's
-    auto-tuning each stream queues megabytes of skbs that have left the caches by the time the
-    receiver copies them out.  Measured with 4 cores per rank (4 ranks, 256 MiB all_reduce):
-    16.2 ms per step with 256 KiB against 20.9 ms with auto-tuning and 17.5 ms with 512 KiB; no
-    difference with 16 cores per rank.  0 leaves the auto-tuning on (what a real network wants)."""
+                          chunk_bytes: int = 512 * 1024, pool_mb: int = 1024, sndbuf: int = -1) -> None:
+    """Environment defaults for the transport under the engine (only where unset).  `sndbuf`: SO_SNDBUF of
+    the data sockets; -1 = `loopback_sndbuf` for this box's cores per rank (affinity mask / LOCAL_WORLD_SIZE)."""
+    if sndbuf < 0:
+        sndbuf = loopback_sndbuf(len(os.sched_getaffinity(0)) // max(1, int(os.environ.get("LOCAL_WORLD_SIZE", "1"))))
     for k, v in {
         "NCCL_GPUDIRECTTCPX_SOCKET_SNDBUF": str(sndbuf),
         "NCCL_GPUDIRECTTCPX_SOCKET_IFNAME": "lo",

@@ -64,8 +64,10 @@ def test_socket_settings_follow_the_cores_per_rank(monkeypatch):
     plug = pe.plugin_env(nthreads=2)
     assert plug["NCCL_MAX_NCHANNELS"] == "4" and plug["NCCL_GPUDIRECTTCPX_SOCKET_SNDBUF"] == str(256 * 1024)
     assert pe.plugin_env(nthreads=2, sndbuf=0, max_channels=0).get("NCCL_MAX_NCHANNELS") is None
-    monkeypatch.setenv("LOCAL_WORLD_SIZE", "2")  # sixteen cores per rank: NCCL's own choice
-    assert "NCCL_MAX_NCHANNELS" not in pe.plugin_env(nthreads=2)
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "2")  # sixteen cores per rank: NCCL's own choice, the kernel's buffer tuning
+    roomy = pe.plugin_env(nthreads=2)
+    assert "NCCL_MAX_NCHANNELS" not in roomy and roomy["NCCL_GPUDIRECTTCPX_SOCKET_SNDBUF"] == "0"
+    assert pe.loopback_sndbuf(4) == 256 * 1024 and pe.loopback_sndbuf(8) == 256 * 1024 and pe.loopback_sndbuf(16) == 0
     monkeypatch.setenv("LOCAL_WORLD_SIZE", "8")
     monkeypatch.setenv("NCCL_MAX_NCHANNELS", "12")
     assert "NCCL_MAX_NCHANNELS" not in pe.plugin_env(nthreads=2)
