@@ -147,6 +147,8 @@ struct Engine {
   gpu::Stream async_stream = nullptr;
 };
 
+constexpr double kSmallExchangeSpinUs = 250.0;
+
 // One look at every receive comm's control socket: a single poll() with no wait, then a
 // hint to the comms whose socket has data.  Replaces one recv() attempt per comm and
 // progress round.
@@ -318,7 +320,10 @@ int exchange(Engine* e, const SendSpec& ss, const RecvSpec& rs, void* stream) {
   // Small exchanges are latency-bound: spin a little before sleeping.  Large ones have
   // requests queued on every rail, and every microsecond of spinning is taken from the
   // helper threads when cores are scarce: sleep at once.
-  const double spin_us = (ss.bytes + rs.bytes <= (1u << 20)) ? (double)e->idle_spin_us : 0.0;
+  // A small exchange is over in one round trip of the sockets, some tens of microseconds: a nap (which
+  // lasts 50 us and more once the timer and the scheduler are through) would double its time, so the
+  // driving thread spins through it.
+  const double spin_us = (ss.bytes + rs.bytes <= (1u << 20)) ? std::max((double)e->idle_spin_us, kSmallExchangeSpinUs) : 0.0;
   while (done_s < n_send || launched_r < n_recv) {
     bool moved = false;
     if (launched_r < n_recv) pollCtrlSockets(e);  // which control sockets have records: one system call for all rails
