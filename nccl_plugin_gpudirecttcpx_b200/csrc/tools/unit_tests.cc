@@ -291,6 +291,14 @@ TEST(flags_defaults_and_ranges) {
   bool sw[kSlowKinds];
   EXPECT(!parseSlownessList("SENDRECV,bogus", sw) && sw[kSlowSendRecv] && !sw[kSlowTxComp]);
   EXPECT(flagDocs().size() > 50);
+  // socket buffers: off by default, taken as given, and raised when too small to keep a loopback stream moving
+  EXPECT(f.socket_sndbuf == 0 && f.socket_rcvbuf == 0);
+  setenv("NCCL_GPUDIRECTTCPX_SOCKET_SNDBUF", "262144", 1);
+  setenv("NCCL_GPUDIRECTTCPX_SOCKET_RCVBUF", "4096", 1);
+  loadFlags(&f);
+  EXPECT(f.socket_sndbuf == 262144 && f.socket_rcvbuf == 65536);
+  unsetenv("NCCL_GPUDIRECTTCPX_SOCKET_SNDBUF");
+  unsetenv("NCCL_GPUDIRECTTCPX_SOCKET_RCVBUF");
 }
 
 TEST(page_allocator_random_walk) {

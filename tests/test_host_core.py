@@ -39,6 +39,17 @@ def _loopback(host_lib, args=(), exe="tcpxb_loopback", plugin=None, timeout=300,
     return r
 
 
+def test_api_loopback_with_bounded_socket_buffers(host_lib):
+    """SOCKET_SNDBUF / SOCKET_RCVBUF on the data sockets: byte-exact transfers go on, also with a value that
+    is raised because it would stall a loopback stream."""
+    for snd, rcv in (("262144", "0"), ("4096", "1048576")):
+        r = _loopback(host_lib, ["--sizes", "1000,300000,8388608", "--inflight", "8", "--iters", "2"],
+                      NCCL_GPUDIRECTTCPX_SOCKET_SNDBUF=snd, NCCL_GPUDIRECTTCPX_SOCKET_RCVBUF=rcv)
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+        assert "loopback PASSED" in r.stdout
+        assert ("too small to keep a stream moving" in r.stdout + r.stderr) == (snd == "4096")
+
+
 def test_unit_tests_binary(host_lib):
     r = subprocess.run([str(LIB / "tcpxb_unit_tests")], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
