@@ -34,7 +34,9 @@ def main():
     buf_bytes = max(max(numels), 1000003 + 64) * 4  # the largest case in fp32, padding included
     eng = StandinEngine(gpus_per_node=G, buffer_bytes=buf_bytes if G > 1 else 0, request_bytes=256 << 10,
                         plain_mode=bool(int(os.environ.get("TCPXB_TEST_PLAIN", "0"))),
-                        reduce_impl=int(os.environ.get("TCPXB_TEST_REDUCE_IMPL", "0")))
+                        reduce_impl=int(os.environ.get("TCPXB_TEST_REDUCE_IMPL", "0")),
+                        idle_sleep_us=int(os.environ.get("TCPXB_TEST_IDLE_SLEEP_US", "0")),
+                        wake_on_events=bool(int(os.environ.get("TCPXB_TEST_WAKE_ON_EVENTS", "0"))))
     ranks = world if world > 1 else 2  # a single rank is its own twin
 
     if mode == "rank_leaves":

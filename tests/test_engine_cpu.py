@@ -47,9 +47,13 @@ def test_collectives_match_fp32_sums(nproc, gpn):
 
 
 @pytest.mark.parametrize("envkw", [dict(TCPXB_TEST_PLAIN=1), dict(TCPXB_TEST_REDUCE_IMPL=1),
-                                   dict(NCCL_GPUDIRECTTCPX_RX_POOL_SCATTER=1, NCCL_GPUDIRECTTCPX_RX_POOL_BYTES=8 << 20)])
+                                   dict(NCCL_GPUDIRECTTCPX_RX_POOL_SCATTER=1, NCCL_GPUDIRECTTCPX_RX_POOL_BYTES=8 << 20),
+                                   dict(TCPXB_TEST_WAKE_ON_EVENTS=1, TCPXB_TEST_IDLE_SLEEP_US=200),
+                                   dict(TCPXB_TEST_IDLE_SLEEP_US=-1),
+                                   dict(NCCL_GPUDIRECTTCPX_SOCKET_SNDBUF=65536, NCCL_GPUDIRECTTCPX_HELPER_NAP_US=0)])
 def test_engine_variants(envkw):
-    """The unfused baseline, the add-at-destination reduce, and a small scattered page pool."""
+    """The unfused baseline, the add-at-destination reduce, a small scattered page pool; the driving thread
+    woken by events instead of napping, and spinning; bounded socket buffers with helpers that never nap."""
     r, rows = _run(4, 2, **envkw)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert len(rows) == 4 and all(row["ok"] for row in rows)
