@@ -384,6 +384,7 @@ int main(int argc, char** argv) {
     for (int k : keep) pfds.push_back({k, POLLIN, 0});
     int pr = poll(pfds.data(), (nfds_t)pfds.size(), 500);
     if (pr <= 0) continue;
+    size_t polled = keep.size();  // connections accepted below were not part of this poll
     for (size_t i = 0; i < lfds.size(); ++i) {
       if (!(pfds[i].revents & POLLIN)) continue;
       int cfd = accept(lfds[i], nullptr, nullptr);
@@ -397,7 +398,7 @@ int main(int argc, char** argv) {
         if (serve(&st, &c, services[i])) keep.push_back(c.release());
       }
     }
-    for (size_t k = 0; k < keep.size();) {
+    for (size_t k = 0; k < polled;) {
       const struct pollfd& p = pfds[lfds.size() + k];
       if (p.revents & (POLLIN | POLLHUP | POLLERR)) {
         char b;
@@ -408,6 +409,7 @@ int main(int argc, char** argv) {
           close(keep[k]);
           keep.erase(keep.begin() + (long)k);
           pfds.erase(pfds.begin() + (long)(lfds.size() + k));
+          --polled;
           continue;
         }
       }

@@ -454,6 +454,30 @@ def test_rx_buffer_manager_daemon_survives_garbage(tmp_path, san, wire):
         q = subprocess.run([str(LIB / "tcpxb_rxdm"), "--status", "--prefix", str(prefix)], capture_output=True, text=True, timeout=20)
         assert q.returncode == 0, q.stderr
         assert json.loads(q.stdout)["flow_rules"] == 0
+        # and a well-formed registration afterwards, so that the keep-alive bookkeeping runs under the sanitizer too:
+        # two applications register in one poll round, one leaves
+        regs = []
+        for _ in range(2):
+            s = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+            s.settimeout(2)
+            s.connect(str(prefix / "rxdm_application_registry"))
+            if wire == "proto":
+                body = bytes([0x32, 0x02, 0x08, 0x01])  # ApplicationRegisterRequest{register_client: true}
+            else:
+                body = struct.pack("<IHHii", 0x4d445852, 5, 0, 1, 4242).ljust(144, b"\0")
+            s.sendall(struct.pack("!H", len(body)) + body)
+            regs.append(s)
+        for s in regs:
+            assert len(s.recv(4096)) > 2
+        q = subprocess.run([str(LIB / "tcpxb_rxdm"), "--status", "--prefix", str(prefix)], capture_output=True, text=True, timeout=20)
+        assert json.loads(q.stdout)["applications"] == 2
+        regs[0].close()
+        for _ in range(50):
+            q = subprocess.run([str(LIB / "tcpxb_rxdm"), "--status", "--prefix", str(prefix)], capture_output=True, text=True, timeout=20)
+            if json.loads(q.stdout)["applications"] == 1:
+                break
+        assert json.loads(q.stdout)["applications"] == 1
+        regs[1].close()
     finally:
         daemon.terminate()
         try:
