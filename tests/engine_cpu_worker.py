@@ -51,7 +51,10 @@ def main():
         t0 = time.time()
         outcome = "completed"
         try:
-            eng.all_reduce(x)
+            if os.environ.get("TCPXB_TEST_ASYNC") == "1":
+                eng.all_reduce_async(x, out=torch.empty_like(x)).wait()  # the job's error surfaces at the join
+            else:
+                eng.all_reduce(x)
             if eng.device_status()[0] != 0:
                 outcome = "device_status"
         except RuntimeError as e:

@@ -59,12 +59,13 @@ def test_engine_variants(envkw):
     assert len(rows) == 4 and all(row["ok"] for row in rows)
 
 
-@pytest.mark.parametrize("nproc,gpn", [(2, 1), (3, 1), (4, 2)])
-def test_a_rank_that_leaves_is_an_error_for_the_others(nproc, gpn):
+@pytest.mark.parametrize("nproc,gpn,asynchronous", [(2, 1, 0), (3, 1, 0), (4, 2, 0), (2, 1, 1), (4, 2, 1)])
+def test_a_rank_that_leaves_is_an_error_for_the_others(nproc, gpn, asynchronous):
     """The last rank exits at a step boundary.  Its network neighbours get an error from the
     transport at once; its node-mates' bounded flag waits run out and set the device status.
-    Nobody hangs, and the step before the exit was correct everywhere."""
-    r, rows = _run(nproc, gpn, timeout=180, TCPXB_TEST_MODE="rank_leaves")
+    Nobody hangs, and the step before the exit was correct everywhere.  With the asynchronous
+    call the error of the engine's own thread reaches the caller at `wait()`."""
+    r, rows = _run(nproc, gpn, timeout=180, TCPXB_TEST_MODE="rank_leaves", TCPXB_TEST_ASYNC=asynchronous)
     assert len(rows) == nproc, r.stdout[-3000:] + r.stderr[-3000:]
     assert all(row["first_ok"] for row in rows)
     left = [row for row in rows if row["left"]]
