@@ -4,11 +4,15 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <fcntl.h>
 #include <sys/mman.h>
+#include <sys/stat.h>
 #include <unistd.h>
 
+#include <atomic>
 #include <map>
 #include <mutex>
+#include <string>
 
 #include "tcpxb/flags.h"
 #include "tcpxb/gpu.h"
@@ -97,6 +101,69 @@ void sharedRelease(SharedAllocation* a) {
   *a = SharedAllocation();
 }
 
+// CUDA IPC on the stand-in: the "device memory" is a POSIX shared-memory object whose name
+// travels in the handle, together with the owner's pid (a handle cannot be opened where it was made).
+namespace {
+struct FakeIpcHandle {
+  char magic[8];
+  int32_t owner_pid;
+  uint32_t pad;
+  uint64_t bytes;
+  char name[40];
+};
+static_assert(sizeof(FakeIpcHandle) == kIpcHandleBytes, "handle size");
+std::map<uintptr_t, std::string> g_ipc_owned;  // mapping base -> shm name to unlink
+}  // namespace
+
+Result ipcCreate(int dev, size_t bytes, IpcAllocation* out, unsigned char handle[kIpcHandleBytes]) {
+  if (!fake() || dev != 0) return failed("ipcCreate", "no such device");
+  static std::atomic<int> counter{0};
+  FakeIpcHandle h;
+  memset(&h, 0, sizeof h);
+  memcpy(h.magic, "TCPXBIPC", 8);
+  h.owner_pid = (int32_t)getpid();
+  h.bytes = bytes;
+  snprintf(h.name, sizeof h.name, "/tcpxb-ipc-%d-%d", (int)getpid(), counter.fetch_add(1));
+  int fd = shm_open(h.name, O_CREAT | O_EXCL | O_RDWR, 0600);
+  if (fd < 0 || ftruncate(fd, (off_t)bytes) != 0) { if (fd >= 0) { close(fd); shm_unlink(h.name); } return failed("shm_open", strerror(errno)); }
+  void* p = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) { shm_unlink(h.name); return failed("mmap", strerror(errno)); }
+  { std::lock_guard<std::mutex> l(g_mu); g_ipc_owned[(uintptr_t)p] = h.name; }
+  out->dptr = p; out->bytes = bytes; out->dev = dev; out->opened = false;
+  memcpy(handle, &h, sizeof h);
+  return kSuccess;
+}
+
+Result ipcOpen(int dev, const unsigned char handle[kIpcHandleBytes], IpcAllocation* out) {
+  if (!fake() || dev != 0) return failed("ipcOpen", "no such device");
+  FakeIpcHandle h;
+  memcpy(&h, handle, sizeof h);
+  h.name[sizeof h.name - 1] = 0;
+  if (memcmp(h.magic, "TCPXBIPC", 8) != 0) return failed("ipcOpen", "not a memory handle");
+  if (h.owner_pid == (int32_t)getpid()) return failed("ipcOpen", "a handle cannot be opened by the process that made it");
+  int fd = shm_open(h.name, O_RDWR, 0);
+  if (fd < 0) return failed("shm_open", strerror(errno));
+  struct stat sb;
+  if (fstat(fd, &sb) != 0 || (uint64_t)sb.st_size < h.bytes) { close(fd); return failed("ipcOpen", "the memory behind the handle is gone or too small"); }
+  void* p = mmap(nullptr, (size_t)h.bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) return failed("mmap", strerror(errno));
+  out->dptr = p; out->bytes = (size_t)h.bytes; out->dev = dev; out->opened = true;
+  return kSuccess;
+}
+
+void ipcRelease(IpcAllocation* a) {
+  if (a == nullptr || a->dptr == nullptr) return;
+  if (!a->opened) {
+    std::lock_guard<std::mutex> l(g_mu);
+    auto it = g_ipc_owned.find((uintptr_t)a->dptr);
+    if (it != g_ipc_owned.end()) { shm_unlink(it->second.c_str()); g_ipc_owned.erase(it); }
+  }
+  munmap(a->dptr, a->bytes);
+  *a = IpcAllocation();
+}
+
 Result streamWriteValue32(void*, void* dev_word, uint32_t value) {
   if (!fake()) return failed("streamWriteValue32", "no device");
   __atomic_store_n(static_cast<uint32_t*>(dev_word), value, __ATOMIC_RELEASE);  // the stand-in's streams run everything at once
@@ -146,6 +213,12 @@ struct Api {
   CUresult (*MemRelease)(CUmemGenericAllocationHandle) = nullptr;
   CUresult (*MemGetHandleForAddressRange)(void*, CUdeviceptr, size_t, CUmemRangeHandleType, unsigned long long) = nullptr;
   CUresult (*StreamWriteValue32)(CUstream, CUdeviceptr, cuuint32_t, unsigned int) = nullptr;
+  CUresult (*MemAlloc)(CUdeviceptr*, size_t) = nullptr;
+  CUresult (*MemFree)(CUdeviceptr) = nullptr;
+  CUresult (*MemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr) = nullptr;
+  CUresult (*IpcGetMemHandle)(CUipcMemHandle*, CUdeviceptr) = nullptr;
+  CUresult (*IpcOpenMemHandle)(CUdeviceptr*, CUipcMemHandle, unsigned int) = nullptr;
+  CUresult (*IpcCloseMemHandle)(CUdeviceptr) = nullptr;
 };
 
 template <typename F>
@@ -176,6 +249,12 @@ const Api& api() {
     // optional: present from CUDA 11.7 drivers on
     sym(x.lib, "cuMemGetHandleForAddressRange", &x.MemGetHandleForAddressRange);
     sym(x.lib, "cuStreamWriteValue32_v2", &x.StreamWriteValue32);
+    sym(x.lib, "cuMemAlloc_v2", &x.MemAlloc);
+    sym(x.lib, "cuMemFree_v2", &x.MemFree);
+    sym(x.lib, "cuMemGetAddressRange_v2", &x.MemGetAddressRange);
+    sym(x.lib, "cuIpcGetMemHandle", &x.IpcGetMemHandle);
+    sym(x.lib, "cuIpcOpenMemHandle_v2", &x.IpcOpenMemHandle);
+    sym(x.lib, "cuIpcCloseMemHandle", &x.IpcCloseMemHandle);
     x.ok = ok && x.Init(0) == CUDA_SUCCESS;
     return x;
   }();
@@ -337,6 +416,52 @@ void sharedRelease(SharedAllocation* s) {
   a.MemAddressFree(va, s->bytes);
   a.MemRelease(s->handle);
   *s = SharedAllocation();
+}
+
+Result ipcCreate(int dev, size_t bytes, IpcAllocation* out, unsigned char handle[kIpcHandleBytes]) {
+  const Api& a = api();
+  if (!a.ok || a.MemAlloc == nullptr || a.IpcGetMemHandle == nullptr) return failed("ipcCreate", "this driver offers no memory handles");
+  static_assert(sizeof(CUipcMemHandle) == kIpcHandleBytes, "handle size");
+  ScopedContext ctx(dev);
+  if (!ctx.ok()) return failed("ipcCreate", "no context on the device");
+  CUdeviceptr p = 0;
+  TCPXB_CHECK(CUD(a.MemAlloc(&p, bytes)));
+  CUipcMemHandle h;
+  Result r = CUD(a.IpcGetMemHandle(&h, p));
+  if (r != kSuccess) { a.MemFree(p); return r; }
+  memcpy(handle, &h, sizeof h);
+  out->dptr = reinterpret_cast<void*>(p); out->bytes = bytes; out->dev = dev; out->opened = false;
+  return kSuccess;
+}
+
+Result ipcOpen(int dev, const unsigned char handle[kIpcHandleBytes], IpcAllocation* out) {
+  const Api& a = api();
+  if (!a.ok || a.IpcOpenMemHandle == nullptr || a.MemGetAddressRange == nullptr) return failed("ipcOpen", "this driver offers no memory handles");
+  ScopedContext ctx(dev);
+  if (!ctx.ok()) return failed("ipcOpen", "no context on the device");
+  CUipcMemHandle h;
+  memcpy(&h, handle, sizeof h);
+  CUdeviceptr p = 0;
+  TCPXB_CHECK(CUD(a.IpcOpenMemHandle(&p, h, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS)));
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  Result r = CUD(a.MemGetAddressRange(&base, &size, p));
+  if (r != kSuccess || base != p) {  // the owner exports whole allocations
+    if (a.IpcCloseMemHandle != nullptr) a.IpcCloseMemHandle(p);
+    return r != kSuccess ? r : failed("ipcOpen", "the handle does not name the start of an allocation");
+  }
+  out->dptr = reinterpret_cast<void*>(p); out->bytes = size; out->dev = dev; out->opened = true;
+  return kSuccess;
+}
+
+void ipcRelease(IpcAllocation* x) {
+  if (x == nullptr || x->dptr == nullptr || !api().ok) return;
+  ScopedContext ctx(x->dev);
+  const Api& a = api();
+  const CUdeviceptr p = reinterpret_cast<CUdeviceptr>(x->dptr);
+  if (x->opened) { if (a.IpcCloseMemHandle != nullptr) a.IpcCloseMemHandle(p); }
+  else if (a.MemFree != nullptr) a.MemFree(p);
+  *x = IpcAllocation();
 }
 
 Result streamWriteValue32(void* stream, void* dev_word, uint32_t value) {

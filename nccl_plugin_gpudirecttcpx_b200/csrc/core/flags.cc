@@ -64,8 +64,8 @@ const IntSpec kInts[] = {
     {kOwn, "NIC_N_RXQS", &Flags::nic_n_rxqs, 1, 4096, "receive queues per NIC assumed by the queue-balance bookkeeping"},
     {kOwn, "FLOW_STEERING_STRATEGY", &Flags::flow_steering_strategy, 0, 4, "3 = rules through the rx buffer manager"},
     {kOwn, "PROGRAM_FLOW_STEERING_WAIT_MICROS", &Flags::flow_steering_wait_us, 0, kMax, "receiver pause after accept"},
-    {"NCCL_TCPX_", "RXMEM_IMPORT_USE_GPU_PCI_CLIENT", &Flags::rxmem_import_use_gpu_pci_client, 0, 2, "accepted for compatibility"},
-    {"NCCL_TCPX_", "RXMEM_IMPORT_SKIP_ODDS", &Flags::rxmem_import_skip_odds, 0, 2, "accepted for compatibility"},
+    {"NCCL_TCPX_", "RXMEM_IMPORT_USE_GPU_PCI_CLIENT", &Flags::rxmem_import_use_gpu_pci_client, 0, 2, "with RX_BUF_MGR=daemon: 1 = pool descriptor from the daemon's sockets, 0 = 64-byte memory handle from <UNIX_CLIENT_PREFIX>/nvdma-<pci>"},
+    {"NCCL_TCPX_", "RXMEM_IMPORT_SKIP_ODDS", &Flags::rxmem_import_skip_odds, 0, 2, "1 = odd-numbered GPUs get no rx pool (receives into their memory fail)"},
     {kOwn, "REG_DMABUF_USE_INTERNAL_API", &Flags::reg_dmabuf_use_internal_api, 0, 2, "1 asks for the driver's procfs dma-buf interface, which is not offered: the CUDA export call is used"},
     {kOwn, "WORKER_PIN_THREADS", &Flags::worker_pin_threads, 0, 2, "pin every helper thread to one core"},
     {kOwn, "WORKER_SPRAY_COUNT", &Flags::worker_spray_count, 1, 4096, "helper placement: candidates per thread"},

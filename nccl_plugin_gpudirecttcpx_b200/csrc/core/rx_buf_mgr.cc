@@ -5,6 +5,7 @@
 #include <memory>
 #include <unistd.h>
 
+#include <stdio.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
 
@@ -192,6 +193,7 @@ class DaemonRxBufMgr final : public RxBufMgr {
   ~DaemonRxBufMgr() override {
     if (device_pool_) {
       cu::sharedRelease(&imported_);
+      cu::ipcRelease(&ipc_);
       gpu::hostFreeMapped(host_base_);
     } else if (host_base_ != nullptr) {
       gpu::hostUnregister(host_base_);
@@ -204,7 +206,24 @@ class DaemonRxBufMgr final : public RxBufMgr {
     pci_ = dev_ >= 0 ? gpu::pciBusId(dev_) : std::string("host");
     if (pci_.empty()) pci_ = "gpu" + std::to_string(dev_);
     proto_wire_ = flags().rxdm_wire_proto;
-    if (proto_wire_) {
+    if (!flags().rxmem_import_use_gpu_pci_client) {
+      // The reference's older import (reference: src/gpu/rx_pool.cu:30-55, chosen by
+      // NCCL_TCPX_RXMEM_IMPORT_USE_GPU_PCI_CLIENT=0): the pool's owner left a 64-byte memory handle
+      // in <prefix>/nvdma-<pci>; open it and ask the driver how large the allocation is.
+      if (dev_ < 0) { WARN("the memory-handle import needs a GPU"); return kInvalidUsage; }
+      const std::string path = prefix_ + "/nvdma-" + pci_;
+      unsigned char handle[cu::kIpcHandleBytes];
+      FILE* f = fopen(path.c_str(), "rb");
+      if (f == nullptr) { WARN("no memory handle at %s: %s", path.c_str(), strerror(errno)); return kSystemError; }
+      const size_t got = fread(handle, 1, sizeof handle, f);
+      fclose(f);
+      if (got != sizeof handle) { WARN("%s holds %zu bytes, a memory handle has %zu", path.c_str(), got, sizeof handle); return kRemoteError; }
+      TCPXB_CHECK(cu::deviceInit(dev_));
+      if (cu::ipcOpen(dev_, handle, &ipc_) != kSuccess) { WARN("opening the memory handle of %s failed: %s", path.c_str(), cu::lastError()); return kUnhandledCudaError; }
+      bytes_ = ipc_.bytes / kRxPageBytes * kRxPageBytes;
+      device_pool_ = true;
+      legacy_ipc_ = true;
+    } else if (proto_wire_) {
       // the reference's exchange: one socket pair per GPU, the request carries the PCI
       // address as raw bytes, the descriptor comes first and {fd, size, align} second
       // (reference: src/gpu/rx_pool.cu:62-124)
@@ -236,13 +255,17 @@ class DaemonRxBufMgr final : public RxBufMgr {
       q.type = kRxdmGetGpuFd;
       TCPXB_CHECK(rxdmCall(prefix_, "get_gpu_fd", q, &rep, &pool_fd_));
     }
-    if (pool_fd_ < 0 || bytes_ == 0) { WARN("rx buffer manager sent no pool for %s", pci_.c_str()); return kRemoteError; }
+    if ((pool_fd_ < 0 && !legacy_ipc_) || bytes_ == 0) { WARN("rx buffer manager sent no pool for %s", pci_.c_str()); return kRemoteError; }
     if (bytes_ > (4ull << 30)) { WARN("rx pool of %lu bytes is larger than 4 GiB (record offsets are 32-bit)", (unsigned long)bytes_); return kInvalidUsage; }
     if (device_pool_) {
       if (dev_ < 0) { WARN("a device rx pool needs a GPU"); return kInvalidUsage; }
-      TCPXB_CHECK(cu::deviceInit(dev_));
-      TCPXB_CHECK(cu::sharedImport(dev_, pool_fd_, bytes_, &imported_));
-      dev_base_ = static_cast<uint8_t*>(imported_.dptr);
+      if (legacy_ipc_) {
+        dev_base_ = static_cast<uint8_t*>(ipc_.dptr);
+      } else {
+        TCPXB_CHECK(cu::deviceInit(dev_));
+        TCPXB_CHECK(cu::sharedImport(dev_, pool_fd_, bytes_, &imported_));
+        dev_base_ = static_cast<uint8_t*>(imported_.dptr);
+      }
       void* h = nullptr;
       void* hd = nullptr;
       TCPXB_CHECK(gpu::hostAllocMapped(bytes_, &h, &hd));  // landing mirror
@@ -387,6 +410,8 @@ class DaemonRxBufMgr final : public RxBufMgr {
   int pool_fd_ = -1;
   bool device_pool_ = false;
   cu::SharedAllocation imported_;
+  cu::IpcAllocation ipc_;     // the pool when it came by memory handle
+  bool legacy_ipc_ = false;
   std::vector<FlowRule> rules_;
   UnixSocketConnection keepalive_;
 };
@@ -401,6 +426,12 @@ RxBufMgr* rxBufMgrFor(int dev) {
   auto it = g_mgrs.find(dev);
   if (it != g_mgrs.end()) return it->second.get();
   const Flags& f = flags();
+  if (f.rxmem_import_skip_odds && dev >= 0 && dev % 2 == 1) {
+    // the reference's four-pool layout: only even GPUs own receive memory (reference:
+    // src/gpu/cuda_wrapper.cu:179-196); a receive into an odd GPU's memory is then an error
+    WARN("GPU %d has no rx pool: NCCL_TCPX_RXMEM_IMPORT_SKIP_ODDS leaves odd GPUs without one", dev);
+    return nullptr;
+  }
   if (f.rx_buf_mgr_daemon) {
     auto m = std::make_unique<DaemonRxBufMgr>(dev, f.unix_client_prefix);
     if (m->init() != kSuccess) return nullptr;

@@ -75,6 +75,23 @@ Result sharedCreate(int dev, size_t bytes, SharedAllocation* out, int* fd_out);
 Result sharedImport(int dev, int fd, size_t bytes, SharedAllocation* out);
 void sharedRelease(SharedAllocation* a);
 
+// ---- device memory shared by an opaque handle (CUDA IPC), the older of the two ways -------
+// The reference's first import path reads a 64-byte CUipcMemHandle that the pool's owner left
+// in a file and opens it (reference: src/gpu/rx_pool.cu:30-55).  Owner: ordinary device memory
+// (`cuMemAlloc`) and its handle.  Client: the mapping of that memory in another process; its
+// size comes from the driver's address-range query.  A handle cannot be opened by the process
+// that made it.
+constexpr size_t kIpcHandleBytes = 64;
+struct IpcAllocation {
+  void* dptr = nullptr;
+  size_t bytes = 0;
+  int dev = -1;
+  bool opened = false;  // true: a client's mapping (closed, not freed, on release)
+};
+Result ipcCreate(int dev, size_t bytes, IpcAllocation* out, unsigned char handle[kIpcHandleBytes]);
+Result ipcOpen(int dev, const unsigned char handle[kIpcHandleBytes], IpcAllocation* out);
+void ipcRelease(IpcAllocation* a);
+
 // ---- stream-ordered host flags -----------------------------------------------------------
 // Makes `stream` write `value` to the 32-bit word at device address `dev_word` (pinned,
 // device-mapped host memory) once everything queued before it has finished, with the

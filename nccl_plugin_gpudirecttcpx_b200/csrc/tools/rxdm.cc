@@ -2,7 +2,7 @@
 // application tables, and serves them to plugin processes over AF_UNIX sockets.
 //
 //   tcpxb_rxdm --prefix /tmp/tcpxb --pool-mb 1024 [--max-rules 65536] [--device-pool]
-//              [--wire proto [--gpu-pci ADDR,ADDR,...]]
+//              [--wire proto [--gpu-pci ADDR,ADDR,...]] [--legacy-ipc-files]
 //
 // It stands in for the external daemon the reference depends on (reference:
 // README.md:14-16 names it; its clients are src/rx_buf_mgr_client/*).  One pool per
@@ -15,6 +15,11 @@
 // the one that can do that on real hardware.  A client that registers keeps its connection open; when
 // the connection closes the client is deregistered and its flow rules are dropped,
 // which is how a crashed job is cleaned up.
+//
+// --legacy-ipc-files also serves the reference's older import path (reference:
+// src/gpu/rx_pool.cu:30-55): for every GPU the daemon allocates a pool of ordinary device
+// memory and leaves its 64-byte memory handle in <prefix>/nvdma-<pci>, where a plugin started
+// with NCCL_TCPX_RXMEM_IMPORT_USE_GPU_PCI_CLIENT=0 opens it.
 //
 // --wire proto serves the reference's own wire format instead of this repository's
 // fixed structs: protobuf `UnixSocketProto` bodies, one `get_gpu_fd_<pci>` /
@@ -64,6 +69,8 @@ struct State {
   size_t max_rules = 65536;
   bool device_pool = false;
   bool proto_wire = false;
+  bool legacy_ipc_files = false;
+  std::map<std::string, cu::IpcAllocation> ipc_pools;  // by PCI address; the handle files name them
   std::vector<std::string> gpu_pcis;  // proto wire: the GPUs that get a socket pair of their own
   std::vector<Rule> rules;
   std::map<int, App> apps;  // keep-alive connection fd -> application
@@ -305,7 +312,7 @@ int main(int argc, char** argv) {
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
     if (a == "--help" || a == "-h") {
-      printf("usage: tcpxb_rxdm [--prefix DIR] [--pool-mb N] [--max-rules N] [--device-pool] [--wire native|proto] [--gpu-pci A,B,...]\n"
+      printf("usage: tcpxb_rxdm [--prefix DIR] [--pool-mb N] [--max-rules N] [--device-pool] [--wire native|proto] [--gpu-pci A,B,...] [--legacy-ipc-files]\n"
              "       tcpxb_rxdm --status [--prefix DIR]\n"
              "Serves the rx buffer manager's UNIX sockets under DIR (default /tmp) until SIGINT or SIGTERM;\n"
              "with --status asks a running daemon under DIR for its counters and prints one JSON line.\n"
@@ -315,6 +322,7 @@ int main(int argc, char** argv) {
     }
     if (a == "--status") { status_only = true; continue; }
     if (a == "--device-pool") { st.device_pool = true; continue; }
+    if (a == "--legacy-ipc-files") { st.legacy_ipc_files = true; continue; }
     if (i + 1 >= argc) { fprintf(stderr, "%s needs a value (see --help)\n", a.c_str()); return 2; }
     const char* v = argv[++i];
     if (a == "--prefix") st.prefix = v;
@@ -374,6 +382,25 @@ int main(int argc, char** argv) {
     if (fd < 0) { fprintf(stderr, "[rxdm] cannot listen on %s/%s\n", st.prefix.c_str(), s.c_str()); return 1; }
     lfds.push_back(fd);
   }
+  if (st.legacy_ipc_files) {
+    for (int d = 0; d < gpu::deviceCount(); ++d) {
+      std::string pci = gpu::pciBusId(d);
+      if (pci.empty()) pci = "gpu" + std::to_string(d);
+      cu::IpcAllocation pool;
+      unsigned char handle[cu::kIpcHandleBytes];
+      if (cu::deviceInit(d, /*owns_its_memory=*/true) != kSuccess || cu::ipcCreate(d, st.pool_bytes, &pool, handle) != kSuccess) {
+        fprintf(stderr, "[rxdm] memory-handle pool on GPU %s failed: %s\n", pci.c_str(), cu::lastError());
+        return 1;
+      }
+      const std::string path = st.prefix + "/nvdma-" + pci;
+      FILE* f = fopen(path.c_str(), "wb");
+      if (f == nullptr || fwrite(handle, 1, sizeof handle, f) != sizeof handle) { fprintf(stderr, "[rxdm] cannot write %s\n", path.c_str()); return 1; }
+      fclose(f);
+      st.ipc_pools[pci] = pool;
+      fprintf(stderr, "[rxdm] pool for GPU %s: %lu MiB of device memory, handle in %s\n", pci.c_str(), (unsigned long)(pool.bytes >> 20), path.c_str());
+    }
+    if (st.ipc_pools.empty()) { fprintf(stderr, "[rxdm] --legacy-ipc-files needs a GPU\n"); return 1; }
+  }
   fprintf(stderr, "[rxdm] serving under %s (%s wire format)\n", st.prefix.c_str(), st.proto_wire ? "protobuf" : "native");
   printf("ready\n");
   fflush(stdout);
@@ -421,6 +448,10 @@ int main(int argc, char** argv) {
   for (auto& p : st.pools) {
     close(p.second.fd);
     cu::sharedRelease(&p.second.dev);
+  }
+  for (auto& p : st.ipc_pools) {
+    unlink((st.prefix + "/nvdma-" + p.first).c_str());
+    cu::ipcRelease(&p.second);
   }
   return 0;
 }

@@ -623,6 +623,18 @@ TEST(rxdm_proto_wire_bytes) {
   }
 }
 
+TEST(rx_pool_skip_odds) {
+  setenv("NCCL_TCPX_RXMEM_IMPORT_SKIP_ODDS", "1", 1);
+  setenv("NCCL_GPUDIRECTTCPX_RX_POOL_BYTES", "4194304", 1);
+  reloadFlags();
+  EXPECT(rxBufMgrFor(1) == nullptr && rxBufMgrFor(3) == nullptr);  // whatever devices exist: odd ones get none
+  RxBufMgr* even = rxBufMgrFor(-1);  // the host-only pool is not a GPU's and is not skipped
+  EXPECT(even != nullptr && even->totalPages() == 1024);
+  unsetenv("NCCL_TCPX_RXMEM_IMPORT_SKIP_ODDS");
+  unsetenv("NCCL_GPUDIRECTTCPX_RX_POOL_BYTES");
+  reloadFlags();
+}
+
 TEST(dev_queue_fifo) {
   DevQueue q;
   EXPECT(q.init(nullptr, false) == kSuccess);

@@ -411,6 +411,49 @@ def test_daemon_pool_carries_device_receives_on_standin_device(host_lib, tmp_pat
     assert f"pool for GPU 0000:00:00.0: 32 MiB of {pool} memory" in log, log[-2000:]  # the pool came from the daemon
 
 
+def test_daemon_pool_imported_by_memory_handle_on_standin_device(host_lib, tmp_path):
+    """The reference's older import path (reference: src/gpu/rx_pool.cu:30-55): the daemon leaves a 64-byte
+    memory handle in <prefix>/nvdma-<pci>, a plugin started with NCCL_TCPX_RXMEM_IMPORT_USE_GPU_PCI_CLIENT=0
+    opens it and receives into that pool; flow rules and registration still go through the daemon's sockets."""
+    prefix = tmp_path / "rxdm"
+    daemon = subprocess.Popen([str(LIB / "tcpxb_rxdm"), "--prefix", str(prefix), "--pool-mb", "32", "--legacy-ipc-files"],
+                              env=dict(os.environ, TCPXB_FAKE_GPU="1"), stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        assert daemon.stdout.readline().strip() == "ready", daemon.stderr.read()
+        handle = prefix / "nvdma-0000:00:00.0"
+        assert handle.stat().st_size == 64
+        env = dict(TCPXB_FAKE_GPU=1, NCCL_GPUDIRECTTCPX_RX_BUF_MGR="daemon", NCCL_GPUDIRECTTCPX_UNIX_CLIENT_PREFIX=str(prefix),
+                   NCCL_TCPX_RXMEM_IMPORT_USE_GPU_PCI_CLIENT=0, NCCL_GPUDIRECTTCPX_RECV_MODE="unpack", NCCL_DEBUG="INFO")
+        r = _loopback(host_lib, ["--ptr", "cuda", "--sizes", "0,1000,300000,4194304", "--inflight", "8", "--iters", "2"], **env)
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+        assert "loopback PASSED" in r.stdout
+        assert "32 MiB of device memory" in r.stdout + r.stderr  # the client's own log line about the imported pool
+        q = subprocess.run([str(LIB / "tcpxb_rxdm"), "--status", "--prefix", str(prefix)], capture_output=True, text=True, timeout=20)
+        st = json.loads(q.stdout)
+        assert st["flow_rules"] == 0 and st["applications"] == 0 and st["pools"] == 0  # no descriptor was ever asked for
+        # a handle file that is not a handle, and none at all
+        handle.write_bytes(b"x" * 64)
+        bad = _loopback(host_lib, ["--ptr", "cuda", "--sizes", "1000", "--iters", "1"], **env)
+        assert bad.returncode != 0 and "opening the memory handle" in bad.stdout + bad.stderr
+        handle.unlink()
+        bad = _loopback(host_lib, ["--ptr", "cuda", "--sizes", "1000", "--iters", "1"], **env)
+        assert bad.returncode != 0 and "no memory handle at" in bad.stdout + bad.stderr
+    finally:
+        daemon.terminate()
+        try:
+            daemon.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            daemon.kill()
+    assert "handle in" in daemon.stderr.read()
+
+
+def test_odd_gpus_without_rx_pool(host_lib):
+    """NCCL_TCPX_RXMEM_IMPORT_SKIP_ODDS=1: device 0 keeps its pool, an odd device has none."""
+    r = subprocess.run([str(LIB / "tcpxb_unit_tests"), "rx_pool_skip_odds"], capture_output=True, text=True, timeout=60,
+                       env=dict(os.environ, TCPXB_FAKE_GPU="1"))
+    assert r.returncode == 0 and "ok rx_pool_skip_odds" in r.stdout, r.stdout + r.stderr
+
+
 @pytest.mark.parametrize("wire", ["native", "proto"])
 @pytest.mark.parametrize("san", ["", "address"])
 def test_rx_buffer_manager_daemon_survives_garbage(tmp_path, san, wire):
