@@ -15,6 +15,7 @@
 #include <linux/errqueue.h>
 #include <netinet/in.h>
 #include <sys/socket.h>
+#include <sys/wait.h>
 #include <unistd.h>
 
 #include <atomic>
@@ -621,6 +622,37 @@ TEST(rxdm_proto_wire_bytes) {
     EXPECT(b.recv(&back, &fd) == kSuccess && fd < 0 && back.kind == kRawBytes && back.raw_bytes == "Ok.");
     EXPECT(b.recv(&back, &fd, 50) == kInProgress);
   }
+}
+
+TEST(memory_handles_on_standin_device) {
+  if (!cu::available()) { printf("  skipped: no device (set TCPXB_FAKE_GPU=1)\n"); return; }
+  cu::IpcAllocation mine, theirs;
+  unsigned char handle[cu::kIpcHandleBytes];
+  EXPECT(cu::ipcCreate(0, 1 << 20, &mine, handle) == kSuccess && mine.dptr != nullptr && mine.bytes == (1u << 20) && !mine.opened);
+  // as with the real driver, the process that made a handle cannot open it
+  EXPECT(cu::ipcOpen(0, handle, &theirs) != kSuccess && theirs.dptr == nullptr);
+  // another process can, and sees the owner's bytes
+  memset(mine.dptr, 0x6b, 4096);
+  const pid_t child = fork();
+  if (child == 0) {
+    cu::IpcAllocation c;
+    int rc = 1;
+    if (cu::ipcOpen(0, handle, &c) == kSuccess && c.opened && c.bytes == (1u << 20) && static_cast<unsigned char*>(c.dptr)[4095] == 0x6b) {
+      static_cast<unsigned char*>(c.dptr)[8192] = 0x2a;
+      cu::ipcRelease(&c);
+      rc = 0;
+    }
+    _exit(rc);
+  }
+  int status = -1;
+  EXPECT(waitpid(child, &status, 0) == child && WIFEXITED(status) && WEXITSTATUS(status) == 0);
+  EXPECT(static_cast<unsigned char*>(mine.dptr)[8192] == 0x2a);
+  unsigned char junk[cu::kIpcHandleBytes];
+  memset(junk, 'x', sizeof junk);
+  EXPECT(cu::ipcOpen(0, junk, &theirs) != kSuccess);
+  cu::ipcRelease(&mine);
+  EXPECT(mine.dptr == nullptr);
+  cu::ipcRelease(&mine);  // twice is harmless
 }
 
 TEST(rx_pool_skip_odds) {

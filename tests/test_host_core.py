@@ -155,10 +155,10 @@ def _props(stdout):
     return rows
 
 
-@pytest.mark.parametrize("which", ["shared_device_allocation", "stream_counter"])
+@pytest.mark.parametrize("which", ["shared_device_allocation", "stream_counter", "memory_handles"])
 def test_unit_tests_that_need_the_standin_device(host_lib, which):
-    """Driver-API services (shareable allocation by file descriptor, dma-buf export, context guard) and
-    the stream-ordered host counter, on the host-only library's stand-in device."""
+    """Driver-API services (shareable allocation by file descriptor, dma-buf export, context guard, memory
+    handles between processes) and the stream-ordered host counter, on the host-only library's stand-in device."""
     r = subprocess.run([str(LIB / "tcpxb_unit_tests"), which], capture_output=True, text=True, timeout=120,
                        env=dict(os.environ, TCPXB_FAKE_GPU="1"))
     assert r.returncode == 0, r.stdout + r.stderr
