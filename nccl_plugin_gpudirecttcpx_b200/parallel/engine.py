@@ -304,6 +304,62 @@ class HierarchicalEngine:
             raise RuntimeError("engine call failed: " + self._api.tcpxb_engine_last_error().decode())
         return AsyncWork(self, ticket, res, keep=(keep, x, res))
 
+    def all_gather_async(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> AsyncWork:
+        """`all_gather` on the engine's own thread and stream.  `x` contiguous, its byte size a multiple
+        of 16.  With one GPU per node `out` (world x x.numel() elements) may be given; with several the
+        result is a view of the symmetric output buffer, so one such job may be outstanding at a time."""
+        nbytes = x.numel() * x.element_size()
+        blocks = self.nodes * self.G
+        if nbytes % 16 != 0 or not x.is_contiguous():
+            raise ValueError("all_gather_async needs a contiguous block whose size is a multiple of 16 bytes")
+        if self.G == 1:
+            res = out if out is not None else torch.empty(blocks * x.numel(), dtype=x.dtype, device=x.device)
+            if res.numel() * res.element_size() != blocks * nbytes or not res.is_contiguous():
+                raise ValueError(f"out must be contiguous and hold {blocks} blocks of {nbytes} bytes")
+            dst = res.data_ptr()
+        else:
+            if out is not None:
+                raise ValueError("with several GPUs per node the result lives in the symmetric output buffer")
+            if nbytes * blocks > self.buffer_bytes:
+                raise ValueError(f"all_gather of {blocks} x {nbytes} bytes does not fit the {self.buffer_bytes}-byte symmetric buffers")
+            res = self.out.view(torch.uint8)[:nbytes * blocks].view(x.dtype)
+            dst = self.out.data_ptr()
+        keep, after = self._event_after_current_stream()
+        ticket = self._api.tcpxb_engine_all_gather_async(self._h, x.data_ptr(), dst, nbytes, after)
+        if not ticket:
+            raise RuntimeError("engine call failed: " + self._api.tcpxb_engine_last_error().decode())
+        return AsyncWork(self, ticket, res, keep=(keep, x, res))
+
+    def reduce_scatter_async(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> AsyncWork:
+        """`reduce_scatter` on the engine's own thread and stream.  `x` contiguous, divisible into one part
+        per rank whose byte size is a multiple of 16.  With several GPUs per node `x` is copied into the
+        symmetric work buffer at once (unless it already is that buffer), so one such job may be
+        outstanding at a time."""
+        blocks = self.nodes * self.G if self.world > 1 else 1
+        if x.numel() % blocks != 0 or not x.is_contiguous():
+            raise ValueError(f"reduce_scatter_async needs a contiguous input that divides into {blocks} parts")
+        per = x.numel() // blocks
+        nbytes = per * x.element_size()
+        if nbytes % 16 != 0:
+            raise ValueError("reduce_scatter_async needs parts whose size is a multiple of 16 bytes")
+        res = out if out is not None else torch.empty(per, dtype=x.dtype, device=x.device)
+        if res.numel() != per or res.dtype != x.dtype or not res.is_contiguous():
+            raise ValueError(f"out must be a contiguous tensor of {per} elements of {x.dtype}")
+        src = x
+        if self.G > 1:
+            total = x.numel() * x.element_size()
+            if total > self.buffer_bytes:
+                raise ValueError(f"reduce_scatter input of {total} bytes does not fit the symmetric buffers")
+            w = self.work.view(torch.uint8)[:total].view(x.dtype)
+            if x.data_ptr() != w.data_ptr():
+                w.copy_(x.reshape(-1))
+            src = self.work
+        keep, after = self._event_after_current_stream()
+        ticket = self._api.tcpxb_engine_reduce_scatter_async(self._h, src.data_ptr(), res.data_ptr(), nbytes, DTYPE_CODE[x.dtype], after)
+        if not ticket:
+            raise RuntimeError("engine call failed: " + self._api.tcpxb_engine_last_error().decode())
+        return AsyncWork(self, ticket, res, keep=(keep, x, res))
+
     def work_view(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         """The symmetric work buffer as a tensor, for producers that write in place."""
         return self.work.view(torch.uint8)[:numel * dtype.itemsize].view(dtype)

@@ -132,6 +132,21 @@ def main():
             good = good and torch.allclose(y, torch.stack(xs3[k]).sum(0), atol=1e-4 * ranks) and works[k].done()
         ok = ok and good
         detail.append(("all_reduce_async_x3", "f32", 98304, 0, 0.0, good))
+    # asynchronous all_gather and reduce_scatter: one job of each at a time (with several GPUs per node their
+    # buffers are the symmetric ones), the reduce_scatter queued behind the all_gather
+    per = 4096
+    xs = [torch.randn(per * ranks, generator=torch.Generator().manual_seed(17 * r + 3)).float() for r in range(world)]
+    if world == 1:
+        xs = xs * 2
+    wg = eng.all_gather_async(xs[rank][:per].clone())
+    g = wg.wait().clone()
+    good = torch.equal(g, torch.cat([t[:per] for t in xs])) and wg.done()
+    if world > 1:
+        wr = eng.reduce_scatter_async(xs[rank].clone())
+        r_ = wr.wait()
+        good = good and torch.allclose(r_, torch.stack(xs).sum(0)[rank * per:(rank + 1) * per], atol=1e-4 * ranks)
+    ok = ok and good
+    detail.append(("all_gather_reduce_scatter_async", "f32", per, 0, 0.0, good))
     # all_gather and reduce_scatter blocks that are no multiple of 16 bytes
     per = 1001
     xs = [torch.randn(per * ranks, generator=torch.Generator().manual_seed(11 * r + 5)).float() for r in range(world)]
